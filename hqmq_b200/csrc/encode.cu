@@ -1,0 +1,423 @@
+// KV-cache encoder for sm_100a: chunk norms, per-token-max radius codes, nearest codeword of
+// the 24*S product codebook, Med3x median / flags / outlier side buffer, bit-packed rows.
+//
+// Arithmetic contract (bit-exact with the reference evaluated on the fp32 upcast of x):
+//   norm   = sqrt(((x0^2 + x1^2) + x2^2) + x3^2), every op a separate IEEE fp32 op
+//   radius = max(norm, 1e-8); r_max = max over the token's chunks (flagged ones included)
+//   rq     = clamp(rint((radius / (r_max / qmax))), 0, qmax) with two IEEE divisions
+//   idx    = argmax_k <x/radius, joint[k]>; exhaustive search evaluates, for every secondary
+//            s, y = u * conj(q_s) and snaps y to the 24-cell in closed form
+//   med    = torch.quantile(norms of the head, 0.5): the two middle order statistics a <= b,
+//            med = a if N odd else b - (b - a) * 0.5; flag = norm > med * C (strict)
+#include <string.h>
+
+#include "common.cuh"
+
+namespace hqmq {
+
+namespace {
+
+constexpr int kEncThreads = 256;
+constexpr int kEncWarps = kEncThreads / 32;
+constexpr int kEncIters = 16;     // token groups per block
+constexpr int kHistBins = 2048;   // 11-bit digits: bits [31:21], [20:10], then 10 bits [9:0]
+constexpr int kMaxRowWords = 20;
+
+struct Maps24 { uint8_t ref_to_native[24]; };
+
+struct EncGeom {
+  int B, H, T_new, n, npl, tpw;  // npl = lanes per token (power of two >= n), tpw = tokens per warp
+  int S, ib, rbits, qmax;
+  int x_dtype;
+  int64_t xs_b, xs_h, xs_t;
+};
+
+// Workspace layout (uint32 words)
+struct EncWs {
+  uint32_t* status;   // [4]
+  uint32_t* hist;     // [H][3 levels][2 queries][kHistBins]
+  uint32_t* sel;      // [H][8]: prefix_lo, rank_lo, prefix_hi, rank_hi, a_bits, b_bits, thr_bits, med_bits
+  uint32_t* blk;      // [B*H][nblk_call + 1] flagged chunks per 64-token block of this call
+};
+
+__device__ __forceinline__ void load_chunk(const void* x, int64_t off, int dtype, float v[4]) {
+  if (dtype == HQMQ_F32) {
+    float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + off);
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+  } else {
+    uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(x) + off);
+    uint16_t a = r.x & 0xffff, b = r.x >> 16, c = r.y & 0xffff, d = r.y >> 16;
+    v[0] = bits16_to_float(a, dtype); v[1] = bits16_to_float(b, dtype);
+    v[2] = bits16_to_float(c, dtype); v[3] = bits16_to_float(d, dtype);
+  }
+}
+
+__device__ __forceinline__ float chunk_norm(const float v[4]) {
+  float s = __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(v[0], v[0]), __fmul_rn(v[1], v[1])), __fmul_rn(v[2], v[2])),
+                      __fmul_rn(v[3], v[3]));
+  return __fsqrt_rn(s);
+}
+
+// Closed-form nearest 24-cell vertex to y: returns similarity and writes the reference
+// primary index (axis candidates 0..7, half-integer candidates 8..23).
+__device__ __forceinline__ float snap24(float y0, float y1, float y2, float y3, int& p) {
+  float a0 = fabsf(y0), a1 = fabsf(y1), a2 = fabsf(y2), a3 = fabsf(y3);
+  float best = a0; int ax = 0;
+  if (a1 > best) { best = a1; ax = 1; }
+  if (a2 > best) { best = a2; ax = 2; }
+  if (a3 > best) { best = a3; ax = 3; }
+  float yv = ax == 0 ? y0 : ax == 1 ? y1 : ax == 2 ? y2 : y3;
+  p = 2 * ax + (yv < 0.f ? 1 : 0);
+  float half = 0.5f * (((a0 + a1) + a2) + a3);
+  if (half > best) {
+    best = half;
+    p = 8 + ((y0 < 0.f) << 3) + ((y1 < 0.f) << 2) + ((y2 < 0.f) << 1) + (y3 < 0.f);
+  }
+  return best;
+}
+
+// Exhaustive search: for every secondary quaternion q_s (shared memory, fp32), rotate the
+// unit direction by conj(q_s) and snap.  Ties keep the smallest reference index p*S + s.
+__device__ __forceinline__ int search_exhaustive(const float4* __restrict__ qs, int S, float u0, float u1, float u2,
+                                                 float u3, int& best_s) {
+  float best = -1.f; int bp = 0, bs = 0;
+  for (int s = 0; s < S; ++s) {
+    float4 q = qs[s];
+    float y0 = u0 * q.x + u1 * q.y + u2 * q.z + u3 * q.w;
+    float y1 = -u0 * q.y + u1 * q.x - u2 * q.w + u3 * q.z;
+    float y2 = -u0 * q.z + u1 * q.w + u2 * q.x - u3 * q.y;
+    float y3 = -u0 * q.w - u1 * q.z + u2 * q.y + u3 * q.x;
+    int p;
+    float sim = snap24(y0, y1, y2, y3, p);
+    if (sim > best || (sim == best && p < bp)) { best = sim; bp = p; bs = s; }
+  }
+  best_s = bs;
+  return bp;
+}
+
+__global__ void __launch_bounds__(kEncThreads)
+encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
+                   int t_start, uint32_t* __restrict__ hist, Maps24 maps) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float4* qs = reinterpret_cast<float4*>(smem_raw);
+  uint32_t* rows = reinterpret_cast<uint32_t*>(qs + g.S);            // [warps][tpw][kMaxRowWords]
+  uint32_t* shist = rows + kEncWarps * g.tpw * kMaxRowWords;          // [kHistBins] when hist != nullptr
+
+  const int bh = blockIdx.y;
+  const int h = bh % g.H, b = bh / g.H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < g.S; i += blockDim.x) qs[i] = reinterpret_cast<const float4*>(qs_all)[(int64_t)h * g.S + i];
+  if (hist) for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) shist[i] = 0;
+  __syncthreads();
+
+  const int sub = lane / g.npl, c = lane % g.npl;
+  const int rw = dst.row_bytes >> 2;
+  const int cb = g.ib + g.rbits;
+  uint32_t* myrow = rows + (warp * g.tpw + sub) * kMaxRowWords;
+  const int tok_per_iter = kEncWarps * g.tpw;
+  const int t_block0 = blockIdx.x * tok_per_iter * kEncIters;
+
+  for (int it = 0; it < kEncIters; ++it) {
+    const int t = t_block0 + it * tok_per_iter + warp * g.tpw + sub;
+    const bool tok_ok = t < g.T_new;
+    const bool active = tok_ok && c < g.n;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
+    const float nrm = chunk_norm(v);
+    const float radius = fmaxf(nrm, 1e-8f);
+    float rmax = active ? radius : 0.f;
+    for (int o = g.npl >> 1; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+    rmax = fmaxf(rmax, 1e-8f);
+    const float scale = __fdiv_rn(rmax, (float)g.qmax);
+    float rqf = rintf(__fdiv_rn(radius, scale));
+    rqf = fminf(fmaxf(rqf, 0.f), (float)g.qmax);
+
+    for (int w = lane; w < g.tpw * kMaxRowWords; w += 32) rows[warp * g.tpw * kMaxRowWords + w] = 0;
+    __syncwarp();
+    if (active) {
+      const float u0 = __fdiv_rn(v[0], radius), u1 = __fdiv_rn(v[1], radius), u2 = __fdiv_rn(v[2], radius),
+                  u3 = __fdiv_rn(v[3], radius);
+      int s;
+      const int p = search_exhaustive(qs, g.S, u0, u1, u2, u3, s);
+      const int au = maps.ref_to_native[p];
+      const uint32_t ni = (uint32_t)((((au >> 3) * g.S + s) << 3) | (au & 7));
+      const uint32_t f = ni | ((uint32_t)rqf << g.ib);
+      const int bit = c * cb, w = bit >> 5, sh = bit & 31;
+      atomicOr(&myrow[w], f << sh);
+      if (sh + cb > 32) atomicOr(&myrow[w + 1], f >> (32 - sh));
+      if (hist) atomicAdd(&shist[__float_as_uint(nrm) >> 21], 1u);
+    }
+    __syncwarp();
+    if (tok_ok) {
+      const int64_t row = (int64_t)bh * dst.T_cap + t_start + t;
+      uint32_t* out = reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes);
+      for (int w = c; w < rw; w += g.npl) out[w] = myrow[w];
+      if (c == 0) {
+        store_scale(dst, row, rmax);
+        if (dst.flags) dst.flags[row] = 0u;
+      }
+    }
+    __syncwarp();
+  }
+  if (hist) {
+    __syncthreads();
+    uint32_t* gh = hist + (int64_t)h * 3 * 2 * kHistBins;  // level 0, query 0
+    for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) {
+      uint32_t cnt = shist[i];
+      if (cnt) atomicAdd(&gh[i], cnt);
+    }
+  }
+}
+
+// ---- Med3x: radix select of the two middle order statistics ------------------------------
+// Level 0 histogram (bits 31:21) is accumulated by encode_main_kernel into query slot 0.
+__global__ void select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level, uint64_t N,
+                              float C, float* __restrict__ med_out) {
+  const int h = blockIdx.x;
+  if (threadIdx.x != 0) return;
+  uint32_t* st = sel + h * 8;
+  const uint64_t lo = (N - 1) / 2, hi = N / 2;
+  uint32_t* hl = hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
+  const int shift = level == 0 ? 21 : level == 1 ? 10 : 0;
+  const int bins = level == 2 ? 1024 : kHistBins;
+  for (int q = 0; q < 2; ++q) {
+    uint64_t rank = level == 0 ? (q == 0 ? lo : hi) : st[2 * q + 1];
+    uint32_t prefix = level == 0 ? 0u : st[2 * q];
+    // level 0 has one histogram (slot 0); deeper levels have one per query
+    const uint32_t* hq = hl + (level == 0 ? 0 : q * kHistBins);
+    uint64_t acc = 0; int bin = bins - 1;
+    for (int i = 0; i < bins; ++i) {
+      uint32_t cnt = hq[i];
+      if (acc + cnt > rank) { bin = i; break; }
+      acc += cnt;
+    }
+    st[2 * q] = prefix | ((uint32_t)bin << shift);
+    st[2 * q + 1] = (uint32_t)(rank - acc);
+  }
+  if (level == 2) {
+    const float a = __uint_as_float(st[0]), b = __uint_as_float(st[2]);
+    float med = (N & 1) ? a : __fsub_rn(b, __fmul_rn(__fsub_rn(b, a), 0.5f));
+    const float thr = __fmul_rn(med, C);
+    st[4] = st[0]; st[5] = st[2];
+    st[6] = __float_as_uint(thr);
+    st[7] = __float_as_uint(med);
+    if (med_out) med_out[h] = med;
+  }
+}
+
+// Levels 1 and 2: re-read x, recompute the norms, histogram the next digit of the keys that
+// match each query's prefix.
+__global__ void __launch_bounds__(256)
+hist_kernel(EncGeom g, const void* __restrict__ x, uint32_t* __restrict__ hist, const uint32_t* __restrict__ sel,
+            int level) {
+  __shared__ uint32_t sh[2][kHistBins];
+  const int bh = blockIdx.y;
+  const int h = bh % g.H, b = bh / g.H;
+  for (int i = threadIdx.x; i < 2 * kHistBins; i += blockDim.x) (&sh[0][0])[i] = 0;
+  __syncthreads();
+  const uint32_t p0 = sel[h * 8 + 0], p1 = sel[h * 8 + 2];
+  const int hs = level == 1 ? 21 : 10;                   // bits already fixed are above hs
+  const int ds = level == 1 ? 10 : 0;
+  const uint32_t dm = level == 1 ? 0x7ffu : 0x3ffu;
+  const int64_t total = (int64_t)g.T_new * g.n;
+  const int64_t per_block = (total + gridDim.x - 1) / gridDim.x;
+  const int64_t i0 = blockIdx.x * per_block, i1 = min(total, i0 + per_block);
+  for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+    const int t = (int)(i / g.n), c = (int)(i % g.n);
+    float v[4];
+    load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
+    const uint32_t key = __float_as_uint(chunk_norm(v));
+    const uint32_t dig = (key >> ds) & dm;
+    if ((key >> hs) == (p0 >> hs)) atomicAdd(&sh[0][dig], 1u);
+    if ((key >> hs) == (p1 >> hs)) atomicAdd(&sh[1][dig], 1u);
+  }
+  __syncthreads();
+  uint32_t* gh = hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
+  for (int i = threadIdx.x; i < 2 * kHistBins; i += blockDim.x) {
+    uint32_t cnt = (&sh[0][0])[i];
+    if (cnt) atomicAdd(&gh[i], cnt);
+  }
+}
+
+// Flags: one lane group per token; counts flagged chunks per 64-token block of the cache.
+__global__ void __launch_bounds__(256)
+flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, const uint32_t* __restrict__ sel,
+             uint32_t* __restrict__ blk, int blk0, int nblk) {
+  const int bh = blockIdx.y;
+  const int h = bh % g.H, b = bh / g.H;
+  const float thr = __uint_as_float(sel[h * 8 + 6]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / g.npl, c = lane % g.npl;
+  const int tok_per_iter = (blockDim.x >> 5) * g.tpw;
+  for (int tb = blockIdx.x * tok_per_iter; tb < g.T_new; tb += gridDim.x * tok_per_iter) {
+    const int t = tb + warp * g.tpw + sub;
+    const bool active = t < g.T_new && c < g.n;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
+    const bool f = active && chunk_norm(v) > thr;
+    const uint32_t bal = __ballot_sync(0xffffffffu, f);
+    if (t < g.T_new && c == 0) {
+      const uint32_t mask = g.npl == 32 ? 0xffffffffu : ((1u << g.npl) - 1u);
+      const uint32_t word = (bal >> (sub * g.npl)) & mask;
+      const int ta = t_start + t;
+      dst.flags[(int64_t)bh * dst.T_cap + ta] = word;
+      if (word) atomicAdd(&blk[(int64_t)bh * (nblk + 1) + (ta / HQMQ_OUT_BLOCK - blk0)], (uint32_t)__popc(word));
+    }
+  }
+}
+
+// Per (b,h): running offsets of the outlier payload for the blocks this call touches.
+__global__ void scan_kernel(hqmq_packed dst, int t_start, int T_new, uint32_t* __restrict__ blk, int blk0, int nblk,
+                            uint32_t* __restrict__ status) {
+  const int bh = blockIdx.x * blockDim.x + threadIdx.x;
+  if (bh >= dst.B * dst.H) return;
+  const int nb_cap = dst.T_cap / HQMQ_OUT_BLOCK + 1;
+  uint32_t* off = dst.out_off + (int64_t)bh * nb_cap;
+  uint32_t* cnt = blk + (int64_t)bh * (nblk + 1);
+  uint32_t run = dst.out_count[bh];
+  for (int i = 0; i < nblk; ++i) {
+    const int ba = blk0 + i;
+    // A block that already holds tokens from an earlier call keeps its offset.
+    if (!(i == 0 && (t_start % HQMQ_OUT_BLOCK) != 0)) off[ba] = run;
+    run += cnt[i];
+  }
+  off[blk0 + nblk] = run;
+  if (run > (uint32_t)dst.out_cap) atomicOr(&status[0], 1u);
+  dst.out_count[bh] = run;
+}
+
+// Payload: the original values of every flagged chunk, in (token, chunk) order.
+__global__ void __launch_bounds__(256)
+payload_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start) {
+  const int bh = blockIdx.y;
+  const int h = bh % g.H, b = bh / g.H;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= g.T_new) return;
+  const int ta = t_start + t;
+  const uint32_t* fl = dst.flags + (int64_t)bh * dst.T_cap;
+  uint32_t word = fl[ta];
+  if (!word) return;
+  const int blk = ta / HQMQ_OUT_BLOCK;
+  uint32_t pos = dst.out_off[(int64_t)bh * (dst.T_cap / HQMQ_OUT_BLOCK + 1) + blk];
+  for (int tt = blk * HQMQ_OUT_BLOCK; tt < ta; ++tt) pos += __popc(fl[tt]);
+  const int esz = dst.out_dtype == HQMQ_F32 ? 4 : 2;
+  unsigned char* base = reinterpret_cast<unsigned char*>(dst.out_vals) + (int64_t)bh * dst.out_cap * 4 * esz;
+  while (word) {
+    const int c = __ffs(word) - 1;
+    word &= word - 1;
+    if (pos < (uint32_t)dst.out_cap) {
+      float v[4];
+      load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
+      if (dst.out_dtype == HQMQ_F32) {
+        *reinterpret_cast<float4*>(base + (int64_t)pos * 16) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+        uint2 o;
+        o.x = float_to_bits16(v[0], dst.out_dtype) | ((uint32_t)float_to_bits16(v[1], dst.out_dtype) << 16);
+        o.y = float_to_bits16(v[2], dst.out_dtype) | ((uint32_t)float_to_bits16(v[3], dst.out_dtype) << 16);
+        *reinterpret_cast<uint2*>(base + (int64_t)pos * 8) = o;
+      }
+    }
+    ++pos;
+  }
+}
+
+struct WsPlan { size_t status, hist, sel, blk, total; int blk0, nblk; };
+WsPlan plan_ws(const hqmq_encode_args& a) {
+  WsPlan w;
+  const int H = a.dst.H, BH = a.dst.B * a.dst.H;
+  w.blk0 = a.t_start / HQMQ_OUT_BLOCK;
+  w.nblk = a.T_new > 0 ? (a.t_start + a.T_new - 1) / HQMQ_OUT_BLOCK - w.blk0 + 1 : 0;
+  size_t o = 0;
+  w.status = o; o += 4;
+  w.hist = o; o += (size_t)H * 3 * 2 * kHistBins;
+  w.sel = o; o += (size_t)H * 8;
+  w.blk = o; o += (size_t)BH * (w.nblk + 1);
+  w.total = o * sizeof(uint32_t);
+  return w;
+}
+
+}  // namespace
+
+}  // namespace hqmq
+
+using namespace hqmq;
+
+static int validate_encode(const hqmq_encode_args* a) {
+  if (!a || a->struct_size != sizeof(hqmq_encode_args)) return HQMQ_ERR_ARG;
+  if (!a->x || !a->qs || !a->joint) return HQMQ_ERR_ARG;
+  if (!is_float_dtype(a->x_dtype)) return HQMQ_ERR_DTYPE;
+  const bool med = a->median_mult > 0.f;
+  int rc = check_packed(a->dst, med);
+  if (rc) return rc;
+  if (a->T_new < 0 || a->t_start < 0) return HQMQ_ERR_SHAPE;
+  if ((int64_t)a->t_start + a->T_new > a->dst.T_cap) return HQMQ_ERR_CAPACITY;
+  const int align = a->x_dtype == HQMQ_F32 ? 16 : 8;
+  if ((uintptr_t)a->x & (align - 1)) return HQMQ_ERR_ALIGN;
+  for (int i = 0; i < 3; ++i)
+    if (a->x_stride[i] % 4) return HQMQ_ERR_ALIGN;
+  if (((uintptr_t)a->qs & 15) || ((uintptr_t)a->joint & 15)) return HQMQ_ERR_ALIGN;
+  return HQMQ_OK;
+}
+
+extern "C" size_t hqmq_encode_workspace_bytes(const hqmq_encode_args* a) {
+  if (validate_encode(a) != HQMQ_OK) return 0;
+  return plan_ws(*a).total;
+}
+
+extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = validate_encode(a);
+  if (rc) return rc;
+  const WsPlan wp = plan_ws(*a);
+  if (!workspace || workspace_bytes < wp.total) return HQMQ_ERR_WORKSPACE;
+  if ((uintptr_t)workspace & 15) return HQMQ_ERR_ALIGN;
+  if (a->T_new == 0) return HQMQ_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const hqmq_packed& d = a->dst;
+  const bool med = a->median_mult > 0.f;
+
+  EncGeom g;
+  g.B = d.B; g.H = d.H; g.T_new = a->T_new; g.n = d.n_chunks;
+  g.npl = 1; while (g.npl < g.n) g.npl <<= 1;
+  g.tpw = 32 / g.npl;
+  g.S = d.S; g.ib = idx_bits_for(d.S); g.rbits = d.radius_bits; g.qmax = (1 << d.radius_bits) - 1;
+  g.x_dtype = a->x_dtype;
+  g.xs_b = a->x_stride[0]; g.xs_h = a->x_stride[1]; g.xs_t = a->x_stride[2];
+
+  uint32_t* ws = reinterpret_cast<uint32_t*>(workspace);
+  HQMQ_CHECK_CUDA(cudaMemsetAsync(ws, 0, wp.total, st));
+  Maps24 maps;
+  memcpy(maps.ref_to_native, index_maps().ref_to_native, 24);
+
+  const int tok_per_block = kEncWarps * g.tpw * kEncIters;
+  dim3 grid((a->T_new + tok_per_block - 1) / tok_per_block, d.B * d.H);
+  size_t smem = (size_t)g.S * 16 + (size_t)kEncWarps * g.tpw * kMaxRowWords * 4 + (med ? kHistBins * 4 : 0);
+  if (smem > 200 * 1024) return HQMQ_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024)
+    HQMQ_CHECK_CUDA(cudaFuncSetAttribute(encode_main_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  encode_main_kernel<<<grid, kEncThreads, smem, st>>>(g, a->x, a->qs, d, a->t_start, med ? ws + wp.hist : nullptr, maps);
+  HQMQ_LAUNCH_CHECK();
+  if (!med) return HQMQ_OK;
+
+  const uint64_t N = (uint64_t)d.B * a->T_new * d.n_chunks;
+  const int64_t per_bh = (int64_t)a->T_new * d.n_chunks;
+  int hb = (int)((per_bh + 256 * 32 - 1) / (256 * 32));
+  if (hb < 1) hb = 1;
+  if (hb > 1024) hb = 1024;
+  uint32_t* hist = ws + wp.hist;
+  uint32_t* sel = ws + wp.sel;
+  select_kernel<<<d.H, 32, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr);
+  hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 1);
+  select_kernel<<<d.H, 32, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr);
+  hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 2);
+  select_kernel<<<d.H, 32, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out);
+  HQMQ_LAUNCH_CHECK();
+
+  const int tok_per_fblock = 8 * g.tpw;
+  int fb = (a->T_new + tok_per_fblock - 1) / tok_per_fblock;
+  if (fb > 4096) fb = 4096;
+  flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel, ws + wp.blk, wp.blk0, wp.nblk);
+  scan_kernel<<<(d.B * d.H + 63) / 64, 64, 0, st>>>(d, a->t_start, a->T_new, ws + wp.blk, wp.blk0, wp.nblk, ws + wp.status);
+  payload_kernel<<<dim3((a->T_new + 255) / 256, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start);
+  HQMQ_LAUNCH_CHECK();
+  return HQMQ_OK;
+}

@@ -1,0 +1,244 @@
+/*
+ * hqmq_b200 -- C ABI of the B200 (sm_100a) kernels for the HQMQ KV-cache hot path:
+ * encode (chunk norm, Med3x flag, per-token-max radius code, nearest codeword of the
+ * 24*S product codebook), packed dequant, and fused decode attention over the compressed
+ * cache.  Everything the Python host layer does on a GPU goes through these entry points.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative HQMQ_ERR_* code; nothing throws,
+ *     prints or exits.  hqmq_strerror() names a code.
+ *   - the caller owns every buffer (device pointers unless stated otherwise); the library
+ *     allocates no device memory and keeps no pointer after returning.
+ *   - all work is enqueued on the given CUDA stream (a cudaStream_t passed as void*);
+ *     nothing synchronises.  Argument problems are detected on the host before any launch.
+ *   - structs start with struct_size = sizeof(the struct) so that layouts can grow.
+ *
+ * The interfaces these replace live in the reference repository (kswain98/hqmq); each
+ * declaration cites them as path:line.
+ */
+#ifndef HQMQ_B200_H
+#define HQMQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HQMQ_ABI_VERSION 1
+
+/* error codes */
+#define HQMQ_OK 0
+#define HQMQ_ERR_ARG (-1)         /* null pointer, bad struct_size, bad enum */
+#define HQMQ_ERR_SHAPE (-2)       /* d % 4, H_q % H_kv, sizes out of the supported range */
+#define HQMQ_ERR_DTYPE (-3)
+#define HQMQ_ERR_ALIGN (-4)       /* pointer or stride not aligned as documented */
+#define HQMQ_ERR_WORKSPACE (-5)   /* workspace missing or too small */
+#define HQMQ_ERR_ARCH (-6)        /* device is not compute capability 10.x */
+#define HQMQ_ERR_CUDA (-7)        /* a CUDA runtime call failed (launch configuration etc.) */
+#define HQMQ_ERR_UNSUPPORTED (-8)
+#define HQMQ_ERR_CAPACITY (-9)    /* packed cache or outlier side buffer too small */
+
+/* element types */
+#define HQMQ_F32 0
+#define HQMQ_F16 1
+#define HQMQ_BF16 2
+#define HQMQ_I32 3
+#define HQMQ_I16 4
+#define HQMQ_I8 5
+#define HQMQ_U8 6
+#define HQMQ_I64 7
+
+/* Number of tokens per outlier-offset block of the native layout. */
+#define HQMQ_OUT_BLOCK 64
+
+/*
+ * Native compressed layout of one K or V tensor (what the roofline is measured on).
+ * The reference has no in-memory compressed format: its packed tuple is int32 indices +
+ * integer radius codes + per-token scale (src/quantizers/hqmq_attention.py:11-18) and
+ * its outlier wrapper keeps dense tensors (src/quantizers/outlier_aware.py:86).
+ *
+ * Per (batch b, KV head h) there are four token-major planes of capacity T_cap tokens
+ * (T_cap a multiple of 64):
+ *   codes  [B][H][T_cap][row_bytes]  one bit-packed row per token; chunk c occupies bits
+ *          [c*cb, (c+1)*cb) of the row, little-endian, cb = idx_bits + radius_bits,
+ *          field = native_idx | (rq << idx_bits), idx_bits = ceil(log2(24*S)).
+ *          native_idx = ((a*S + s) << 3) | u where the reference's primary index p
+ *          (src/quantizers/spherical.py:22-43) is factored as p = u * omega^a with u one
+ *          of the 8 axis units (reference order 0..7) and omega = (1+i+j+k)/2;
+ *          hqmq_native_index_maps() gives both directions.  row_bytes is a multiple of 4.
+ *   rs     [B][H][T_cap]             per-token radius scale r_max: fp16 / bf16 bits (2 B per
+ *          token, what the byte accounting assumes) or fp32 (exact fake-quant round trips)
+ *   flags  [B][H][T_cap]             uint32, bit c set = chunk c is an outlier kept in
+ *          full precision (NULL when the tensor was encoded without Med3x)
+ *   out_vals [B][H][out_cap][4]      the original 4 values of every flagged chunk as
+ *          fp16 / bf16 / fp32, in (token, chunk) order
+ *   out_off  [B][H][T_cap/64 + 1]    number of flagged chunks before each 64-token block
+ *   out_count[B][H]                  flagged chunks stored so far
+ * Appending tokens never rewrites an earlier row.
+ */
+typedef struct hqmq_packed {
+  uint32_t struct_size;
+  int32_t B, H;
+  int32_t T_cap;        /* plane capacity in tokens, multiple of 64 */
+  int32_t n_chunks;     /* d_head / 4, 1..32 */
+  int32_t S;            /* secondary codebook size, 24*S <= 65536 */
+  int32_t radius_bits;  /* 1..8 */
+  int32_t row_bytes;    /* hqmq_row_bytes(n_chunks, S, radius_bits) */
+  int32_t scale_dtype;  /* HQMQ_F16, HQMQ_BF16 or HQMQ_F32: element type of rs */
+  int32_t out_dtype;    /* HQMQ_F16, HQMQ_BF16 or HQMQ_F32: element type of out_vals */
+  int32_t out_cap;      /* capacity of out_vals per (b,h), in chunks */
+  int32_t reserved;
+  uint8_t* codes;
+  void* rs;
+  uint32_t* flags;
+  void* out_vals;
+  uint32_t* out_off;
+  uint32_t* out_count;
+} hqmq_packed;
+
+/*
+ * The reference's packed tuple (src/quantizers/hqmq_attention.py:11-18): idx and rq are
+ * (B,H,T,n_chunks) with unit stride on the last dim, rs is (B,H,T); strides in elements.
+ */
+typedef struct hqmq_ref_packed {
+  uint32_t struct_size;
+  int32_t idx_dtype;    /* HQMQ_I32 or HQMQ_I64 or HQMQ_I16 */
+  int32_t rq_dtype;     /* HQMQ_I32, HQMQ_I16, HQMQ_I8, HQMQ_U8, HQMQ_I64 */
+  int32_t rs_dtype;     /* HQMQ_F32, HQMQ_F16, HQMQ_BF16 */
+  const void* idx;
+  const void* rq;
+  const void* rs;
+  int64_t idx_stride[3]; /* b, h, t */
+  int64_t rq_stride[3];
+  int64_t rs_stride[2];  /* b, h (t has unit stride) */
+} hqmq_ref_packed;
+
+/* ---- library ------------------------------------------------------------------------ */
+int hqmq_abi_version(void);
+const char* hqmq_strerror(int code);
+/* HQMQ_OK if `device` has compute capability 10.x, else HQMQ_ERR_ARCH. */
+int hqmq_device_check(int device);
+int hqmq_idx_bits(int S);
+int hqmq_row_bytes(int n_chunks, int S, int radius_bits);
+/* Host tables, 24 entries each: ref_to_native[p] = (a << 3) | u, native_to_ref[(a << 3) | u] = p. */
+int hqmq_native_index_maps(uint8_t* ref_to_native, uint8_t* native_to_ref);
+
+/* ---- codebook ----------------------------------------------------------------------- */
+/*
+ * Derive the device tables the kernels use from the reference-order joint table
+ * joint[H][24*S][4] (fp32, k = p*S + s; src/quantizers/hqmq.py:119-143):
+ *   table16[H][24*S][4] fp16 in NATIVE index order (gathered by the attention/dequant kernels).
+ */
+int hqmq_codebook_tables(const float* joint, int H, int S, uint16_t* table16, void* stream);
+
+/* ---- encode --------------------------------------------------------------------------- */
+typedef struct hqmq_encode_args {
+  uint32_t struct_size;
+  int32_t x_dtype;          /* HQMQ_F32 / HQMQ_F16 / HQMQ_BF16 */
+  const void* x;            /* (B,H,T_new,d), last dim contiguous */
+  int64_t x_stride[3];      /* b, h, t in elements */
+  int32_t T_new;            /* tokens in this call */
+  int32_t t_start;          /* row of the packed planes that receives token 0 of x */
+  const float* qs;          /* (H,S,4) unit secondary quaternions, fp32 */
+  const float* joint;       /* (H,24*S,4) fp32 joint table, reference order */
+  float median_mult;        /* Med3x multiplier C; <= 0 disables outlier flagging */
+  int32_t search;           /* 0 = default, 1 = exhaustive scan over the S secondaries */
+  hqmq_packed dst;          /* destination planes */
+  float* med_out;           /* optional (H,) fp32: the per-head median of this call */
+} hqmq_encode_args;
+
+/*
+ * Replaces HQMQQuantizer._qdq (src/quantizers/hqmq.py:145-216, unit-magnitude linear
+ * radius path) and OutlierAwareHQMQQuantizer._qdq (src/quantizers/outlier_aware.py:56-87,
+ * threshold_mode="median_mult"), emitting the compressed representation instead of a
+ * dense fake-quantised tensor.  The Med3x median is taken over all B*T_new*n_chunks chunk
+ * norms of each head of THIS call, like the reference.
+ */
+size_t hqmq_encode_workspace_bytes(const hqmq_encode_args* args);
+int hqmq_encode(const hqmq_encode_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- layout conversion ---------------------------------------------------------------- */
+/*
+ * native -> reference tuple for tokens [t0, t0+T): idx int32 (B,H,T,n) in reference order,
+ * rq int32 (B,H,T,n), rs fp32 (B,H,T), flags uint8 (B,H,T,n) (may be NULL), all contiguous.
+ */
+int hqmq_unpack(const hqmq_packed* src, int t0, int T, int32_t* idx, int32_t* rq, float* rs,
+                uint8_t* flags, void* stream);
+/* reference tuple -> native planes at rows [t_start, t_start+T); indices are reference order. */
+int hqmq_pack(const hqmq_ref_packed* src, int T, hqmq_packed* dst, int t_start, void* stream);
+
+/* ---- dequant -------------------------------------------------------------------------- */
+typedef struct hqmq_dequant_args {
+  uint32_t struct_size;
+  int32_t layout;            /* 0 = native (src_native, table16 native order), 1 = reference tuple */
+  hqmq_packed src_native;
+  hqmq_ref_packed src_ref;
+  int32_t B, H, T, n_chunks; /* reference layout only (native takes them from src_native) */
+  int32_t t0;                /* first token (native layout) */
+  int32_t r_qmax;
+  int32_t scale_first;       /* 0: cw*((rq*rs)/qmax) as hqmq_attention.py:61; 1: cw*(rq*(rs/qmax)) as hqmq.py:210-216 */
+  int32_t joint_dtype;       /* reference layout: dtype of `joint` (arithmetic is done in it) */
+  const void* joint;         /* reference layout: (H,K,4), reference order */
+  int32_t K;                 /* reference layout: rows of joint per head */
+  const float* joint_f32;    /* native layout: (H,24S,4) fp32 reference order */
+  int32_t out_dtype;
+  void* out;                 /* (B,H,T,4*n_chunks) contiguous */
+  int32_t merge_outliers;    /* native layout with flags: write the original values of flagged chunks */
+} hqmq_dequant_args;
+
+/*
+ * Replaces _decode_kv_torch (src/quantizers/hqmq_attention.py:39-65) and
+ * hqmq_decode_triton (src/quantizers/hqmq_kernel.py:102-132).
+ */
+int hqmq_dequant(const hqmq_dequant_args* args, void* stream);
+
+/* ---- decode attention ------------------------------------------------------------------ */
+typedef struct hqmq_attn_args {
+  uint32_t struct_size;
+  int32_t layout;            /* 0 = native, 1 = reference tuple */
+  int32_t q_dtype;           /* dtype of Q and O */
+  const void* Q;             /* (B,H_q,T_q,d) */
+  int64_t q_stride[3];       /* b, h, t in elements; last dim contiguous */
+  void* O;                   /* (B,H_q,T_q,d) */
+  int64_t o_stride[3];
+  int32_t B, H_q, H_kv, T_q, T_kv, d;
+  int32_t r_qmax;
+  int32_t causal;            /* top-left aligned: query i sees keys 0..i (hqmq_attention.py:100,229) */
+  int32_t window;            /* > 0: only the last `window` keys (sliding window); 0 = all */
+  float softmax_scale;       /* <= 0: 1/sqrt(d) */
+  int32_t kv_splits;         /* 0 = choose; n > 0 = split the key range into n pieces */
+  int32_t partials_only;     /* 1: leave (m,l,o) partials of ONE piece per (b,h_q) in `partials` (sequence-parallel use) */
+  /* native layout */
+  hqmq_packed K, V;
+  const uint16_t* table_K;   /* (H_kv,24S,4) fp16 native order (hqmq_codebook_tables) */
+  const uint16_t* table_V;
+  /* reference layout */
+  hqmq_ref_packed K_ref, V_ref;
+  int32_t joint_dtype;
+  int32_t K_size;            /* rows per head of joint_K / joint_V */
+  const void* joint_K;       /* (H_kv,K,4) */
+  const void* joint_V;
+  float* partials;           /* partials_only: (B,H_q,T_q,d+2) fp32: o[d], m, l */
+} hqmq_attn_args;
+
+/*
+ * Replaces fused_hqmq_attention_triton (src/quantizers/hqmq_attention.py:425-518; kernel
+ * :120-265) with the semantics of its oracle fused_hqmq_attention_torch (:68-101).
+ */
+size_t hqmq_attn_workspace_bytes(const hqmq_attn_args* args);
+int hqmq_attn_decode(const hqmq_attn_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Merge n_parts partial results (o[d], m, l per row, as written with partials_only) into
+ * normalised outputs: parts is (n_parts, rows, d+2) fp32, out is (rows, d) of out_dtype.
+ * Used after gathering the partials of a sequence-split cache from the other GPUs.
+ */
+int hqmq_combine_partials(const float* parts, int n_parts, int64_t rows, int d, int out_dtype,
+                          void* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HQMQ_B200_H */

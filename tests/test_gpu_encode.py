@@ -1,0 +1,165 @@
+"""Encoder parity on the GPU, through the C ABI: indices, radius codes, per-token scales, Med3x
+medians, flags and outlier payloads against the oracle and the reference-generated fixtures.
+Integer outputs must be bit-exact; an index may differ only where the oracle's two best
+similarities are closer than 1e-6 (tolerance of the path's parity contract)."""
+import numpy as np
+import pytest
+import torch
+
+import hqmq_b200 as hqmq
+from oracle import hqmq_oracle as orc
+from tests.util import classify_idx, load_npz, make_kv
+
+pytestmark = pytest.mark.gpu
+NEAR_TIE = 1e-6
+
+
+def _encode_and_compare(x, S, br, C, layer=0, kv=0, n_layers=2, search=0, scale_dtype=torch.float32):
+    B, H, T, d = x.shape
+    q = hqmq.HQMQ(n_layers=n_layers, n_heads=H, secondary_size=S, radius_bits=br, device="cuda", seed=42)
+    joint = orc.joint_codebook(orc.secondary_raw(n_layers, H, S, 42)[layer, :, kv])
+    enc = orc.encode(x, joint, br, C)
+    med = torch.zeros(H, device="cuda")
+    pk = q.encode(x.cuda(), layer, kv, median_mult=C, scale_dtype=scale_dtype, search=search,
+                  med_out=med if C is not None else None)
+    idx, rq, rs, flags = pk.to_reference()
+    torch.cuda.synchronize()
+    assert torch.equal(rq.cpu(), enc["rq"]), "radius codes differ"
+    if scale_dtype == torch.float32:
+        assert torch.equal(rs.cpu(), enc["r_max"]), "per-token scales differ"
+    else:
+        assert torch.equal(rs.cpu(), enc["r_max"].to(scale_dtype).float())
+    n_mis, n_bad = classify_idx(idx, enc, NEAR_TIE)
+    assert n_bad == 0, f"{n_bad} index mismatches with oracle top-2 gap >= {NEAR_TIE}"
+    assert n_mis <= max(2, int(2e-3 * idx.numel())), f"{n_mis} near-tie mismatches is implausibly many"
+    if C is not None:
+        assert torch.equal(med.cpu(), enc["med"]), "median differs"
+        assert torch.equal(flags.cpu(), enc["flags"]), "outlier flags differ"
+        # payload: original values of flagged chunks in (token, chunk) order per (b,h)
+        n = d // 4
+        xc = x.view(B, H, T, n, 4)
+        cnt = pk.out_count.cpu().view(B, H)
+        ov = pk.out_vals.cpu()[: B * H * pk.out_cap * 4].view(B, H, pk.out_cap, 4).float()
+        for b in range(B):
+            for h in range(H):
+                want = xc[b, h][enc["flags"][b, h]].float()
+                assert cnt[b, h] == want.shape[0]
+                assert torch.equal(ov[b, h, : want.shape[0]], want), (b, h)
+    return q, pk, enc, n_mis
+
+
+@pytest.mark.parametrize("name", ["s24_r3", "s24_r3_med3", "s96_r4_med3", "s192_r6_med3", "s96_r4_d64"])
+def test_encode_matches_reference_fixtures(name):
+    z = load_npz("golden_encode.npz")
+    S, br, C, B, H, T, d = z[name + ".meta"]
+    S, br, C = int(S), int(br), (None if C < 0 else float(C))
+    for kv, layer in ((0, 0), (1, 1)):
+        key = f"{name}.kv{kv}"
+        x = torch.from_numpy(z[key + ".x"])
+        q, pk, enc, _ = _encode_and_compare(x, S, br, C, layer=layer, kv=kv)
+        # against the stored reference-derived integers, not only the live oracle
+        idx, rq, rs, flags = pk.to_reference()
+        assert np.array_equal(rq.cpu().numpy().astype(np.uint8), z[key + ".rq"])
+        mism = idx.cpu().numpy().astype(np.uint16) != z[key + ".idx"]
+        assert not (mism & (z[key + ".gap"] >= NEAR_TIE)).any()
+        # fake-quant output against the reference's own quantize_K / quantize_V output
+        qq = hqmq.with_outlier_extraction(q, C) if C is not None else q
+        fq = (qq.quantize_K if kv == 0 else qq.quantize_V)(x.cuda(), layer).cpu()
+        ref = torch.from_numpy(z[key + ".ref_fake_quant"])
+        if not mism.any():
+            assert torch.equal(fq, ref), "fake-quant output is not bit-identical to the reference"
+        else:
+            bad = (fq != ref).view(int(B), int(H), int(T), -1, 4).any(-1)
+            assert int(bad.sum()) <= int(mism.sum())
+
+
+@pytest.mark.parametrize("S,br,kind,C", [(24, 3, "randn", None), (96, 4, "hot", 3.0), (192, 6, "student", 3.0),
+                                         (24, 3, "spiky", 3.0)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_encode_16bit_inputs_upcast_contract(S, br, kind, C, dtype):
+    x16 = make_kv(kind, (2, 2, 96, 128), seed=11, dtype=dtype)
+    if dtype == torch.float16:
+        x16 = x16.clamp(-6e4, 6e4)
+    _encode_and_compare(x16.float(), S, br, C)                       # oracle sees the upcast
+    # the 16-bit tensor itself gives the same integers
+    H = 2
+    q = hqmq.HQMQ(n_layers=2, n_heads=H, secondary_size=S, radius_bits=br, device="cuda")
+    a = q.encode(x16.cuda(), 0, 0, median_mult=C, scale_dtype=torch.float32).to_reference()
+    b = q.encode(x16.float().cuda(), 0, 0, median_mult=C, scale_dtype=torch.float32).to_reference()
+    for u, v in zip(a, b):
+        if u is not None:
+            assert torch.equal(u, v)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1, 16), (1, 2, 3, 32), (2, 1, 33, 48), (1, 2, 129, 64), (3, 2, 31, 128)])
+def test_encode_ragged_shapes(shape):
+    x = make_kv("hot" if shape[3] >= 64 else "randn", shape, seed=5)
+    _encode_and_compare(x, 24, 3, 3.0)
+    _encode_and_compare(x, 96, 4, None)
+
+
+def test_encode_zero_and_tiny_chunks():
+    x = make_kv("randn", (1, 2, 8, 32), seed=9)
+    x[0, 0, 0] = 0.0                 # whole token zero: radius clamps to 1e-8
+    x[0, 1, 3, 4:8] = 0.0            # one zero chunk
+    x[0, 1, 5] *= 1e-12
+    _encode_and_compare(x, 24, 3, 3.0)
+
+
+def test_encode_append_keeps_earlier_rows_and_offsets():
+    S, br, C = 96, 4, 3.0
+    x = make_kv("hot", (2, 2, 200, 64), seed=21)
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, 2, S, br, device="cuda"), C)
+    joint = orc.joint_codebook(orc.secondary_raw(1, 2, S, 42)[0, :, 0])
+    cache = q.inner.new_cache(2, 256, 64, "cuda", scale_dtype=torch.float32, with_outliers=True,
+                              out_dtype=torch.float32)
+    cuts = [0, 70, 71, 128, 200]
+    encs = []
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        q.encode(x[:, :, lo:hi].cuda(), 0, 0, out=cache)
+        encs.append(orc.encode(x[:, :, lo:hi], joint, br, C))      # each call has its own median
+    idx, rq, rs, flags = cache.to_reference()
+    want = {k: torch.cat([e[k] for e in encs], dim=2) for k in ("idx", "rq", "r_max", "flags", "gap")}
+    assert torch.equal(rq.cpu(), want["rq"]) and torch.equal(rs.cpu(), want["r_max"])
+    assert torch.equal(flags.cpu(), want["flags"])
+    assert classify_idx(idx, want)[1] == 0
+    # merged dequant == oracle fake-quant with originals restored
+    dense = q.decode(cache, 0, 0, dtype=torch.float32, scale_first=True).cpu()
+    for (lo, hi), e in zip(zip(cuts[:-1], cuts[1:]), encs):
+        ref = orc.fake_quant(x[:, :, lo:hi], joint, br, C, enc=e)
+        same_idx = (idx.cpu()[:, :, lo:hi] == e["idx"]).repeat_interleave(4, dim=-1).view_as(ref)
+        assert torch.equal(dense[:, :, lo:hi][same_idx], ref[same_idx])
+    assert abs(q._observed_outlier_rate - np.mean([float(e["flags"].float().mean()) for e in encs])) < 1e-6
+
+
+def test_exhaustive_and_default_search_agree():
+    x = make_kv("hot", (1, 2, 64, 128), seed=33)
+    a = _encode_and_compare(x, 96, 4, None, search=0)[1].to_reference()[0]
+    b = _encode_and_compare(x, 96, 4, None, search=1)[1].to_reference()[0]
+    assert (a != b).float().mean().item() < 1e-3
+
+
+def test_full_size_properties_config2_slice():
+    """One (b, h) column of the Llama-3-8B-shaped configuration at its full context (32768 tokens):
+    size-independent properties instead of an element-wise oracle."""
+    S, br, C = 96, 4, 3.0
+    x = make_kv("hot", (1, 2, 32768, 128), seed=1002, dtype=torch.bfloat16).cuda()
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, 2, S, br, device="cuda"), C)
+    med = torch.zeros(2, device="cuda")
+    pk = q.encode(x, 0, 0, scale_dtype=torch.float32, med_out=med)
+    idx, rq, rs, flags = pk.to_reference()
+    xf = x.float().view(1, 2, 32768, 32, 4)
+    nrm = xf.norm(dim=-1)
+    # median property: at least half of the norms are <= med and at least half are >= med
+    for h in range(2):
+        v = nrm[0, h].reshape(-1)
+        assert (v <= med[h]).float().mean() >= 0.5 and (v >= med[h]).float().mean() >= 0.5
+        assert torch.equal(flags[0, h], nrm[0, h] > med[h] * C) or (flags[0, h] != (nrm[0, h] > med[h] * C)).sum() <= 2
+    assert int(rq.max()) == 15 and int(rq.min()) >= 0
+    assert (rq.max(dim=-1).values == 15).all()            # the token's largest chunk always codes qmax
+    assert int(idx.max()) < 24 * S and int(idx.min()) >= 0
+    assert pk.n_outliers() == int(flags.sum())
+    # idempotence: re-encoding the fake-quantised tensor reproduces the same codes (outliers restored)
+    dense = q.decode(pk, 0, 0, dtype=torch.float32, scale_first=True)
+    cos = torch.nn.functional.cosine_similarity(dense.view(-1, 4), x.float().view(-1, 4), dim=-1)
+    assert cos.mean() > 0.98

@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the HQMQ hot path on B200: fused decode attention over the compressed KV cache
+(headline) and KV-cache encode throughput, on synthetic data of the shapes the baseline names.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4_128k|c1] [--impl reference]
+
+One "step" = one decode-attention call for one new query token per sequence over the whole resident
+compressed cache of one layer (the cache is state that lives in HBM, like weights; the step's inputs
+are the queries, its result the attention output).  Rank 0 prints one JSON line:
+  value / unit   achieved HBM GB/s on the algorithmic compressed bytes, whole job (all ranks);
+                 us_per_step and ms_per_step carry the latency side of the same measurement
+  e2e            the same through the public Python API with the queries in pinned host memory
+                 (H2D inside the timed region) and the output read back (D2H)
+  roofline       the dominant kernel (attn_decode_kernel) against the measured HBM peak
+  cpu_baseline   the oracle (a torch-CPU restatement of the reference's path) timed on a bounded sample
+  encode         encoder throughput (tokens/s, GB/s) on a bounded slice of the same workload
+With --gpus N > 1 (launched by torchrun, one rank per GPU) every rank holds its own batch shard of the
+same shape (weak scaling by batch; no data-path collective).
+"""
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: B, Hq, Hkv, d, T, S, b_r, C, K-kind, V-kind
+    "c1": dict(B=1, Hq=32, Hkv=8, d=128, T=4096, S=24, br=3, C=None, kk="randn", vk="randn", dtype="fp16",
+               desc="Mistral-7B-shaped layer, s24_r3, no outliers"),
+    "c2": dict(B=16, Hq=32, Hkv=8, d=128, T=32768, S=96, br=4, C=3.0, kk="hot", vk="randn", dtype="bf16",
+               desc="Llama-3-8B-shaped GQA decode, s96_r4 + Med3x"),
+    "c3": dict(B=32, Hq=28, Hkv=4, d=128, T=8192, S=192, br=6, C=3.0, kk="student", vk="randn", dtype="bf16",
+               desc="Qwen2.5-7B-shaped outlier-heavy cache, s192_r6 + Med3x"),
+    "c4_128k": dict(B=1, Hq=32, Hkv=8, d=128, T=131072, S=24, br=3, C=3.0, kk="spiky", vk="spiky", dtype="bf16",
+                    desc="long-context single sequence, s24_r3 + Med3x"),
+    "c5_layer": dict(B=64, Hq=64, Hkv=8, d=64, T=16384, S=96, br=4, C=3.0, kk="onehot", vk="onehot", dtype="bf16",
+                     desc="gpt-oss-20b-shaped full-attention layer, s96_r4 + Med3x"),
+}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def synth(kind, shape, seed, device, dtype):
+    """Seeded synthetic K/V with the value distribution the workload names."""
+    B, H, T, d = shape
+    g = torch.Generator(device=device).manual_seed(seed)
+    gc = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, H, T, d, generator=g, device=device, dtype=torch.float32)
+    if kind == "hot":
+        for h in range(H):
+            ch = torch.randperm(d, generator=gc)[:4].to(device)
+            x[:, h, :, ch] *= 8.0
+    elif kind == "onehot":
+        for h in range(H):
+            ch = torch.randperm(d, generator=gc)[:1].to(device)
+            scale = math.exp(torch.rand(1, generator=gc).item() * math.log(200.0))
+            x[:, h, :, ch] *= scale
+    elif kind == "student":
+        for h in range(H):
+            ch = torch.randperm(d, generator=gc)[:2].to(device)
+            z = torch.randn(B, T, 2, generator=g, device=device)
+            chi = (torch.randn(B, T, 2, generator=g, device=device) ** 2 + torch.randn(B, T, 2, generator=g, device=device) ** 2) / 2
+            x[:, h, :, ch] = 100.0 * z / chi.sqrt()
+    elif kind == "spiky":
+        m = torch.rand(B, H, T, d // 4, generator=g, device=device) < 0.005
+        x = (x.view(B, H, T, d // 4, 4) * torch.where(m, 20.0, 1.0).unsqueeze(-1)).view(B, H, T, d)
+    return x.to(dtype)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 8 for n, v in zip(names, r[4:8]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": reasons}
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------------
+def cpu_port_run(w, sample_T, reps, threads=None):
+    """The oracle (CPU restatement of the reference's path) on a bounded sample: B=1, sample_T tokens of
+    the workload's distribution.  Returns seconds per decode step, encode seconds, and the sample's
+    algorithmic bytes."""
+    from oracle import hqmq_oracle as orc
+    if threads:
+        torch.set_num_threads(threads)
+    Hkv, Hq, d, S, br, Cm = w["Hkv"], w["Hq"], w["d"], w["S"], w["br"], w["C"]
+    dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
+    K = synth(w["kk"], (1, Hkv, sample_T, d), 1002, "cpu", dtype)
+    V = synth(w["vk"], (1, Hkv, sample_T, d), 1003, "cpu", dtype)
+    Q = (torch.randn(1, Hq, 1, d, generator=torch.Generator().manual_seed(7)) / math.sqrt(d)).to(dtype)
+    raw = orc.secondary_raw(1, Hkv, S, 42)
+    jk, jv = orc.joint_codebook(raw[0, :, 0]), orc.joint_codebook(raw[0, :, 1])
+    t0 = time.perf_counter()
+    ek = orc.encode(K, jk, br, Cm)
+    ev = orc.encode(V, jv, br, Cm)
+    t_enc = time.perf_counter() - t0
+    qmax = (1 << br) - 1
+    kw = {}
+    if Cm is not None:
+        kw = dict(K_flags=ek["flags"], K_orig=K, V_flags=ev["flags"], V_orig=V)
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        orc.fused_attention(Q, ek["idx"], ek["rq"], ek["r_max"], jk, ev["idx"], ev["rq"], ev["r_max"], jv, qmax,
+                            causal=False, **kw)
+        ts.append(time.perf_counter() - t0)
+    n = d // 4
+    ib = math.ceil(math.log2(24 * S))
+    per_tok = n * (ib + br) / 8 + 2
+    nbytes = 2 * Hkv * sample_T * per_tok
+    if Cm is not None:
+        nbytes += 2 * Hkv * sample_T * n / 8 + 8 * (int(ek["flags"].sum()) + int(ev["flags"].sum()))
+    return dict(step_s=sorted(ts)[len(ts) // 2], encode_s=t_enc, bytes=nbytes, tokens=sample_T,
+                threads=torch.get_num_threads())
+
+
+def run_reference_arm(args, w, rank, world):
+    """--impl reference: the reference's CPU implementation of the path (its torch restatement under
+    oracle/, since the Python reference itself does not travel to the GPU box), all host threads, on a
+    bounded sample of the same workload."""
+    if rank != 0:
+        return
+    sample_T = min(w["T"], 4096)
+    ts = []
+    info = None
+    for i in range(args.warmup + args.steps):
+        info = cpu_port_run(w, sample_T, reps=1)
+        if i >= args.warmup:
+            ts.append(info["step_s"])
+    step = sum(ts) / len(ts)
+    gbs = info["bytes"] / step / 1e9
+    line = {
+        "metric": "decode-attn achieved HBM GB/s on the compressed cache (us/step in us_per_step)", "value": gbs,
+        "unit": "GB/s", "impl": "reference", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": step * 1e3, "us_per_step": step * 1e6, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "desc": w["desc"], "sample": f"B=1, T={sample_T} of the workload"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": info["threads"], "kind": "port",
+                         "sample": f"B=1, H_kv={w['Hkv']}, T={sample_T}: decode_packed + SDPA in fp32 per step"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "encode": {"tokens_per_s": sample_T / info["encode_s"], "sample_tokens": sample_T},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kv-splits", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size")
+    ap.add_argument("--context", type=int, default=0, help="override the workload's context length")
+    ap.add_argument("--no-med3x", action="store_true", help="encode without outlier extraction")
+    args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+    if args.batch:
+        w["B"] = args.batch
+    if args.context:
+        w["T"] = args.context
+    if args.no_med3x:
+        w["C"] = None
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+
+    if args.impl == "reference":
+        run_reference_arm(args, w, rank, world)
+        return
+
+    import hqmq_b200 as hqmq
+    from hqmq_b200 import _lib
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+        dist = dist_
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, Hq, Hkv, d, T, S, br, Cm = (w[k] for k in ("B", "Hq", "Hkv", "d", "T", "S", "br", "C"))
+    dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
+    inner = hqmq.HQMQ(n_layers=1, n_heads=Hkv, secondary_size=S, radius_bits=br, device=dev, seed=42)
+    quant = hqmq.with_outlier_extraction(inner, Cm) if Cm is not None else inner
+
+    # ---- build the resident compressed cache (untimed set-up) -------------------------------------------
+    caches = []
+    enc_times = []
+    for kv, kind, seed in ((0, w["kk"], 1002), (1, w["vk"], 1003)):
+        x = synth(kind, (B, Hkv, T, d), seed + 100 * rank, dev, dtype)
+        cap = None if Cm is None else max(1024, int(0.2 * T * (d // 4)))
+        pk = inner.new_cache(B, T, d, dev, scale_dtype=dtype, with_outliers=Cm is not None, out_dtype=dtype, out_cap=cap)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        quant.encode(x, 0, kv, out=pk)
+        e1.record()
+        torch.cuda.synchronize()
+        enc_times.append(e0.elapsed_time(e1) * 1e-3)
+        if Cm is not None and int(pk.out_count.max()) > pk.out_cap:
+            raise RuntimeError("outlier side buffer too small for this data")
+        caches.append(pk)
+        del x
+    Kp, Vp = caches
+    tk, tv = inner.tables(0, 0, dev), inner.tables(0, 1, dev)
+    algo_bytes = Kp.algorithmic_bytes() + Vp.algorithmic_bytes()
+    enc_in_bytes = 2 * B * Hkv * T * d * 2
+    enc_tokens_per_s = B * T / sum(enc_times)
+    enc_gbs = (enc_in_bytes + algo_bytes) / sum(enc_times) / 1e9
+    outl_frac = [(pk.n_outliers() / (B * Hkv * T * (d // 4))) if Cm is not None else 0.0 for pk in caches]
+
+    # ---- one decode step through the C ABI, descriptors built once -------------------------------------
+    Qh = (torch.randn(B, Hq, 1, d, generator=torch.Generator().manual_seed(7 + rank)) / math.sqrt(d)).to(dtype).pin_memory()
+    Oh = torch.empty(B, Hq, 1, d, dtype=dtype).pin_memory()
+    Qd = Qh.to(dev)
+    Od = torch.empty_like(Qd)
+    a = _lib.AttnArgs()
+    a.struct_size = C.sizeof(_lib.AttnArgs)
+    a.layout = 0
+    a.q_dtype = a.o_dtype = _lib.dtype_enum(dtype)
+    a.Q, a.O = Qd.data_ptr(), Od.data_ptr()
+    a.q_stride = (C.c_int64 * 3)(*Qd.stride()[:3])
+    a.o_stride = (C.c_int64 * 3)(*Od.stride()[:3])
+    a.B, a.H_q, a.H_kv, a.T_q, a.T_kv, a.d = B, Hq, Hkv, 1, T, d
+    a.r_qmax, a.causal, a.window, a.softmax_scale, a.kv_splits = Kp.qmax, 0, 0, 0.0, args.kv_splits
+    a.K, a.V = Kp.c_struct(), Vp.c_struct()
+    a.table_K, a.table_V = tk["table16"].data_ptr(), tv["table16"].data_ptr()
+    L = _lib.lib()
+    ws_bytes = L.hqmq_attn_workspace_bytes(C.byref(a))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        rc = L.hqmq_attn_decode(C.byref(a), ws.data_ptr(), ws_bytes, stream.cuda_stream)
+        if rc:
+            raise RuntimeError(L.hqmq_strerror(rc).decode())
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # the timed region: exactly `steps` steps between barriers; the cache (>= 100 MB) exceeds what L2 keeps
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    barrier()
+    dev_s = ev0.elapsed_time(ev1) * 1e-3
+    # e2e: host queries -> device, attention, output -> host, every step
+    for _ in range(3):
+        Qd.copy_(Qh, non_blocking=True); step(); Oh.copy_(Od, non_blocking=True)
+    barrier()
+    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev2.record(stream)
+    for _ in range(args.steps):
+        Qd.copy_(Qh, non_blocking=True)
+        step()
+        Oh.copy_(Od, non_blocking=True)
+        stream.synchronize()        # the caller consumes the output before the next token
+    ev3.record(stream)
+    barrier()
+    e2e_s = ev2.elapsed_time(ev3) * 1e-3
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([dev_s, e2e_s], device=dev, dtype=torch.float64)
+    tot_bytes = torch.tensor([float(algo_bytes)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot_bytes, op=dist.ReduceOp.SUM)
+    dev_s, e2e_s = float(t[0]), float(t[1])
+    total_bytes = float(tot_bytes[0])
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    step_s = dev_s / args.steps
+    gbs = total_bytes / step_s / 1e9
+    peak, peak_kind = hbm_peak()
+    per_gpu_gbs = algo_bytes / step_s / 1e9
+    line = {
+        "metric": "decode-attn achieved HBM GB/s on the compressed cache (us/step in us_per_step)",
+        "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": step_s * 1e3, "us_per_step": step_s * 1e6, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 mma / f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "desc": w["desc"], "batch_per_gpu": B, "global_batch": B * world,
+                   "q_heads": Hq, "kv_heads": Hkv, "d_head": d, "context": T, "S": S, "radius_bits": br,
+                   "median_mult": Cm, "outlier_fraction_K_V": outl_frac, "sharding": f"batch x{world}",
+                   "l2": "compressed cache per GPU exceeds L2 (inputs larger than L2, no flush needed)"
+                   if algo_bytes > 2 * 126e6 else "cache smaller than 2x L2: numbers include L2 hits"},
+        "compressed_bytes_per_step": total_bytes,
+        "fp16_cache_bytes_equiv": 2 * 2 * B * Hkv * T * d * world,
+        "e2e": {"value": total_bytes / (e2e_s / args.steps) / 1e9, "unit": "GB/s",
+                "us_per_step": e2e_s / args.steps * 1e6,
+                "h2d_bytes_per_step": Qh.numel() * Qh.element_size(), "d2h_bytes_per_step": Oh.numel() * Oh.element_size()},
+        "gpu_launches": 2 * args.steps,
+        "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
+                     "peak_kind": f"of {peak_kind}", "frac_of_8TBs_nominal": per_gpu_gbs / 8000.0,
+                     "kernel": "attn_decode_kernel (+ combine_kernel, inside the same timed step)",
+                     "traffic": None},
+        "encode": {"tokens_per_s": enc_tokens_per_s * world, "GBps_per_gpu": enc_gbs, "frac_of_peak": enc_gbs / peak,
+                   "tokens": B * T, "seconds_K_V": enc_times,
+                   "note": "one call per tensor over the whole (B, H_kv, T, d) input, Med3x median per call"},
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        sample_T = min(T, 4096)
+        info = cpu_port_run(w, sample_T, reps=3)
+        line["cpu_baseline"] = {"value": info["bytes"] / info["step_s"] / 1e9, "unit": "GB/s", "cores": info["threads"],
+                                "kind": "port", "us_per_step_sample": info["step_s"] * 1e6,
+                                "encode_tokens_per_s": sample_T / info["encode_s"],
+                                "sample": f"B=1, H_kv={Hkv}, T={sample_T} of the workload; decode_packed + SDPA fp32"}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -13,7 +13,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libhqmq_b200.so")
 
 F32, F16, BF16, I32, I16, I8, U8, I64 = range(8)
-OUT_BLOCK = 64
+OUT_BLOCK = 16
+T_ALIGN = 64
 
 _TORCH_TO_ENUM = {
     torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: I32,
@@ -75,7 +76,8 @@ class DequantArgs(C.Structure):
 
 class AttnArgs(C.Structure):
     _fields_ = [
-        ("struct_size", C.c_uint32), ("layout", C.c_int32), ("q_dtype", C.c_int32), ("Q", C.c_void_p),
+        ("struct_size", C.c_uint32), ("layout", C.c_int32), ("q_dtype", C.c_int32), ("o_dtype", C.c_int32),
+        ("Q", C.c_void_p),
         ("q_stride", C.c_int64 * 3), ("O", C.c_void_p), ("o_stride", C.c_int64 * 3),
         ("B", C.c_int32), ("H_q", C.c_int32), ("H_kv", C.c_int32), ("T_q", C.c_int32), ("T_kv", C.c_int32),
         ("d", C.c_int32), ("r_qmax", C.c_int32), ("causal", C.c_int32), ("window", C.c_int32),

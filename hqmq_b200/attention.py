@@ -22,7 +22,11 @@ from .packed import PackedKV
 def _fill_q(a: _lib.AttnArgs, Q: torch.Tensor, O: Optional[torch.Tensor]):
     a.q_dtype, a.Q = _lib.dtype_enum(Q.dtype), Q.data_ptr()
     a.q_stride = (C.c_int64 * 3)(*Q.stride()[:3])
+    a.o_dtype = a.q_dtype
     if O is not None:
+        if O.stride(-1) != 1:
+            raise _lib.HqmqError("hqmq_b200: the output tensor needs unit stride on the last dim")
+        a.o_dtype = _lib.dtype_enum(O.dtype)
         a.O = O.data_ptr()
         a.o_stride = (C.c_int64 * 3)(*O.stride()[:3])
 

@@ -251,7 +251,50 @@ __device__ __forceinline__ void static_for(F&& f) {
   }
 }
 
-template <int N, int CB>
+// ---- Med3x outliers ----------------------------------------------------------------------------------
+// Flagged chunks keep their original 4 values in a side buffer.  They are merged by overwriting the
+// decoded fragment with x * qmax / rs (the token's scale is its largest chunk norm, flagged chunks
+// included, so the patched value never exceeds qmax in magnitude and cannot overflow fp16).
+static_assert(kTile == HQMQ_OUT_BLOCK, "one outlier-offset entry per KV tile");
+
+struct OutlRaw { uint32_t fk, fv, offk, offv; };   // lanes 0..15: flag words of the tile's tokens
+
+struct OutlSide {
+  const uint32_t* flags; const uint32_t* off; const unsigned char* vals; int dtype;
+  __device__ __forceinline__ void init(const hqmq_packed& pk, int64_t bh) {
+    flags = pk.flags ? pk.flags + bh * pk.T_cap : nullptr;
+    off = pk.flags ? pk.out_off + bh * (pk.T_cap / HQMQ_OUT_BLOCK + 1) : nullptr;
+    dtype = pk.out_dtype;
+    vals = reinterpret_cast<const unsigned char*>(pk.out_vals) + bh * pk.out_cap * 4 * (dtype == HQMQ_F32 ? 4 : 2);
+  }
+  // original values of payload entry `pos`, scaled by `inv`, as two half2 registers
+  __device__ __forceinline__ void load(uint32_t pos, float inv, uint32_t& lo, uint32_t& hi) const {
+    float x0, x1, x2, x3;
+    if (dtype == HQMQ_F32) {
+      const float4 v = *reinterpret_cast<const float4*>(vals + (int64_t)pos * 16);
+      x0 = v.x; x1 = v.y; x2 = v.z; x3 = v.w;
+    } else {
+      const uint2 v = *reinterpret_cast<const uint2*>(vals + (int64_t)pos * 8);
+      x0 = bits16_to_float((uint16_t)(v.x & 0xffff), dtype); x1 = bits16_to_float((uint16_t)(v.x >> 16), dtype);
+      x2 = bits16_to_float((uint16_t)(v.y & 0xffff), dtype); x3 = bits16_to_float((uint16_t)(v.y >> 16), dtype);
+    }
+    lo = pack_half2(x0 * inv, x1 * inv);
+    hi = pack_half2(x2 * inv, x3 * inv);
+  }
+};
+
+// Exclusive prefix sum of v over lanes 0..15 (lanes >= 16 hold 0).
+__device__ __forceinline__ uint32_t excl_scan16(uint32_t v, int lane) {
+  uint32_t x = v;
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) {
+    const uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  return x - v;
+}
+
+template <int N, int CB, bool OUTL>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnParams p) {
   using G_ = Geo<N>;
   using Loader = typename LoaderFor<N, CB>::type;
@@ -319,13 +362,64 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
 
   Loader ld(p, b, h, lane);
   typename Loader::Raw cur, nxt;
+  OutlSide ok_, ov_;
+  OutlRaw ocur = {0, 0, 0, 0}, onxt = {0, 0, 0, 0};
+  if constexpr (OUTL) {
+    ok_.init(p.K, (int64_t)b * p.Hkv + h);
+    ov_.init(p.V, (int64_t)b * p.Hkv + h);
+  }
+  auto fetch_outl = [&](OutlRaw& o, int tl) {
+    o.fk = o.fv = o.offk = o.offv = 0;
+    const int tt = tl * kTile + (lane & 15);
+    if (lane < 16 && tt < t_end) {
+      if (ok_.flags) o.fk = ok_.flags[tt];
+      if (ov_.flags) o.fv = ov_.flags[tt];
+    }
+    if (ok_.flags) o.offk = ok_.off[tl];
+    if (ov_.flags) o.offv = ov_.off[tl];
+  };
   int tile = my_lo + warp;
-  if (tile < my_hi) ld.fetch(cur, tile, t_end);
+  if (tile < my_hi) {
+    ld.fetch(cur, tile, t_end);
+    if constexpr (OUTL) fetch_outl(ocur, tile);
+  }
 
   for (; tile < my_hi; tile += kAttnWarps) {
     const int tn = tile + kAttnWarps;
-    if (tn < my_hi) ld.fetch(nxt, tn, t_end);
+    if (tn < my_hi) {
+      ld.fetch(nxt, tn, t_end);
+      if constexpr (OUTL) fetch_outl(onxt, tn);
+    }
     const int t0 = tile * kTile;
+
+    // ---- outlier bookkeeping of this tile -------------------------------------------------------------
+    bool anyK = false, anyV = false;
+    uint32_t kfl[2] = {0, 0}, kpre[2] = {0, 0}, vfl[4] = {0, 0, 0, 0}, vpre[4] = {0, 0, 0, 0};
+    float kinv[2] = {0.f, 0.f};
+    if constexpr (OUTL) {
+      anyK = __ballot_sync(0xffffffffu, ocur.fk != 0) != 0;
+      anyV = __ballot_sync(0xffffffffu, ocur.fv != 0) != 0;
+      if (anyK) {
+        const uint32_t ex = excl_scan16(__popc(ocur.fk), lane) + ocur.offk;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          kfl[nt] = __shfl_sync(0xffffffffu, ocur.fk, nt * 8 + r);
+          kpre[nt] = __shfl_sync(0xffffffffu, ex, nt * 8 + r);
+          // the K-side lane owns token nt*8 + r; its scale is not among the ones the tile data carries
+          const int t = t0 + nt * 8 + r;
+          kinv[nt] = (kfl[nt] && t < t_end) ? (float)((1 << p.K.radius_bits) - 1) / load_scale(p.K, ((int64_t)b * p.Hkv + h) * p.K.T_cap + t) : 0.f;
+        }
+      }
+      if (anyV) {
+        const uint32_t ex = excl_scan16(__popc(ocur.fv), lane) + ocur.offv;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int tl = 2 * j + (i & 1) + (i >> 1) * 8;
+          vfl[i] = __shfl_sync(0xffffffffu, ocur.fv, tl);
+          vpre[i] = __shfl_sync(0xffffffffu, ex, tl);
+        }
+      }
+    }
 
     // ---- S = Q K^T ---------------------------------------------------------------------------------
     float s[2][4];
@@ -338,7 +432,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
         const uint32_t f = ld.template kfield<nt, ks>(cur);
         const uint2 cw = tblK[f & ((1u << p.ib) - 1u)];
         const __half2 rr = radius_half2(f >> p.ib);
-        mma16816(s[nt], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], hmul2_u32(cw.x, rr), hmul2_u32(cw.y, rr));
+        uint32_t b0 = hmul2_u32(cw.x, rr), b1 = hmul2_u32(cw.y, rr);
+        if constexpr (OUTL) {
+          if (anyK) {
+            const int c = j * NKS + ks;
+            if ((kfl[nt] >> c) & 1u) ok_.load(kpre[nt] + __popc(kfl[nt] & ((1u << c) - 1u)), kinv[nt], b0, b1);
+          }
+        }
+        mma16816(s[nt], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
       });
     });
 
@@ -401,6 +502,15 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
         const __half2 rr = radius_half2(f >> p.ib);
         lo[i] = hmul2_u32(cw.x, rr);
         hi[i] = hmul2_u32(cw.y, rr);
+        if constexpr (OUTL) {
+          if (anyV) {
+            const int c = r * NVG + g;
+            if (c < N && ((vfl[i] >> c) & 1u)) {
+              const float rsv = ld.vscale(cur, i >> 1, i & 1);
+              ov_.load(vpre[i] + __popc(vfl[i] & ((1u << c) - 1u)), (float)((1 << p.V.radius_bits) - 1) / rsv, lo[i], hi[i]);
+            }
+          }
+        }
       });
       mma16816(o[g * 4 + 0], pa0, pa1, pa2, pa3, __byte_perm(lo[0], lo[1], 0x5410), __byte_perm(lo[2], lo[3], 0x5410));
       mma16816(o[g * 4 + 1], pa0, pa1, pa2, pa3, __byte_perm(lo[0], lo[1], 0x7632), __byte_perm(lo[2], lo[3], 0x7632));
@@ -408,6 +518,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnPar
       mma16816(o[g * 4 + 3], pa0, pa1, pa2, pa3, __byte_perm(hi[0], hi[1], 0x7632), __byte_perm(hi[2], hi[3], 0x7632));
     });
     cur = nxt;
+    if constexpr (OUTL) ocur = onxt;
   }
 
   // ---- per-warp partial: o[d], m, l for every query head of this KV head ---------------------------
@@ -496,7 +607,7 @@ int make_plan(const hqmq_attn_args* a, Plan& pl) {
 int validate_attn(const hqmq_attn_args* a) {
   if (!a || a->struct_size != sizeof(hqmq_attn_args)) return HQMQ_ERR_ARG;
   if (!a->Q || (!a->O && !a->partials_only)) return HQMQ_ERR_ARG;
-  if (!is_float_dtype(a->q_dtype)) return HQMQ_ERR_DTYPE;
+  if (!is_float_dtype(a->q_dtype) || !is_float_dtype(a->o_dtype)) return HQMQ_ERR_DTYPE;
   if (a->B < 1 || a->H_q < 1 || a->H_kv < 1 || a->T_q < 1 || a->T_kv < 0 || a->d < 1) return HQMQ_ERR_SHAPE;
   if (a->H_q % a->H_kv) return HQMQ_ERR_SHAPE;
   if (a->H_q / a->H_kv > 16) return HQMQ_ERR_UNSUPPORTED;
@@ -529,9 +640,9 @@ int validate_attn(const hqmq_attn_args* a) {
   return HQMQ_OK;
 }
 
-template <int N, int CB>
+template <int N, int CB, bool OUTL>
 int launch(const AttnParams& p, const Plan& pl, cudaStream_t st) {
-  auto kern = attn_decode_kernel<N, CB>;
+  auto kern = attn_decode_kernel<N, CB, OUTL>;
   if (pl.smem > 48 * 1024) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
       return HQMQ_ERR_CUDA;
@@ -541,16 +652,20 @@ int launch(const AttnParams& p, const Plan& pl, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? HQMQ_OK : HQMQ_ERR_CUDA;
 }
 
-template <int N>
+template <int N, bool OUTL>
 int dispatch_cb(const AttnParams& p, const Plan& pl, int cb, bool fast_ok, cudaStream_t st) {
   if constexpr (N == 16 || N == 32) {
     if (fast_ok) {
-      if (cb == 13) return launch<N, 13>(p, pl, st);
-      if (cb == 16) return launch<N, 16>(p, pl, st);
-      if (cb == 19) return launch<N, 19>(p, pl, st);
+      if (cb == 13) return launch<N, 13, OUTL>(p, pl, st);
+      if (cb == 16) return launch<N, 16, OUTL>(p, pl, st);
+      if (cb == 19) return launch<N, 19, OUTL>(p, pl, st);
     }
   }
-  return launch<N, 0>(p, pl, st);
+  return launch<N, 0, OUTL>(p, pl, st);
+}
+template <int N>
+int dispatch_outl(const AttnParams& p, const Plan& pl, int cb, bool fast_ok, bool outl, cudaStream_t st) {
+  return outl ? dispatch_cb<N, true>(p, pl, cb, fast_ok, st) : dispatch_cb<N, false>(p, pl, cb, fast_ok, st);
 }
 
 }  // namespace
@@ -612,18 +727,19 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
     p.Kr = a->K_ref; p.Vr = a->V_ref; p.jK = a->joint_K; p.jV = a->joint_V; p.j_dtype = a->joint_dtype;
     p.ib = 16;
   }
+  const bool outl = a->layout == 0 && (a->K.flags != nullptr || a->V.flags != nullptr);
   switch (n) {
-    case 4: rc = dispatch_cb<4>(p, pl, cb, fast_ok, st); break;
-    case 8: rc = dispatch_cb<8>(p, pl, cb, fast_ok, st); break;
-    case 12: rc = dispatch_cb<12>(p, pl, cb, fast_ok, st); break;
-    case 16: rc = dispatch_cb<16>(p, pl, cb, fast_ok, st); break;
-    case 32: rc = dispatch_cb<32>(p, pl, cb, fast_ok, st); break;
+    case 4: rc = dispatch_outl<4>(p, pl, cb, fast_ok, outl, st); break;
+    case 8: rc = dispatch_outl<8>(p, pl, cb, fast_ok, outl, st); break;
+    case 12: rc = dispatch_outl<12>(p, pl, cb, fast_ok, outl, st); break;
+    case 16: rc = dispatch_outl<16>(p, pl, cb, fast_ok, outl, st); break;
+    case 32: rc = dispatch_outl<32>(p, pl, cb, fast_ok, outl, st); break;
     default: return HQMQ_ERR_UNSUPPORTED;
   }
   if (rc) return rc;
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
   combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, 0, st>>>(
-      p.partials, pl.n_parts, rows, a->d, a->q_dtype, a->O, 0, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
+      p.partials, pl.n_parts, rows, a->d, a->o_dtype, a->O, 0, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
       a->T_q, a->partials_only ? a->partials : nullptr);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;

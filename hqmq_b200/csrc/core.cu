@@ -53,7 +53,7 @@ const IndexMaps& index_maps() {
 
 int check_packed(const hqmq_packed& p, bool need_flags) {
   if (p.struct_size != sizeof(hqmq_packed)) return HQMQ_ERR_ARG;
-  if (p.B <= 0 || p.H <= 0 || p.T_cap <= 0 || (p.T_cap % HQMQ_OUT_BLOCK)) return HQMQ_ERR_SHAPE;
+  if (p.B <= 0 || p.H <= 0 || p.T_cap <= 0 || (p.T_cap % HQMQ_T_ALIGN)) return HQMQ_ERR_SHAPE;
   if (p.n_chunks < 1 || p.n_chunks > 32) return HQMQ_ERR_SHAPE;
   if (p.S < 1 || 24 * p.S > 65536 || p.radius_bits < 1 || p.radius_bits > 8) return HQMQ_ERR_SHAPE;
   if (p.row_bytes != row_bytes_for(p.n_chunks, p.S, p.radius_bits)) return HQMQ_ERR_SHAPE;

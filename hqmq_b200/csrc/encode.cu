@@ -37,7 +37,7 @@ struct EncWs {
   uint32_t* status;   // [4]
   uint32_t* hist;     // [H][3 levels][2 queries][kHistBins]
   uint32_t* sel;      // [H][8]: prefix_lo, rank_lo, prefix_hi, rank_hi, a_bits, b_bits, thr_bits, med_bits
-  uint32_t* blk;      // [B*H][nblk_call + 1] flagged chunks per 64-token block of this call
+  uint32_t* blk;      // [B*H][nblk_call + 1] flagged chunks per 16-token block of this call
 };
 
 __device__ __forceinline__ void load_chunk(const void* x, int64_t off, int dtype, float v[4]) {
@@ -239,7 +239,7 @@ hist_kernel(EncGeom g, const void* __restrict__ x, uint32_t* __restrict__ hist, 
   }
 }
 
-// Flags: one lane group per token; counts flagged chunks per 64-token block of the cache.
+// Flags: one lane group per token; counts flagged chunks per 16-token block of the cache.
 __global__ void __launch_bounds__(256)
 flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, const uint32_t* __restrict__ sel,
              uint32_t* __restrict__ blk, int blk0, int nblk) {

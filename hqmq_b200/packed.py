@@ -33,7 +33,7 @@ class PackedKV:
         if n_chunks < 1 or n_chunks > 32:
             raise ValueError(f"n_chunks={n_chunks}: the native layout supports d_head <= 128")
         self.B, self.H, self.n_chunks, self.S, self.radius_bits = B, H, n_chunks, S, radius_bits
-        self.T_cap = max(_lib.OUT_BLOCK, ((T_cap + _lib.OUT_BLOCK - 1) // _lib.OUT_BLOCK) * _lib.OUT_BLOCK)
+        self.T_cap = max(_lib.T_ALIGN, ((T_cap + _lib.T_ALIGN - 1) // _lib.T_ALIGN) * _lib.T_ALIGN)
         self.T = 0
         self.row_bytes = row_bytes(n_chunks, S, radius_bits)
         self.scale_dtype, self.out_dtype = scale_dtype, out_dtype

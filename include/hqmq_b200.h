@@ -50,8 +50,10 @@ extern "C" {
 #define HQMQ_U8 6
 #define HQMQ_I64 7
 
-/* Number of tokens per outlier-offset block of the native layout. */
-#define HQMQ_OUT_BLOCK 64
+/* Tokens per outlier-offset block of the native layout (= the attention kernel's KV tile). */
+#define HQMQ_OUT_BLOCK 16
+/* Plane capacities (T_cap) are multiples of this many tokens. */
+#define HQMQ_T_ALIGN 64
 
 /*
  * Native compressed layout of one K or V tensor (what the roofline is measured on).
@@ -74,7 +76,7 @@ extern "C" {
  *          full precision (NULL when the tensor was encoded without Med3x)
  *   out_vals [B][H][out_cap][4]      the original 4 values of every flagged chunk as
  *          fp16 / bf16 / fp32, in (token, chunk) order
- *   out_off  [B][H][T_cap/64 + 1]    number of flagged chunks before each 64-token block
+ *   out_off  [B][H][T_cap/16 + 1]    number of flagged chunks before each 16-token block
  *   out_count[B][H]                  flagged chunks stored so far
  * Appending tokens never rewrites an earlier row.
  */
@@ -198,7 +200,8 @@ int hqmq_dequant(const hqmq_dequant_args* args, void* stream);
 typedef struct hqmq_attn_args {
   uint32_t struct_size;
   int32_t layout;            /* 0 = native, 1 = reference tuple */
-  int32_t q_dtype;           /* dtype of Q and O */
+  int32_t q_dtype;           /* element type of Q */
+  int32_t o_dtype;           /* element type of O (may differ from Q, e.g. fp32 output for bf16 queries) */
   const void* Q;             /* (B,H_q,T_q,d) */
   int64_t q_stride[3];       /* b, h, t in elements; last dim contiguous */
   void* O;                   /* (B,H_q,T_q,d) */

@@ -1,0 +1,33 @@
+// Decode-attention kernels for the native layouts with a compile-time field layout:
+// (index bits, radius bits) = (10,3) s24_r3, (12,4) s96_r4, (13,6) s192_r6; d_head 64 or 128; G <= 8.
+#include "attn_kernel.cuh"
+
+namespace hqmq {
+namespace attn {
+
+template <int N, int IB, int RB, bool OUTL>
+__global__ void __launch_bounds__(kAttnThreads, OUTL ? 3 : 4) attn_fast_kernel(const AttnParams p) {
+  attn_decode_body<N, FastLoader<N, IB, RB>, OUTL, false>(p);
+}
+
+template <int N, int IB, int RB, bool OUTL>
+static const void* fn() { return reinterpret_cast<const void*>(&attn_fast_kernel<N, IB, RB, OUTL>); }
+
+template <int N, bool OUTL>
+static const void* pick(int ib, int rb) {
+  if (ib == 10 && rb == 3) return fn<N, 10, 3, OUTL>();
+  if (ib == 12 && rb == 4) return fn<N, 12, 4, OUTL>();
+  if (ib == 13 && rb == 6) return fn<N, 13, 6, OUTL>();
+  return nullptr;
+}
+
+// Kernel for (n_chunks, idx bits, radius bits, outliers) or nullptr when no specialisation exists.
+const void* fast_kernel(int n_chunks, int ib, int rb, bool outl) {
+  if ((n_chunks * (ib + rb)) % 32) return nullptr;   // rows must be whole words without padding
+  if (n_chunks == 32) return outl ? pick<32, true>(ib, rb) : pick<32, false>(ib, rb);
+  if (n_chunks == 16) return outl ? pick<16, true>(ib, rb) : pick<16, false>(ib, rb);
+  return nullptr;
+}
+
+}  // namespace attn
+}  // namespace hqmq

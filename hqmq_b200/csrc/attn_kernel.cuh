@@ -1,0 +1,677 @@
+// Fused decode attention over the compressed KV cache (sm_100a): kernel body and loaders.
+//
+// Work decomposition.  A "unit" is one (KV head, batch, query position); its keys are walked in
+// 16-token tiles.  The tiles of all units form one flat sequence that is cut into equal pieces,
+// one per CTA, so every SM gets the same amount of work whatever the shape; a CTA's piece is a
+// list of segments (unit, tile range).  All G = H_q/H_kv query heads of a unit share every
+// decoded key/value.  Within a segment the CTA's warps take tiles round-robin:
+//   K side  S^T = K Q^T on tensor cores (m16n8k16, fp16 in, fp32 accumulate) with the 16 tokens of
+//           the tile as the M rows and the (up to 8) query heads as the N columns, so no row of
+//           the instruction is padding.  The head dimension is permuted so that the codeword a
+//           lane gathers from the shared-memory table (4 fp16) is exactly its share of the A
+//           fragment; it is scaled by the integer radius code on the way.  The per-token scale
+//           rs/qmax and the softmax scale are applied to the fp32 scores.
+//   softmax online (running max / sum per query head, exp2 domain); the accumulators are only
+//           rescaled when some head's maximum actually grew.
+//   V side  O^T += V^T P^T with 16 head-dims as M rows and the heads as N columns: gather +
+//           radius, byte-permute token pairs into A fragments; P is transposed between the two
+//           products with movmatrix; the per-token V scale is folded into P.
+// Every warp writes an un-normalised partial (o[d], m, l) per query head and segment; a second
+// kernel merges the partials of a unit (and is also what merges partials gathered from other GPUs).
+#pragma once
+#include <math.h>
+#include <string.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace hqmq {
+namespace attn {
+
+constexpr int kAttnWarps = 4;
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kTile = 16;
+constexpr int kStage = 64;   // outlier payload entries staged per tile and tensor
+static_assert(kTile == HQMQ_OUT_BLOCK, "one outlier-offset entry per KV tile");
+
+struct AttnParams {
+  int B, Hq, Hkv, G, Tq, Tkv, d;
+  int causal, window;
+  float sscale;  // softmax_scale * log2(e) / qmax
+  float vscale;  // 1 / qmax
+  float qmaxf;
+  // flat tile space: units * tpu_v virtual tiles, L per CTA; a unit is touched by at most P CTAs
+  int units, tpu_v, L, P;
+  const void* Q; int q_dtype; int64_t qs_b, qs_h, qs_t;
+  float* partials;  // [row][P * kAttnWarps][d+2]
+  int layout;       // 0 native, 1 reference tuple
+  int ib;           // index bits of a field (native: idx_bits; reference: 16)
+  int table_rows;   // codewords per head in the shared-memory tables
+  hqmq_packed K, V;
+  const uint16_t* tblK; const uint16_t* tblV;
+  hqmq_ref_packed Kr, Vr;
+  const void* jK; const void* jV; int j_dtype;
+};
+
+// Key range [beg, end) of query position tq and the tiles that cover it.
+__host__ __device__ inline void key_range(int Tkv, int causal, int window, int tq, int& beg, int& end) {
+  end = causal ? (tq + 1 < Tkv ? tq + 1 : Tkv) : Tkv;
+  beg = window > 0 ? (end - window > 0 ? end - window : 0) : 0;
+}
+
+__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Transpose an 8x8 matrix of 16-bit elements held one row-pair per lane (the C-fragment layout of
+// one half of an accumulator, packed to half2) into the B-fragment layout.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, __half2 r) {
+  __half2 v = __hmul2(*reinterpret_cast<__half2*>(&a), r);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Integer radius code (< 1024) as half2 (r, r): 0x6400 | r is the half 1024 + r.
+__device__ __forceinline__ __half2 radius_half2(uint32_t rq) {
+  uint32_t bits = 0x64006400u | (rq * 0x10001u);
+  return __hsub2(*reinterpret_cast<__half2*>(&bits), __float2half2_rn(1024.f));
+}
+
+template <int N>
+struct Geo {
+  static constexpr int NKS = N / 4;        // 16-wide k slices of the head dimension
+  static constexpr int NVG = (N + 7) / 8;  // chunks per lane row on the V side
+  static constexpr int NOT = NVG * 4;      // 8-wide output tiles (padded)
+};
+
+// Words a lane must read to cover `L` bits starting at bit j*L (j = 0..lanes-1) of a row.
+constexpr int span_words(int L, int lanes) {
+  int m = 0;
+  for (int j = 0; j < lanes; ++j) {
+    int w = (((j * L) & 31) + L + 31) / 32;
+    if (w > m) m = w;
+  }
+  return m;
+}
+
+// ---- loaders ---------------------------------------------------------------------------------------
+// Raw data of one 16-token tile for one lane.  Lane (j = lane & 3, r = lane >> 2):
+//   K side: tokens nt*8 + r (nt = 0,1), chunks j*NKS .. j*NKS + NKS-1
+//   V side: tokens {2j, 2j+1, 2j+8, 2j+9}, chunks r*NVG .. r*NVG + NVG-1
+//   scales of tokens r and r+8 for K and for V.
+
+// Native layout, compile-time field layout (IB index bits + RB radius bits): rows are read as raw
+// words and fields are cut in registers.
+template <int N, int IB, int RB>
+struct FastLoader {
+  static constexpr int CB = IB + RB;
+  static constexpr int NKS = Geo<N>::NKS, NVG = Geo<N>::NVG;
+  static constexpr int LK = NKS * CB, LV = NVG * CB;
+  static constexpr int KW = span_words(LK, 4), VW = span_words(LV, 8);
+  struct Raw { uint32_t kw[2][KW + 1]; uint32_t vw[4][VW + 1]; uint16_t rsk[2], rsv[2]; };
+  const uint8_t* kc; const uint8_t* vc; const uint16_t* krs; const uint16_t* vrs;
+  int row_bytes, row_words, j, r, sdt;
+
+  __device__ __forceinline__ void init(const AttnParams& p, int b, int h, int lane) {
+    const int64_t bh = (int64_t)b * p.Hkv + h;
+    row_bytes = p.K.row_bytes; row_words = row_bytes >> 2;
+    kc = p.K.codes + bh * p.K.T_cap * row_bytes;
+    vc = p.V.codes + bh * p.V.T_cap * row_bytes;
+    krs = reinterpret_cast<const uint16_t*>(p.K.rs) + bh * p.K.T_cap;
+    vrs = reinterpret_cast<const uint16_t*>(p.V.rs) + bh * p.V.T_cap;
+    j = lane & 3; r = lane >> 2; sdt = p.K.scale_dtype;
+  }
+  template <int W, int L>
+  __device__ __forceinline__ void load_span(uint32_t* dst, const uint8_t* row, int part, bool ok) const {
+    const uint32_t* rp = reinterpret_cast<const uint32_t*>(row);
+    const int sb = part * L, w0 = sb >> 5, sh = sb & 31;
+    if constexpr (L % 128 == 0) {
+#pragma unroll
+      for (int i = 0; i < W; i += 4) {
+        uint4 v = ok ? *reinterpret_cast<const uint4*>(rp + w0 + i) : make_uint4(0, 0, 0, 0);
+        dst[i] = v.x; dst[i + 1] = v.y; dst[i + 2] = v.z; dst[i + 3] = v.w;
+      }
+      dst[W] = 0;
+    } else if constexpr (L % 64 == 0) {
+#pragma unroll
+      for (int i = 0; i < W; i += 2) {
+        uint2 v = ok ? *reinterpret_cast<const uint2*>(rp + w0 + i) : make_uint2(0, 0);
+        dst[i] = v.x; dst[i + 1] = v.y;
+      }
+      dst[W] = 0;
+    } else if constexpr (L % 32 == 0) {
+#pragma unroll
+      for (int i = 0; i < W; ++i) dst[i] = ok ? rp[w0 + i] : 0u;
+      dst[W] = 0;
+    } else {
+      uint32_t t[W + 1];
+#pragma unroll
+      for (int i = 0; i < W; ++i) t[i] = ok ? rp[min(w0 + i, row_words - 1)] : 0u;
+      t[W] = 0;
+#pragma unroll
+      for (int i = 0; i < W; ++i) dst[i] = __funnelshift_r(t[i], t[i + 1], sh);
+      dst[W] = 0;
+    }
+  }
+  __device__ __forceinline__ void fetch(Raw& raw, int tile, int t_end) const {
+    const int t0 = tile * kTile;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int t = t0 + nt * 8 + r;
+      load_span<KW, LK>(raw.kw[nt], kc + (int64_t)t * row_bytes, j, t < t_end);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = t0 + 2 * j + (i & 1) + (i >> 1) * 8;
+      load_span<VW, LV>(raw.vw[i], vc + (int64_t)t * row_bytes, r, t < t_end);
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int t = t0 + nt * 8 + r;
+      raw.rsk[nt] = krs[t];
+      raw.rsv[nt] = vrs[t];
+    }
+  }
+  // byte offset of field F's codeword in the table, and its radius as half2 (r, r)
+  template <int F>
+  static __device__ __forceinline__ void cut(const uint32_t* w, uint32_t& off8, __half2& rr) {
+    constexpr int bit = F * CB, a = bit >> 5, s = bit & 31;
+    if constexpr (CB == 16) {
+      // two fields per word: both radii come out of one subtraction
+      const uint32_t word = w[a];
+      off8 = s == 0 ? ((word << 3) & (((1u << IB) - 1u) << 3)) : ((word >> (s - 3)) & (((1u << IB) - 1u) << 3));
+      uint32_t bits = ((word >> IB) & 0x000f000fu) | 0x64006400u;
+      const __half2 pair = __hsub2(*reinterpret_cast<__half2*>(&bits), __float2half2_rn(1024.f));
+      rr = s == 0 ? __low2half2(pair) : __high2half2(pair);
+    } else {
+      uint32_t v = (s + CB > 32) ? __funnelshift_r(w[a], w[a + 1], s) : (w[a] >> s);
+      off8 = (v & ((1u << IB) - 1u)) << 3;
+      rr = radius_half2((v >> IB) & ((1u << RB) - 1u));
+    }
+  }
+  template <int NT, int KS> __device__ __forceinline__ void kfield(const Raw& raw, uint32_t& off8, __half2& rr) const {
+    cut<KS>(raw.kw[NT], off8, rr);
+  }
+  template <int I, int GG> __device__ __forceinline__ void vfield(const Raw& raw, uint32_t& off8, __half2& rr) const {
+    cut<GG>(raw.vw[I], off8, rr);
+    if constexpr (N % 8 != 0) { if (r * NVG + GG >= N) { off8 = 0; rr = __float2half2_rn(0.f); } }
+  }
+  // scale of token nt*8 + r
+  __device__ __forceinline__ float kscale(const Raw& raw, int nt) const { return bits16_to_float(raw.rsk[nt], sdt); }
+  __device__ __forceinline__ float vscale(const Raw& raw, int nt) const { return bits16_to_float(raw.rsv[nt], sdt); }
+};
+
+// Any field width, native or reference layout: fields are extracted one by one at load time.
+template <int N>
+struct SlowLoader {
+  static constexpr int NKS = Geo<N>::NKS, NVG = Geo<N>::NVG;
+  struct Raw { uint32_t kf[2][NKS]; uint32_t vf[4][NVG]; float rsk[2], rsv[2]; };
+  const AttnParams* pp; int b, h, j, r;
+  __device__ __forceinline__ void init(const AttnParams& p_, int b_, int h_, int lane) {
+    pp = &p_; b = b_; h = h_; j = lane & 3; r = lane >> 2;
+  }
+  __device__ __forceinline__ uint32_t field(const hqmq_packed& pk, const hqmq_ref_packed& rf, int t, int c) const {
+    const AttnParams& p = *pp;
+    if (p.layout == 0) {
+      const int cb = p.ib + pk.radius_bits;
+      const int64_t row = ((int64_t)b * p.Hkv + h) * pk.T_cap + t;
+      return row_field(reinterpret_cast<const uint32_t*>(pk.codes + row * pk.row_bytes), c, cb);
+    }
+    long long k = load_int(rf.idx, b * rf.idx_stride[0] + h * rf.idx_stride[1] + t * rf.idx_stride[2] + c, rf.idx_dtype);
+    k = k < 0 ? 0 : (k >= p.table_rows ? p.table_rows - 1 : k);
+    long long q = load_int(rf.rq, b * rf.rq_stride[0] + h * rf.rq_stride[1] + t * rf.rq_stride[2] + c, rf.rq_dtype);
+    q = q < 0 ? 0 : (q > 1023 ? 1023 : q);
+    return (uint32_t)k | ((uint32_t)q << 16);
+  }
+  __device__ __forceinline__ float rscale(const hqmq_packed& pk, const hqmq_ref_packed& rf, int t) const {
+    const AttnParams& p = *pp;
+    if (p.layout == 0) return load_scale(pk, ((int64_t)b * p.Hkv + h) * pk.T_cap + t);
+    return load_float(rf.rs, b * rf.rs_stride[0] + h * rf.rs_stride[1] + t, rf.rs_dtype);
+  }
+  __device__ __forceinline__ void fetch(Raw& raw, int tile, int t_end) const {
+    const AttnParams& p = *pp;
+    const int t0 = tile * kTile;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int t = t0 + nt * 8 + r;
+#pragma unroll
+      for (int ks = 0; ks < NKS; ++ks) raw.kf[nt][ks] = t < t_end ? field(p.K, p.Kr, t, j * NKS + ks) : 0u;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = t0 + 2 * j + (i & 1) + (i >> 1) * 8;
+#pragma unroll
+      for (int g = 0; g < NVG; ++g) {
+        const int c = r * NVG + g;
+        raw.vf[i][g] = (t < t_end && c < N) ? field(p.V, p.Vr, t, c) : 0u;
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int t = t0 + nt * 8 + r;
+      raw.rsk[nt] = t < t_end ? rscale(p.K, p.Kr, t) : 0.f;
+      raw.rsv[nt] = t < t_end ? rscale(p.V, p.Vr, t) : 0.f;
+    }
+  }
+  __device__ __forceinline__ void split(uint32_t f, uint32_t& off8, __half2& rr) const {
+    off8 = (f & ((1u << pp->ib) - 1u)) << 3;
+    rr = radius_half2(f >> pp->ib);
+  }
+  template <int NT, int KS> __device__ __forceinline__ void kfield(const Raw& raw, uint32_t& off8, __half2& rr) const {
+    split(raw.kf[NT][KS], off8, rr);
+  }
+  template <int I, int GG> __device__ __forceinline__ void vfield(const Raw& raw, uint32_t& off8, __half2& rr) const {
+    split(raw.vf[I][GG], off8, rr);
+  }
+  __device__ __forceinline__ float kscale(const Raw& raw, int nt) const { return raw.rsk[nt]; }
+  __device__ __forceinline__ float vscale(const Raw& raw, int nt) const { return raw.rsv[nt]; }
+};
+
+// ---- Med3x outliers ----------------------------------------------------------------------------------
+// Flagged chunks keep their original 4 values in a side buffer, in (token, chunk) order, with one
+// offset per 16-token tile, so a tile's entries are one contiguous range.  They are merged by
+// overwriting the decoded fragment with x * qmax / rs: the token's scale rs is its largest chunk
+// norm, flagged chunks included, so the patched value never exceeds qmax in magnitude and cannot
+// overflow fp16.  The first kStage entries of a tile are prefetched a tile ahead and staged in
+// shared memory; anything beyond (or an fp32 side buffer) is read from global memory in place.
+struct OutlRaw { uint32_t fk, fv, offk, offv; uint2 pk[kStage / 32], pv[kStage / 32]; };
+
+struct OutlSide {
+  const uint32_t* flags; const uint32_t* off; const unsigned char* vals; int dtype; uint2* stage;
+  __device__ __forceinline__ void init(const hqmq_packed& pk, int64_t bh, uint2* stage_) {
+    flags = pk.flags ? pk.flags + bh * pk.T_cap : nullptr;
+    off = pk.flags ? pk.out_off + bh * (pk.T_cap / HQMQ_OUT_BLOCK + 1) : nullptr;
+    dtype = pk.out_dtype;
+    vals = reinterpret_cast<const unsigned char*>(pk.out_vals) + bh * pk.out_cap * 4 * (dtype == HQMQ_F32 ? 4 : 2);
+    stage = stage_;
+  }
+  // original values of payload entry `pos` (tile-relative index `rel`), scaled by `inv`, as two half2 registers
+  __device__ __forceinline__ void load(uint32_t pos, uint32_t rel, float inv, uint32_t& lo, uint32_t& hi) const {
+    float x0, x1, x2, x3;
+    if (dtype == HQMQ_F32) {
+      const float4 v = *reinterpret_cast<const float4*>(vals + (int64_t)pos * 16);
+      x0 = v.x; x1 = v.y; x2 = v.z; x3 = v.w;
+    } else {
+      const uint2 v = rel < (uint32_t)kStage ? stage[rel] : *reinterpret_cast<const uint2*>(vals + (int64_t)pos * 8);
+      x0 = bits16_to_float((uint16_t)(v.x & 0xffff), dtype); x1 = bits16_to_float((uint16_t)(v.x >> 16), dtype);
+      x2 = bits16_to_float((uint16_t)(v.y & 0xffff), dtype); x3 = bits16_to_float((uint16_t)(v.y >> 16), dtype);
+    }
+    lo = pack_half2(x0 * inv, x1 * inv);
+    hi = pack_half2(x2 * inv, x3 * inv);
+  }
+};
+
+// Exclusive prefix sum of v over lanes 0..15 (lanes >= 16 hold 0).
+__device__ __forceinline__ uint32_t excl_scan16(uint32_t v, int lane) {
+  uint32_t x = v;
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) {
+    const uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  return x - v;
+}
+
+template <int I, int End, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < End) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, End>(f);
+  }
+}
+
+// Loader: FastLoader<N, IB, RB> or SlowLoader<N>.  OUTL: merge Med3x outliers.  WIDE: 8 < G <= 16.
+template <int N, class Loader, bool OUTL, bool WIDE>
+__device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
+  using G_ = Geo<N>;
+  constexpr int NKS = G_::NKS, NVG = G_::NVG, NOT = 2 * G_::NVG;   // NOT: 16-row tiles of O^T
+  constexpr int NH = WIDE ? 2 : 1;   // 8-wide head tiles
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned char* tblK = smem_raw;
+  unsigned char* tblV = smem_raw + (size_t)p.table_rows * 8;
+  uint2* stage_base = reinterpret_cast<uint2*>(smem_raw + (size_t)p.table_rows * 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = lane & 3, r = lane >> 2;
+  const int64_t flat_lo = (int64_t)blockIdx.x * p.L;
+  const int64_t flat_total = (int64_t)p.units * p.tpu_v;
+  const int64_t flat_hi = flat_lo + p.L < flat_total ? flat_lo + p.L : flat_total;
+  const int upb = p.B * p.Tq;   // units per KV head
+  int cur_h = -1;
+
+  for (int u = (int)(flat_lo / p.tpu_v); (int64_t)u * p.tpu_v < flat_hi; ++u) {
+    const int h = u / upb, bt = u - h * upb;
+    const int b = bt / p.Tq, tq = bt - b * p.Tq;
+    // ---- codeword tables of this KV head into shared memory (fp16 x 4 per entry) ---------------------
+    if (h != cur_h) {
+      __syncthreads();
+      uint2* sk = reinterpret_cast<uint2*>(tblK);
+      uint2* sv = reinterpret_cast<uint2*>(tblV);
+      if (p.layout == 0) {
+        const uint2* gk = reinterpret_cast<const uint2*>(p.tblK) + (int64_t)h * p.table_rows;
+        const uint2* gv = reinterpret_cast<const uint2*>(p.tblV) + (int64_t)h * p.table_rows;
+        for (int i = threadIdx.x; i < p.table_rows; i += kAttnThreads) { sk[i] = gk[i]; sv[i] = gv[i]; }
+      } else {
+        for (int i = threadIdx.x; i < p.table_rows; i += kAttnThreads) {
+          const int64_t base = ((int64_t)h * p.table_rows + i) * 4;
+          sk[i] = make_uint2(pack_half2(load_float(p.jK, base, p.j_dtype), load_float(p.jK, base + 1, p.j_dtype)),
+                             pack_half2(load_float(p.jK, base + 2, p.j_dtype), load_float(p.jK, base + 3, p.j_dtype)));
+          sv[i] = make_uint2(pack_half2(load_float(p.jV, base, p.j_dtype), load_float(p.jV, base + 1, p.j_dtype)),
+                             pack_half2(load_float(p.jV, base + 2, p.j_dtype), load_float(p.jV, base + 3, p.j_dtype)));
+        }
+      }
+      __syncthreads();
+      cur_h = h;
+    }
+
+    // ---- this CTA's tiles of the unit ----------------------------------------------------------------
+    int t_beg, t_end;
+    key_range(p.Tkv, p.causal, p.window, tq, t_beg, t_end);
+    const int tile_lo = t_beg / kTile, tile_hi = (t_end + kTile - 1) / kTile;
+    const int64_t ubase = (int64_t)u * p.tpu_v;
+    const int rel_lo = (int)(flat_lo > ubase ? flat_lo - ubase : 0);
+    const int rel_hi = (int)(flat_hi < ubase + p.tpu_v ? flat_hi - ubase : p.tpu_v);
+    const int my_lo = tile_lo + rel_lo;
+    const int my_hi = min(tile_hi, tile_lo + rel_hi);
+    const int part = ((int)blockIdx.x - (int)(ubase / p.L)) * kAttnWarps + warp;
+
+    // ---- Q as B fragments: column n = r is a query head, k slots {2j,2j+1,2j+8,2j+9} = one chunk -----
+    uint32_t qb[NH][NKS][2];
+    {
+      const int64_t q0off = (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t;
+#pragma unroll
+      for (int nh = 0; nh < NH; ++nh) {
+        const int g = r + 8 * nh;
+#pragma unroll
+        for (int ks = 0; ks < NKS; ++ks) {
+          const int dim = 4 * (j * NKS + ks);
+          float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+          if (g < p.G) {
+            const int64_t o = q0off + (int64_t)(h * p.G + g) * p.qs_h + dim;
+            q0 = load_float(p.Q, o, p.q_dtype); q1 = load_float(p.Q, o + 1, p.q_dtype);
+            q2 = load_float(p.Q, o + 2, p.q_dtype); q3 = load_float(p.Q, o + 3, p.q_dtype);
+          }
+          qb[nh][ks][0] = pack_half2(q0, q1);
+          qb[nh][ks][1] = pack_half2(q2, q3);
+        }
+      }
+    }
+
+    // running max and sum of heads 2j, 2j+1 (+8 per extra head tile); O^T accumulators: tile mt holds
+    // head-dims (rows r, r+8) x heads (2j, 2j+1)
+    float m_run[NH][2], l_run[NH][2];
+    float o[NH][NOT][4];
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+      m_run[nh][0] = m_run[nh][1] = -INFINITY;
+      l_run[nh][0] = l_run[nh][1] = 0.f;
+#pragma unroll
+      for (int i = 0; i < NOT; ++i) o[nh][i][0] = o[nh][i][1] = o[nh][i][2] = o[nh][i][3] = 0.f;
+    }
+
+    Loader ld;
+    ld.init(p, b, h, lane);
+    typename Loader::Raw cur, nxt;
+    OutlSide ok_, ov_;
+    OutlRaw ocur, onxt;
+    uint32_t offk_nn = 0, offv_nn = 0, offk_nn1 = 0, offv_nn1 = 0;   // payload ranges two tiles ahead
+    if constexpr (OUTL) {
+      ok_.init(p.K, (int64_t)b * p.Hkv + h, stage_base + (warp * 2 + 0) * kStage);
+      ov_.init(p.V, (int64_t)b * p.Hkv + h, stage_base + (warp * 2 + 1) * kStage);
+    }
+    // flags and the first staged payload entries of tile tl, given its payload ranges
+    auto fetch_outl = [&](OutlRaw& oo, int tl, uint32_t k0, uint32_t k1, uint32_t v0, uint32_t v1) {
+      oo.fk = oo.fv = 0; oo.offk = k0; oo.offv = v0;
+      const int tt = tl * kTile + (lane & 15);
+      if (lane < 16 && tt < t_end) {
+        if (ok_.flags) oo.fk = ok_.flags[tt];
+        if (ov_.flags) oo.fv = ov_.flags[tt];
+      }
+#pragma unroll
+      for (int q = 0; q < kStage / 32; ++q) {
+        const uint32_t e = q * 32 + lane;
+        oo.pk[q] = make_uint2(0, 0); oo.pv[q] = make_uint2(0, 0);
+        if (ok_.dtype != HQMQ_F32 && k0 + e < k1) oo.pk[q] = *reinterpret_cast<const uint2*>(ok_.vals + (int64_t)(k0 + e) * 8);
+        if (ov_.dtype != HQMQ_F32 && v0 + e < v1) oo.pv[q] = *reinterpret_cast<const uint2*>(ov_.vals + (int64_t)(v0 + e) * 8);
+      }
+    };
+    auto fetch_off = [&](int tl, uint32_t& k0, uint32_t& k1, uint32_t& v0, uint32_t& v1) {
+      k0 = k1 = v0 = v1 = 0;
+      if (tl < my_hi) {
+        if (ok_.flags) { k0 = ok_.off[tl]; k1 = ok_.off[tl + 1]; }
+        if (ov_.flags) { v0 = ov_.off[tl]; v1 = ov_.off[tl + 1]; }
+      }
+    };
+
+    int tile = my_lo + warp;
+    if (tile < my_hi) {
+      ld.fetch(cur, tile, t_end);
+      if constexpr (OUTL) {
+        uint32_t k0, k1, v0, v1;
+        fetch_off(tile, k0, k1, v0, v1);
+        fetch_outl(ocur, tile, k0, k1, v0, v1);
+        fetch_off(tile + kAttnWarps, offk_nn, offk_nn1, offv_nn, offv_nn1);
+      }
+    }
+
+    for (; tile < my_hi; tile += kAttnWarps) {
+      const int tn = tile + kAttnWarps;
+      if (tn < my_hi) {
+        ld.fetch(nxt, tn, t_end);
+        if constexpr (OUTL) {
+          fetch_outl(onxt, tn, offk_nn, offk_nn1, offv_nn, offv_nn1);
+          fetch_off(tn + kAttnWarps, offk_nn, offk_nn1, offv_nn, offv_nn1);
+        }
+      }
+      const int t0 = tile * kTile;
+      const bool edge = t0 < t_beg || t0 + kTile > t_end;
+      // per-token factors of this lane's tokens r and r+8
+      float ksc[2], vsc[2];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        ksc[nt] = ld.kscale(cur, nt) * p.sscale;
+        vsc[nt] = ld.vscale(cur, nt) * p.vscale;
+      }
+      bool okt[2] = {true, true};
+      if (edge) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int t = t0 + nt * 8 + r;
+          okt[nt] = t >= t_beg && t < t_end;
+          if (!okt[nt]) vsc[nt] = 0.f;
+        }
+      }
+
+      // ---- outlier bookkeeping of this tile -----------------------------------------------------------
+      bool anyK = false, anyV = false;
+      uint32_t kfl[2] = {0, 0}, kpre[2] = {0, 0}, vfl[4] = {0, 0, 0, 0}, vpre[4] = {0, 0, 0, 0};
+      float kinv[2] = {0.f, 0.f}, vinv[4] = {0.f, 0.f, 0.f, 0.f};
+      if constexpr (OUTL) {
+        anyK = __ballot_sync(0xffffffffu, ocur.fk != 0) != 0;
+        anyV = __ballot_sync(0xffffffffu, ocur.fv != 0) != 0;
+        if (anyK || anyV) {
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < kStage / 32; ++q) {
+            ok_.stage[q * 32 + lane] = ocur.pk[q];
+            ov_.stage[q * 32 + lane] = ocur.pv[q];
+          }
+          __syncwarp();
+        }
+        if (anyK) {
+          const uint32_t ex = excl_scan16(__popc(ocur.fk), lane);
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            kfl[nt] = __shfl_sync(0xffffffffu, ocur.fk, nt * 8 + r);
+            kpre[nt] = __shfl_sync(0xffffffffu, ex, nt * 8 + r);
+            kinv[nt] = kfl[nt] ? p.qmaxf / ld.kscale(cur, nt) : 0.f;
+          }
+        }
+        if (anyV) {
+          const uint32_t ex = excl_scan16(__popc(ocur.fv), lane);
+          const float i0 = p.qmaxf / ld.vscale(cur, 0), i1 = p.qmaxf / ld.vscale(cur, 1);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int tl = 2 * j + (i & 1) + (i >> 1) * 8;
+            vfl[i] = __shfl_sync(0xffffffffu, ocur.fv, tl);
+            vpre[i] = __shfl_sync(0xffffffffu, ex, tl);
+            // the scale of token tl lives in the lanes whose r is tl & 7
+            vinv[i] = __shfl_sync(0xffffffffu, (i >> 1) ? i1 : i0, (tl & 7) * 4);
+          }
+        }
+      }
+
+      // ---- S^T = K Q^T: rows = tokens r, r+8; columns = heads 2j, 2j+1 -----------------------------------
+      float s[NH][4];
+#pragma unroll
+      for (int nh = 0; nh < NH; ++nh) s[nh][0] = s[nh][1] = s[nh][2] = s[nh][3] = 0.f;
+      static_for<0, NKS>([&](auto ks_) {
+        constexpr int ks = decltype(ks_)::value;
+        uint32_t a[4];   // a0: token r (e0,e1), a1: token r+8 (e0,e1), a2: token r (e2,e3), a3: token r+8 (e2,e3)
+        static_for<0, 2>([&](auto nt_) {
+          constexpr int nt = decltype(nt_)::value;
+          uint32_t off8; __half2 rr;
+          ld.template kfield<nt, ks>(cur, off8, rr);
+          const uint2 cw = *reinterpret_cast<const uint2*>(tblK + off8);
+          a[nt] = hmul2_u32(cw.x, rr);
+          a[2 + nt] = hmul2_u32(cw.y, rr);
+          if constexpr (OUTL) {
+            if (anyK) {
+              const int c = j * NKS + ks;
+              if ((kfl[nt] >> c) & 1u) {
+                const uint32_t rel = kpre[nt] + __popc(kfl[nt] & ((1u << c) - 1u));
+                ok_.load(ocur.offk + rel, rel, kinv[nt], a[nt], a[2 + nt]);
+              }
+            }
+          }
+        });
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) mma16816(s[nh], a[0], a[1], a[2], a[3], qb[nh][ks][0], qb[nh][ks][1]);
+      });
+
+      // ---- scale, mask, online softmax -------------------------------------------------------------------
+      bool grew = false;
+      float mx[NH][2];
+#pragma unroll
+      for (int nh = 0; nh < NH; ++nh) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          s[nh][e] = okt[0] ? s[nh][e] * ksc[0] : -INFINITY;          // token r
+          s[nh][2 + e] = okt[1] ? s[nh][2 + e] * ksc[1] : -INFINITY;  // token r+8
+          float m = fmaxf(s[nh][e], s[nh][2 + e]);
+          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+          mx[nh][e] = m;
+          grew |= m > m_run[nh][e];
+        }
+      }
+      if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float m_new = fmaxf(m_run[nh][e], mx[nh][e]);
+            const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run[nh][e] - m_new);
+            m_run[nh][e] = m_new;
+            l_run[nh][e] *= alpha;
+#pragma unroll
+            for (int i = 0; i < NOT; ++i) { o[nh][i][e] *= alpha; o[nh][i][2 + e] *= alpha; }
+          }
+      }
+      uint32_t pb[NH][2];   // P^T as B fragments: b0 = tokens 2j,2j+1 of head r, b1 = tokens 2j+8,2j+9
+#pragma unroll
+      for (int nh = 0; nh < NH; ++nh) {
+        float pe[4];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float m_use = m_run[nh][e] == -INFINITY ? 0.f : m_run[nh][e];
+          pe[e] = fast_exp2(s[nh][e] - m_use);
+          pe[2 + e] = fast_exp2(s[nh][2 + e] - m_use);
+          l_run[nh][e] += pe[e] + pe[2 + e];
+        }
+        pb[nh][0] = movmatrix_trans(pack_half2(pe[0] * vsc[0], pe[1] * vsc[0]));
+        pb[nh][1] = movmatrix_trans(pack_half2(pe[2] * vsc[1], pe[3] * vsc[1]));
+      }
+
+      // ---- O^T += V^T P^T: rows = head-dims, k = the 16 tokens, columns = heads ---------------------------
+      static_for<0, NVG>([&](auto g_) {
+        constexpr int g = decltype(g_)::value;
+        uint32_t lo[4], hi[4];
+        static_for<0, 4>([&](auto i_) {
+          constexpr int i = decltype(i_)::value;
+          uint32_t off8; __half2 rr;
+          ld.template vfield<i, g>(cur, off8, rr);
+          const uint2 cw = *reinterpret_cast<const uint2*>(tblV + off8);
+          lo[i] = hmul2_u32(cw.x, rr);
+          hi[i] = hmul2_u32(cw.y, rr);
+          if constexpr (OUTL) {
+            if (anyV) {
+              const int c = r * NVG + g;
+              if (c < N && ((vfl[i] >> c) & 1u)) {
+                const uint32_t rel = vpre[i] + __popc(vfl[i] & ((1u << c) - 1u));
+                ov_.load(ocur.offv + rel, rel, vinv[i], lo[i], hi[i]);
+              }
+            }
+          }
+        });
+        // tile 2g: rows r / r+8 = elements 0 / 1 of the lane's chunk; tile 2g+1: elements 2 / 3
+        const uint32_t a0 = __byte_perm(lo[0], lo[1], 0x5410), a1 = __byte_perm(lo[0], lo[1], 0x7632);
+        const uint32_t a2 = __byte_perm(lo[2], lo[3], 0x5410), a3 = __byte_perm(lo[2], lo[3], 0x7632);
+        const uint32_t c0 = __byte_perm(hi[0], hi[1], 0x5410), c1 = __byte_perm(hi[0], hi[1], 0x7632);
+        const uint32_t c2 = __byte_perm(hi[2], hi[3], 0x5410), c3 = __byte_perm(hi[2], hi[3], 0x7632);
+#pragma unroll
+        for (int nh = 0; nh < NH; ++nh) {
+          mma16816(o[nh][2 * g], a0, a1, a2, a3, pb[nh][0], pb[nh][1]);
+          mma16816(o[nh][2 * g + 1], c0, c1, c2, c3, pb[nh][0], pb[nh][1]);
+        }
+      });
+      cur = nxt;
+      if constexpr (OUTL) ocur = onxt;
+    }
+
+    // ---- per-warp partial: o[d], m, l for every query head of this KV head -----------------------------
+    const int n_parts = p.P * kAttnWarps;
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float l = l_run[nh][e];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        const int g = 8 * nh + 2 * j + e;
+        if (g >= p.G) continue;
+        const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
+        float* dst = p.partials + (row * n_parts + part) * (p.d + 2);
+#pragma unroll
+        for (int i = 0; i < NOT; ++i) {
+          const int chunk = r * NVG + (i >> 1);
+          if (chunk < N) {
+            dst[4 * chunk + 2 * (i & 1)] = o[nh][i][e];          // row r
+            dst[4 * chunk + 2 * (i & 1) + 1] = o[nh][i][2 + e];  // row r+8
+          }
+        }
+        if (r == 0) { dst[p.d] = m_run[nh][e]; dst[p.d + 1] = l; }
+      }
+  }
+}
+
+}  // namespace attn
+}  // namespace hqmq

@@ -23,6 +23,25 @@ constexpr int kEncIters = 16;     // token groups per block
 constexpr int kHistBins = 2048;   // 11-bit digits: bits [31:21], [20:10], then 10 bits [9:0]
 constexpr int kMaxRowWords = 20;
 
+// ---- nearest-codeword look-up table -------------------------------------------------------------------
+// The unit direction u is first folded by the axis unit g = sign(u_i*) e_i* of its largest component
+// (v = conj(g) * u, an exact signed permutation), which makes v0 the largest component and positive; the
+// joint codebook is invariant under left multiplication by the 8 axis units, so the nearest codeword of
+// u is g times the nearest codeword of v.  v is located in a grid over w = (v1,v2,v3)/v0 in [-1,1]^3 with
+// kLutN cells per axis; each cell lists every codeword that can be the nearest one for some direction in
+// the cell (all k not beaten over the whole cell by the winner at the cell's centre: the comparison of two
+// codewords is linear in w, so its maximum over the box is attained at a corner).  Only the listed
+// codewords are evaluated, with the same fp32 dot product an exhaustive scan of the joint table would use.
+constexpr int kLutN = 16;
+constexpr int kLutCells = kLutN * kLutN * kLutN;
+constexpr int kLutHdr = kLutCells + 4;      // per head: offsets[kLutCells + 1], valid flag, padding
+constexpr int kLutCandCap = 49152;          // candidate entries per head
+constexpr int kLutMaxList = 64;             // longest list a cell may have; longer -> exhaustive search there
+constexpr float kLutBoxEps = 1e-5f;         // the boxes are grown by this much (cell assignment rounding)
+constexpr float kLutMargin = 1e-5f;         // a codeword is dropped only if it loses by more than this
+
+struct Mul8x24 { uint8_t v[8][24]; };      // index of (axis unit g) * (primary p)
+
 struct Maps24 { uint8_t ref_to_native[24]; };
 
 struct EncGeom {
@@ -95,19 +114,76 @@ __device__ __forceinline__ int search_exhaustive(const float4* __restrict__ qs, 
   return bp;
 }
 
+// Nearest codeword through the look-up table.  Returns the reference primary index and the secondary.
+__device__ __forceinline__ int search_lut(const float4* __restrict__ joint, const uint32_t* __restrict__ off,
+                                          const uint16_t* __restrict__ cand, const float4* __restrict__ qs, int S,
+                                          float inv_S, float u0, float u1, float u2, float u3, const Mul8x24& mul,
+                                          int& best_s) {
+  const float a0 = fabsf(u0), a1 = fabsf(u1), a2 = fabsf(u2), a3 = fabsf(u3);
+  int ax = 0; float am = a0;
+  if (a1 > am) { am = a1; ax = 1; }
+  if (a2 > am) { am = a2; ax = 2; }
+  if (a3 > am) { am = a3; ax = 3; }
+  if (!(am > 0.f)) { best_s = 0; return 0; }   // zero direction: every similarity is 0, the first index wins
+  float v0, v1, v2, v3;
+  if (ax == 0) { v0 = u0; v1 = u1; v2 = u2; v3 = u3; }
+  else if (ax == 1) { v0 = u1; v1 = -u0; v2 = u3; v3 = -u2; }
+  else if (ax == 2) { v0 = u2; v1 = -u3; v2 = -u0; v3 = u1; }
+  else { v0 = u3; v1 = u2; v2 = -u1; v3 = -u0; }
+  const bool neg = v0 < 0.f;
+  if (neg) { v0 = -v0; v1 = -v1; v2 = -v2; v3 = -v3; }
+  const float inv = __frcp_rn(v0);
+  const int cx = min(kLutN - 1, max(0, (int)((v1 * inv + 1.f) * (0.5f * kLutN))));
+  const int cy = min(kLutN - 1, max(0, (int)((v2 * inv + 1.f) * (0.5f * kLutN))));
+  const int cz = min(kLutN - 1, max(0, (int)((v3 * inv + 1.f) * (0.5f * kLutN))));
+  const int cell = (cx * kLutN + cy) * kLutN + cz;
+  const uint32_t beg = off[cell], end = off[cell + 1];
+  if (beg == end) return search_exhaustive(qs, S, u0, u1, u2, u3, best_s);
+  float best = -2.f; int bk = 0;
+  for (uint32_t e = beg; e < end; ++e) {
+    const int k = cand[e];
+    const float4 c = joint[k];
+    const float sim = fmaf(v3, c.w, fmaf(v2, c.z, fmaf(v1, c.y, v0 * c.x)));
+    if (sim > best) { best = sim; bk = k; }
+  }
+  const int pf = (int)(((float)bk + 0.5f) * inv_S);
+  best_s = bk - pf * S;
+  return mul.v[2 * ax + (neg ? 1 : 0)][pf];
+}
+
+template <bool LUT>
 __global__ void __launch_bounds__(kEncThreads)
 encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
-                   int t_start, uint32_t* __restrict__ hist, Maps24 maps) {
+                   int t_start, uint32_t* __restrict__ hist, Maps24 maps, const float* __restrict__ joint_all,
+                   const uint32_t* __restrict__ lut, int lut_cand_smem, Mul8x24 mul) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float4* qs = reinterpret_cast<float4*>(smem_raw);
   uint32_t* rows = reinterpret_cast<uint32_t*>(qs + g.S);            // [warps][tpw][kMaxRowWords]
-  uint32_t* shist = rows + kEncWarps * g.tpw * kMaxRowWords;          // [kHistBins] when hist != nullptr
+  uint32_t* shist = rows + kEncWarps * g.tpw * kMaxRowWords;          // [kHistBins]
+  float4* sjoint = reinterpret_cast<float4*>(shist + kHistBins);      // LUT: [24 S]
+  uint32_t* soff = reinterpret_cast<uint32_t*>(sjoint + 24 * g.S);     // LUT: [kLutCells + 1]
+  uint16_t* scand = reinterpret_cast<uint16_t*>(soff + kLutCells + 4); // LUT: [lut_cand_smem]
 
   const int bh = blockIdx.y;
   const int h = bh % g.H, b = bh / g.H;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < g.S; i += blockDim.x) qs[i] = reinterpret_cast<const float4*>(qs_all)[(int64_t)h * g.S + i];
   if (hist) for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) shist[i] = 0;
+  bool use_lut = false;
+  if constexpr (LUT) {
+    const uint32_t* hdr = lut + (int64_t)h * kLutHdr;
+    const uint16_t* gc = reinterpret_cast<const uint16_t*>(lut + (int64_t)g.H * kLutHdr) + (int64_t)h * kLutCandCap;
+    const uint32_t total = hdr[kLutCells];
+    use_lut = hdr[kLutCells + 1] == 1u && total <= (uint32_t)lut_cand_smem;
+    if (use_lut) {
+      for (int i = threadIdx.x; i < 24 * g.S; i += blockDim.x) sjoint[i] = reinterpret_cast<const float4*>(joint_all)[(int64_t)h * 24 * g.S + i];
+      for (int i = threadIdx.x; i <= kLutCells; i += blockDim.x) soff[i] = hdr[i];
+      const uint32_t* gc32 = reinterpret_cast<const uint32_t*>(gc);
+      uint32_t* sc32 = reinterpret_cast<uint32_t*>(scand);
+      for (uint32_t i = threadIdx.x; i < (total + 1) / 2; i += blockDim.x) sc32[i] = gc32[i];
+    }
+  }
+  const float inv_S = 1.0f / (float)g.S;
   __syncthreads();
 
   const int sub = lane / g.npl, c = lane % g.npl;
@@ -137,8 +213,9 @@ encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restric
     if (active) {
       const float u0 = __fdiv_rn(v[0], radius), u1 = __fdiv_rn(v[1], radius), u2 = __fdiv_rn(v[2], radius),
                   u3 = __fdiv_rn(v[3], radius);
-      int s;
-      const int p = search_exhaustive(qs, g.S, u0, u1, u2, u3, s);
+      int s, p;
+      if (LUT && use_lut) p = search_lut(sjoint, soff, scand, qs, g.S, inv_S, u0, u1, u2, u3, mul, s);
+      else p = search_exhaustive(qs, g.S, u0, u1, u2, u3, s);
       const int au = maps.ref_to_native[p];
       const uint32_t ni = (uint32_t)((((au >> 3) * g.S + s) << 3) | (au & 7));
       const uint32_t f = ni | ((uint32_t)rqf << g.ib);
@@ -321,6 +398,134 @@ payload_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_sta
   }
 }
 
+
+// ---- look-up table construction ---------------------------------------------------------------------
+// One CTA per (cell, head).  tmp: [H][kLutCells][kLutMaxList] uint16 candidate lists, cnt: [H][kLutCells].
+__global__ void __launch_bounds__(128)
+lut_cells_kernel(const float* __restrict__ joint_all, int S, uint16_t* __restrict__ tmp, uint32_t* __restrict__ cnt) {
+  __shared__ float s_best[4];
+  __shared__ int s_bk[4];
+  __shared__ int s_n;
+  __shared__ uint16_t s_list[kLutMaxList];
+  const int cell = blockIdx.x, h = blockIdx.y, K = 24 * S;
+  const float4* joint = reinterpret_cast<const float4*>(joint_all) + (int64_t)h * K;
+  const int cz = cell % kLutN, cy = (cell / kLutN) % kLutN, cx = cell / (kLutN * kLutN);
+  const float step = 2.0f / kLutN;
+  const float w1 = (cx + 0.5f) * step - 1.f, w2 = (cy + 0.5f) * step - 1.f, w3 = (cz + 0.5f) * step - 1.f;
+  const float hh = 0.5f * step + kLutBoxEps;
+  // winner at the centre of the cell
+  float best = -1e30f; int bk = 0;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    const float4 c = joint[k];
+    const float sim = c.x + w1 * c.y + w2 * c.z + w3 * c.w;
+    if (sim > best) { best = sim; bk = k; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int ok = __shfl_xor_sync(0xffffffffu, bk, o);
+    if (ob > best || (ob == best && ok < bk)) { best = ob; bk = ok; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_best[threadIdx.x >> 5] = best; s_bk[threadIdx.x >> 5] = bk; }
+  if (threadIdx.x == 0) s_n = 0;
+  __syncthreads();
+  best = s_best[0]; bk = s_bk[0];
+  for (int i = 1; i < 4; ++i)
+    if (s_best[i] > best || (s_best[i] == best && s_bk[i] < bk)) { best = s_best[i]; bk = s_bk[i]; }
+  const float4 cs = joint[bk];
+  // every codeword that is not beaten by the centre's winner over the whole (grown) box
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    const float4 c = joint[k];
+    const float d0 = c.x - cs.x, d1 = c.y - cs.y, d2 = c.z - cs.z, d3 = c.w - cs.w;
+    const float ub = d0 + d1 * w1 + d2 * w2 + d3 * w3 + hh * (fabsf(d1) + fabsf(d2) + fabsf(d3));
+    if (ub >= -kLutMargin) {
+      const int pos = atomicAdd(&s_n, 1);
+      if (pos < kLutMaxList) s_list[pos] = (uint16_t)k;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = s_n;
+    if (n > kLutMaxList) n = 0;       // too long: this cell falls back to the exhaustive search
+    for (int i = 1; i < n; ++i) {     // ascending order makes the table reproducible
+      const uint16_t v = s_list[i];
+      int q = i - 1;
+      while (q >= 0 && s_list[q] > v) { s_list[q + 1] = s_list[q]; --q; }
+      s_list[q + 1] = v;
+    }
+    cnt[(int64_t)h * kLutCells + cell] = (uint32_t)n;
+    uint16_t* dst = tmp + ((int64_t)h * kLutCells + cell) * kLutMaxList;
+    for (int i = 0; i < n; ++i) dst[i] = s_list[i];
+  }
+}
+
+// Per head: exclusive scan of the list lengths -> offsets; valid flag = the lists fit the capacity.
+__global__ void __launch_bounds__(1024) lut_scan_kernel(const uint32_t* __restrict__ cnt, uint32_t* __restrict__ lut) {
+  __shared__ uint32_t s_sum[1024];
+  const int h = blockIdx.x;
+  constexpr int PER = kLutCells / 1024;
+  uint32_t loc[PER], tot = 0;
+  for (int i = 0; i < PER; ++i) { loc[i] = cnt[(int64_t)h * kLutCells + threadIdx.x * PER + i]; tot += loc[i]; }
+  s_sum[threadIdx.x] = tot;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    uint32_t v = threadIdx.x >= o ? s_sum[threadIdx.x - o] : 0;
+    __syncthreads();
+    s_sum[threadIdx.x] += v;
+    __syncthreads();
+  }
+  uint32_t run = s_sum[threadIdx.x] - tot;
+  uint32_t* hdr = lut + (int64_t)h * kLutHdr;
+  for (int i = 0; i < PER; ++i) { hdr[threadIdx.x * PER + i] = run; run += loc[i]; }
+  if (threadIdx.x == 1023) {
+    hdr[kLutCells] = run;
+    hdr[kLutCells + 1] = run <= (uint32_t)kLutCandCap ? 1u : 0u;
+  }
+}
+
+__global__ void lut_fill_kernel(const uint16_t* __restrict__ tmp, const uint32_t* __restrict__ cnt, uint32_t* __restrict__ lut,
+                                int H) {
+  const int h = blockIdx.y;
+  const int cell = blockIdx.x * blockDim.x + threadIdx.x;
+  if (cell >= kLutCells) return;
+  const uint32_t* hdr = lut + (int64_t)h * kLutHdr;
+  if (hdr[kLutCells + 1] != 1u) return;
+  uint16_t* cand = reinterpret_cast<uint16_t*>(lut + (int64_t)H * kLutHdr) + (int64_t)h * kLutCandCap;
+  const uint32_t n = cnt[(int64_t)h * kLutCells + cell], o = hdr[cell];
+  const uint16_t* src = tmp + ((int64_t)h * kLutCells + cell) * kLutMaxList;
+  for (uint32_t i = 0; i < n; ++i) cand[o + i] = src[i];
+}
+
+Mul8x24 make_mul() {
+  // (axis unit g) * (primary p) in the reference's index order, from exact arithmetic on doubles
+  auto prim = [](int p, double v[4]) {
+    for (int i = 0; i < 4; ++i) v[i] = 0;
+    if (p < 8) v[p >> 1] = (p & 1) ? -1.0 : 1.0;
+    else for (int i = 0; i < 4; ++i) v[i] = (((p - 8) >> (3 - i)) & 1) ? -0.5 : 0.5;
+  };
+  Mul8x24 m;
+  for (int g = 0; g < 8; ++g)
+    for (int p = 0; p < 24; ++p) {
+      double a[4], b[4], c[4];
+      prim(g, a); prim(p, b);
+      c[0] = a[0] * b[0] - a[1] * b[1] - a[2] * b[2] - a[3] * b[3];
+      c[1] = a[0] * b[1] + a[1] * b[0] + a[2] * b[3] - a[3] * b[2];
+      c[2] = a[0] * b[2] - a[1] * b[3] + a[2] * b[0] + a[3] * b[1];
+      c[3] = a[0] * b[3] + a[1] * b[2] - a[2] * b[1] + a[3] * b[0];
+      m.v[g][p] = 0;
+      for (int q = 0; q < 24; ++q) {
+        double e[4];
+        prim(q, e);
+        double dd = 0;
+        for (int i = 0; i < 4; ++i) dd += (e[i] - c[i]) * (e[i] - c[i]);
+        if (dd < 1e-12) m.v[g][p] = (uint8_t)q;
+      }
+    }
+  return m;
+}
+
+inline size_t lut_bytes(int H) { return (size_t)H * kLutHdr * 4 + (size_t)H * kLutCandCap * 2; }
+inline size_t lut_ws_bytes(int H) { return (size_t)H * kLutCells * 4 + (size_t)H * kLutCells * kLutMaxList * 2; }
+
 struct WsPlan { size_t status, hist, sel, blk, total; int blk0, nblk; };
 WsPlan plan_ws(const hqmq_encode_args& a) {
   WsPlan w;
@@ -359,6 +564,44 @@ static int validate_encode(const hqmq_encode_args* a) {
   return HQMQ_OK;
 }
 
+extern "C" size_t hqmq_encode_lut_bytes(int H, int S) {
+  if (H < 1 || S < 1 || 24 * S > 65536) return 0;
+  return lut_bytes(H);
+}
+extern "C" size_t hqmq_encode_lut_workspace_bytes(int H, int S) {
+  if (H < 1 || S < 1 || 24 * S > 65536) return 0;
+  return lut_ws_bytes(H);
+}
+extern "C" int hqmq_encode_lut_build(const float* joint, int H, int S, void* lut, size_t lut_nbytes, void* workspace,
+                                     size_t ws_nbytes, void* stream) {
+  if (!joint || !lut || !workspace) return HQMQ_ERR_ARG;
+  if (H < 1 || S < 1 || 24 * S > 65536) return HQMQ_ERR_SHAPE;
+  if (lut_nbytes < lut_bytes(H) || ws_nbytes < lut_ws_bytes(H)) return HQMQ_ERR_WORKSPACE;
+  if (((uintptr_t)joint & 15) || ((uintptr_t)lut & 15) || ((uintptr_t)workspace & 15)) return HQMQ_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint32_t* cnt = reinterpret_cast<uint32_t*>(workspace);
+  uint16_t* tmp = reinterpret_cast<uint16_t*>(cnt + (size_t)H * kLutCells);
+  lut_cells_kernel<<<dim3(kLutCells, H), 128, 0, st>>>(joint, S, tmp, cnt);
+  lut_scan_kernel<<<H, 1024, 0, st>>>(cnt, reinterpret_cast<uint32_t*>(lut));
+  lut_fill_kernel<<<dim3(kLutCells / 256, H), 256, 0, st>>>(tmp, cnt, reinterpret_cast<uint32_t*>(lut), H);
+  HQMQ_LAUNCH_CHECK();
+  return HQMQ_OK;
+}
+extern "C" int hqmq_encode_lut_max_candidates(const void* lut, int H, int* max_cand, void* stream) {
+  if (!lut || !max_cand || H < 1) return HQMQ_ERR_ARG;
+  int best = 0;
+  for (int h = 0; h < H; ++h) {
+    uint32_t v[2];
+    HQMQ_CHECK_CUDA(cudaMemcpyAsync(v, reinterpret_cast<const uint32_t*>(lut) + (size_t)h * kLutHdr + kLutCells, 8,
+                                    cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    HQMQ_CHECK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (v[1] != 1u) { *max_cand = -1; return HQMQ_OK; }
+    if ((int)v[0] > best) best = (int)v[0];
+  }
+  *max_cand = best;
+  return HQMQ_OK;
+}
+
 extern "C" size_t hqmq_encode_workspace_bytes(const hqmq_encode_args* a) {
   if (validate_encode(a) != HQMQ_OK) return 0;
   return plan_ws(*a).total;
@@ -390,11 +633,27 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
 
   const int tok_per_block = kEncWarps * g.tpw * kEncIters;
   dim3 grid((a->T_new + tok_per_block - 1) / tok_per_block, d.B * d.H);
-  size_t smem = (size_t)g.S * 16 + (size_t)kEncWarps * g.tpw * kMaxRowWords * 4 + (med ? kHistBins * 4 : 0);
-  if (smem > 200 * 1024) return HQMQ_ERR_UNSUPPORTED;
-  if (smem > 48 * 1024)
-    HQMQ_CHECK_CUDA(cudaFuncSetAttribute(encode_main_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  encode_main_kernel<<<grid, kEncThreads, smem, st>>>(g, a->x, a->qs, d, a->t_start, med ? ws + wp.hist : nullptr, maps);
+  const size_t smem_base = (size_t)g.S * 16 + (size_t)kEncWarps * g.tpw * kMaxRowWords * 4 + kHistBins * 4;
+  if (smem_base > 200 * 1024) return HQMQ_ERR_UNSUPPORTED;
+  // look-up-table search when a table is given and it fits shared memory next to the joint codebook
+  int cand_smem = a->lut_max_cand > 0 ? a->lut_max_cand : kLutCandCap;
+  cand_smem = (cand_smem + 7) & ~7;
+  const size_t smem_lut = smem_base + (size_t)24 * g.S * 16 + (size_t)(kLutCells + 4) * 4 + (size_t)cand_smem * 2;
+  const bool use_lut = a->search == 0 && a->lut != nullptr && a->lut_max_cand >= 0 && smem_lut <= 220 * 1024;
+  static const Mul8x24 mul = make_mul();
+  if (use_lut) {
+    if ((uintptr_t)a->lut & 15) return HQMQ_ERR_ALIGN;
+    if (smem_lut > 48 * 1024)
+      HQMQ_CHECK_CUDA(cudaFuncSetAttribute(encode_main_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_lut));
+    encode_main_kernel<true><<<grid, kEncThreads, smem_lut, st>>>(g, a->x, a->qs, d, a->t_start, med ? ws + wp.hist : nullptr,
+                                                                  maps, a->joint, reinterpret_cast<const uint32_t*>(a->lut),
+                                                                  cand_smem, mul);
+  } else {
+    if (smem_base > 48 * 1024)
+      HQMQ_CHECK_CUDA(cudaFuncSetAttribute(encode_main_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_base));
+    encode_main_kernel<false><<<grid, kEncThreads, smem_base, st>>>(g, a->x, a->qs, d, a->t_start, med ? ws + wp.hist : nullptr,
+                                                                    maps, a->joint, nullptr, 0, mul);
+  }
   HQMQ_LAUNCH_CHECK();
   if (!med) return HQMQ_OK;
 

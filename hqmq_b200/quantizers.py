@@ -161,6 +161,17 @@ class HQMQQuantizer(KVQuantizer):
                     _lib.check(_lib.lib().hqmq_codebook_tables(t["joint"].data_ptr(), H, S, t16.data_ptr(),
                                                                _lib.stream_ptr()), "hqmq_codebook_tables")
                 t["table16"] = t16
+                # nearest-codeword look-up table for the encoder
+                L = _lib.lib()
+                lut = torch.empty(L.hqmq_encode_lut_bytes(H, S), dtype=torch.uint8, device=device)
+                ws = torch.empty(L.hqmq_encode_lut_workspace_bytes(H, S), dtype=torch.uint8, device=device)
+                mc = C.c_int(0)
+                with torch.cuda.device(device):
+                    _lib.check(L.hqmq_encode_lut_build(t["joint"].data_ptr(), H, S, lut.data_ptr(), lut.numel(),
+                                                       ws.data_ptr(), ws.numel(), _lib.stream_ptr()), "hqmq_encode_lut_build")
+                    _lib.check(L.hqmq_encode_lut_max_candidates(lut.data_ptr(), H, C.byref(mc), _lib.stream_ptr()),
+                               "hqmq_encode_lut_max_candidates")
+                t["lut"], t["lut_max_cand"] = lut, mc.value
             self._tables[key] = t
         return t
 
@@ -208,6 +219,7 @@ class HQMQQuantizer(KVQuantizer):
         a.search = search
         a.dst = out.c_struct()
         a.med_out = med_out.data_ptr() if med_out is not None else None
+        a.lut, a.lut_max_cand = tb["lut"].data_ptr(), tb["lut_max_cand"]
         L = _lib.lib()
         with torch.cuda.device(x.device):
             nbytes = L.hqmq_encode_workspace_bytes(C.byref(a))

@@ -136,6 +136,20 @@ int hqmq_native_index_maps(uint8_t* ref_to_native, uint8_t* native_to_ref);
 int hqmq_codebook_tables(const float* joint, int H, int S, uint16_t* table16, void* stream);
 
 /* ---- encode --------------------------------------------------------------------------- */
+/*
+ * Nearest-codeword look-up table of one joint codebook (H heads): a 16^3 grid over directions folded
+ * by the 8 axis units, each cell listing every codeword that can win somewhere in the cell.  It turns
+ * the reference's exhaustive argmax over 24*S similarities (src/quantizers/hqmq.py:158,164) into a
+ * handful of dot products per chunk with the same result.  Build once per (layer, K|V) codebook.
+ * hqmq_encode_lut_max_candidates synchronises the stream and returns the longest per-head candidate
+ * array (-1 if some head's lists exceed the table capacity: the encoder then searches exhaustively).
+ */
+size_t hqmq_encode_lut_bytes(int H, int S);
+size_t hqmq_encode_lut_workspace_bytes(int H, int S);
+int hqmq_encode_lut_build(const float* joint, int H, int S, void* lut, size_t lut_bytes, void* workspace,
+                          size_t workspace_bytes, void* stream);
+int hqmq_encode_lut_max_candidates(const void* lut, int H, int* max_cand, void* stream);
+
 typedef struct hqmq_encode_args {
   uint32_t struct_size;
   int32_t x_dtype;          /* HQMQ_F32 / HQMQ_F16 / HQMQ_BF16 */
@@ -146,9 +160,12 @@ typedef struct hqmq_encode_args {
   const float* qs;          /* (H,S,4) unit secondary quaternions, fp32 */
   const float* joint;       /* (H,24*S,4) fp32 joint table, reference order */
   float median_mult;        /* Med3x multiplier C; <= 0 disables outlier flagging */
-  int32_t search;           /* 0 = default, 1 = exhaustive scan over the S secondaries */
+  int32_t search;           /* 0 = default (look-up table when `lut` is given), 1 = exhaustive scan over the S secondaries */
   hqmq_packed dst;          /* destination planes */
   float* med_out;           /* optional (H,) fp32: the per-head median of this call */
+  const void* lut;          /* optional nearest-codeword table of this codebook (hqmq_encode_lut_build) */
+  int32_t lut_max_cand;     /* hqmq_encode_lut_max_candidates() of `lut` (0 = unknown, assume the capacity) */
+  int32_t reserved;
 } hqmq_encode_args;
 
 /*

@@ -8,8 +8,8 @@ namespace attn {
 const void* fast_kernel(int n_chunks, int ib, int rb, bool outl);
 
 template <int N, bool OUTL, bool WIDE>
-__global__ void __launch_bounds__(kAttnThreads) attn_slow_kernel(const AttnParams p) {
-  attn_decode_body<N, SlowLoader<N>, OUTL, WIDE>(p);
+__global__ void __launch_bounds__(kSlowWarps * 32) attn_slow_kernel(const AttnParams p) {
+  attn_decode_body<N, SlowLoader<N>, kSlowWarps, OUTL, WIDE>(p);
 }
 
 template <int N>
@@ -32,7 +32,7 @@ static const void* slow_kernel(int n, bool outl, bool wide) {
 // With tpu_v > 0 the number of valid parts of a row follows from the work decomposition.
 __global__ void combine_kernel(const float* __restrict__ parts, int n_parts, int64_t rows, int d, int out_dtype,
                                void* __restrict__ out, int64_t os_b, int64_t os_h, int64_t os_t, int Hq, int Tq, int G,
-                               int B, int tpu_v, int L, float* __restrict__ merged) {
+                               int B, int tpu_v, int L, int nw, float* __restrict__ merged) {
   const int64_t row = blockIdx.x;
   if (row >= rows) return;
   const int64_t tq = row % Tq, bh = row / Tq, hq = bh % Hq, b = bh / Hq;
@@ -40,7 +40,7 @@ __global__ void combine_kernel(const float* __restrict__ parts, int n_parts, int
   if (tpu_v > 0) {
     const int64_t u = (hq / G) * (int64_t)(B * Tq) + b * Tq + tq;
     const int64_t c0 = (u * tpu_v) / L, c1 = ((u + 1) * tpu_v - 1) / L;
-    n_valid = (int)(c1 - c0 + 1) * kAttnWarps;
+    n_valid = (int)(c1 - c0 + 1) * nw;
   }
   const float* base = parts + row * n_parts * (d + 2);
   float m_star = -INFINITY;
@@ -63,7 +63,7 @@ __global__ void combine_kernel(const float* __restrict__ parts, int n_parts, int
 struct Plan {
   const void* kernel;
   size_t smem;
-  int table_rows, ib;
+  int table_rows, ib, nw, rep_log2;
   int units, tpu_v, L, P, grid;
   size_t ws_bytes;
 };
@@ -106,7 +106,7 @@ static int validate_attn(const hqmq_attn_args* a) {
 }
 
 // Resident CTAs of `kernel` on the current device (cached per kernel and shared-memory size).
-static int resident_ctas(const void* kernel, size_t smem) {
+static int resident_ctas(const void* kernel, size_t smem, int threads) {
   struct Entry { const void* k; size_t smem; int dev; int val; };
   static Entry cache[64];
   static int n_cache = 0;
@@ -117,7 +117,7 @@ static int resident_ctas(const void* kernel, size_t smem) {
   int sms = 0, occ = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kAttnThreads, smem) != cudaSuccess || occ < 1) occ = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem) != cudaSuccess || occ < 1) occ = 1;
   cudaGetLastError();
   const int val = (sms > 0 ? sms : 148) * occ;
   if (n_cache < 64) cache[n_cache++] = {kernel, smem, dev, val};
@@ -129,17 +129,27 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   const int G = a->H_q / a->H_kv;
   const bool outl = a->layout == 0 && (a->K.flags != nullptr || a->V.flags != nullptr);
   pl.kernel = nullptr;
+  pl.nw = kSlowWarps;
+  pl.rep_log2 = 0;
   if (a->layout == 0) {
     pl.ib = idx_bits_for(a->K.S);
     pl.table_rows = 24 * a->K.S;
     if (G <= 8 && is_half_dtype(a->K.scale_dtype)) pl.kernel = fast_kernel(n, pl.ib, a->K.radius_bits, outl);
+    if (pl.kernel) pl.nw = outl ? kFastWarpsOutl : kFastWarps;
   } else {
     pl.ib = 16;
     pl.table_rows = a->K_size;
   }
+  const bool fast = pl.kernel != nullptr;
   if (!pl.kernel) pl.kernel = slow_kernel(n, outl, G > 8);
   if (!pl.kernel) return HQMQ_ERR_UNSUPPORTED;
-  pl.smem = (size_t)pl.table_rows * 16 + (outl ? (size_t)kAttnWarps * 2 * kStage * sizeof(uint2) : 0);
+  const int nheads = G > 8 ? 16 : 8;
+  const size_t extra = outl ? (size_t)nheads * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * nheads * 4) : 0;
+  // The big-CTA kernels own a whole SM: replicate the tables (interleaved) as far as shared memory
+  // allows, which spreads the random codeword gathers over more banks.
+  if (fast)
+    while (pl.rep_log2 < 4 && ((size_t)pl.table_rows * 16 << (pl.rep_log2 + 1)) + extra <= 200 * 1024) ++pl.rep_log2;
+  pl.smem = ((size_t)pl.table_rows * 16 << pl.rep_log2) + extra;
   if (pl.smem > 220 * 1024) return HQMQ_ERR_UNSUPPORTED;
 
   // tiles a unit can have (a window may straddle one extra tile)
@@ -153,11 +163,11 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
     pl.tpu_v = pl.L * splits;
   } else {
     // equal pieces of the flat tile sequence, one per resident CTA; at least one tile per warp
-    const int slots = query_device ? resident_ctas(pl.kernel, pl.smem) : 148 * 4;
+    const int slots = query_device ? resident_ctas(pl.kernel, pl.smem, pl.nw * 32) : 148;
     pl.tpu_v = tpu;
     const int64_t total = (int64_t)pl.units * tpu;
     int64_t L = (total + slots - 1) / slots;
-    if (L < kAttnWarps) L = kAttnWarps;
+    if (L < pl.nw) L = pl.nw;
     if (L > total) L = total;
     pl.L = (int)L;
   }
@@ -165,7 +175,7 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   pl.grid = (int)((total + pl.L - 1) / pl.L);
   pl.P = (pl.tpu_v - 1 + pl.L - 1) / pl.L + 1;
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
-  pl.ws_bytes = (size_t)rows * pl.P * kAttnWarps * (a->d + 2) * sizeof(float);
+  pl.ws_bytes = (size_t)rows * pl.P * pl.nw * (a->d + 2) * sizeof(float);
   return HQMQ_OK;
 }
 
@@ -192,7 +202,7 @@ extern "C" int hqmq_combine_partials(const float* parts, int n_parts, int64_t ro
   if (rows == 0) return HQMQ_OK;
   // rows are laid out contiguously: treat as B = rows, Hq = Tq = 1
   combine_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(parts, n_parts, rows, d, out_dtype, out, d, 0, 0, 1, 1, 1,
-                                                                  (int)rows, 0, 1, nullptr);
+                                                                  (int)rows, 0, 1, 1, nullptr);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }
@@ -213,6 +223,8 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   p.causal = a->causal; p.window = a->window;
   const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)a->d);
   p.sscale = scale * 1.4426950408889634f / (float)a->r_qmax;
+  p.qscale = scale * 1.4426950408889634f;
+  p.nw = pl.nw; p.rep_log2 = pl.rep_log2;
   p.vscale = 1.0f / (float)a->r_qmax;
   p.qmaxf = (float)a->r_qmax;
   p.units = pl.units; p.tpu_v = pl.tpu_v; p.L = pl.L; p.P = pl.P;
@@ -229,11 +241,11 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   if (pl.smem > 48 * 1024)
     HQMQ_CHECK_CUDA(cudaFuncSetAttribute(pl.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
   void* kargs[] = {&p};
-  HQMQ_CHECK_CUDA(cudaLaunchKernel(pl.kernel, dim3(pl.grid), dim3(kAttnThreads), kargs, pl.smem, st));
+  HQMQ_CHECK_CUDA(cudaLaunchKernel(pl.kernel, dim3(pl.grid), dim3(pl.nw * 32), kargs, pl.smem, st));
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
   combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, 0, st>>>(
-      p.partials, pl.P * kAttnWarps, rows, a->d, a->o_dtype, a->O, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
-      a->T_q, p.G, a->B, pl.tpu_v, pl.L, a->partials_only ? a->partials : nullptr);
+      p.partials, pl.P * pl.nw, rows, a->d, a->o_dtype, a->O, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
+      a->T_q, p.G, a->B, pl.tpu_v, pl.L, pl.nw, a->partials_only ? a->partials : nullptr);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }

@@ -5,9 +5,11 @@
 namespace hqmq {
 namespace attn {
 
+// One CTA per SM: 16 warps (12 with the outlier path, which needs more registers) share the
+// replicated codeword tables.
 template <int N, int IB, int RB, bool OUTL>
-__global__ void __launch_bounds__(kAttnThreads, OUTL ? 3 : 4) attn_fast_kernel(const AttnParams p) {
-  attn_decode_body<N, FastLoader<N, IB, RB>, OUTL, false>(p);
+__global__ void __launch_bounds__(OUTL ? kFastWarpsOutl * 32 : kFastWarps * 32, 1) attn_fast_kernel(const AttnParams p) {
+  attn_decode_body<N, FastLoader<N, IB, RB>, OUTL ? kFastWarpsOutl : kFastWarps, OUTL, false>(p);
 }
 
 template <int N, int IB, int RB, bool OUTL>

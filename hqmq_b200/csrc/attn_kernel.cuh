@@ -29,9 +29,8 @@
 namespace hqmq {
 namespace attn {
 
-constexpr int kAttnWarps = 4;
-constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kTile = 16;
+constexpr int kFastWarps = 16, kFastWarpsOutl = 12, kSlowWarps = 4;   // warps per CTA of the kernel families
 constexpr int kStage = 64;   // outlier payload entries staged per tile and tensor
 static_assert(kTile == HQMQ_OUT_BLOCK, "one outlier-offset entry per KV tile");
 
@@ -39,12 +38,15 @@ struct AttnParams {
   int B, Hq, Hkv, G, Tq, Tkv, d;
   int causal, window;
   float sscale;  // softmax_scale * log2(e) / qmax
+  float qscale;  // softmax_scale * log2(e)
   float vscale;  // 1 / qmax
   float qmaxf;
+  int nw;        // warps per CTA
+  int rep_log2;  // the codeword tables are replicated 2^rep_log2 times, interleaved entry by entry
   // flat tile space: units * tpu_v virtual tiles, L per CTA; a unit is touched by at most P CTAs
   int units, tpu_v, L, P;
   const void* Q; int q_dtype; int64_t qs_b, qs_h, qs_t;
-  float* partials;  // [row][P * kAttnWarps][d+2]
+  float* partials;  // [row][P * nw][d+2]
   int layout;       // 0 native, 1 reference tuple
   int ib;           // index bits of a field (native: idx_bits; reference: 16)
   int table_rows;   // codewords per head in the shared-memory tables
@@ -188,29 +190,29 @@ struct FastLoader {
       raw.rsv[nt] = vrs[t];
     }
   }
-  // byte offset of field F's codeword in the table, and its radius as half2 (r, r)
+  // codeword index of field F and its radius as half2 (r, r)
   template <int F>
-  static __device__ __forceinline__ void cut(const uint32_t* w, uint32_t& off8, __half2& rr) {
+  static __device__ __forceinline__ void cut(const uint32_t* w, uint32_t& idx, __half2& rr) {
     constexpr int bit = F * CB, a = bit >> 5, s = bit & 31;
     if constexpr (CB == 16) {
       // two fields per word: both radii come out of one subtraction
       const uint32_t word = w[a];
-      off8 = s == 0 ? ((word << 3) & (((1u << IB) - 1u) << 3)) : ((word >> (s - 3)) & (((1u << IB) - 1u) << 3));
+      idx = (word >> s) & ((1u << IB) - 1u);
       uint32_t bits = ((word >> IB) & 0x000f000fu) | 0x64006400u;
       const __half2 pair = __hsub2(*reinterpret_cast<__half2*>(&bits), __float2half2_rn(1024.f));
       rr = s == 0 ? __low2half2(pair) : __high2half2(pair);
     } else {
       uint32_t v = (s + CB > 32) ? __funnelshift_r(w[a], w[a + 1], s) : (w[a] >> s);
-      off8 = (v & ((1u << IB) - 1u)) << 3;
+      idx = v & ((1u << IB) - 1u);
       rr = radius_half2((v >> IB) & ((1u << RB) - 1u));
     }
   }
-  template <int NT, int KS> __device__ __forceinline__ void kfield(const Raw& raw, uint32_t& off8, __half2& rr) const {
-    cut<KS>(raw.kw[NT], off8, rr);
+  template <int NT, int KS> __device__ __forceinline__ void kfield(const Raw& raw, uint32_t& idx, __half2& rr) const {
+    cut<KS>(raw.kw[NT], idx, rr);
   }
-  template <int I, int GG> __device__ __forceinline__ void vfield(const Raw& raw, uint32_t& off8, __half2& rr) const {
-    cut<GG>(raw.vw[I], off8, rr);
-    if constexpr (N % 8 != 0) { if (r * NVG + GG >= N) { off8 = 0; rr = __float2half2_rn(0.f); } }
+  template <int I, int GG> __device__ __forceinline__ void vfield(const Raw& raw, uint32_t& idx, __half2& rr) const {
+    cut<GG>(raw.vw[I], idx, rr);
+    if constexpr (N % 8 != 0) { if (r * NVG + GG >= N) { idx = 0; rr = __float2half2_rn(0.f); } }
   }
   // scale of token nt*8 + r
   __device__ __forceinline__ float kscale(const Raw& raw, int nt) const { return bits16_to_float(raw.rsk[nt], sdt); }
@@ -269,15 +271,15 @@ struct SlowLoader {
       raw.rsv[nt] = t < t_end ? rscale(p.V, p.Vr, t) : 0.f;
     }
   }
-  __device__ __forceinline__ void split(uint32_t f, uint32_t& off8, __half2& rr) const {
-    off8 = (f & ((1u << pp->ib) - 1u)) << 3;
+  __device__ __forceinline__ void split(uint32_t f, uint32_t& idx, __half2& rr) const {
+    idx = f & ((1u << pp->ib) - 1u);
     rr = radius_half2(f >> pp->ib);
   }
-  template <int NT, int KS> __device__ __forceinline__ void kfield(const Raw& raw, uint32_t& off8, __half2& rr) const {
-    split(raw.kf[NT][KS], off8, rr);
+  template <int NT, int KS> __device__ __forceinline__ void kfield(const Raw& raw, uint32_t& idx, __half2& rr) const {
+    split(raw.kf[NT][KS], idx, rr);
   }
-  template <int I, int GG> __device__ __forceinline__ void vfield(const Raw& raw, uint32_t& off8, __half2& rr) const {
-    split(raw.vf[I][GG], off8, rr);
+  template <int I, int GG> __device__ __forceinline__ void vfield(const Raw& raw, uint32_t& idx, __half2& rr) const {
+    split(raw.vf[I][GG], idx, rr);
   }
   __device__ __forceinline__ float kscale(const Raw& raw, int nt) const { return raw.rsk[nt]; }
   __device__ __forceinline__ float vscale(const Raw& raw, int nt) const { return raw.rsv[nt]; }
@@ -285,11 +287,14 @@ struct SlowLoader {
 
 // ---- Med3x outliers ----------------------------------------------------------------------------------
 // Flagged chunks keep their original 4 values in a side buffer, in (token, chunk) order, with one
-// offset per 16-token tile, so a tile's entries are one contiguous range.  They are merged by
-// overwriting the decoded fragment with x * qmax / rs: the token's scale rs is its largest chunk
-// norm, flagged chunks included, so the patched value never exceeds qmax in magnitude and cannot
-// overflow fp16.  The first kStage entries of a tile are prefetched a tile ahead and staged in
-// shared memory; anything beyond (or an fp32 side buffer) is read from global memory in place.
+// offset per 16-token tile, so a tile's entries are one contiguous range; their radius code in the
+// packed row is 0, so the tensor-core path contributes nothing for them.
+//   K: after S^T is accumulated, the lanes walk the tile's flagged chunks and add <q, x> in fp32 to the
+//      scores (exact whatever the magnitude of the outlier).
+//   V: the decoded fragment is overwritten with x * qmax / rs: the token's scale rs is its largest chunk
+//      norm, flagged chunks included, so the patched value never exceeds qmax and cannot overflow fp16.
+// The first kStage entries of a tile are prefetched a tile ahead and staged in shared memory; anything
+// beyond (or an fp32 side buffer) is read from global memory in place.
 struct OutlRaw { uint32_t fk, fv, offk, offv; uint2 pk[kStage / 32], pv[kStage / 32]; };
 
 struct OutlSide {
@@ -301,7 +306,14 @@ struct OutlSide {
     vals = reinterpret_cast<const unsigned char*>(pk.out_vals) + bh * pk.out_cap * 4 * (dtype == HQMQ_F32 ? 4 : 2);
     stage = stage_;
   }
-  // original values of payload entry `pos` (tile-relative index `rel`), scaled by `inv`, as two half2 registers
+  // original values of payload entry `pos` (tile-relative index `rel`)
+  __device__ __forceinline__ float4 loadf(uint32_t pos, uint32_t rel) const {
+    if (dtype == HQMQ_F32) return *reinterpret_cast<const float4*>(vals + (int64_t)pos * 16);
+    const uint2 v = rel < (uint32_t)kStage ? stage[rel] : *reinterpret_cast<const uint2*>(vals + (int64_t)pos * 8);
+    return make_float4(bits16_to_float((uint16_t)(v.x & 0xffff), dtype), bits16_to_float((uint16_t)(v.x >> 16), dtype),
+                       bits16_to_float((uint16_t)(v.y & 0xffff), dtype), bits16_to_float((uint16_t)(v.y >> 16), dtype));
+  }
+  // the same scaled by `inv`, as two half2 registers
   __device__ __forceinline__ void load(uint32_t pos, uint32_t rel, float inv, uint32_t& lo, uint32_t& hi) const {
     float x0, x1, x2, x3;
     if (dtype == HQMQ_F32) {
@@ -336,19 +348,28 @@ __device__ __forceinline__ void static_for(F&& f) {
   }
 }
 
-// Loader: FastLoader<N, IB, RB> or SlowLoader<N>.  OUTL: merge Med3x outliers.  WIDE: 8 < G <= 16.
-template <int N, class Loader, bool OUTL, bool WIDE>
+// Loader: FastLoader<N, IB, RB> or SlowLoader<N>.  NW: warps per CTA.  OUTL: merge Med3x outliers.
+// WIDE: 8 < G <= 16.
+template <int N, class Loader, int NW, bool OUTL, bool WIDE>
 __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   using G_ = Geo<N>;
   constexpr int NKS = G_::NKS, NVG = G_::NVG, NOT = 2 * G_::NVG;   // NOT: 16-row tiles of O^T
   constexpr int NH = WIDE ? 2 : 1;   // 8-wide head tiles
+  constexpr int NHEADS = 8 * NH;
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  const uint32_t rstride = 8u << p.rep_log2;                       // bytes between consecutive codewords
+  const size_t tbl_bytes = (size_t)p.table_rows * rstride;
   unsigned char* tblK = smem_raw;
-  unsigned char* tblV = smem_raw + (size_t)p.table_rows * 8;
-  uint2* stage_base = reinterpret_cast<uint2*>(smem_raw + (size_t)p.table_rows * 16);
+  unsigned char* tblV = smem_raw + tbl_bytes;
+  float* qf32 = reinterpret_cast<float*>(smem_raw + 2 * tbl_bytes);                // [NHEADS][d]   (OUTL)
+  unsigned char* warp_base = reinterpret_cast<unsigned char*>(qf32 + NHEADS * p.d); // per warp      (OUTL)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = lane & 3, r = lane >> 2;
+  const uint32_t lane_off = (uint32_t)(lane & ((1 << p.rep_log2) - 1)) * 8u;       // this lane's replica
+  uint2* stageK = reinterpret_cast<uint2*>(warp_base + (size_t)warp * (2 * kStage * 8 + 16 * NHEADS * 4));
+  uint2* stageV = stageK + kStage;
+  float* dS = reinterpret_cast<float*>(stageV + kStage);                            // [16 tokens][NHEADS]
   const int64_t flat_lo = (int64_t)blockIdx.x * p.L;
   const int64_t flat_total = (int64_t)p.units * p.tpu_v;
   const int64_t flat_hi = flat_lo + p.L < flat_total ? flat_lo + p.L : flat_total;
@@ -358,27 +379,37 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
   for (int u = (int)(flat_lo / p.tpu_v); (int64_t)u * p.tpu_v < flat_hi; ++u) {
     const int h = u / upb, bt = u - h * upb;
     const int b = bt / p.Tq, tq = bt - b * p.Tq;
-    // ---- codeword tables of this KV head into shared memory (fp16 x 4 per entry) ---------------------
+    // ---- codeword tables of this KV head into shared memory (fp16 x 4 per entry, replicated) ---------
+    if (h != cur_h || OUTL) __syncthreads();
     if (h != cur_h) {
-      __syncthreads();
-      uint2* sk = reinterpret_cast<uint2*>(tblK);
-      uint2* sv = reinterpret_cast<uint2*>(tblV);
-      if (p.layout == 0) {
-        const uint2* gk = reinterpret_cast<const uint2*>(p.tblK) + (int64_t)h * p.table_rows;
-        const uint2* gv = reinterpret_cast<const uint2*>(p.tblV) + (int64_t)h * p.table_rows;
-        for (int i = threadIdx.x; i < p.table_rows; i += kAttnThreads) { sk[i] = gk[i]; sv[i] = gv[i]; }
-      } else {
-        for (int i = threadIdx.x; i < p.table_rows; i += kAttnThreads) {
+      const int reps = 1 << p.rep_log2;
+      for (int i = threadIdx.x; i < p.table_rows; i += NW * 32) {
+        uint2 ek, ev;
+        if (p.layout == 0) {
+          ek = (reinterpret_cast<const uint2*>(p.tblK) + (int64_t)h * p.table_rows)[i];
+          ev = (reinterpret_cast<const uint2*>(p.tblV) + (int64_t)h * p.table_rows)[i];
+        } else {
           const int64_t base = ((int64_t)h * p.table_rows + i) * 4;
-          sk[i] = make_uint2(pack_half2(load_float(p.jK, base, p.j_dtype), load_float(p.jK, base + 1, p.j_dtype)),
-                             pack_half2(load_float(p.jK, base + 2, p.j_dtype), load_float(p.jK, base + 3, p.j_dtype)));
-          sv[i] = make_uint2(pack_half2(load_float(p.jV, base, p.j_dtype), load_float(p.jV, base + 1, p.j_dtype)),
-                             pack_half2(load_float(p.jV, base + 2, p.j_dtype), load_float(p.jV, base + 3, p.j_dtype)));
+          ek = make_uint2(pack_half2(load_float(p.jK, base, p.j_dtype), load_float(p.jK, base + 1, p.j_dtype)),
+                          pack_half2(load_float(p.jK, base + 2, p.j_dtype), load_float(p.jK, base + 3, p.j_dtype)));
+          ev = make_uint2(pack_half2(load_float(p.jV, base, p.j_dtype), load_float(p.jV, base + 1, p.j_dtype)),
+                          pack_half2(load_float(p.jV, base + 2, p.j_dtype), load_float(p.jV, base + 3, p.j_dtype)));
         }
+        uint2* dk = reinterpret_cast<uint2*>(tblK + (size_t)i * rstride);
+        uint2* dv = reinterpret_cast<uint2*>(tblV + (size_t)i * rstride);
+        for (int q = 0; q < reps; ++q) { dk[q] = ek; dv[q] = ev; }
       }
-      __syncthreads();
       cur_h = h;
     }
+    if constexpr (OUTL) {
+      // queries of this unit in fp32 for the K outlier correction
+      for (int i = threadIdx.x; i < NHEADS * p.d; i += NW * 32) {
+        const int g = i / p.d, x = i - g * p.d;
+        qf32[i] = g < p.G ? load_float(p.Q, (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t + (int64_t)(h * p.G + g) * p.qs_h + x,
+                                       p.q_dtype) : 0.f;
+      }
+    }
+    __syncthreads();
 
     // ---- this CTA's tiles of the unit ----------------------------------------------------------------
     int t_beg, t_end;
@@ -389,7 +420,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
     const int rel_hi = (int)(flat_hi < ubase + p.tpu_v ? flat_hi - ubase : p.tpu_v);
     const int my_lo = tile_lo + rel_lo;
     const int my_hi = min(tile_hi, tile_lo + rel_hi);
-    const int part = ((int)blockIdx.x - (int)(ubase / p.L)) * kAttnWarps + warp;
+    const int part = ((int)blockIdx.x - (int)(ubase / p.L)) * NW + warp;
 
     // ---- Q as B fragments: column n = r is a query head, k slots {2j,2j+1,2j+8,2j+9} = one chunk -----
     uint32_t qb[NH][NKS][2];
@@ -427,13 +458,11 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
 
     Loader ld;
     ld.init(p, b, h, lane);
-    typename Loader::Raw cur, nxt;
     OutlSide ok_, ov_;
-    OutlRaw ocur, onxt;
     uint32_t offk_nn = 0, offv_nn = 0, offk_nn1 = 0, offv_nn1 = 0;   // payload ranges two tiles ahead
     if constexpr (OUTL) {
-      ok_.init(p.K, (int64_t)b * p.Hkv + h, stage_base + (warp * 2 + 0) * kStage);
-      ov_.init(p.V, (int64_t)b * p.Hkv + h, stage_base + (warp * 2 + 1) * kStage);
+      ok_.init(p.K, (int64_t)b * p.Hkv + h, stageK);
+      ov_.init(p.V, (int64_t)b * p.Hkv + h, stageV);
     }
     // flags and the first staged payload entries of tile tl, given its payload ranges
     auto fetch_outl = [&](OutlRaw& oo, int tl, uint32_t k0, uint32_t k1, uint32_t v0, uint32_t v1) {
@@ -458,27 +487,17 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
         if (ov_.flags) { v0 = ov_.off[tl]; v1 = ov_.off[tl + 1]; }
       }
     };
-
-    int tile = my_lo + warp;
-    if (tile < my_hi) {
-      ld.fetch(cur, tile, t_end);
+    // prefetch of tile tl into (raw, oo)
+    auto fetch = [&](typename Loader::Raw& raw, OutlRaw& oo, int tl) {
+      ld.fetch(raw, tl, t_end);
       if constexpr (OUTL) {
-        uint32_t k0, k1, v0, v1;
-        fetch_off(tile, k0, k1, v0, v1);
-        fetch_outl(ocur, tile, k0, k1, v0, v1);
-        fetch_off(tile + kAttnWarps, offk_nn, offk_nn1, offv_nn, offv_nn1);
+        fetch_outl(oo, tl, offk_nn, offk_nn1, offv_nn, offv_nn1);
+        fetch_off(tl + NW, offk_nn, offk_nn1, offv_nn, offv_nn1);
       }
-    }
+    };
 
-    for (; tile < my_hi; tile += kAttnWarps) {
-      const int tn = tile + kAttnWarps;
-      if (tn < my_hi) {
-        ld.fetch(nxt, tn, t_end);
-        if constexpr (OUTL) {
-          fetch_outl(onxt, tn, offk_nn, offk_nn1, offv_nn, offv_nn1);
-          fetch_off(tn + kAttnWarps, offk_nn, offk_nn1, offv_nn, offv_nn1);
-        }
-      }
+    // ---- one tile -------------------------------------------------------------------------------------------
+    auto compute = [&](const typename Loader::Raw& cur, const OutlRaw& ocur, int tile) {
       const int t0 = tile * kTile;
       const bool edge = t0 < t_beg || t0 + kTile > t_end;
       // per-token factors of this lane's tokens r and r+8
@@ -500,8 +519,8 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
 
       // ---- outlier bookkeeping of this tile -----------------------------------------------------------
       bool anyK = false, anyV = false;
-      uint32_t kfl[2] = {0, 0}, kpre[2] = {0, 0}, vfl[4] = {0, 0, 0, 0}, vpre[4] = {0, 0, 0, 0};
-      float kinv[2] = {0.f, 0.f}, vinv[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t vfl[4] = {0, 0, 0, 0}, vpre[4] = {0, 0, 0, 0};
+      float vinv[4] = {0.f, 0.f, 0.f, 0.f};
       if constexpr (OUTL) {
         anyK = __ballot_sync(0xffffffffu, ocur.fk != 0) != 0;
         anyV = __ballot_sync(0xffffffffu, ocur.fv != 0) != 0;
@@ -515,13 +534,36 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
           __syncwarp();
         }
         if (anyK) {
-          const uint32_t ex = excl_scan16(__popc(ocur.fk), lane);
+          // Lane t < 16 owns token t (lanes 16..31 idle along).  The warp walks the distinct chunk
+          // positions that are flagged anywhere in the tile (hot channels make them few); for each, the
+          // query values are one broadcast read and every flagged token adds <q_g, x> for all heads.
+          const uint32_t fl = ocur.fk;                       // 0 for lanes >= 16
+          const uint32_t pre = excl_scan16(__popc(fl), lane);
+          uint32_t any_c = fl;
 #pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
-            kfl[nt] = __shfl_sync(0xffffffffu, ocur.fk, nt * 8 + r);
-            kpre[nt] = __shfl_sync(0xffffffffu, ex, nt * 8 + r);
-            kinv[nt] = kfl[nt] ? p.qmaxf / ld.kscale(cur, nt) : 0.f;
+          for (int o_ = 16; o_ > 0; o_ >>= 1) any_c |= __shfl_xor_sync(0xffffffffu, any_c, o_);
+          float acc[NHEADS];
+#pragma unroll
+          for (int g = 0; g < NHEADS; ++g) acc[g] = 0.f;
+          while (any_c) {
+            const int c = __ffs(any_c) - 1;
+            any_c &= any_c - 1;
+            if ((fl >> c) & 1u) {
+              const uint32_t rel = pre + __popc(fl & ((1u << c) - 1u));
+              const float4 x = ok_.loadf(ocur.offk + rel, rel);
+#pragma unroll
+              for (int g = 0; g < NHEADS; ++g) {
+                const float4 q = *reinterpret_cast<const float4*>(qf32 + g * p.d + 4 * c);
+                acc[g] = fmaf(q.w, x.w, fmaf(q.z, x.z, fmaf(q.y, x.y, fmaf(q.x, x.x, acc[g]))));
+              }
+            }
           }
+          if (lane < 16) {
+#pragma unroll
+            for (int g = 0; g < NHEADS; g += 4)
+              *reinterpret_cast<float4*>(dS + lane * NHEADS + g) = make_float4(acc[g], acc[g + 1], acc[g + 2], acc[g + 3]);
+          }
+          __syncwarp();
         }
         if (anyV) {
           const uint32_t ex = excl_scan16(__popc(ocur.fv), lane);
@@ -538,42 +580,48 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
       }
 
       // ---- S^T = K Q^T: rows = tokens r, r+8; columns = heads 2j, 2j+1 -----------------------------------
-      float s[NH][4];
+      // (even and odd k slices accumulate separately so that consecutive MMAs do not depend on each other)
+      float s[NH][4], s2[NH][4];
 #pragma unroll
-      for (int nh = 0; nh < NH; ++nh) s[nh][0] = s[nh][1] = s[nh][2] = s[nh][3] = 0.f;
+      for (int nh = 0; nh < NH; ++nh) {
+        s[nh][0] = s[nh][1] = s[nh][2] = s[nh][3] = 0.f;
+        s2[nh][0] = s2[nh][1] = s2[nh][2] = s2[nh][3] = 0.f;
+      }
       static_for<0, NKS>([&](auto ks_) {
         constexpr int ks = decltype(ks_)::value;
         uint32_t a[4];   // a0: token r (e0,e1), a1: token r+8 (e0,e1), a2: token r (e2,e3), a3: token r+8 (e2,e3)
         static_for<0, 2>([&](auto nt_) {
           constexpr int nt = decltype(nt_)::value;
-          uint32_t off8; __half2 rr;
-          ld.template kfield<nt, ks>(cur, off8, rr);
-          const uint2 cw = *reinterpret_cast<const uint2*>(tblK + off8);
+          uint32_t idx; __half2 rr;
+          ld.template kfield<nt, ks>(cur, idx, rr);
+          const uint2 cw = *reinterpret_cast<const uint2*>(tblK + (idx * rstride + lane_off));
           a[nt] = hmul2_u32(cw.x, rr);
           a[2 + nt] = hmul2_u32(cw.y, rr);
-          if constexpr (OUTL) {
-            if (anyK) {
-              const int c = j * NKS + ks;
-              if ((kfl[nt] >> c) & 1u) {
-                const uint32_t rel = kpre[nt] + __popc(kfl[nt] & ((1u << c) - 1u));
-                ok_.load(ocur.offk + rel, rel, kinv[nt], a[nt], a[2 + nt]);
-              }
-            }
-          }
         });
 #pragma unroll
-        for (int nh = 0; nh < NH; ++nh) mma16816(s[nh], a[0], a[1], a[2], a[3], qb[nh][ks][0], qb[nh][ks][1]);
+        for (int nh = 0; nh < NH; ++nh)
+          mma16816((ks & 1) ? s2[nh] : s[nh], a[0], a[1], a[2], a[3], qb[nh][ks][0], qb[nh][ks][1]);
       });
+#pragma unroll
+      for (int nh = 0; nh < NH; ++nh) { s[nh][0] += s2[nh][0]; s[nh][1] += s2[nh][1]; s[nh][2] += s2[nh][2]; s[nh][3] += s2[nh][3]; }
 
-      // ---- scale, mask, online softmax -------------------------------------------------------------------
+      // ---- scale, outlier scores, mask, online softmax -----------------------------------------------------
       bool grew = false;
       float mx[NH][2];
 #pragma unroll
       for (int nh = 0; nh < NH; ++nh) {
+        float d0[2] = {0.f, 0.f}, d1[2] = {0.f, 0.f};
+        if constexpr (OUTL) {
+          if (anyK) {
+            const float2 u0 = *reinterpret_cast<const float2*>(dS + r * NHEADS + 8 * nh + 2 * j);
+            const float2 u1 = *reinterpret_cast<const float2*>(dS + (r + 8) * NHEADS + 8 * nh + 2 * j);
+            d0[0] = u0.x * p.qscale; d0[1] = u0.y * p.qscale; d1[0] = u1.x * p.qscale; d1[1] = u1.y * p.qscale;
+          }
+        }
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          s[nh][e] = okt[0] ? s[nh][e] * ksc[0] : -INFINITY;          // token r
-          s[nh][2 + e] = okt[1] ? s[nh][2 + e] * ksc[1] : -INFINITY;  // token r+8
+          s[nh][e] = okt[0] ? fmaf(s[nh][e], ksc[0], d0[e]) : -INFINITY;          // token r
+          s[nh][2 + e] = okt[1] ? fmaf(s[nh][2 + e], ksc[1], d1[e]) : -INFINITY;  // token r+8
           float m = fmaxf(s[nh][e], s[nh][2 + e]);
           m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
           m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
@@ -611,43 +659,64 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
       }
 
       // ---- O^T += V^T P^T: rows = head-dims, k = the 16 tokens, columns = heads ---------------------------
-      static_for<0, NVG>([&](auto g_) {
-        constexpr int g = decltype(g_)::value;
-        uint32_t lo[4], hi[4];
-        static_for<0, 4>([&](auto i_) {
-          constexpr int i = decltype(i_)::value;
-          uint32_t off8; __half2 rr;
-          ld.template vfield<i, g>(cur, off8, rr);
-          const uint2 cw = *reinterpret_cast<const uint2*>(tblV + off8);
-          lo[i] = hmul2_u32(cw.x, rr);
-          hi[i] = hmul2_u32(cw.y, rr);
-          if constexpr (OUTL) {
-            if (anyV) {
+      auto v_side = [&](auto patch_) {
+        constexpr bool PATCH = decltype(patch_)::value;
+        static_for<0, NVG>([&](auto g_) {
+          constexpr int g = decltype(g_)::value;
+          uint32_t lo[4], hi[4];
+          static_for<0, 4>([&](auto i_) {
+            constexpr int i = decltype(i_)::value;
+            uint32_t idx; __half2 rr;
+            ld.template vfield<i, g>(cur, idx, rr);
+            const uint2 cw = *reinterpret_cast<const uint2*>(tblV + (idx * rstride + lane_off));
+            lo[i] = hmul2_u32(cw.x, rr);
+            hi[i] = hmul2_u32(cw.y, rr);
+            if constexpr (PATCH) {
               const int c = r * NVG + g;
               if (c < N && ((vfl[i] >> c) & 1u)) {
                 const uint32_t rel = vpre[i] + __popc(vfl[i] & ((1u << c) - 1u));
                 ov_.load(ocur.offv + rel, rel, vinv[i], lo[i], hi[i]);
               }
             }
+          });
+          // tile 2g: rows r / r+8 = elements 0 / 1 of the lane's chunk; tile 2g+1: elements 2 / 3
+          const uint32_t a0 = __byte_perm(lo[0], lo[1], 0x5410), a1 = __byte_perm(lo[0], lo[1], 0x7632);
+          const uint32_t a2 = __byte_perm(lo[2], lo[3], 0x5410), a3 = __byte_perm(lo[2], lo[3], 0x7632);
+          const uint32_t c0 = __byte_perm(hi[0], hi[1], 0x5410), c1 = __byte_perm(hi[0], hi[1], 0x7632);
+          const uint32_t c2 = __byte_perm(hi[2], hi[3], 0x5410), c3 = __byte_perm(hi[2], hi[3], 0x7632);
+#pragma unroll
+          for (int nh = 0; nh < NH; ++nh) {
+            mma16816(o[nh][2 * g], a0, a1, a2, a3, pb[nh][0], pb[nh][1]);
+            mma16816(o[nh][2 * g + 1], c0, c1, c2, c3, pb[nh][0], pb[nh][1]);
           }
         });
-        // tile 2g: rows r / r+8 = elements 0 / 1 of the lane's chunk; tile 2g+1: elements 2 / 3
-        const uint32_t a0 = __byte_perm(lo[0], lo[1], 0x5410), a1 = __byte_perm(lo[0], lo[1], 0x7632);
-        const uint32_t a2 = __byte_perm(lo[2], lo[3], 0x5410), a3 = __byte_perm(lo[2], lo[3], 0x7632);
-        const uint32_t c0 = __byte_perm(hi[0], hi[1], 0x5410), c1 = __byte_perm(hi[0], hi[1], 0x7632);
-        const uint32_t c2 = __byte_perm(hi[2], hi[3], 0x5410), c3 = __byte_perm(hi[2], hi[3], 0x7632);
-#pragma unroll
-        for (int nh = 0; nh < NH; ++nh) {
-          mma16816(o[nh][2 * g], a0, a1, a2, a3, pb[nh][0], pb[nh][1]);
-          mma16816(o[nh][2 * g + 1], c0, c1, c2, c3, pb[nh][0], pb[nh][1]);
-        }
-      });
-      cur = nxt;
-      if constexpr (OUTL) ocur = onxt;
+      };
+      if (OUTL && anyV) v_side(std::true_type{});
+      else v_side(std::false_type{});
+    };
+
+    // ---- the warp's tiles, two at a time so that the prefetch buffers swap roles without copies ---------
+    {
+      typename Loader::Raw rawA, rawB;
+      OutlRaw oA, oB;
+      int tile = my_lo + warp;
+      if (tile < my_hi) {
+        if constexpr (OUTL) fetch_off(tile, offk_nn, offk_nn1, offv_nn, offv_nn1);
+        fetch(rawA, oA, tile);
+      }
+      while (tile < my_hi) {
+        if (tile + NW < my_hi) fetch(rawB, oB, tile + NW);
+        compute(rawA, oA, tile);
+        tile += NW;
+        if (tile >= my_hi) break;
+        if (tile + NW < my_hi) fetch(rawA, oA, tile + NW);
+        compute(rawB, oB, tile);
+        tile += NW;
+      }
     }
 
     // ---- per-warp partial: o[d], m, l for every query head of this KV head -----------------------------
-    const int n_parts = p.P * kAttnWarps;
+    const int n_parts = p.P * NW;
 #pragma unroll
     for (int nh = 0; nh < NH; ++nh)
 #pragma unroll

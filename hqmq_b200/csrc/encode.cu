@@ -9,6 +9,7 @@
 //            s, y = u * conj(q_s) and snaps y to the 24-cell in closed form
 //   med    = torch.quantile(norms of the head, 0.5): the two middle order statistics a <= b,
 //            med = a if N odd else b - (b - a) * 0.5; flag = norm > med * C (strict)
+// A flagged chunk keeps its index but its stored radius code is 0: its values live in the side buffer.
 #include <string.h>
 
 #include "common.cuh"
@@ -333,6 +334,18 @@ flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start
     if (active) load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
     const bool f = active && chunk_norm(v) > thr;
     const uint32_t bal = __ballot_sync(0xffffffffu, f);
+    if (f) {
+      // A flagged chunk is stored in the side buffer: its radius code in the packed row becomes 0 so
+      // that decoding the row contributes nothing for it.
+      const int cb = g.ib + g.rbits;
+      uint32_t* rowp = reinterpret_cast<uint32_t*>(dst.codes + ((int64_t)bh * dst.T_cap + t_start + t) * dst.row_bytes);
+      const int lo = c * cb + g.ib, hi = (c + 1) * cb;   // bit range of the radius code
+      const int w0 = lo >> 5, w1 = (hi - 1) >> 5;
+      const uint32_t m0 = ~0u << (lo & 31);
+      const uint32_t m1 = (hi & 31) ? ~(~0u << (hi & 31)) : ~0u;
+      if (w0 == w1) atomicAnd(&rowp[w0], ~(m0 & m1));
+      else { atomicAnd(&rowp[w0], ~m0); atomicAnd(&rowp[w1], ~m1); }
+    }
     if (t < g.T_new && c == 0) {
       const uint32_t mask = g.npl == 32 ? 0xffffffffu : ((1u << g.npl) - 1u);
       const uint32_t word = (bal >> (sub * g.npl)) & mask;

@@ -73,7 +73,9 @@ extern "C" {
  *   rs     [B][H][T_cap]             per-token radius scale r_max: fp16 / bf16 bits (2 B per
  *          token, what the byte accounting assumes) or fp32 (exact fake-quant round trips)
  *   flags  [B][H][T_cap]             uint32, bit c set = chunk c is an outlier kept in
- *          full precision (NULL when the tensor was encoded without Med3x)
+ *          full precision (NULL when the tensor was encoded without Med3x); the radius code
+ *          stored in the row for a flagged chunk is 0 (the reference would compute one, but its
+ *          wrapper discards the quantised value of a flagged chunk: outlier_aware.py:86)
  *   out_vals [B][H][out_cap][4]      the original 4 values of every flagged chunk as
  *          fp16 / bf16 / fp32, in (token, chunk) order
  *   out_off  [B][H][T_cap/16 + 1]    number of flagged chunks before each 16-token block

@@ -24,7 +24,9 @@ def _encode_and_compare(x, S, br, C, layer=0, kv=0, n_layers=2, search=0, scale_
                   med_out=med if C is not None else None)
     idx, rq, rs, flags = pk.to_reference()
     torch.cuda.synchronize()
-    assert torch.equal(rq.cpu(), enc["rq"]), "radius codes differ"
+    # the packed row stores 0 as the radius code of a flagged chunk (its values are in the side buffer)
+    want_rq = enc["rq"] if C is None else torch.where(enc["flags"], 0, enc["rq"])
+    assert torch.equal(rq.cpu(), want_rq), "radius codes differ"
     if scale_dtype == torch.float32:
         assert torch.equal(rs.cpu(), enc["r_max"]), "per-token scales differ"
     else:
@@ -59,7 +61,10 @@ def test_encode_matches_reference_fixtures(name):
         q, pk, enc, _ = _encode_and_compare(x, S, br, C, layer=layer, kv=kv)
         # against the stored reference-derived integers, not only the live oracle
         idx, rq, rs, flags = pk.to_reference()
-        assert np.array_equal(rq.cpu().numpy().astype(np.uint8), z[key + ".rq"])
+        gold_rq = z[key + ".rq"].copy()
+        if C is not None:
+            gold_rq[np.unpackbits(z[key + ".flags"])[: gold_rq.size].reshape(gold_rq.shape).astype(bool)] = 0
+        assert np.array_equal(rq.cpu().numpy().astype(np.uint8), gold_rq)
         mism = idx.cpu().numpy().astype(np.uint16) != z[key + ".idx"]
         assert not (mism & (z[key + ".gap"] >= NEAR_TIE)).any()
         # fake-quant output against the reference's own quantize_K / quantize_V output
@@ -120,7 +125,7 @@ def test_encode_append_keeps_earlier_rows_and_offsets():
         encs.append(orc.encode(x[:, :, lo:hi], joint, br, C))      # each call has its own median
     idx, rq, rs, flags = cache.to_reference()
     want = {k: torch.cat([e[k] for e in encs], dim=2) for k in ("idx", "rq", "r_max", "flags", "gap")}
-    assert torch.equal(rq.cpu(), want["rq"]) and torch.equal(rs.cpu(), want["r_max"])
+    assert torch.equal(rq.cpu(), torch.where(want["flags"], 0, want["rq"])) and torch.equal(rs.cpu(), want["r_max"])
     assert torch.equal(flags.cpu(), want["flags"])
     assert classify_idx(idx, want)[1] == 0
     # merged dequant == oracle fake-quant with originals restored
@@ -156,7 +161,7 @@ def test_full_size_properties_config2_slice():
         assert (v <= med[h]).float().mean() >= 0.5 and (v >= med[h]).float().mean() >= 0.5
         assert torch.equal(flags[0, h], nrm[0, h] > med[h] * C) or (flags[0, h] != (nrm[0, h] > med[h] * C)).sum() <= 2
     assert int(rq.max()) == 15 and int(rq.min()) >= 0
-    assert (rq.max(dim=-1).values == 15).all()            # the token's largest chunk always codes qmax
+    assert (torch.where(flags, 15, rq).max(dim=-1).values == 15).all()   # the token's largest chunk codes qmax (or is flagged)
     assert int(idx.max()) < 24 * S and int(idx.min()) >= 0
     assert pk.n_outliers() == int(flags.sum())
     # idempotence: re-encoding the fake-quantised tensor reproduces the same codes (outliers restored)

@@ -6,6 +6,8 @@ namespace hqmq {
 namespace attn {
 
 const void* fast_kernel(int n_chunks, int ib, int rb, bool outl);
+size_t fast_warp_bytes(int n_chunks, int ib, int rb, bool outl);
+constexpr int kFastStages = 3;
 
 template <int N, bool OUTL, bool WIDE>
 __global__ void __launch_bounds__(kSlowWarps * 32) attn_slow_kernel(const AttnParams p) {
@@ -32,9 +34,11 @@ static const void* slow_kernel(int n, bool outl, bool wide) {
 // With tpu_v > 0 the number of valid parts of a row follows from the work decomposition.
 __global__ void combine_kernel(const float* __restrict__ parts, int n_parts, int64_t rows, int d, int out_dtype,
                                void* __restrict__ out, int64_t os_b, int64_t os_h, int64_t os_t, int Hq, int Tq, int G,
-                               int B, int tpu_v, int L, int nw, float* __restrict__ merged) {
+                               int B, int tpu_v, int L, int nw, float* __restrict__ merged,
+                               const uint32_t* __restrict__ status, uint32_t epoch) {
   const int64_t row = blockIdx.x;
   if (row >= rows) return;
+  const bool failed = status != nullptr && *status == epoch;   // the attention kernel gave up on a wait
   const int64_t tq = row % Tq, bh = row / Tq, hq = bh % Hq, b = bh / Hq;
   int n_valid = n_parts;
   if (tpu_v > 0) {
@@ -54,8 +58,9 @@ __global__ void combine_kernel(const float* __restrict__ parts, int n_parts, int
       const float w = exp2f(base[i * (d + 2) + d] - m_use);
       if (w != 0.f) acc += base[i * (d + 2) + x] * w;
     }
+    if (failed) acc = NAN;
     if (merged) merged[row * (d + 2) + x] = acc;
-    else store_float(out, b * os_b + hq * os_h + tq * os_t + x, l_star > 0.f ? acc / l_star : 0.f, out_dtype);
+    else store_float(out, b * os_b + hq * os_h + tq * os_t + x, l_star > 0.f || failed ? acc / l_star : 0.f, out_dtype);
   }
   if (merged && threadIdx.x == 0) { merged[row * (d + 2) + d] = m_star; merged[row * (d + 2) + d + 1] = l_star; }
 }
@@ -134,7 +139,10 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   if (a->layout == 0) {
     pl.ib = idx_bits_for(a->K.S);
     pl.table_rows = 24 * a->K.S;
-    if (G <= 8 && is_half_dtype(a->K.scale_dtype)) pl.kernel = fast_kernel(n, pl.ib, a->K.radius_bits, outl);
+    // the staged kernels copy 16-byte aligned pieces: side buffers must start on 16 bytes per (b,h)
+    const bool side_ok = !outl || (((!a->K.flags || (a->K.out_cap % 2 == 0 && ((uintptr_t)a->K.out_vals & 15) == 0))) &&
+                                   ((!a->V.flags || (a->V.out_cap % 2 == 0 && ((uintptr_t)a->V.out_vals & 15) == 0))));
+    if (G <= 8 && is_half_dtype(a->K.scale_dtype) && side_ok) pl.kernel = fast_kernel(n, pl.ib, a->K.radius_bits, outl);
     if (pl.kernel) pl.nw = outl ? kFastWarpsOutl : kFastWarps;
   } else {
     pl.ib = 16;
@@ -144,13 +152,23 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   if (!pl.kernel) pl.kernel = slow_kernel(n, outl, G > 8);
   if (!pl.kernel) return HQMQ_ERR_UNSUPPORTED;
   const int nheads = G > 8 ? 16 : 8;
-  const size_t extra = outl ? (size_t)nheads * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * nheads * 4) : 0;
+  size_t extra = outl ? (size_t)nheads * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * nheads * 4) : 0;
+  if (fast)
+    extra = (outl ? (size_t)8 * a->d * 4 : 0) + (((size_t)pl.nw * kFastStages * 8 + 15) & ~(size_t)15) +
+            (size_t)pl.nw * fast_warp_bytes(n, pl.ib, a->K.radius_bits, outl);
   // The big-CTA kernels own a whole SM: replicate the tables (interleaved) as far as shared memory
   // allows, which spreads the random codeword gathers over more banks.
   if (fast)
-    while (pl.rep_log2 < 4 && ((size_t)pl.table_rows * 16 << (pl.rep_log2 + 1)) + extra <= 200 * 1024) ++pl.rep_log2;
+    while (pl.rep_log2 < 4 && ((size_t)pl.table_rows * 16 << (pl.rep_log2 + 1)) + extra <= 220 * 1024) ++pl.rep_log2;
   pl.smem = ((size_t)pl.table_rows * 16 << pl.rep_log2) + extra;
-  if (pl.smem > 220 * 1024) return HQMQ_ERR_UNSUPPORTED;
+  if (pl.smem > 226 * 1024) {
+    if (!fast) return HQMQ_ERR_UNSUPPORTED;
+    // the staged kernel does not fit next to this codebook: use the generic one
+    pl.kernel = slow_kernel(n, outl, false);
+    pl.nw = kSlowWarps; pl.rep_log2 = 0;
+    pl.smem = (size_t)pl.table_rows * 16 + (outl ? (size_t)8 * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * 8 * 4) : 0);
+    if (pl.smem > 226 * 1024) return HQMQ_ERR_UNSUPPORTED;
+  }
 
   // tiles a unit can have (a window may straddle one extra tile)
   const int keys = a->window > 0 ? (a->window < a->T_kv ? a->window : a->T_kv) : a->T_kv;
@@ -175,7 +193,7 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   pl.grid = (int)((total + pl.L - 1) / pl.L);
   pl.P = (pl.tpu_v - 1 + pl.L - 1) / pl.L + 1;
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
-  pl.ws_bytes = (size_t)rows * pl.P * pl.nw * (a->d + 2) * sizeof(float);
+  pl.ws_bytes = 16 + (size_t)rows * pl.P * pl.nw * (a->d + 2) * sizeof(float);
   return HQMQ_OK;
 }
 
@@ -202,7 +220,7 @@ extern "C" int hqmq_combine_partials(const float* parts, int n_parts, int64_t ro
   if (rows == 0) return HQMQ_OK;
   // rows are laid out contiguously: treat as B = rows, Hq = Tq = 1
   combine_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(parts, n_parts, rows, d, out_dtype, out, d, 0, 0, 1, 1, 1,
-                                                                  (int)rows, 0, 1, 1, nullptr);
+                                                                  (int)rows, 0, 1, 1, nullptr, nullptr, 0u);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }
@@ -229,7 +247,10 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   p.qmaxf = (float)a->r_qmax;
   p.units = pl.units; p.tpu_v = pl.tpu_v; p.L = pl.L; p.P = pl.P;
   p.Q = a->Q; p.q_dtype = a->q_dtype; p.qs_b = a->q_stride[0]; p.qs_h = a->q_stride[1]; p.qs_t = a->q_stride[2];
-  p.partials = reinterpret_cast<float*>(workspace);
+  static uint32_t epoch_counter = 0x5eed0000u;
+  p.status = reinterpret_cast<uint32_t*>(workspace);
+  p.epoch = ++epoch_counter;
+  p.partials = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 16);
   p.layout = a->layout;
   p.table_rows = pl.table_rows;
   p.ib = pl.ib;
@@ -245,7 +266,7 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
   combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, 0, st>>>(
       p.partials, pl.P * pl.nw, rows, a->d, a->o_dtype, a->O, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
-      a->T_q, p.G, a->B, pl.tpu_v, pl.L, pl.nw, a->partials_only ? a->partials : nullptr);
+      a->T_q, p.G, a->B, pl.tpu_v, pl.L, pl.nw, a->partials_only ? a->partials : nullptr, p.status, p.epoch);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }

@@ -1,15 +1,22 @@
 // Decode-attention kernels for the native layouts with a compile-time field layout:
 // (index bits, radius bits) = (10,3) s24_r3, (12,4) s96_r4, (13,6) s192_r6; d_head 64 or 128; G <= 8.
-#include "attn_kernel.cuh"
+#include "attn_tma.cuh"
 
 namespace hqmq {
 namespace attn {
 
-// One CTA per SM: 16 warps (12 with the outlier path, which needs more registers) share the
-// replicated codeword tables.
+// One CTA per SM; its warps share the codeword tables and each streams its own tiles through
+// shared memory with bulk asynchronous copies.
 template <int N, int IB, int RB, bool OUTL>
 __global__ void __launch_bounds__(OUTL ? kFastWarpsOutl * 32 : kFastWarps * 32, 1) attn_fast_kernel(const AttnParams p) {
-  attn_decode_body<N, FastLoader<N, IB, RB>, OUTL ? kFastWarpsOutl : kFastWarps, OUTL, false>(p);
+  attn_decode_tma_body<N, IB, RB, OUTL ? kFastWarpsOutl : kFastWarps, OUTL>(p, p.status);
+}
+
+// Shared memory of one warp's staging ring (must match StageLayout).
+size_t fast_warp_bytes(int n_chunks, int ib, int rb, bool outl) {
+  const size_t row = (size_t)n_chunks * (ib + rb) / 8;
+  const size_t stage = 2 * kTile * row + 64 + (outl ? 128 + 2 * (kPay + 2) * 8 + 16 : 0);
+  return kStages * stage + (outl ? 16 * 8 * 4 : 0);
 }
 
 template <int N, int IB, int RB, bool OUTL>

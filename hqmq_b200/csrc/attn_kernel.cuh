@@ -54,6 +54,8 @@ struct AttnParams {
   const uint16_t* tblK; const uint16_t* tblV;
   hqmq_ref_packed Kr, Vr;
   const void* jK; const void* jV; int j_dtype;
+  uint32_t* status;   // a kernel that gave up on a bounded wait stores `epoch` here; the merge kernel then emits NaN
+  uint32_t epoch;
 };
 
 // Key range [beg, end) of query position tq and the tiles that cover it.

@@ -1,0 +1,475 @@
+// Decode attention over the native compressed cache with the KV tiles staged through shared memory
+// by bulk asynchronous copies (cp.async.bulk + mbarrier), one CTA per SM.
+//
+// Every warp owns a ring of kStages tile buffers.  One lane issues, for the tile kStages-1 ahead, one
+// bulk copy per plane piece (16 code rows of K, 16 of V, the two scale vectors, and with Med3x the flag
+// words and the tile's slice of the outlier side buffers); all lanes wait on the stage's mbarrier and
+// then cut their bit fields out of shared memory.  Compared with prefetching into registers this keeps
+// several tiles in flight per warp at a cost of no registers, so more warps fit on the SM.
+// The arithmetic (fragment layouts, softmax, outlier handling) is the one described in attn_kernel.cuh.
+#pragma once
+#include "attn_kernel.cuh"
+
+namespace hqmq {
+namespace attn {
+
+constexpr int kStages = 3;
+constexpr int kPay = 64;                 // outlier entries staged per tile and tensor (+2 alignment slack)
+constexpr uint32_t kWaitLimit = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+// Shared-memory layout of one stage (all pieces 16-byte aligned).
+template <int N, int IB, int RB, bool OUTL>
+struct StageLayout {
+  static constexpr int ROW = N * (IB + RB) / 8;
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kTile * ROW;
+  static constexpr int kRsK = kV + kTile * ROW;
+  static constexpr int kRsV = kRsK + 32;
+  static constexpr int kFlK = kRsV + 32;
+  static constexpr int kFlV = kFlK + 64;
+  static constexpr int kPayK = kFlV + 64;
+  static constexpr int kPayV = kPayK + (kPay + 2) * 8;
+  static constexpr int kHdr = kPayV + (kPay + 2) * 8;   // off0K, off0V (uint32 each)
+  static constexpr int BYTES = OUTL ? kHdr + 16 : kFlK;
+  static_assert((kTile * ROW) % 16 == 0, "tile of code rows must be a multiple of 16 bytes");
+};
+
+template <int N, int IB, int RB, int NW, bool OUTL>
+__device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32_t* status) {
+  using G_ = Geo<N>;
+  using FL = FastLoader<N, IB, RB>;
+  using SL = StageLayout<N, IB, RB, OUTL>;
+  constexpr int NKS = G_::NKS, NVG = G_::NVG, NOT = 2 * G_::NVG;
+  constexpr int NHEADS = 8;
+  constexpr int ROW = SL::ROW;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const uint32_t rstride = 8u << p.rep_log2;
+  const size_t tbl_bytes = (size_t)p.table_rows * rstride;
+  unsigned char* tblK = smem_raw;
+  unsigned char* tblV = smem_raw + tbl_bytes;
+  float* qf32 = reinterpret_cast<float*>(smem_raw + 2 * tbl_bytes);                          // [8][d] (OUTL)
+  unsigned char* after_q = smem_raw + 2 * tbl_bytes + (OUTL ? (size_t)NHEADS * p.d * 4 : 0);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after_q);                                      // [NW][kStages]
+  unsigned char* warp_area = after_q + ((NW * kStages * 8 + 15) & ~15);
+  constexpr int WARP_BYTES = kStages * SL::BYTES + (OUTL ? 16 * NHEADS * 4 : 0);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = lane & 3, r = lane >> 2;
+  const uint32_t lane_off = (uint32_t)(lane & ((1 << p.rep_log2) - 1)) * 8u;
+  unsigned char* my_area = warp_area + (size_t)warp * WARP_BYTES;
+  float* dS = reinterpret_cast<float*>(my_area + kStages * SL::BYTES);                       // [16][8] (OUTL)
+  const uint32_t bar0 = smem_u32(bars + warp * kStages);
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  uint32_t it = 0;        // tiles this warp has consumed so far (stage = it % kStages, parity from it / kStages)
+  bool failed = false;
+
+  const int64_t flat_lo = (int64_t)blockIdx.x * p.L;
+  const int64_t flat_total = (int64_t)p.units * p.tpu_v;
+  const int64_t flat_hi = flat_lo + p.L < flat_total ? flat_lo + p.L : flat_total;
+  const int upb = p.B * p.Tq;
+  int cur_h = -1;
+
+  for (int u = (int)(flat_lo / p.tpu_v); (int64_t)u * p.tpu_v < flat_hi; ++u) {
+    const int h = u / upb, bt = u - h * upb;
+    const int b = bt / p.Tq, tq = bt - b * p.Tq;
+    if (h != cur_h || OUTL) __syncthreads();
+    if (h != cur_h) {
+      const int reps = 1 << p.rep_log2;
+      for (int i = threadIdx.x; i < p.table_rows; i += NW * 32) {
+        const uint2 ek = (reinterpret_cast<const uint2*>(p.tblK) + (int64_t)h * p.table_rows)[i];
+        const uint2 ev = (reinterpret_cast<const uint2*>(p.tblV) + (int64_t)h * p.table_rows)[i];
+        uint2* dk = reinterpret_cast<uint2*>(tblK + (size_t)i * rstride);
+        uint2* dv = reinterpret_cast<uint2*>(tblV + (size_t)i * rstride);
+        for (int q = 0; q < reps; ++q) { dk[q] = ek; dv[q] = ev; }
+      }
+      cur_h = h;
+    }
+    if constexpr (OUTL) {
+      for (int i = threadIdx.x; i < NHEADS * p.d; i += NW * 32) {
+        const int g = i / p.d, x = i - g * p.d;
+        qf32[i] = g < p.G ? load_float(p.Q, (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t + (int64_t)(h * p.G + g) * p.qs_h + x,
+                                       p.q_dtype) : 0.f;
+      }
+    }
+    __syncthreads();
+
+    int t_beg, t_end;
+    key_range(p.Tkv, p.causal, p.window, tq, t_beg, t_end);
+    const int tile_lo = t_beg / kTile, tile_hi = (t_end + kTile - 1) / kTile;
+    const int64_t ubase = (int64_t)u * p.tpu_v;
+    const int rel_lo = (int)(flat_lo > ubase ? flat_lo - ubase : 0);
+    const int rel_hi = (int)(flat_hi < ubase + p.tpu_v ? flat_hi - ubase : p.tpu_v);
+    const int my_lo = tile_lo + rel_lo;
+    const int my_hi = min(tile_hi, tile_lo + rel_hi);
+    const int part = ((int)blockIdx.x - (int)(ubase / p.L)) * NW + warp;
+
+    // ---- Q as B fragments -------------------------------------------------------------------------------
+    uint32_t qb[NKS][2];
+    {
+      const int64_t q0off = (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t;
+#pragma unroll
+      for (int ks = 0; ks < NKS; ++ks) {
+        const int dim = 4 * (j * NKS + ks);
+        float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+        if (r < p.G) {
+          const int64_t o = q0off + (int64_t)(h * p.G + r) * p.qs_h + dim;
+          q0 = load_float(p.Q, o, p.q_dtype); q1 = load_float(p.Q, o + 1, p.q_dtype);
+          q2 = load_float(p.Q, o + 2, p.q_dtype); q3 = load_float(p.Q, o + 3, p.q_dtype);
+        }
+        qb[ks][0] = pack_half2(q0, q1);
+        qb[ks][1] = pack_half2(q2, q3);
+      }
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[NOT][4];
+#pragma unroll
+    for (int i = 0; i < NOT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    // ---- producer side (lane 0): plane bases and the bulk copies of one tile -----------------------------
+    const int64_t bh = (int64_t)b * p.Hkv + h;
+    const unsigned char* gK = p.K.codes + bh * p.K.T_cap * ROW;
+    const unsigned char* gV = p.V.codes + bh * p.V.T_cap * ROW;
+    const unsigned char* gRsK = reinterpret_cast<const unsigned char*>(p.K.rs) + bh * p.K.T_cap * 2;
+    const unsigned char* gRsV = reinterpret_cast<const unsigned char*>(p.V.rs) + bh * p.V.T_cap * 2;
+    const uint32_t* gFlK = OUTL && p.K.flags ? p.K.flags + bh * p.K.T_cap : nullptr;
+    const uint32_t* gFlV = OUTL && p.V.flags ? p.V.flags + bh * p.V.T_cap : nullptr;
+    const uint32_t* gOffK = gFlK ? p.K.out_off + bh * (p.K.T_cap / HQMQ_OUT_BLOCK + 1) : nullptr;
+    const uint32_t* gOffV = gFlV ? p.V.out_off + bh * (p.V.T_cap / HQMQ_OUT_BLOCK + 1) : nullptr;
+    const unsigned char* gPayK = gFlK ? reinterpret_cast<const unsigned char*>(p.K.out_vals) + bh * p.K.out_cap * 8 : nullptr;
+    const unsigned char* gPayV = gFlV ? reinterpret_cast<const unsigned char*>(p.V.out_vals) + bh * p.V.out_cap * 8 : nullptr;
+    const bool stageK = gFlK && p.K.out_dtype != HQMQ_F32, stageV = gFlV && p.V.out_dtype != HQMQ_F32;
+    uint32_t nk0 = 0, nk1 = 0, nv0 = 0, nv1 = 0;   // payload ranges of the tile to be issued next
+    auto load_offsets = [&](int tl) {
+      nk0 = nk1 = nv0 = nv1 = 0;
+      if (tl < my_hi) {
+        if (gOffK) { nk0 = gOffK[tl]; nk1 = gOffK[tl + 1]; }
+        if (gOffV) { nv0 = gOffV[tl]; nv1 = gOffV[tl + 1]; }
+      }
+    };
+    auto issue = [&](int tl, uint32_t seq) {   // lane 0 only
+      const int st = seq % kStages;
+      unsigned char* sb = my_area + st * SL::BYTES;
+      const uint32_t sb32 = smem_u32(sb), bar = bar0 + 8 * st;
+      uint32_t bytes = 2 * kTile * ROW + 64;
+      uint32_t pk_bytes = 0, pv_bytes = 0, ak = 0, av = 0;
+      if constexpr (OUTL) {
+        if (gFlK) bytes += 64;
+        if (gFlV) bytes += 64;
+        if (stageK && nk1 > nk0) {
+          ak = nk0 & ~1u;
+          uint32_t n = nk1 - ak; if (n > kPay + 1) n = kPay + 1;
+          pk_bytes = ((n + 1) & ~1u) * 8; bytes += pk_bytes;
+        }
+        if (stageV && nv1 > nv0) {
+          av = nv0 & ~1u;
+          uint32_t n = nv1 - av; if (n > kPay + 1) n = kPay + 1;
+          pv_bytes = ((n + 1) & ~1u) * 8; bytes += pv_bytes;
+        }
+        uint32_t* hdr = reinterpret_cast<uint32_t*>(sb + SL::kHdr);
+        hdr[0] = nk0; hdr[1] = nv0;
+      }
+      mbar_expect_tx(bar, bytes);
+      bulk_g2s(sb32 + SL::kK, gK + (int64_t)tl * kTile * ROW, kTile * ROW, bar);
+      bulk_g2s(sb32 + SL::kV, gV + (int64_t)tl * kTile * ROW, kTile * ROW, bar);
+      bulk_g2s(sb32 + SL::kRsK, gRsK + (int64_t)tl * 32, 32, bar);
+      bulk_g2s(sb32 + SL::kRsV, gRsV + (int64_t)tl * 32, 32, bar);
+      if constexpr (OUTL) {
+        if (gFlK) bulk_g2s(sb32 + SL::kFlK, gFlK + (int64_t)tl * kTile, 64, bar);
+        if (gFlV) bulk_g2s(sb32 + SL::kFlV, gFlV + (int64_t)tl * kTile, 64, bar);
+        if (pk_bytes) bulk_g2s(sb32 + SL::kPayK, gPayK + (int64_t)ak * 8, pk_bytes, bar);
+        if (pv_bytes) bulk_g2s(sb32 + SL::kPayV, gPayV + (int64_t)av * 8, pv_bytes, bar);
+      }
+    };
+
+    const int n_my = my_hi > my_lo + warp ? (my_hi - my_lo - warp + NW - 1) / NW : 0;
+    // prologue: kStages-1 tiles in flight
+    if (lane == 0 && !failed) {
+      if constexpr (OUTL) load_offsets(my_lo + warp);
+#pragma unroll
+      for (int k = 0; k < kStages - 1; ++k) {
+        if (k < n_my) {
+          issue(my_lo + warp + k * NW, it + k);
+          if constexpr (OUTL) load_offsets(my_lo + warp + (k + 1) * NW);
+        }
+      }
+    }
+
+    for (int k = 0; k < n_my && !failed; ++k, ++it) {
+      const int tile = my_lo + warp + k * NW;
+      if (lane == 0 && k + kStages - 1 < n_my) {
+        issue(tile + (kStages - 1) * NW, it + kStages - 1);
+        if constexpr (OUTL) load_offsets(tile + kStages * NW);
+      }
+      const int st = it % kStages;
+      const uint32_t parity = (it / kStages) & 1u;
+      {
+        uint32_t spins = 0;
+        while (!mbar_try_wait(bar0 + 8 * st, parity)) {
+          if (++spins > kWaitLimit) { failed = true; break; }
+        }
+        failed = __any_sync(0xffffffffu, failed);
+        if (failed) { if (lane == 0) *status = p.epoch; break; }
+        __syncwarp();
+      }
+      const unsigned char* sb = my_area + st * SL::BYTES;
+      const int t0 = tile * kTile;
+      const bool edge = t0 < t_beg || t0 + kTile > t_end;
+
+      // ---- this lane's fields and scales out of the stage ------------------------------------------------
+      typename FL::Raw cur;
+      FL ld;
+      ld.row_bytes = ROW; ld.row_words = ROW / 4; ld.j = j; ld.r = r; ld.sdt = p.K.scale_dtype;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int tr = nt * 8 + r;
+        ld.template load_span<FL::KW, FL::LK>(cur.kw[nt], sb + SL::kK + tr * ROW, j, !edge || t0 + tr < t_end);
+        cur.rsk[nt] = reinterpret_cast<const uint16_t*>(sb + SL::kRsK)[tr];
+        cur.rsv[nt] = reinterpret_cast<const uint16_t*>(sb + SL::kRsV)[tr];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int tr = 2 * j + (i & 1) + (i >> 1) * 8;
+        ld.template load_span<FL::VW, FL::LV>(cur.vw[i], sb + SL::kV + tr * ROW, r, !edge || t0 + tr < t_end);
+      }
+      float ksc[2], vsc[2];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        ksc[nt] = ld.kscale(cur, nt) * p.sscale;
+        vsc[nt] = ld.vscale(cur, nt) * p.vscale;
+      }
+      bool okt[2] = {true, true};
+      if (edge) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int t = t0 + nt * 8 + r;
+          okt[nt] = t >= t_beg && t < t_end;
+          if (!okt[nt]) vsc[nt] = 0.f;
+        }
+      }
+
+      // ---- outliers --------------------------------------------------------------------------------------
+      bool anyK = false, anyV = false;
+      uint32_t vfl[4] = {0, 0, 0, 0}, vpre[4] = {0, 0, 0, 0};
+      float vinv[4] = {0.f, 0.f, 0.f, 0.f};
+      OutlSide ok_, ov_;
+      uint32_t offk = 0, offv = 0;
+      if constexpr (OUTL) {
+        const uint32_t* hdr = reinterpret_cast<const uint32_t*>(sb + SL::kHdr);
+        offk = hdr[0]; offv = hdr[1];
+        uint32_t fk = 0, fv = 0;
+        if (lane < 16 && t0 + lane < t_end) {
+          if (gFlK) fk = reinterpret_cast<const uint32_t*>(sb + SL::kFlK)[lane];
+          if (gFlV) fv = reinterpret_cast<const uint32_t*>(sb + SL::kFlV)[lane];
+        }
+        anyK = __ballot_sync(0xffffffffu, fk != 0) != 0;
+        anyV = __ballot_sync(0xffffffffu, fv != 0) != 0;
+        // staged entries start at the even entry index at or below the tile's first entry
+        ok_.flags = gFlK; ok_.off = gOffK; ok_.dtype = p.K.out_dtype;
+        ok_.vals = reinterpret_cast<const unsigned char*>(p.K.out_vals) + bh * p.K.out_cap * 4 * (p.K.out_dtype == HQMQ_F32 ? 4 : 2);
+        ok_.stage = reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayK);
+        ov_.flags = gFlV; ov_.off = gOffV; ov_.dtype = p.V.out_dtype;
+        ov_.vals = reinterpret_cast<const unsigned char*>(p.V.out_vals) + bh * p.V.out_cap * 4 * (p.V.out_dtype == HQMQ_F32 ? 4 : 2);
+        ov_.stage = reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayV);
+        if (anyK) {
+          const uint32_t fl = fk;
+          const uint32_t pre = excl_scan16(__popc(fl), lane);
+          const uint32_t skew = offk & 1u;
+          uint32_t any_c = fl;
+#pragma unroll
+          for (int o_ = 16; o_ > 0; o_ >>= 1) any_c |= __shfl_xor_sync(0xffffffffu, any_c, o_);
+          float acc[NHEADS];
+#pragma unroll
+          for (int g = 0; g < NHEADS; ++g) acc[g] = 0.f;
+          while (any_c) {
+            const int c = __ffs(any_c) - 1;
+            any_c &= any_c - 1;
+            if ((fl >> c) & 1u) {
+              const uint32_t rel = pre + __popc(fl & ((1u << c) - 1u));
+              const float4 x = ok_.loadf(offk + rel, rel + skew <= (uint32_t)kPay ? rel + skew : 0xffffffffu);
+#pragma unroll
+              for (int g = 0; g < NHEADS; ++g) {
+                const float4 q = *reinterpret_cast<const float4*>(qf32 + g * p.d + 4 * c);
+                acc[g] = fmaf(q.w, x.w, fmaf(q.z, x.z, fmaf(q.y, x.y, fmaf(q.x, x.x, acc[g]))));
+              }
+            }
+          }
+          if (lane < 16) {
+#pragma unroll
+            for (int g = 0; g < NHEADS; g += 4)
+              *reinterpret_cast<float4*>(dS + lane * NHEADS + g) = make_float4(acc[g], acc[g + 1], acc[g + 2], acc[g + 3]);
+          }
+          __syncwarp();
+        }
+        if (anyV) {
+          const uint32_t ex = excl_scan16(__popc(fv), lane);
+          const float i0 = p.qmaxf / ld.vscale(cur, 0), i1 = p.qmaxf / ld.vscale(cur, 1);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int tl = 2 * j + (i & 1) + (i >> 1) * 8;
+            vfl[i] = __shfl_sync(0xffffffffu, fv, tl);
+            vpre[i] = __shfl_sync(0xffffffffu, ex, tl);
+            vinv[i] = __shfl_sync(0xffffffffu, (i >> 1) ? i1 : i0, (tl & 7) * 4);
+          }
+        }
+      }
+
+      // ---- S^T = K Q^T ----------------------------------------------------------------------------------------
+      float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+      static_for<0, NKS>([&](auto ks_) {
+        constexpr int ks = decltype(ks_)::value;
+        uint32_t a[4];
+        static_for<0, 2>([&](auto nt_) {
+          constexpr int nt = decltype(nt_)::value;
+          uint32_t idx; __half2 rr;
+          ld.template kfield<nt, ks>(cur, idx, rr);
+          const uint2 cw = *reinterpret_cast<const uint2*>(tblK + (idx * rstride + lane_off));
+          a[nt] = hmul2_u32(cw.x, rr);
+          a[2 + nt] = hmul2_u32(cw.y, rr);
+        });
+        mma16816((ks & 1) ? s2 : s, a[0], a[1], a[2], a[3], qb[ks][0], qb[ks][1]);
+      });
+#pragma unroll
+      for (int x = 0; x < 4; ++x) s[x] += s2[x];
+
+      // ---- scale, outlier scores, mask, online softmax -----------------------------------------------------
+      float d0[2] = {0.f, 0.f}, d1[2] = {0.f, 0.f};
+      if constexpr (OUTL) {
+        if (anyK) {
+          const float2 u0 = *reinterpret_cast<const float2*>(dS + r * NHEADS + 2 * j);
+          const float2 u1 = *reinterpret_cast<const float2*>(dS + (r + 8) * NHEADS + 2 * j);
+          d0[0] = u0.x * p.qscale; d0[1] = u0.y * p.qscale; d1[0] = u1.x * p.qscale; d1[1] = u1.y * p.qscale;
+        }
+      }
+      bool grew = false;
+      float mx[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        s[e] = okt[0] ? fmaf(s[e], ksc[0], d0[e]) : -INFINITY;
+        s[2 + e] = okt[1] ? fmaf(s[2 + e], ksc[1], d1[e]) : -INFINITY;
+        float m = fmaxf(s[e], s[2 + e]);
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+        mx[e] = m;
+        grew |= m > m_run[e];
+      }
+      if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float m_new = fmaxf(m_run[e], mx[e]);
+          const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run[e] - m_new);
+          m_run[e] = m_new;
+          l_run[e] *= alpha;
+#pragma unroll
+          for (int i = 0; i < NOT; ++i) { o[i][e] *= alpha; o[i][2 + e] *= alpha; }
+        }
+      }
+      uint32_t pb[2];
+      {
+        float pe[4];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float m_use = m_run[e] == -INFINITY ? 0.f : m_run[e];
+          pe[e] = fast_exp2(s[e] - m_use);
+          pe[2 + e] = fast_exp2(s[2 + e] - m_use);
+          l_run[e] += pe[e] + pe[2 + e];
+        }
+        pb[0] = movmatrix_trans(pack_half2(pe[0] * vsc[0], pe[1] * vsc[0]));
+        pb[1] = movmatrix_trans(pack_half2(pe[2] * vsc[1], pe[3] * vsc[1]));
+      }
+
+      // ---- O^T += V^T P^T -------------------------------------------------------------------------------------
+      auto v_side = [&](auto patch_) {
+        constexpr bool PATCH = decltype(patch_)::value;
+        static_for<0, NVG>([&](auto g_) {
+          constexpr int g = decltype(g_)::value;
+          uint32_t lo[4], hi[4];
+          static_for<0, 4>([&](auto i_) {
+            constexpr int i = decltype(i_)::value;
+            uint32_t idx; __half2 rr;
+            ld.template vfield<i, g>(cur, idx, rr);
+            const uint2 cw = *reinterpret_cast<const uint2*>(tblV + (idx * rstride + lane_off));
+            lo[i] = hmul2_u32(cw.x, rr);
+            hi[i] = hmul2_u32(cw.y, rr);
+            if constexpr (PATCH) {
+              const int c = r * NVG + g;
+              if (c < N && ((vfl[i] >> c) & 1u)) {
+                const uint32_t rel = vpre[i] + __popc(vfl[i] & ((1u << c) - 1u));
+                const uint32_t skew = offv & 1u;
+                ov_.load(offv + rel, rel + skew <= (uint32_t)kPay ? rel + skew : 0xffffffffu, vinv[i], lo[i], hi[i]);
+              }
+            }
+          });
+          const uint32_t a0 = __byte_perm(lo[0], lo[1], 0x5410), a1 = __byte_perm(lo[0], lo[1], 0x7632);
+          const uint32_t a2 = __byte_perm(lo[2], lo[3], 0x5410), a3 = __byte_perm(lo[2], lo[3], 0x7632);
+          const uint32_t c0 = __byte_perm(hi[0], hi[1], 0x5410), c1 = __byte_perm(hi[0], hi[1], 0x7632);
+          const uint32_t c2 = __byte_perm(hi[2], hi[3], 0x5410), c3 = __byte_perm(hi[2], hi[3], 0x7632);
+          mma16816(o[2 * g], a0, a1, a2, a3, pb[0], pb[1]);
+          mma16816(o[2 * g + 1], c0, c1, c2, c3, pb[0], pb[1]);
+        });
+      };
+      if (OUTL && anyV) v_side(std::true_type{});
+      else v_side(std::false_type{});
+      __syncwarp();   // every lane is done with the stage before lane 0 refills it
+    }
+    if (failed) {
+      // drain: the copies still in flight for this warp land in its own buffers; wait for them (bounded)
+      // so that no copy is outstanding when the CTA exits
+      for (int k = 0; k < kStages; ++k) {
+        uint32_t spins = 0;
+        while (!mbar_try_wait(bar0 + 8 * ((it + k) % kStages), ((it + k) / kStages) & 1u) && ++spins < kWaitLimit) {}
+      }
+    }
+
+    // ---- per-warp partial ---------------------------------------------------------------------------------
+    const int n_parts = p.P * NW;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float l = l_run[e];
+      l += __shfl_xor_sync(0xffffffffu, l, 4);
+      l += __shfl_xor_sync(0xffffffffu, l, 8);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+      const int g = 2 * j + e;
+      if (g >= p.G) continue;
+      const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
+      float* dst = p.partials + (row * n_parts + part) * (p.d + 2);
+#pragma unroll
+      for (int i = 0; i < NOT; ++i) {
+        const int chunk = r * NVG + (i >> 1);
+        if (chunk < N) {
+          dst[4 * chunk + 2 * (i & 1)] = o[i][e];
+          dst[4 * chunk + 2 * (i & 1) + 1] = o[i][2 + e];
+        }
+      }
+      if (r == 0) { dst[p.d] = m_run[e]; dst[p.d + 1] = l; }
+    }
+    if (failed) break;
+  }
+}
+
+}  // namespace attn
+}  // namespace hqmq

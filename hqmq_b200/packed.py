@@ -44,7 +44,7 @@ class PackedKV:
         self.rs = torch.zeros(rows + 8, dtype=scale_dtype, device=dev)
         self.with_outliers = with_outliers
         if with_outliers:
-            self.out_cap = int(out_cap) if out_cap is not None else self.T_cap * n_chunks
+            self.out_cap = (int(out_cap) + 1) & ~1 if out_cap is not None else self.T_cap * n_chunks
             self.flags = torch.zeros(rows + 4, dtype=torch.int32, device=dev)
             self.out_vals = torch.zeros(B * H * self.out_cap * 4 + 8, dtype=out_dtype, device=dev)
             self.out_off = torch.zeros(B * H * (self.T_cap // _lib.OUT_BLOCK + 1), dtype=torch.int32, device=dev)

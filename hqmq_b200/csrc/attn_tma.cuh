@@ -273,10 +273,8 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
 
       // ---- outliers --------------------------------------------------------------------------------------
       bool anyK = false, anyV = false;
-      uint32_t vfl[4] = {0, 0, 0, 0}, vpre[4] = {0, 0, 0, 0};
-      float vinv[4] = {0.f, 0.f, 0.f, 0.f};
       OutlSide ok_, ov_;
-      uint32_t offk = 0, offv = 0;
+      uint32_t offk = 0, offv = 0, fv_tile = 0;
       if constexpr (OUTL) {
         const uint32_t* hdr = reinterpret_cast<const uint32_t*>(sb + SL::kHdr);
         offk = hdr[0]; offv = hdr[1];
@@ -287,6 +285,7 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         }
         anyK = __ballot_sync(0xffffffffu, fk != 0) != 0;
         anyV = __ballot_sync(0xffffffffu, fv != 0) != 0;
+        fv_tile = fv;
         // staged entries start at the even entry index at or below the tile's first entry
         ok_.flags = gFlK; ok_.off = gOffK; ok_.dtype = p.K.out_dtype;
         ok_.vals = reinterpret_cast<const unsigned char*>(p.K.out_vals) + bh * p.K.out_cap * 4 * (p.K.out_dtype == HQMQ_F32 ? 4 : 2);
@@ -295,45 +294,36 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         ov_.vals = reinterpret_cast<const unsigned char*>(p.V.out_vals) + bh * p.V.out_cap * 4 * (p.V.out_dtype == HQMQ_F32 ? 4 : 2);
         ov_.stage = reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayV);
         if (anyK) {
-          const uint32_t fl = fk;
-          const uint32_t pre = excl_scan16(__popc(fl), lane);
+          // Lane (t = lane & 15, hh = lane >> 4) owns token t and heads 4*hh .. 4*hh+3.  The warp walks the
+          // distinct chunk positions flagged anywhere in the tile (hot channels make them few); for each,
+          // the query values are a broadcast read and every flagged token adds <q_g, x> in fp32.
+          const uint32_t pre16 = excl_scan16(__popc(fk), lane);
+          const uint32_t fl = __shfl_sync(0xffffffffu, fk, lane & 15);
+          const uint32_t pre = __shfl_sync(0xffffffffu, pre16, lane & 15);
           const uint32_t skew = offk & 1u;
           uint32_t any_c = fl;
 #pragma unroll
-          for (int o_ = 16; o_ > 0; o_ >>= 1) any_c |= __shfl_xor_sync(0xffffffffu, any_c, o_);
-          float acc[NHEADS];
-#pragma unroll
-          for (int g = 0; g < NHEADS; ++g) acc[g] = 0.f;
+          for (int o_ = 8; o_ > 0; o_ >>= 1) any_c |= __shfl_xor_sync(0xffffffffu, any_c, o_);
+          const float* qh = qf32 + (lane >> 4) * 4 * p.d;
+          float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
           while (any_c) {
             const int c = __ffs(any_c) - 1;
             any_c &= any_c - 1;
             if ((fl >> c) & 1u) {
               const uint32_t rel = pre + __popc(fl & ((1u << c) - 1u));
               const float4 x = ok_.loadf(offk + rel, rel + skew <= (uint32_t)kPay ? rel + skew : 0xffffffffu);
-#pragma unroll
-              for (int g = 0; g < NHEADS; ++g) {
-                const float4 q = *reinterpret_cast<const float4*>(qf32 + g * p.d + 4 * c);
-                acc[g] = fmaf(q.w, x.w, fmaf(q.z, x.z, fmaf(q.y, x.y, fmaf(q.x, x.x, acc[g]))));
-              }
+              const float4 q0 = *reinterpret_cast<const float4*>(qh + 4 * c);
+              const float4 q1 = *reinterpret_cast<const float4*>(qh + p.d + 4 * c);
+              const float4 q2 = *reinterpret_cast<const float4*>(qh + 2 * p.d + 4 * c);
+              const float4 q3 = *reinterpret_cast<const float4*>(qh + 3 * p.d + 4 * c);
+              acc0 = fmaf(q0.w, x.w, fmaf(q0.z, x.z, fmaf(q0.y, x.y, fmaf(q0.x, x.x, acc0))));
+              acc1 = fmaf(q1.w, x.w, fmaf(q1.z, x.z, fmaf(q1.y, x.y, fmaf(q1.x, x.x, acc1))));
+              acc2 = fmaf(q2.w, x.w, fmaf(q2.z, x.z, fmaf(q2.y, x.y, fmaf(q2.x, x.x, acc2))));
+              acc3 = fmaf(q3.w, x.w, fmaf(q3.z, x.z, fmaf(q3.y, x.y, fmaf(q3.x, x.x, acc3))));
             }
           }
-          if (lane < 16) {
-#pragma unroll
-            for (int g = 0; g < NHEADS; g += 4)
-              *reinterpret_cast<float4*>(dS + lane * NHEADS + g) = make_float4(acc[g], acc[g + 1], acc[g + 2], acc[g + 3]);
-          }
+          *reinterpret_cast<float4*>(dS + (lane & 15) * NHEADS + (lane >> 4) * 4) = make_float4(acc0, acc1, acc2, acc3);
           __syncwarp();
-        }
-        if (anyV) {
-          const uint32_t ex = excl_scan16(__popc(fv), lane);
-          const float i0 = p.qmaxf / ld.vscale(cur, 0), i1 = p.qmaxf / ld.vscale(cur, 1);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int tl = 2 * j + (i & 1) + (i >> 1) * 8;
-            vfl[i] = __shfl_sync(0xffffffffu, fv, tl);
-            vpre[i] = __shfl_sync(0xffffffffu, ex, tl);
-            vinv[i] = __shfl_sync(0xffffffffu, (i >> 1) ? i1 : i0, (tl & 7) * 4);
-          }
         }
       }
 
@@ -405,6 +395,20 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
       // ---- O^T += V^T P^T -------------------------------------------------------------------------------------
       auto v_side = [&](auto patch_) {
         constexpr bool PATCH = decltype(patch_)::value;
+        // flag words, payload positions and inverse scales of this lane's four tokens (patch path only)
+        uint32_t vfl[4] = {0, 0, 0, 0}, vpre[4] = {0, 0, 0, 0};
+        float vinv[4] = {0.f, 0.f, 0.f, 0.f};
+        if constexpr (PATCH) {
+          const uint32_t ex = excl_scan16(__popc(fv_tile), lane);
+          const float i0 = p.qmaxf / ld.vscale(cur, 0), i1 = p.qmaxf / ld.vscale(cur, 1);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int tl = 2 * j + (i & 1) + (i >> 1) * 8;
+            vfl[i] = __shfl_sync(0xffffffffu, fv_tile, tl);
+            vpre[i] = __shfl_sync(0xffffffffu, ex, tl);
+            vinv[i] = __shfl_sync(0xffffffffu, (i >> 1) ? i1 : i0, (tl & 7) * 4);   // token tl's scale lives where r == tl & 7
+          }
+        }
         static_for<0, NVG>([&](auto g_) {
           constexpr int g = decltype(g_)::value;
           uint32_t lo[4], hi[4];

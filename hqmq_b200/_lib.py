@@ -128,7 +128,7 @@ def lib():
     L.hqmq_attn_workspace_bytes.restype = C.c_size_t
     L.hqmq_attn_workspace_bytes.argtypes = [C.POINTER(AttnArgs)]
     L.hqmq_attn_decode.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]
-    L.hqmq_combine_partials.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    L.hqmq_combine_partials.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     if L.hqmq_abi_version() != 1:
         raise HqmqError("hqmq_b200: library ABI version mismatch; rebuild with `python -m hqmq_b200.build --force`")
     _lib = L

@@ -127,11 +127,10 @@ def combine_partials(parts: torch.Tensor, out_dtype: torch.dtype = torch.float32
     rows = 1
     for s in lead:
         rows *= s
-    # kernel layout is (rows, n_parts, d+2)
-    p = parts.reshape(n_parts, rows, d + 2).transpose(0, 1).contiguous()
+    p = parts.reshape(n_parts, rows, d + 2).contiguous()      # part-major, as an all_gather leaves it
     out = torch.empty(rows, d, dtype=out_dtype, device=parts.device)
     with torch.cuda.device(parts.device):
-        _lib.check(_lib.lib().hqmq_combine_partials(p.data_ptr(), n_parts, rows, d, _lib.dtype_enum(out_dtype),
+        _lib.check(_lib.lib().hqmq_combine_partials(p.data_ptr(), n_parts, rows, d, 1, _lib.dtype_enum(out_dtype),
                                                     out.data_ptr(), _lib.stream_ptr()), "hqmq_combine_partials")
     return out.view(*lead, d)
 

@@ -35,7 +35,7 @@ static const void* slow_kernel(int n, bool outl, bool wide) {
 __global__ void combine_kernel(const float* __restrict__ parts, int n_parts, int64_t rows, int d, int out_dtype,
                                void* __restrict__ out, int64_t os_b, int64_t os_h, int64_t os_t, int Hq, int Tq, int G,
                                int B, int tpu_v, int L, int nw, float* __restrict__ merged,
-                               const uint32_t* __restrict__ status, uint32_t epoch) {
+                               const uint32_t* __restrict__ status, uint32_t epoch, int part_major) {
   const int64_t row = blockIdx.x;
   if (row >= rows) return;
   const bool failed = status != nullptr && *status == epoch;   // the attention kernel gave up on a wait
@@ -46,17 +46,19 @@ __global__ void combine_kernel(const float* __restrict__ parts, int n_parts, int
     const int64_t c0 = (u * tpu_v) / L, c1 = ((u + 1) * tpu_v - 1) / L;
     n_valid = (int)(c1 - c0 + 1) * nw;
   }
-  const float* base = parts + row * n_parts * (d + 2);
+  // part i of this row: [row][i] (row-major parts) or [i][row] (one block of rows per part, as gathered from ranks)
+  const float* base = part_major ? parts + row * (d + 2) : parts + row * n_parts * (d + 2);
+  const int64_t ps = part_major ? rows * (int64_t)(d + 2) : (int64_t)(d + 2);
   float m_star = -INFINITY;
-  for (int i = 0; i < n_valid; ++i) m_star = fmaxf(m_star, base[i * (d + 2) + d]);
+  for (int i = 0; i < n_valid; ++i) m_star = fmaxf(m_star, base[i * ps + d]);
   const float m_use = m_star == -INFINITY ? 0.f : m_star;
   float l_star = 0.f;
-  for (int i = 0; i < n_valid; ++i) l_star += base[i * (d + 2) + d + 1] * exp2f(base[i * (d + 2) + d] - m_use);
+  for (int i = 0; i < n_valid; ++i) l_star += base[i * ps + d + 1] * exp2f(base[i * ps + d] - m_use);
   for (int x = threadIdx.x; x < d; x += blockDim.x) {
     float acc = 0.f;
     for (int i = 0; i < n_valid; ++i) {
-      const float w = exp2f(base[i * (d + 2) + d] - m_use);
-      if (w != 0.f) acc += base[i * (d + 2) + x] * w;
+      const float w = exp2f(base[i * ps + d] - m_use);
+      if (w != 0.f) acc += base[i * ps + x] * w;
     }
     if (failed) acc = NAN;
     if (merged) merged[row * (d + 2) + x] = acc;
@@ -212,15 +214,15 @@ extern "C" size_t hqmq_attn_workspace_bytes(const hqmq_attn_args* a) {
   return pl.ws_bytes;
 }
 
-extern "C" int hqmq_combine_partials(const float* parts, int n_parts, int64_t rows, int d, int out_dtype, void* out,
-                                     void* stream) {
+extern "C" int hqmq_combine_partials(const float* parts, int n_parts, int64_t rows, int d, int part_major, int out_dtype,
+                                     void* out, void* stream) {
   if (!parts || !out) return HQMQ_ERR_ARG;
   if (n_parts < 1 || rows < 0 || d < 1) return HQMQ_ERR_SHAPE;
   if (!is_float_dtype(out_dtype)) return HQMQ_ERR_DTYPE;
   if (rows == 0) return HQMQ_OK;
   // rows are laid out contiguously: treat as B = rows, Hq = Tq = 1
   combine_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(parts, n_parts, rows, d, out_dtype, out, d, 0, 0, 1, 1, 1,
-                                                                  (int)rows, 0, 1, 1, nullptr, nullptr, 0u);
+                                                                  (int)rows, 0, 1, 1, nullptr, nullptr, 0u, part_major ? 1 : 0);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }
@@ -266,7 +268,7 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
   combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, 0, st>>>(
       p.partials, pl.P * pl.nw, rows, a->d, a->o_dtype, a->O, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
-      a->T_q, p.G, a->B, pl.tpu_v, pl.L, pl.nw, a->partials_only ? a->partials : nullptr, p.status, p.epoch);
+      a->T_q, p.G, a->B, pl.tpu_v, pl.L, pl.nw, a->partials_only ? a->partials : nullptr, p.status, p.epoch, 0);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }

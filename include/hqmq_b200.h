@@ -253,11 +253,12 @@ size_t hqmq_attn_workspace_bytes(const hqmq_attn_args* args);
 int hqmq_attn_decode(const hqmq_attn_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
- * Merge n_parts partial results (o[d], m, l per row, as written with partials_only) into
- * normalised outputs: parts is (n_parts, rows, d+2) fp32, out is (rows, d) of out_dtype.
- * Used after gathering the partials of a sequence-split cache from the other GPUs.
+ * Merge n_parts partial results (o[d], m, l per row, as written with partials_only; m is the maximum
+ * of score * log2(e)) into normalised outputs.  parts is (rows, n_parts, d+2) fp32, or with
+ * part_major != 0 (n_parts, rows, d+2): the layout an all_gather of per-GPU partials produces.  out is
+ * (rows, d) of out_dtype.  No counterpart in the reference (it has no split-KV or multi-GPU path).
  */
-int hqmq_combine_partials(const float* parts, int n_parts, int64_t rows, int d, int out_dtype,
+int hqmq_combine_partials(const float* parts, int n_parts, int64_t rows, int d, int part_major, int out_dtype,
                           void* out, void* stream);
 
 #ifdef __cplusplus

@@ -138,7 +138,7 @@ def test_validation_returns_error_codes_without_launching(built_lib):
     at.struct_size = C.sizeof(_lib.AttnArgs)
     assert L.hqmq_attn_decode(C.byref(at), None, 0, None) == -1    # Q missing
     assert L.hqmq_dequant(None, None) == -1
-    assert L.hqmq_combine_partials(None, 1, 1, 4, 0, None, None) == -1
+    assert L.hqmq_combine_partials(None, 1, 1, 4, 0, 0, None, None) == -1
     assert L.hqmq_codebook_tables(None, 1, 24, None, None) == -1
     p = _lib.Packed()
     assert L.hqmq_unpack(C.byref(p), 0, 1, None, None, None, None, None) == -1

@@ -13,7 +13,7 @@ no backend dispatch and no CPU fallback (CPU tensors raise).
 from . import attention as kernels_ada          # noqa: F401  one kernel family serves all three names
 from . import attention as kernels_hopper       # noqa: F401
 from . import attention as kernels_blackwell    # noqa: F401
-from .attention import fused_attention_packed, combine_partials, decode_dequant  # noqa: F401
+from .attention import fused_attention_packed, fused_attention_packed_noalloc, combine_partials, decode_dequant  # noqa: F401
 from .attention import fused_hqmq_attention as fused_attention
 from .attention import fused_hqmq_attention_dequant_sdpa as fused_attention_reference
 from .packed import PackedKV  # noqa: F401

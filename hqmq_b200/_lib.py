@@ -16,6 +16,7 @@ LIB_PATH = os.environ.get("HQMQ_B200_LIB") or os.path.join(HERE, "libhqmq_b200.s
 F32, F16, BF16, I32, I16, I8, U8, I64 = range(8)
 OUT_BLOCK = 16
 T_ALIGN = 64
+ATTN_STATIC_SCRATCH_BYTES = 16 << 20
 
 _TORCH_TO_ENUM = {
     torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: I32,
@@ -128,6 +129,7 @@ def lib():
     L.hqmq_attn_workspace_bytes.restype = C.c_size_t
     L.hqmq_attn_workspace_bytes.argtypes = [C.POINTER(AttnArgs)]
     L.hqmq_attn_decode.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    L.hqmq_attn_decode_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
     L.hqmq_combine_partials.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     if L.hqmq_abi_version() != 1:
         raise HqmqError("hqmq_b200: library ABI version mismatch; rebuild with `python -m hqmq_b200.build --force`")

@@ -119,6 +119,34 @@ def fused_attention_packed(
     return partials if partials is not None else O
 
 
+def fused_attention_packed_noalloc(Q: torch.Tensor, K: PackedKV, V: PackedKV, table_K: torch.Tensor,
+                                   table_V: torch.Tensor, out: torch.Tensor, causal: bool = False,
+                                   softmax_scale: Optional[float] = None, window: Optional[int] = None) -> torch.Tensor:
+    """``fused_attention_packed`` for callers that must not allocate device memory while they run (for
+    example a server whose memory pool already owns the whole GPU).  ``out`` has to exist already; the
+    kernel's scratch is a fixed ``_lib.ATTN_STATIC_SCRATCH_BYTES`` buffer inside the library, shared by all
+    calls on the device, so calls must not overlap on the GPU.  Shapes whose scratch would be larger raise
+    ``HqmqError``.  The first call on a device resolves the buffer's address: make it during set-up."""
+    _lib.require_cuda(Q, "fused_attention_packed_noalloc")
+    _lib.check_device(Q.device)
+    if Q.stride(-1) != 1:
+        raise _lib.HqmqError("hqmq_b200: Q needs unit stride on the last dim (no copy is made here)")
+    B, H_q, T_q, d_h = Q.shape
+    a = _lib.AttnArgs()
+    a.struct_size = C.sizeof(_lib.AttnArgs)
+    a.layout = 0
+    _fill_q(a, Q, out)
+    a.B, a.H_q, a.H_kv, a.T_q, a.d, a.T_kv = B, H_q, K.H, T_q, d_h, K.T
+    a.r_qmax, a.causal = K.qmax, int(bool(causal))
+    a.window = int(window) if window else 0
+    a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 0.0
+    a.K, a.V = K.c_struct(), V.c_struct()
+    a.table_K, a.table_V = table_K.data_ptr(), table_V.data_ptr()
+    with torch.cuda.device(Q.device):
+        _lib.check(_lib.lib().hqmq_attn_decode_static(C.byref(a), _lib.stream_ptr()), "hqmq_attn_decode_static")
+    return out
+
+
 def combine_partials(parts: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """Merge (n_parts, ..., d+2) fp32 partials (o[d], m, l; m in the exp2 domain) into (..., d)."""
     _lib.require_cuda(parts, "combine_partials")

@@ -272,3 +272,39 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }
+
+
+// ---- decode attention without any allocation by anybody ---------------------------------------------------
+// Some hosts cannot hand this library a workspace: a serving process that gave every free byte of HBM to its
+// KV-cache pool at start-up (so a later cudaMalloc fails), or a thin foreign-language binding that exposes no
+// device allocator at all.  For them the partials of hqmq_attn_decode live in a buffer that is part of the
+// library image: every GPU that loads the library holds HQMQ_ATTN_STATIC_SCRATCH_BYTES of it until the process
+// exits.  The array's name is only a host-side handle, so its device address is looked up once per device
+// (with that device current) and cached.
+namespace {
+__device__ __align__(256) unsigned char g_attn_static_scratch[HQMQ_ATTN_STATIC_SCRATCH_BYTES];
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};
+}  // namespace
+
+extern "C" int hqmq_attn_decode_static(const hqmq_attn_args* a, void* stream) {
+  int rc = validate_attn(a);
+  if (rc) return rc;
+  Plan pl;
+  rc = make_plan(a, pl, true);
+  if (rc) return rc;
+  if (pl.ws_bytes > (size_t)HQMQ_ATTN_STATIC_SCRATCH_BYTES) return HQMQ_ERR_STATIC_SCRATCH;
+  int dev = -1;
+  HQMQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return HQMQ_ERR_UNSUPPORTED;
+  void* ptr = __atomic_load_n(&g_static_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) {
+    // first call on this device: resolve the device address of the array (racing first calls resolve
+    // the same address, so the last store wins harmlessly)
+    if (cudaGetSymbolAddress(&ptr, g_attn_static_scratch) != cudaSuccess || !ptr) return HQMQ_ERR_CUDA;
+    __atomic_store_n(&g_static_scratch_ptr[dev], ptr, __ATOMIC_RELEASE);
+  }
+  // Nothing in the scratch has to start at zero: every partial that is read was written by this call, and
+  // the give-up word is compared with a per-call epoch.
+  return hqmq_attn_decode(a, ptr, (size_t)HQMQ_ATTN_STATIC_SCRATCH_BYTES, stream);
+}

@@ -245,6 +245,8 @@ const char* hqmq_strerror(int code) {
     case HQMQ_ERR_CUDA: return "CUDA runtime error";
     case HQMQ_ERR_UNSUPPORTED: return "configuration not supported";
     case HQMQ_ERR_CAPACITY: return "packed cache or outlier buffer capacity exceeded";
+    case HQMQ_ERR_STATIC_SCRATCH:
+      return "the problem needs more scratch than the library's built-in buffer; call hqmq_attn_decode with a workspace";
     default: return "unknown error";
   }
 }

@@ -39,6 +39,7 @@ extern "C" {
 #define HQMQ_ERR_CUDA (-7)        /* a CUDA runtime call failed (launch configuration etc.) */
 #define HQMQ_ERR_UNSUPPORTED (-8)
 #define HQMQ_ERR_CAPACITY (-9)    /* packed cache or outlier side buffer too small */
+#define HQMQ_ERR_STATIC_SCRATCH (-10) /* needs more scratch than the library's built-in buffer holds */
 
 /* element types */
 #define HQMQ_F32 0
@@ -251,6 +252,29 @@ typedef struct hqmq_attn_args {
  */
 size_t hqmq_attn_workspace_bytes(const hqmq_attn_args* args);
 int hqmq_attn_decode(const hqmq_attn_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * hqmq_attn_decode for hosts that cannot provide a workspace.  No counterpart in the reference.
+ *
+ * Who needs it: a process that has no device allocator to call -- an inference server that handed all free
+ * HBM to its cache pool when it started, so that any later cudaMalloc fails, or a binding from another
+ * language that wraps only this header.  The scratch that hqmq_attn_decode takes from the caller (the
+ * per-warp partial results) is here a fixed buffer of HQMQ_ATTN_STATIC_SCRATCH_BYTES inside the library
+ * itself; each GPU that loads the library carries that much until the process ends.  The function calls
+ * no cudaMalloc / cudaFree and no allocating library routine; Q, O and the cache planes are still the
+ * caller's.
+ *
+ *   - A problem whose partials do not fit (hqmq_attn_workspace_bytes(args) > HQMQ_ATTN_STATIC_SCRATCH_BYTES)
+ *     is rejected with HQMQ_ERR_STATIC_SCRATCH before anything is launched; use hqmq_attn_decode then.
+ *   - The first call on a device looks up the buffer's device address (cudaGetSymbolAddress) with that
+ *     device current, and caches it; make that first call during set-up, before any stream capture begins.
+ *     Call it with the device current that owns `stream`.
+ *   - All calls on a device share the one buffer, and it keeps what the previous call left.  Nothing in it
+ *     needs clearing between calls (every value read was written by the same call), but two calls that
+ *     overlap on the GPU -- different streams, or graphs replayed concurrently -- race on it: serialise them.
+ */
+#define HQMQ_ATTN_STATIC_SCRATCH_BYTES (16u << 20)
+int hqmq_attn_decode_static(const hqmq_attn_args* args, void* stream);
 
 /*
  * Merge n_parts partial results (o[d], m, l per row, as written with partials_only; m is the maximum

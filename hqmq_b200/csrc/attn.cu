@@ -49,15 +49,33 @@ __global__ void combine_kernel(const float* __restrict__ parts, int n_parts, int
   // part i of this row: [row][i] (row-major parts) or [i][row] (one block of rows per part, as gathered from ranks)
   const float* base = part_major ? parts + row * (d + 2) : parts + row * n_parts * (d + 2);
   const int64_t ps = part_major ? rows * (int64_t)(d + 2) : (int64_t)(d + 2);
+  // weights of the parts, computed once by the block: w_i = 2^(m_i - m*)
+  extern __shared__ float s_w[];          // [n_valid]
+  __shared__ float s_red[32];
+  float m_loc = -INFINITY;
+  for (int i = threadIdx.x; i < n_valid; i += blockDim.x) m_loc = fmaxf(m_loc, base[i * ps + d]);
+  for (int o = 16; o > 0; o >>= 1) m_loc = fmaxf(m_loc, __shfl_xor_sync(0xffffffffu, m_loc, o));
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m_loc;
+  __syncthreads();
   float m_star = -INFINITY;
-  for (int i = 0; i < n_valid; ++i) m_star = fmaxf(m_star, base[i * ps + d]);
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) m_star = fmaxf(m_star, s_red[i]);
+  __syncthreads();
   const float m_use = m_star == -INFINITY ? 0.f : m_star;
+  float l_loc = 0.f;
+  for (int i = threadIdx.x; i < n_valid; i += blockDim.x) {
+    const float w = exp2f(base[i * ps + d] - m_use);
+    s_w[i] = w;
+    l_loc += base[i * ps + d + 1] * w;
+  }
+  for (int o = 16; o > 0; o >>= 1) l_loc += __shfl_xor_sync(0xffffffffu, l_loc, o);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = l_loc;
+  __syncthreads();
   float l_star = 0.f;
-  for (int i = 0; i < n_valid; ++i) l_star += base[i * ps + d + 1] * exp2f(base[i * ps + d] - m_use);
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) l_star += s_red[i];
   for (int x = threadIdx.x; x < d; x += blockDim.x) {
     float acc = 0.f;
     for (int i = 0; i < n_valid; ++i) {
-      const float w = exp2f(base[i * ps + d] - m_use);
+      const float w = s_w[i];
       if (w != 0.f) acc += base[i * ps + x] * w;
     }
     if (failed) acc = NAN;
@@ -221,7 +239,7 @@ extern "C" int hqmq_combine_partials(const float* parts, int n_parts, int64_t ro
   if (!is_float_dtype(out_dtype)) return HQMQ_ERR_DTYPE;
   if (rows == 0) return HQMQ_OK;
   // rows are laid out contiguously: treat as B = rows, Hq = Tq = 1
-  combine_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(parts, n_parts, rows, d, out_dtype, out, d, 0, 0, 1, 1, 1,
+  combine_kernel<<<(unsigned)rows, 128, (size_t)n_parts * 4, (cudaStream_t)stream>>>(parts, n_parts, rows, d, out_dtype, out, d, 0, 0, 1, 1, 1,
                                                                   (int)rows, 0, 1, 1, nullptr, nullptr, 0u, part_major ? 1 : 0);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
@@ -266,7 +284,7 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   void* kargs[] = {&p};
   HQMQ_CHECK_CUDA(cudaLaunchKernel(pl.kernel, dim3(pl.grid), dim3(pl.nw * 32), kargs, pl.smem, st));
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
-  combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, 0, st>>>(
+  combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, (size_t)pl.P * pl.nw * 4, st>>>(
       p.partials, pl.P * pl.nw, rows, a->d, a->o_dtype, a->O, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
       a->T_q, p.G, a->B, pl.tpu_v, pl.L, pl.nw, a->partials_only ? a->partials : nullptr, p.status, p.epoch, 0);
   HQMQ_LAUNCH_CHECK();

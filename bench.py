@@ -76,7 +76,7 @@ def synth(kind, shape, seed, device, dtype):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons sampled every 50 ms while the steps run."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -87,7 +87,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
@@ -196,8 +196,8 @@ def run_reference_arm(args, w, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kv-splits", type=int, default=0)
@@ -314,12 +314,12 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
     # the timed region: exactly `steps` steps between barriers; the cache (>= 100 MB) exceeds what L2 keeps
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -343,6 +343,14 @@ def main():
     ev3.record(stream)
     barrier()
     e2e_s = ev2.elapsed_time(ev3) * 1e-3
+    # a short timed region can fall between two nvidia-smi samples: keep the same step running (untimed)
+    # until the sampler has seen the GPU under this load
+    t_probe = time.perf_counter()
+    while rank == 0 and not seq_mode and len(sampler.rows) < 6 and time.perf_counter() - t_probe < 2.0:
+        for _ in range(20):
+            step()
+        stream.synchronize()
+    barrier()
     clocks = sampler.stop() if rank == 0 else None
 
     t = torch.tensor([dev_s, e2e_s], device=dev, dtype=torch.float64)

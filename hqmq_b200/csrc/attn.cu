@@ -174,7 +174,7 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   const int nheads = G > 8 ? 16 : 8;
   size_t extra = outl ? (size_t)nheads * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * nheads * 4) : 0;
   if (fast)
-    extra = (outl ? (size_t)8 * a->d * 4 : 0) + (((size_t)pl.nw * kFastStages * 8 + 15) & ~(size_t)15) +
+    extra = (outl ? (size_t)8 * a->d * 2 : 0) + (((size_t)pl.nw * kFastStages * 8 + 15) & ~(size_t)15) +
             (size_t)pl.nw * fast_warp_bytes(n, pl.ib, a->K.radius_bits, outl);
   // The big-CTA kernels own a whole SM: replicate the tables (interleaved) as far as shared memory
   // allows, which spreads the random codeword gathers over more banks.

@@ -290,6 +290,12 @@ struct SlowLoader {
   __device__ __forceinline__ float vscale(const Raw& raw, int nt) const { return raw.rsv[nt]; }
 };
 
+// Two packed 16-bit floats (fp16 or bf16) to fp32 with one uniform branch.
+__device__ __forceinline__ float2 pair16_to_float2(uint32_t v, int dtype) {
+  if (dtype == HQMQ_BF16) return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+
 // ---- Med3x outliers ----------------------------------------------------------------------------------
 // Flagged chunks keep their original 4 values in a side buffer, in (token, chunk) order, with one
 // offset per 16-token tile, so a tile's entries are one contiguous range; their radius code in the
@@ -315,8 +321,8 @@ struct OutlSide {
   __device__ __forceinline__ float4 loadf(uint32_t pos, uint32_t rel) const {
     if (dtype == HQMQ_F32) return *reinterpret_cast<const float4*>(vals + (int64_t)pos * 16);
     const uint2 v = rel < (uint32_t)kStage ? stage[rel] : *reinterpret_cast<const uint2*>(vals + (int64_t)pos * 8);
-    return make_float4(bits16_to_float((uint16_t)(v.x & 0xffff), dtype), bits16_to_float((uint16_t)(v.x >> 16), dtype),
-                       bits16_to_float((uint16_t)(v.y & 0xffff), dtype), bits16_to_float((uint16_t)(v.y >> 16), dtype));
+    const float2 a = pair16_to_float2(v.x, dtype), b = pair16_to_float2(v.y, dtype);
+    return make_float4(a.x, a.y, b.x, b.y);
   }
   // the same scaled by `inv`, as two half2 registers
   __device__ __forceinline__ void load(uint32_t pos, uint32_t rel, float inv, uint32_t& lo, uint32_t& hi) const {
@@ -326,8 +332,8 @@ struct OutlSide {
       x0 = v.x; x1 = v.y; x2 = v.z; x3 = v.w;
     } else {
       const uint2 v = rel < (uint32_t)kStage ? stage[rel] : *reinterpret_cast<const uint2*>(vals + (int64_t)pos * 8);
-      x0 = bits16_to_float((uint16_t)(v.x & 0xffff), dtype); x1 = bits16_to_float((uint16_t)(v.x >> 16), dtype);
-      x2 = bits16_to_float((uint16_t)(v.y & 0xffff), dtype); x3 = bits16_to_float((uint16_t)(v.y >> 16), dtype);
+      const float2 a = pair16_to_float2(v.x, dtype), b = pair16_to_float2(v.y, dtype);
+      x0 = a.x; x1 = a.y; x2 = b.x; x3 = b.y;
     }
     lo = pack_half2(x0 * inv, x1 * inv);
     hi = pack_half2(x2 * inv, x3 * inv);

@@ -66,17 +66,16 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
   const size_t tbl_bytes = (size_t)p.table_rows * rstride;
   unsigned char* tblK = smem_raw;
   unsigned char* tblV = smem_raw + tbl_bytes;
-  float* qf32 = reinterpret_cast<float*>(smem_raw + 2 * tbl_bytes);                          // [8][d] (OUTL)
-  unsigned char* after_q = smem_raw + 2 * tbl_bytes + (OUTL ? (size_t)NHEADS * p.d * 4 : 0);
+  __half* qh16 = reinterpret_cast<__half*>(smem_raw + 2 * tbl_bytes);                         // [8][d] (OUTL)
+  unsigned char* after_q = smem_raw + 2 * tbl_bytes + (OUTL ? (size_t)NHEADS * p.d * 2 : 0);
   uint64_t* bars = reinterpret_cast<uint64_t*>(after_q);                                      // [NW][kStages]
   unsigned char* warp_area = after_q + ((NW * kStages * 8 + 15) & ~15);
-  constexpr int WARP_BYTES = kStages * SL::BYTES + (OUTL ? 16 * NHEADS * 4 : 0);
+  constexpr int WARP_BYTES = kStages * SL::BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = lane & 3, r = lane >> 2;
   const uint32_t lane_off = (uint32_t)(lane & ((1 << p.rep_log2) - 1)) * 8u;
   unsigned char* my_area = warp_area + (size_t)warp * WARP_BYTES;
-  float* dS = reinterpret_cast<float*>(my_area + kStages * SL::BYTES);                       // [16][8] (OUTL)
   const uint32_t bar0 = smem_u32(bars + warp * kStages);
   if (lane == 0) {
 #pragma unroll
@@ -111,8 +110,8 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
     if constexpr (OUTL) {
       for (int i = threadIdx.x; i < NHEADS * p.d; i += NW * 32) {
         const int g = i / p.d, x = i - g * p.d;
-        qf32[i] = g < p.G ? load_float(p.Q, (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t + (int64_t)(h * p.G + g) * p.qs_h + x,
-                                       p.q_dtype) : 0.f;
+        qh16[i] = __float2half_rn(g < p.G ? load_float(p.Q, (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t +
+                                                                 (int64_t)(h * p.G + g) * p.qs_h + x, p.q_dtype) : 0.f);
       }
     }
     __syncthreads();
@@ -274,7 +273,7 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
       // ---- outliers --------------------------------------------------------------------------------------
       bool anyK = false, anyV = false;
       OutlSide ok_, ov_;
-      uint32_t offk = 0, offv = 0, fv_tile = 0;
+      uint32_t offk = 0, offv = 0, fv_tile = 0, fk_tile = 0;
       if constexpr (OUTL) {
         const uint32_t* hdr = reinterpret_cast<const uint32_t*>(sb + SL::kHdr);
         offk = hdr[0]; offv = hdr[1];
@@ -285,7 +284,7 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         }
         anyK = __ballot_sync(0xffffffffu, fk != 0) != 0;
         anyV = __ballot_sync(0xffffffffu, fv != 0) != 0;
-        fv_tile = fv;
+        fv_tile = fv; fk_tile = fk;
         // staged entries start at the even entry index at or below the tile's first entry
         ok_.flags = gFlK; ok_.off = gOffK; ok_.dtype = p.K.out_dtype;
         ok_.vals = reinterpret_cast<const unsigned char*>(p.K.out_vals) + bh * p.K.out_cap * 4 * (p.K.out_dtype == HQMQ_F32 ? 4 : 2);
@@ -293,38 +292,6 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         ov_.flags = gFlV; ov_.off = gOffV; ov_.dtype = p.V.out_dtype;
         ov_.vals = reinterpret_cast<const unsigned char*>(p.V.out_vals) + bh * p.V.out_cap * 4 * (p.V.out_dtype == HQMQ_F32 ? 4 : 2);
         ov_.stage = reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayV);
-        if (anyK) {
-          // Lane (t = lane & 15, hh = lane >> 4) owns token t and heads 4*hh .. 4*hh+3.  The warp walks the
-          // distinct chunk positions flagged anywhere in the tile (hot channels make them few); for each,
-          // the query values are a broadcast read and every flagged token adds <q_g, x> in fp32.
-          const uint32_t pre16 = excl_scan16(__popc(fk), lane);
-          const uint32_t fl = __shfl_sync(0xffffffffu, fk, lane & 15);
-          const uint32_t pre = __shfl_sync(0xffffffffu, pre16, lane & 15);
-          const uint32_t skew = offk & 1u;
-          uint32_t any_c = fl;
-#pragma unroll
-          for (int o_ = 8; o_ > 0; o_ >>= 1) any_c |= __shfl_xor_sync(0xffffffffu, any_c, o_);
-          const float* qh = qf32 + (lane >> 4) * 4 * p.d;
-          float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-          while (any_c) {
-            const int c = __ffs(any_c) - 1;
-            any_c &= any_c - 1;
-            if ((fl >> c) & 1u) {
-              const uint32_t rel = pre + __popc(fl & ((1u << c) - 1u));
-              const float4 x = ok_.loadf(offk + rel, rel + skew <= (uint32_t)kPay ? rel + skew : 0xffffffffu);
-              const float4 q0 = *reinterpret_cast<const float4*>(qh + 4 * c);
-              const float4 q1 = *reinterpret_cast<const float4*>(qh + p.d + 4 * c);
-              const float4 q2 = *reinterpret_cast<const float4*>(qh + 2 * p.d + 4 * c);
-              const float4 q3 = *reinterpret_cast<const float4*>(qh + 3 * p.d + 4 * c);
-              acc0 = fmaf(q0.w, x.w, fmaf(q0.z, x.z, fmaf(q0.y, x.y, fmaf(q0.x, x.x, acc0))));
-              acc1 = fmaf(q1.w, x.w, fmaf(q1.z, x.z, fmaf(q1.y, x.y, fmaf(q1.x, x.x, acc1))));
-              acc2 = fmaf(q2.w, x.w, fmaf(q2.z, x.z, fmaf(q2.y, x.y, fmaf(q2.x, x.x, acc2))));
-              acc3 = fmaf(q3.w, x.w, fmaf(q3.z, x.z, fmaf(q3.y, x.y, fmaf(q3.x, x.x, acc3))));
-            }
-          }
-          *reinterpret_cast<float4*>(dS + (lane & 15) * NHEADS + (lane >> 4) * 4) = make_float4(acc0, acc1, acc2, acc3);
-          __syncwarp();
-        }
       }
 
       // ---- S^T = K Q^T ----------------------------------------------------------------------------------------
@@ -342,24 +309,65 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         });
         mma16816((ks & 1) ? s2 : s, a[0], a[1], a[2], a[3], qb[ks][0], qb[ks][1]);
       });
+      if constexpr (OUTL) {
+        if (anyK) {
+          // K outliers: their rows decode to 0 (radius code 0), so their scores are added by extra MMA
+          // k-slices.  The distinct chunk positions flagged anywhere in the tile are taken four at a time
+          // (lane group j <-> position c_j); A holds x * qmax / rs for the flagged (token, position) pairs,
+          // split into an fp16 head and an fp16 remainder so that the product is exact to ~2^-22, and B
+          // holds the query values of position c_j.  The result lands in the same accumulators and is
+          // scaled with them.
+          const uint32_t pre16 = excl_scan16(__popc(fk_tile), lane);
+          uint32_t any_c = __reduce_or_sync(0xffffffffu, fk_tile);
+          uint32_t fl[2], pre[2]; float kinv[2];
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            fl[nt] = __shfl_sync(0xffffffffu, fk_tile, nt * 8 + r);
+            pre[nt] = __shfl_sync(0xffffffffu, pre16, nt * 8 + r) + (offk & 1u);
+            kinv[nt] = fl[nt] ? __fdividef(p.qmaxf, ld.kscale(cur, nt)) : 0.f;
+          }
+          while (any_c) {
+            int cj = -1;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int c = any_c ? __ffs(any_c) - 1 : -1;
+              any_c &= any_c - 1;
+              if (q == j) cj = c;
+            }
+            uint32_t ahi[4] = {0u, 0u, 0u, 0u}, alo[4] = {0u, 0u, 0u, 0u}, b0 = 0u, b1 = 0u;
+            if (cj >= 0) {
+              const uint2 qv = *reinterpret_cast<const uint2*>(qh16 + r * p.d + 4 * cj);
+              b0 = qv.x; b1 = qv.y;
+#pragma unroll
+              for (int nt = 0; nt < 2; ++nt) {
+                if ((fl[nt] >> cj) & 1u) {
+                  const uint32_t rel = pre[nt] + __popc(fl[nt] & ((1u << cj) - 1u));
+                  const float4 x = ok_.loadf(offk - (offk & 1u) + rel, rel <= (uint32_t)kPay ? rel : 0xffffffffu);
+                  const float v0 = x.x * kinv[nt], v1 = x.y * kinv[nt], v2 = x.z * kinv[nt], v3 = x.w * kinv[nt];
+                  const __half2 h01 = __floats2half2_rn(v0, v1), h23 = __floats2half2_rn(v2, v3);
+                  const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                  ahi[nt] = *reinterpret_cast<const uint32_t*>(&h01);
+                  ahi[2 + nt] = *reinterpret_cast<const uint32_t*>(&h23);
+                  alo[nt] = pack_half2(v0 - f01.x, v1 - f01.y);
+                  alo[2 + nt] = pack_half2(v2 - f23.x, v3 - f23.y);
+                }
+              }
+            }
+            mma16816(s, ahi[0], ahi[1], ahi[2], ahi[3], b0, b1);
+            mma16816(s2, alo[0], alo[1], alo[2], alo[3], b0, b1);
+          }
+        }
+      }
 #pragma unroll
       for (int x = 0; x < 4; ++x) s[x] += s2[x];
 
       // ---- scale, outlier scores, mask, online softmax -----------------------------------------------------
-      float d0[2] = {0.f, 0.f}, d1[2] = {0.f, 0.f};
-      if constexpr (OUTL) {
-        if (anyK) {
-          const float2 u0 = *reinterpret_cast<const float2*>(dS + r * NHEADS + 2 * j);
-          const float2 u1 = *reinterpret_cast<const float2*>(dS + (r + 8) * NHEADS + 2 * j);
-          d0[0] = u0.x * p.qscale; d0[1] = u0.y * p.qscale; d1[0] = u1.x * p.qscale; d1[1] = u1.y * p.qscale;
-        }
-      }
       bool grew = false;
       float mx[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        s[e] = okt[0] ? fmaf(s[e], ksc[0], d0[e]) : -INFINITY;
-        s[2 + e] = okt[1] ? fmaf(s[2 + e], ksc[1], d1[e]) : -INFINITY;
+        s[e] = okt[0] ? s[e] * ksc[0] : -INFINITY;
+        s[2 + e] = okt[1] ? s[2 + e] * ksc[1] : -INFINITY;
         float m = fmaxf(s[e], s[2 + e]);
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
@@ -400,7 +408,7 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         float vinv[4] = {0.f, 0.f, 0.f, 0.f};
         if constexpr (PATCH) {
           const uint32_t ex = excl_scan16(__popc(fv_tile), lane);
-          const float i0 = p.qmaxf / ld.vscale(cur, 0), i1 = p.qmaxf / ld.vscale(cur, 1);
+          const float i0 = __fdividef(p.qmaxf, ld.vscale(cur, 0)), i1 = __fdividef(p.qmaxf, ld.vscale(cur, 1));
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int tl = 2 * j + (i & 1) + (i >> 1) * 8;

@@ -140,12 +140,20 @@ __device__ __forceinline__ int search_lut(const float4* __restrict__ joint, cons
   const int cell = (cx * kLutN + cy) * kLutN + cz;
   const uint32_t beg = off[cell], end = off[cell + 1];
   if (beg == end) return search_exhaustive(qs, S, u0, u1, u2, u3, best_s);
+  // lists are padded to a multiple of four entries (the last one repeated), four evaluated per step
   float best = -2.f; int bk = 0;
-  for (uint32_t e = beg; e < end; ++e) {
-    const int k = cand[e];
-    const float4 c = joint[k];
-    const float sim = fmaf(v3, c.w, fmaf(v2, c.z, fmaf(v1, c.y, v0 * c.x)));
-    if (sim > best) { best = sim; bk = k; }
+  for (uint32_t e = beg; e < end; e += 4) {
+    const uint2 kk = *reinterpret_cast<const uint2*>(cand + e);
+    const int k0 = kk.x & 0xffff, k1 = kk.x >> 16, k2 = kk.y & 0xffff, k3 = kk.y >> 16;
+    const float4 c0 = joint[k0], c1 = joint[k1], c2 = joint[k2], c3 = joint[k3];
+    const float s0 = fmaf(v3, c0.w, fmaf(v2, c0.z, fmaf(v1, c0.y, v0 * c0.x)));
+    const float s1 = fmaf(v3, c1.w, fmaf(v2, c1.z, fmaf(v1, c1.y, v0 * c1.x)));
+    const float s2 = fmaf(v3, c2.w, fmaf(v2, c2.z, fmaf(v1, c2.y, v0 * c2.x)));
+    const float s3 = fmaf(v3, c3.w, fmaf(v2, c3.z, fmaf(v1, c3.y, v0 * c3.x)));
+    if (s0 > best) { best = s0; bk = k0; }
+    if (s1 > best) { best = s1; bk = k1; }
+    if (s2 > best) { best = s2; bk = k2; }
+    if (s3 > best) { best = s3; bk = k3; }
   }
   const int pf = (int)(((float)bk + 0.5f) * inv_S);
   best_s = bk - pf * S;
@@ -194,12 +202,22 @@ encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restric
   const int tok_per_iter = kEncWarps * g.tpw;
   const int t_block0 = blockIdx.x * tok_per_iter * kEncIters;
 
+  // the chunk of the next iteration is loaded before the current one is searched
+  float vn[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const int t = t_block0 + warp * g.tpw + sub;
+    if (t < g.T_new && c < g.n) load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, vn);
+  }
   for (int it = 0; it < kEncIters; ++it) {
     const int t = t_block0 + it * tok_per_iter + warp * g.tpw + sub;
     const bool tok_ok = t < g.T_new;
     const bool active = tok_ok && c < g.n;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (active) load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
+    float v[4] = {vn[0], vn[1], vn[2], vn[3]};
+    vn[0] = vn[1] = vn[2] = vn[3] = 0.f;
+    if (it + 1 < kEncIters) {
+      const int t2 = t + tok_per_iter;
+      if (t2 < g.T_new && c < g.n) load_chunk(x, b * g.xs_b + h * g.xs_h + t2 * g.xs_t + 4 * c, g.x_dtype, vn);
+    }
     const float nrm = chunk_norm(v);
     const float radius = fmaxf(nrm, 1e-8f);
     float rmax = active ? radius : 0.f;
@@ -252,26 +270,42 @@ encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restric
 __global__ void select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level, uint64_t N,
                               float C, float* __restrict__ med_out) {
   const int h = blockIdx.x;
-  if (threadIdx.x != 0) return;
+  const int lane = threadIdx.x;       // launched with one warp
   uint32_t* st = sel + h * 8;
   const uint64_t lo = (N - 1) / 2, hi = N / 2;
   uint32_t* hl = hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
   const int shift = level == 0 ? 21 : level == 1 ? 10 : 0;
   const int bins = level == 2 ? 1024 : kHistBins;
+  const int per = bins / 32;          // bins per lane
   for (int q = 0; q < 2; ++q) {
-    uint64_t rank = level == 0 ? (q == 0 ? lo : hi) : st[2 * q + 1];
-    uint32_t prefix = level == 0 ? 0u : st[2 * q];
+    const uint64_t rank = level == 0 ? (q == 0 ? lo : hi) : st[2 * q + 1];
+    const uint32_t prefix = level == 0 ? 0u : st[2 * q];
     // level 0 has one histogram (slot 0); deeper levels have one per query
     const uint32_t* hq = hl + (level == 0 ? 0 : q * kHistBins);
-    uint64_t acc = 0; int bin = bins - 1;
-    for (int i = 0; i < bins; ++i) {
-      uint32_t cnt = hq[i];
-      if (acc + cnt > rank) { bin = i; break; }
-      acc += cnt;
+    uint64_t mine = 0;
+    for (int i = 0; i < per; ++i) mine += hq[lane * per + i];
+    uint64_t incl = mine;
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint64_t y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
     }
-    st[2 * q] = prefix | ((uint32_t)bin << shift);
-    st[2 * q + 1] = (uint32_t)(rank - acc);
+    const uint64_t before = incl - mine;
+    // the lane whose segment holds the rank (the last lane takes an out-of-range rank, as the serial scan did)
+    const bool owner = (rank >= before && rank < incl) || (lane == 31 && rank >= incl);
+    __syncwarp();
+    if (owner) {
+      uint64_t acc = before; int bin = bins - 1;
+      for (int i = 0; i < per; ++i) {
+        const uint32_t cnt = hq[lane * per + i];
+        if (acc + cnt > rank) { bin = lane * per + i; break; }
+        acc += cnt;
+      }
+      st[2 * q] = prefix | ((uint32_t)bin << shift);
+      st[2 * q + 1] = (uint32_t)(rank - acc);
+    }
+    __syncwarp();
   }
+  if (lane != 0) return;
   if (level == 2) {
     const float a = __uint_as_float(st[0]), b = __uint_as_float(st[2]);
     float med = (N & 1) ? a : __fsub_rn(b, __fmul_rn(__fsub_rn(b, a), 0.5f));
@@ -300,14 +334,26 @@ hist_kernel(EncGeom g, const void* __restrict__ x, uint32_t* __restrict__ hist, 
   const int64_t total = (int64_t)g.T_new * g.n;
   const int64_t per_block = (total + gridDim.x - 1) / gridDim.x;
   const int64_t i0 = blockIdx.x * per_block, i1 = min(total, i0 + per_block);
-  for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
-    const int t = (int)(i / g.n), c = (int)(i % g.n);
-    float v[4];
-    load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
-    const uint32_t key = __float_as_uint(chunk_norm(v));
-    const uint32_t dig = (key >> ds) & dm;
-    if ((key >> hs) == (p0 >> hs)) atomicAdd(&sh[0][dig], 1u);
-    if ((key >> hs) == (p1 >> hs)) atomicAdd(&sh[1][dig], 1u);
+  // four independent loads in flight per thread
+  for (int64_t i = i0 + threadIdx.x; i < i1; i += 4 * blockDim.x) {
+    float v[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t iu = i + (int64_t)u * blockDim.x;
+      if (iu < i1) {
+        const int t = (int)(iu / g.n), c = (int)(iu % g.n);
+        load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (i + (int64_t)u * blockDim.x < i1) {
+        const uint32_t key = __float_as_uint(chunk_norm(v[u]));
+        const uint32_t dig = (key >> ds) & dm;
+        if ((key >> hs) == (p0 >> hs)) atomicAdd(&sh[0][dig], 1u);
+        if ((key >> hs) == (p1 >> hs)) atomicAdd(&sh[1][dig], 1u);
+      }
+    }
   }
   __syncthreads();
   uint32_t* gh = hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
@@ -327,11 +373,21 @@ flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / g.npl, c = lane % g.npl;
   const int tok_per_iter = (blockDim.x >> 5) * g.tpw;
-  for (int tb = blockIdx.x * tok_per_iter; tb < g.T_new; tb += gridDim.x * tok_per_iter) {
+  for (int tb4 = blockIdx.x * tok_per_iter * 4; tb4 < g.T_new; tb4 += gridDim.x * tok_per_iter * 4) {
+   float v4[4][4];
+#pragma unroll
+   for (int u = 0; u < 4; ++u) {   // four independent loads in flight per thread
+     const int t = tb4 + u * tok_per_iter + warp * g.tpw + sub;
+     v4[u][0] = v4[u][1] = v4[u][2] = v4[u][3] = 0.f;
+     if (t < g.T_new && c < g.n) load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v4[u]);
+   }
+#pragma unroll
+   for (int u = 0; u < 4; ++u) {
+    const int tb = tb4 + u * tok_per_iter;
+    if (tb >= g.T_new) break;
     const int t = tb + warp * g.tpw + sub;
     const bool active = t < g.T_new && c < g.n;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (active) load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
+    const float* v = v4[u];
     const bool f = active && chunk_norm(v) > thr;
     const uint32_t bal = __ballot_sync(0xffffffffu, f);
     if (f) {
@@ -353,6 +409,7 @@ flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start
       dst.flags[(int64_t)bh * dst.T_cap + ta] = word;
       if (word) atomicAdd(&blk[(int64_t)bh * (nblk + 1) + (ta / HQMQ_OUT_BLOCK - blk0)], (uint32_t)__popc(word));
     }
+   }
   }
 }
 
@@ -456,18 +513,42 @@ lut_cells_kernel(const float* __restrict__ joint_all, int S, uint16_t* __restric
     }
   }
   __syncthreads();
+  __shared__ float4 s_cw[kLutMaxList];
+  __shared__ unsigned char s_drop[kLutMaxList];
+  int n = s_n;
+  if (n > kLutMaxList) n = 0;         // too long: this cell falls back to the exhaustive search
   if (threadIdx.x == 0) {
-    int n = s_n;
-    if (n > kLutMaxList) n = 0;       // too long: this cell falls back to the exhaustive search
     for (int i = 1; i < n; ++i) {     // ascending order makes the table reproducible
       const uint16_t v = s_list[i];
       int q = i - 1;
       while (q >= 0 && s_list[q] > v) { s_list[q + 1] = s_list[q]; --q; }
       s_list[q + 1] = v;
     }
-    cnt[(int64_t)h * kLutCells + cell] = (uint32_t)n;
+  }
+  __syncthreads();
+  if (threadIdx.x < n) s_cw[threadIdx.x] = joint[s_list[threadIdx.x]];
+  __syncthreads();
+  // second filter: drop a codeword that loses to some OTHER listed codeword over the whole box
+  if (threadIdx.x < n) {
+    const float4 ci = s_cw[threadIdx.x];
+    bool drop = false;
+    for (int q = 0; q < n && !drop; ++q) {
+      if (q == threadIdx.x) continue;
+      const float4 cq = s_cw[q];
+      const float d0 = ci.x - cq.x, d1 = ci.y - cq.y, d2 = ci.z - cq.z, d3 = ci.w - cq.w;
+      const float ub = d0 + d1 * w1 + d2 * w2 + d3 * w3 + hh * (fabsf(d1) + fabsf(d2) + fabsf(d3));
+      drop = ub < -kLutMargin;
+    }
+    s_drop[threadIdx.x] = drop ? 1 : 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
     uint16_t* dst = tmp + ((int64_t)h * kLutCells + cell) * kLutMaxList;
-    for (int i = 0; i < n; ++i) dst[i] = s_list[i];
+    int m = 0;
+    for (int i = 0; i < n; ++i)
+      if (!s_drop[i]) dst[m++] = s_list[i];
+    while (m & 3) { dst[m] = dst[m - 1]; ++m; }   // pad to a multiple of four (n <= 64 keeps m <= 64)
+    cnt[(int64_t)h * kLutCells + cell] = (uint32_t)m;
   }
 }
 

@@ -18,9 +18,9 @@ namespace hqmq {
 
 namespace {
 
-constexpr int kEncThreads = 256;
+constexpr int kEncThreads = 512;
 constexpr int kEncWarps = kEncThreads / 32;
-constexpr int kEncIters = 16;     // token groups per block
+constexpr int kEncIters = 8;      // token groups per block
 constexpr int kHistBins = 2048;   // 11-bit digits: bits [31:21], [20:10], then 10 bits [9:0]
 constexpr int kMaxRowWords = 20;
 
@@ -230,8 +230,10 @@ encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restric
     for (int w = lane; w < g.tpw * kMaxRowWords; w += 32) rows[warp * g.tpw * kMaxRowWords + w] = 0;
     __syncwarp();
     if (active) {
-      const float u0 = __fdiv_rn(v[0], radius), u1 = __fdiv_rn(v[1], radius), u2 = __fdiv_rn(v[2], radius),
-                  u3 = __fdiv_rn(v[3], radius);
+      // the nearest codeword does not depend on the length of the chunk: search with a cheaply
+      // normalised copy (keeps the values in range) instead of the reference's exact x / radius
+      const float inv_r = __frcp_rn(radius);
+      const float u0 = v[0] * inv_r, u1 = v[1] * inv_r, u2 = v[2] * inv_r, u3 = v[3] * inv_r;
       int s, p;
       if (LUT && use_lut) p = search_lut(sjoint, soff, scand, qs, g.S, inv_S, u0, u1, u2, u3, mul, s);
       else p = search_exhaustive(qs, g.S, u0, u1, u2, u3, s);
@@ -341,8 +343,10 @@ hist_kernel(EncGeom g, const void* __restrict__ x, uint32_t* __restrict__ hist, 
     for (int u = 0; u < 4; ++u) {
       const int64_t iu = i + (int64_t)u * blockDim.x;
       if (iu < i1) {
-        const int t = (int)(iu / g.n), c = (int)(iu % g.n);
-        load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v[u]);
+        int64_t off = b * g.xs_b + h * g.xs_h;
+        if (g.xs_t == 4 * g.n) off += iu * 4;     // tokens are contiguous: the (t, chunk) grid is flat
+        else { const uint32_t t = (uint32_t)iu / (uint32_t)g.n, c = (uint32_t)iu - t * (uint32_t)g.n; off += (int64_t)t * g.xs_t + 4 * c; }
+        load_chunk(x, off, g.x_dtype, v[u]);
       }
     }
 #pragma unroll
@@ -753,9 +757,12 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
 
   const uint64_t N = (uint64_t)d.B * a->T_new * d.n_chunks;
   const int64_t per_bh = (int64_t)a->T_new * d.n_chunks;
-  int hb = (int)((per_bh + 256 * 32 - 1) / (256 * 32));
+  // about 16 resident CTAs per SM in total; each CTA amortises zeroing and flushing its private histograms
+  const int bh_count = d.B * d.H;
+  int hb = (148 * 16 + bh_count - 1) / bh_count;
+  const int hb_max = (int)((per_bh + 256 * 16 - 1) / (256 * 16));
+  if (hb > hb_max) hb = hb_max;
   if (hb < 1) hb = 1;
-  if (hb > 1024) hb = 1024;
   uint32_t* hist = ws + wp.hist;
   uint32_t* sel = ws + wp.sel;
   select_kernel<<<d.H, 32, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr);
@@ -766,8 +773,10 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   HQMQ_LAUNCH_CHECK();
 
   const int tok_per_fblock = 8 * g.tpw;
-  int fb = (a->T_new + tok_per_fblock - 1) / tok_per_fblock;
-  if (fb > 4096) fb = 4096;
+  int fb = (a->T_new + 4 * tok_per_fblock - 1) / (4 * tok_per_fblock);
+  const int fb_cap = (148 * 32 + bh_count - 1) / bh_count;
+  if (fb > fb_cap) fb = fb_cap;
+  if (fb < 1) fb = 1;
   flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel, ws + wp.blk, wp.blk0, wp.nblk);
   scan_kernel<<<(d.B * d.H + 63) / 64, 64, 0, st>>>(d, a->t_start, a->T_new, ws + wp.blk, wp.blk0, wp.nblk, ws + wp.status);
   payload_kernel<<<dim3((a->T_new + 255) / 256, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start);

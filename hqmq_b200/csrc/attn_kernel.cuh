@@ -205,7 +205,10 @@ struct FastLoader {
       idx = (word >> s) & ((1u << IB) - 1u);
       uint32_t bits = ((word >> IB) & 0x000f000fu) | 0x64006400u;
       const __half2 pair = __hsub2(*reinterpret_cast<__half2*>(&bits), __float2half2_rn(1024.f));
-      rr = s == 0 ? __low2half2(pair) : __high2half2(pair);
+      // broadcast one half to both lanes of the register with a single byte permute
+      const uint32_t pu = *reinterpret_cast<const uint32_t*>(&pair);
+      const uint32_t bu = __byte_perm(pu, pu, s == 0 ? 0x1010 : 0x3232);
+      rr = *reinterpret_cast<const __half2*>(&bu);
     } else {
       uint32_t v = (s + CB > 32) ? __funnelshift_r(w[a], w[a + 1], s) : (w[a] >> s);
       idx = v & ((1u << IB) - 1u);

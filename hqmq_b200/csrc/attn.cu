@@ -7,7 +7,7 @@ namespace attn {
 
 const void* fast_kernel(int n_chunks, int ib, int rb, bool outl);
 size_t fast_warp_bytes(int n_chunks, int ib, int rb, bool outl);
-constexpr int kFastStages = 3;
+constexpr int kFastStages = 2;
 
 template <int N, bool OUTL, bool WIDE>
 __global__ void __launch_bounds__(kSlowWarps * 32) attn_slow_kernel(const AttnParams p) {
@@ -178,9 +178,11 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
             (size_t)pl.nw * fast_warp_bytes(n, pl.ib, a->K.radius_bits, outl);
   // The big-CTA kernels own a whole SM: replicate the tables (interleaved) as far as shared memory
   // allows, which spreads the random codeword gathers over more banks.
+  // bytes of both tables without replication (the staged kernels keep sign-folded, half-size tables)
+  const size_t tbl_unit = (fast && !outl) ? (size_t)pl.table_rows * 8 : (size_t)pl.table_rows * 16;
   if (fast)
-    while (pl.rep_log2 < 4 && ((size_t)pl.table_rows * 16 << (pl.rep_log2 + 1)) + extra <= 220 * 1024) ++pl.rep_log2;
-  pl.smem = ((size_t)pl.table_rows * 16 << pl.rep_log2) + extra;
+    while (pl.rep_log2 < 4 && (tbl_unit << (pl.rep_log2 + 1)) + extra <= 224 * 1024) ++pl.rep_log2;
+  pl.smem = (tbl_unit << pl.rep_log2) + extra;
   if (pl.smem > 226 * 1024) {
     if (!fast) return HQMQ_ERR_UNSUPPORTED;
     // the staged kernel does not fit next to this codebook: use the generic one

@@ -125,7 +125,7 @@ constexpr int span_words(int L, int lanes) {
 
 // Native layout, compile-time field layout (IB index bits + RB radius bits): rows are read as raw
 // words and fields are cut in registers.
-template <int N, int IB, int RB>
+template <int N, int IB, int RB, bool FOLD>
 struct FastLoader {
   static constexpr int CB = IB + RB;
   static constexpr int NKS = Geo<N>::NKS, NVG = Geo<N>::NVG;
@@ -195,24 +195,37 @@ struct FastLoader {
       raw.rsv[nt] = vrs[t];
     }
   }
-  // codeword index of field F and its radius as half2 (r, r)
+  // Field F -> codeword table index and radius as half2 (r, r).
+  // FOLD: the table is SIGN-FOLDED.  The lowest bit of a native index is the sign of the axis unit u
+  // (u = 2*axis + sign) and the codeword of -u is exactly minus the codeword of +u, so the table keeps only
+  // the even entries (half the shared memory, which buys twice the replication against bank conflicts) and
+  // the sign goes into the radius, at the price of a few more instructions per gather.
   template <int F>
   static __device__ __forceinline__ void cut(const uint32_t* w, uint32_t& idx, __half2& rr) {
     constexpr int bit = F * CB, a = bit >> 5, s = bit & 31;
     if constexpr (CB == 16) {
       // two fields per word: both radii come out of one subtraction
       const uint32_t word = w[a];
-      idx = (word >> s) & ((1u << IB) - 1u);
+      idx = FOLD ? (word >> (s + 1)) & ((1u << (IB - 1)) - 1u) : (word >> s) & ((1u << IB) - 1u);
       uint32_t bits = ((word >> IB) & 0x000f000fu) | 0x64006400u;
       const __half2 pair = __hsub2(*reinterpret_cast<__half2*>(&bits), __float2half2_rn(1024.f));
+      uint32_t pu = *reinterpret_cast<const uint32_t*>(&pair);
+      // sign bits of both fields (bits 0 and 16 of the word) into the sign bits of the two halves
+      if constexpr (FOLD) pu ^= (word << 15) & 0x80008000u;
       // broadcast one half to both lanes of the register with a single byte permute
-      const uint32_t pu = *reinterpret_cast<const uint32_t*>(&pair);
       const uint32_t bu = __byte_perm(pu, pu, s == 0 ? 0x1010 : 0x3232);
       rr = *reinterpret_cast<const __half2*>(&bu);
     } else {
       uint32_t v = (s + CB > 32) ? __funnelshift_r(w[a], w[a + 1], s) : (w[a] >> s);
-      idx = v & ((1u << IB) - 1u);
-      rr = radius_half2((v >> IB) & ((1u << RB) - 1u));
+      const __half2 r2 = radius_half2((v >> IB) & ((1u << RB) - 1u));
+      if constexpr (FOLD) {
+        idx = (v & ((1u << IB) - 1u)) >> 1;
+        const uint32_t ru = *reinterpret_cast<const uint32_t*>(&r2) ^ ((0u - (v & 1u)) & 0x80008000u);
+        rr = *reinterpret_cast<const __half2*>(&ru);
+      } else {
+        idx = v & ((1u << IB) - 1u);
+        rr = r2;
+      }
     }
   }
   template <int NT, int KS> __device__ __forceinline__ void kfield(const Raw& raw, uint32_t& idx, __half2& rr) const {

@@ -13,7 +13,7 @@
 namespace hqmq {
 namespace attn {
 
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr int kPay = 64;                 // outlier entries staged per tile and tensor (+2 alignment slack)
 constexpr uint32_t kWaitLimit = 1u << 24;
 
@@ -56,14 +56,16 @@ struct StageLayout {
 template <int N, int IB, int RB, int NW, bool OUTL>
 __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32_t* status) {
   using G_ = Geo<N>;
-  using FL = FastLoader<N, IB, RB>;
+  constexpr bool FOLD = !OUTL;   // the outlier kernel is issue-bound: it keeps the full table and the shorter gather
+  using FL = FastLoader<N, IB, RB, FOLD>;
   using SL = StageLayout<N, IB, RB, OUTL>;
   constexpr int NKS = G_::NKS, NVG = G_::NVG, NOT = 2 * G_::NVG;
   constexpr int NHEADS = 8;
   constexpr int ROW = SL::ROW;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const uint32_t rstride = 8u << p.rep_log2;
-  const size_t tbl_bytes = (size_t)p.table_rows * rstride;
+  const int rows_f = FOLD ? p.table_rows >> 1 : p.table_rows;   // sign-folded tables keep the even native indices only
+  const size_t tbl_bytes = (size_t)rows_f * rstride;
   unsigned char* tblK = smem_raw;
   unsigned char* tblV = smem_raw + tbl_bytes;
   __half* qh16 = reinterpret_cast<__half*>(smem_raw + 2 * tbl_bytes);                         // [8][d] (OUTL)
@@ -98,9 +100,9 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
     if (h != cur_h || OUTL) __syncthreads();
     if (h != cur_h) {
       const int reps = 1 << p.rep_log2;
-      for (int i = threadIdx.x; i < p.table_rows; i += NW * 32) {
-        const uint2 ek = (reinterpret_cast<const uint2*>(p.tblK) + (int64_t)h * p.table_rows)[i];
-        const uint2 ev = (reinterpret_cast<const uint2*>(p.tblV) + (int64_t)h * p.table_rows)[i];
+      for (int i = threadIdx.x; i < rows_f; i += NW * 32) {
+        const uint2 ek = (reinterpret_cast<const uint2*>(p.tblK) + (int64_t)h * p.table_rows)[FOLD ? 2 * i : i];
+        const uint2 ev = (reinterpret_cast<const uint2*>(p.tblV) + (int64_t)h * p.table_rows)[FOLD ? 2 * i : i];
         uint2* dk = reinterpret_cast<uint2*>(tblK + (size_t)i * rstride);
         uint2* dv = reinterpret_cast<uint2*>(tblV + (size_t)i * rstride);
         for (int q = 0; q < reps; ++q) { dk[q] = ek; dv[q] = ev; }
@@ -161,6 +163,11 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
     const unsigned char* gPayK = gFlK ? reinterpret_cast<const unsigned char*>(p.K.out_vals) + bh * p.K.out_cap * 8 : nullptr;
     const unsigned char* gPayV = gFlV ? reinterpret_cast<const unsigned char*>(p.V.out_vals) + bh * p.V.out_cap * 8 : nullptr;
     const bool stageK = gFlK && p.K.out_dtype != HQMQ_F32, stageV = gFlV && p.V.out_dtype != HQMQ_F32;
+    OutlSide ok_seg, ov_seg;   // side-buffer descriptors of this (b, h); only the stage pointer changes per tile
+    ok_seg.flags = gFlK; ok_seg.off = gOffK; ok_seg.dtype = p.K.out_dtype; ok_seg.stage = nullptr;
+    ok_seg.vals = reinterpret_cast<const unsigned char*>(p.K.out_vals) + bh * p.K.out_cap * 4 * (p.K.out_dtype == HQMQ_F32 ? 4 : 2);
+    ov_seg.flags = gFlV; ov_seg.off = gOffV; ov_seg.dtype = p.V.out_dtype; ov_seg.stage = nullptr;
+    ov_seg.vals = reinterpret_cast<const unsigned char*>(p.V.out_vals) + bh * p.V.out_cap * 4 * (p.V.out_dtype == HQMQ_F32 ? 4 : 2);
     uint32_t nk0 = 0, nk1 = 0, nv0 = 0, nv1 = 0;   // payload ranges of the tile to be issued next
     auto load_offsets = [&](int tl) {
       nk0 = nk1 = nv0 = nv1 = 0;
@@ -286,11 +293,8 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         anyV = __ballot_sync(0xffffffffu, fv != 0) != 0;
         fv_tile = fv; fk_tile = fk;
         // staged entries start at the even entry index at or below the tile's first entry
-        ok_.flags = gFlK; ok_.off = gOffK; ok_.dtype = p.K.out_dtype;
-        ok_.vals = reinterpret_cast<const unsigned char*>(p.K.out_vals) + bh * p.K.out_cap * 4 * (p.K.out_dtype == HQMQ_F32 ? 4 : 2);
+        ok_ = ok_seg; ov_ = ov_seg;
         ok_.stage = reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayK);
-        ov_.flags = gFlV; ov_.off = gOffV; ov_.dtype = p.V.out_dtype;
-        ov_.vals = reinterpret_cast<const unsigned char*>(p.V.out_vals) + bh * p.V.out_cap * 4 * (p.V.out_dtype == HQMQ_F32 ? 4 : 2);
         ov_.stage = reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayV);
       }
 

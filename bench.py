@@ -208,6 +208,8 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size")
     ap.add_argument("--context", type=int, default=0, help="override the workload's context length")
     ap.add_argument("--no-med3x", action="store_true", help="encode without outlier extraction")
+    ap.add_argument("--no-ofrag", action="store_true",
+                    help="K cache without fragment records (attention merges K outliers from flags / side buffer)")
     ap.add_argument("--seq-split", action="store_true",
                     help="with N > 1: split ONE cache by sequence across the ranks (flash-decoding over NVLink: "
                          "partials + all_gather + merge) instead of giving every rank its own batch shard")
@@ -262,7 +264,8 @@ def main():
         # a launch configuration costs milliseconds), the median of the other three is reported
         reps = []
         for rep in range(4):
-            pk = inner.new_cache(B, T, d, dev, scale_dtype=dtype, with_outliers=Cm is not None, out_dtype=dtype, out_cap=cap)
+            pk = inner.new_cache(B, T, d, dev, scale_dtype=dtype, with_outliers=Cm is not None, out_dtype=dtype, out_cap=cap,
+                                 ofrag=kv == 0 and Cm is not None and not args.no_ofrag)
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -385,9 +388,10 @@ def main():
         "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": step_s * 1e3, "us_per_step": step_s * 1e6, "higher_is_better": True, "scaling": "strong" if seq_mode else "weak",
         "vs_baseline": None, "dtype": "f16 mma / f32 accumulate", "data": "synthetic",
-        "config": {"workload": args.workload, "desc": w["desc"], "batch_per_gpu": B, "global_batch": B * world,
+        "config": {"workload": args.workload, "desc": w["desc"], "batch_per_gpu": B, "global_batch": B if seq_mode else B * world,
                    "q_heads": Hq, "kv_heads": Hkv, "d_head": d, "context": T, "S": S, "radius_bits": br,
                    "median_mult": Cm, "outlier_fraction_K_V": outl_frac,
+                   "k_fragment_records": bool(Kp.with_ofrag),
                    "sharding": f"sequence x{world} (context {T_full} total, partials all_gather + merge)" if seq_mode else f"batch x{world}",
                    "l2": "compressed cache per GPU exceeds L2 (inputs larger than L2, no flush needed)"
                    if algo_bytes > 2 * 126e6 else "cache smaller than 2x L2: numbers include L2 hits"},

@@ -14,7 +14,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("HQMQ_B200_LIB") or os.path.join(HERE, "libhqmq_b200.so")
 
 F32, F16, BF16, I32, I16, I8, U8, I64 = range(8)
+ABI_VERSION = 2
 OUT_BLOCK = 16
+OFRAG_BYTES = 528
 T_ALIGN = 64
 ATTN_STATIC_SCRATCH_BYTES = 16 << 20
 
@@ -44,9 +46,9 @@ class Packed(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32), ("B", C.c_int32), ("H", C.c_int32), ("T_cap", C.c_int32),
         ("n_chunks", C.c_int32), ("S", C.c_int32), ("radius_bits", C.c_int32), ("row_bytes", C.c_int32),
-        ("scale_dtype", C.c_int32), ("out_dtype", C.c_int32), ("out_cap", C.c_int32), ("reserved", C.c_int32),
+        ("scale_dtype", C.c_int32), ("out_dtype", C.c_int32), ("out_cap", C.c_int32), ("ofrag_cap", C.c_int32),
         ("codes", C.c_void_p), ("rs", C.c_void_p), ("flags", C.c_void_p), ("out_vals", C.c_void_p),
-        ("out_off", C.c_void_p), ("out_count", C.c_void_p),
+        ("out_off", C.c_void_p), ("out_count", C.c_void_p), ("ofrag", C.c_void_p), ("ofrag_off", C.c_void_p),
     ]
 
 
@@ -131,7 +133,7 @@ def lib():
     L.hqmq_attn_decode.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     L.hqmq_attn_decode_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
     L.hqmq_combine_partials.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
-    if L.hqmq_abi_version() != 1:
+    if L.hqmq_abi_version() != ABI_VERSION:
         raise HqmqError("hqmq_b200: library ABI version mismatch; rebuild with `python -m hqmq_b200.build --force`")
     _lib = L
     return L

@@ -7,7 +7,8 @@ namespace attn {
 
 const void* fast_kernel(int n_chunks, int ib, int rb, bool outl);
 size_t fast_warp_bytes(int n_chunks, int ib, int rb, bool outl);
-constexpr int kFastStages = 2;
+constexpr int kFastStages = 2;   // must equal kStages of the staged kernels
+constexpr int kFastQPad = 8;     // must equal kQPad of the staged kernels
 
 template <int N, bool OUTL, bool WIDE>
 __global__ void __launch_bounds__(kSlowWarps * 32) attn_slow_kernel(const AttnParams p) {
@@ -174,7 +175,7 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   const int nheads = G > 8 ? 16 : 8;
   size_t extra = outl ? (size_t)nheads * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * nheads * 4) : 0;
   if (fast)
-    extra = (outl ? (size_t)8 * a->d * 2 : 0) + (((size_t)pl.nw * kFastStages * 8 + 15) & ~(size_t)15) +
+    extra = (outl ? (size_t)8 * (a->d + kFastQPad) * 2 : 0) + (((size_t)pl.nw * kFastStages * 8 + 15) & ~(size_t)15) +
             (size_t)pl.nw * fast_warp_bytes(n, pl.ib, a->K.radius_bits, outl);
   // The big-CTA kernels own a whole SM: replicate the tables (interleaved) as far as shared memory
   // allows, which spreads the random codeword gathers over more banks.

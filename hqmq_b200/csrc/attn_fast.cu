@@ -15,7 +15,7 @@ __global__ void __launch_bounds__(OUTL ? kFastWarpsOutl * 32 : kFastWarps * 32, 
 // Shared memory of one warp's staging ring (must match StageLayout).
 size_t fast_warp_bytes(int n_chunks, int ib, int rb, bool outl) {
   const size_t row = (size_t)n_chunks * (ib + rb) / 8;
-  const size_t stage = 2 * kTile * row + 64 + (outl ? 128 + 2 * (kPay + 2) * 8 + 16 : 0);
+  const size_t stage = 2 * kTile * row + 64 + (outl ? 128 + kSideK + (kPay + 2) * 8 + 16 : 0);
   return kStages * stage;
 }
 

@@ -16,6 +16,10 @@ namespace attn {
 constexpr int kStages = 2;
 constexpr int kPay = 64;                 // outlier entries staged per tile and tensor (+2 alignment slack)
 constexpr uint32_t kWaitLimit = 1u << 24;
+// bytes of a stage that hold either the K payload slice or the tile's fragment records
+constexpr int kSideK = (kPay + 2) * 8 > HQMQ_OFRAG_MAX_PER_TILE * HQMQ_OFRAG_BYTES ? (kPay + 2) * 8
+                                                                                  : HQMQ_OFRAG_MAX_PER_TILE * HQMQ_OFRAG_BYTES;
+constexpr int kQPad = 8;   // halves of padding per query row in shared memory (spreads the rows over banks)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -46,9 +50,9 @@ struct StageLayout {
   static constexpr int kRsV = kRsK + 32;
   static constexpr int kFlK = kRsV + 32;
   static constexpr int kFlV = kFlK + 64;
-  static constexpr int kPayK = kFlV + 64;
-  static constexpr int kPayV = kPayK + (kPay + 2) * 8;
-  static constexpr int kHdr = kPayV + (kPay + 2) * 8;   // off0K, off0V (uint32 each)
+  static constexpr int kPayK = kFlV + 64;               // K side-buffer slice, or the tile's fragment records
+  static constexpr int kPayV = kPayK + kSideK;
+  static constexpr int kHdr = kPayV + (kPay + 2) * 8;   // off0K, off0V, fragment records, staged-flags bits
   static constexpr int BYTES = OUTL ? kHdr + 16 : kFlK;
   static_assert((kTile * ROW) % 16 == 0, "tile of code rows must be a multiple of 16 bytes");
 };
@@ -69,7 +73,8 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
   unsigned char* tblK = smem_raw;
   unsigned char* tblV = smem_raw + tbl_bytes;
   __half* qh16 = reinterpret_cast<__half*>(smem_raw + 2 * tbl_bytes);                         // [8][d] (OUTL)
-  unsigned char* after_q = smem_raw + 2 * tbl_bytes + (OUTL ? (size_t)NHEADS * p.d * 2 : 0);
+  const int qstride = p.d + kQPad;
+  unsigned char* after_q = smem_raw + 2 * tbl_bytes + (OUTL ? (size_t)NHEADS * qstride * 2 : 0);
   uint64_t* bars = reinterpret_cast<uint64_t*>(after_q);                                      // [NW][kStages]
   unsigned char* warp_area = after_q + ((NW * kStages * 8 + 15) & ~15);
   constexpr int WARP_BYTES = kStages * SL::BYTES;
@@ -112,8 +117,8 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
     if constexpr (OUTL) {
       for (int i = threadIdx.x; i < NHEADS * p.d; i += NW * 32) {
         const int g = i / p.d, x = i - g * p.d;
-        qh16[i] = __float2half_rn(g < p.G ? load_float(p.Q, (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t +
-                                                                 (int64_t)(h * p.G + g) * p.qs_h + x, p.q_dtype) : 0.f);
+        qh16[g * qstride + x] = __float2half_rn(g < p.G ? load_float(p.Q, (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t +
+                                                                           (int64_t)(h * p.G + g) * p.qs_h + x, p.q_dtype) : 0.f);
       }
     }
     __syncthreads();
@@ -150,30 +155,29 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
 #pragma unroll
     for (int i = 0; i < NOT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-    // ---- producer side (lane 0): plane bases and the bulk copies of one tile -----------------------------
+    // ---- producer side (lane 0): the bulk copies of one tile ----------------------------------------------
+    // Plane addresses are rebuilt from the launch parameters at every use instead of being held in registers:
+    // only one lane needs them, and twelve 64-bit pointers per thread would push the loop into spills.
     const int64_t bh = (int64_t)b * p.Hkv + h;
-    const unsigned char* gK = p.K.codes + bh * p.K.T_cap * ROW;
-    const unsigned char* gV = p.V.codes + bh * p.V.T_cap * ROW;
-    const unsigned char* gRsK = reinterpret_cast<const unsigned char*>(p.K.rs) + bh * p.K.T_cap * 2;
-    const unsigned char* gRsV = reinterpret_cast<const unsigned char*>(p.V.rs) + bh * p.V.T_cap * 2;
-    const uint32_t* gFlK = OUTL && p.K.flags ? p.K.flags + bh * p.K.T_cap : nullptr;
-    const uint32_t* gFlV = OUTL && p.V.flags ? p.V.flags + bh * p.V.T_cap : nullptr;
-    const uint32_t* gOffK = gFlK ? p.K.out_off + bh * (p.K.T_cap / HQMQ_OUT_BLOCK + 1) : nullptr;
-    const uint32_t* gOffV = gFlV ? p.V.out_off + bh * (p.V.T_cap / HQMQ_OUT_BLOCK + 1) : nullptr;
-    const unsigned char* gPayK = gFlK ? reinterpret_cast<const unsigned char*>(p.K.out_vals) + bh * p.K.out_cap * 8 : nullptr;
-    const unsigned char* gPayV = gFlV ? reinterpret_cast<const unsigned char*>(p.V.out_vals) + bh * p.V.out_cap * 8 : nullptr;
-    const bool stageK = gFlK && p.K.out_dtype != HQMQ_F32, stageV = gFlV && p.V.out_dtype != HQMQ_F32;
-    OutlSide ok_seg, ov_seg;   // side-buffer descriptors of this (b, h); only the stage pointer changes per tile
-    ok_seg.flags = gFlK; ok_seg.off = gOffK; ok_seg.dtype = p.K.out_dtype; ok_seg.stage = nullptr;
-    ok_seg.vals = reinterpret_cast<const unsigned char*>(p.K.out_vals) + bh * p.K.out_cap * 4 * (p.K.out_dtype == HQMQ_F32 ? 4 : 2);
-    ov_seg.flags = gFlV; ov_seg.off = gOffV; ov_seg.dtype = p.V.out_dtype; ov_seg.stage = nullptr;
-    ov_seg.vals = reinterpret_cast<const unsigned char*>(p.V.out_vals) + bh * p.V.out_cap * 4 * (p.V.out_dtype == HQMQ_F32 ? 4 : 2);
-    uint32_t nk0 = 0, nk1 = 0, nv0 = 0, nv1 = 0;   // payload ranges of the tile to be issued next
+    const bool hasFlK = OUTL && p.K.flags != nullptr, hasFlV = OUTL && p.V.flags != nullptr;
+    const bool stageK = hasFlK && p.K.out_dtype != HQMQ_F32, stageV = hasFlV && p.V.out_dtype != HQMQ_F32;
+    const bool hasFr = hasFlK && p.K.ofrag != nullptr;
+    uint32_t nk0 = 0, nk1 = 0, nv0 = 0, nv1 = 0, nf0 = 0, nf1 = 0;   // payload / record ranges of the tile to be issued next
     auto load_offsets = [&](int tl) {
-      nk0 = nk1 = nv0 = nv1 = 0;
+      nk0 = nk1 = nv0 = nv1 = nf0 = nf1 = 0;
       if (tl < my_hi) {
-        if (gOffK) { nk0 = gOffK[tl]; nk1 = gOffK[tl + 1]; }
-        if (gOffV) { nv0 = gOffV[tl]; nv1 = gOffV[tl + 1]; }
+        if (hasFlK) {
+          const uint32_t* o = p.K.out_off + bh * (p.K.T_cap / HQMQ_OUT_BLOCK + 1) + tl;
+          nk0 = o[0]; nk1 = o[1];
+        }
+        if (hasFlV) {
+          const uint32_t* o = p.V.out_off + bh * (p.V.T_cap / HQMQ_OUT_BLOCK + 1) + tl;
+          nv0 = o[0]; nv1 = o[1];
+        }
+        if (hasFr) {
+          const uint32_t* o = p.K.ofrag_off + bh * (p.K.T_cap / HQMQ_OUT_BLOCK + 1) + tl;
+          nf0 = o[0]; nf1 = o[1];
+        }
       }
     };
     auto issue = [&](int tl, uint32_t seq) {   // lane 0 only
@@ -181,33 +185,46 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
       unsigned char* sb = my_area + st * SL::BYTES;
       const uint32_t sb32 = smem_u32(sb), bar = bar0 + 8 * st;
       uint32_t bytes = 2 * kTile * ROW + 64;
-      uint32_t pk_bytes = 0, pv_bytes = 0, ak = 0, av = 0;
+      uint32_t pk_bytes = 0, pv_bytes = 0, fr_bytes = 0, ak = 0, av = 0;
+      bool flk = false, flv = false;   // does this tile need its flag words (it has side-buffer entries to merge)
       if constexpr (OUTL) {
-        if (gFlK) bytes += 64;
-        if (gFlV) bytes += 64;
-        if (stageK && nk1 > nk0) {
-          ak = nk0 & ~1u;
-          uint32_t n = nk1 - ak; if (n > kPay + 1) n = kPay + 1;
-          pk_bytes = ((n + 1) & ~1u) * 8; bytes += pk_bytes;
+        uint32_t nfr = 0;
+        if (nf1 > nf0) {
+          // the tile owns fragment records: they replace its K flag words and payload slice
+          nfr = nf1 - nf0; if (nfr > HQMQ_OFRAG_MAX_PER_TILE) nfr = HQMQ_OFRAG_MAX_PER_TILE;
+          fr_bytes = nfr * HQMQ_OFRAG_BYTES; bytes += fr_bytes;
+        } else if (nk1 > nk0) {
+          flk = true; bytes += 64;
+          if (stageK) {
+            ak = nk0 & ~1u;
+            uint32_t n = nk1 - ak; if (n > kPay + 1) n = kPay + 1;
+            pk_bytes = ((n + 1) & ~1u) * 8; bytes += pk_bytes;
+          }
         }
-        if (stageV && nv1 > nv0) {
-          av = nv0 & ~1u;
-          uint32_t n = nv1 - av; if (n > kPay + 1) n = kPay + 1;
-          pv_bytes = ((n + 1) & ~1u) * 8; bytes += pv_bytes;
+        if (nv1 > nv0) {
+          flv = true; bytes += 64;
+          if (stageV) {
+            av = nv0 & ~1u;
+            uint32_t n = nv1 - av; if (n > kPay + 1) n = kPay + 1;
+            pv_bytes = ((n + 1) & ~1u) * 8; bytes += pv_bytes;
+          }
         }
-        uint32_t* hdr = reinterpret_cast<uint32_t*>(sb + SL::kHdr);
-        hdr[0] = nk0; hdr[1] = nv0;
+        *reinterpret_cast<uint4*>(sb + SL::kHdr) = make_uint4(nk0, nv0, nfr, (flk ? 1u : 0u) | (flv ? 2u : 0u));
       }
       mbar_expect_tx(bar, bytes);
-      bulk_g2s(sb32 + SL::kK, gK + (int64_t)tl * kTile * ROW, kTile * ROW, bar);
-      bulk_g2s(sb32 + SL::kV, gV + (int64_t)tl * kTile * ROW, kTile * ROW, bar);
-      bulk_g2s(sb32 + SL::kRsK, gRsK + (int64_t)tl * 32, 32, bar);
-      bulk_g2s(sb32 + SL::kRsV, gRsV + (int64_t)tl * 32, 32, bar);
+      const int64_t rowK = bh * p.K.T_cap + (int64_t)tl * kTile, rowV = bh * p.V.T_cap + (int64_t)tl * kTile;
+      bulk_g2s(sb32 + SL::kK, p.K.codes + rowK * ROW, kTile * ROW, bar);
+      bulk_g2s(sb32 + SL::kV, p.V.codes + rowV * ROW, kTile * ROW, bar);
+      bulk_g2s(sb32 + SL::kRsK, reinterpret_cast<const unsigned char*>(p.K.rs) + rowK * 2, 32, bar);
+      bulk_g2s(sb32 + SL::kRsV, reinterpret_cast<const unsigned char*>(p.V.rs) + rowV * 2, 32, bar);
       if constexpr (OUTL) {
-        if (gFlK) bulk_g2s(sb32 + SL::kFlK, gFlK + (int64_t)tl * kTile, 64, bar);
-        if (gFlV) bulk_g2s(sb32 + SL::kFlV, gFlV + (int64_t)tl * kTile, 64, bar);
-        if (pk_bytes) bulk_g2s(sb32 + SL::kPayK, gPayK + (int64_t)ak * 8, pk_bytes, bar);
-        if (pv_bytes) bulk_g2s(sb32 + SL::kPayV, gPayV + (int64_t)av * 8, pv_bytes, bar);
+        if (flk) bulk_g2s(sb32 + SL::kFlK, p.K.flags + rowK, 64, bar);
+        if (flv) bulk_g2s(sb32 + SL::kFlV, p.V.flags + rowV, 64, bar);
+        if (fr_bytes) bulk_g2s(sb32 + SL::kPayK, p.K.ofrag + (bh * p.K.ofrag_cap + nf0) * HQMQ_OFRAG_BYTES, fr_bytes, bar);
+        if (pk_bytes)
+          bulk_g2s(sb32 + SL::kPayK, reinterpret_cast<const unsigned char*>(p.K.out_vals) + (bh * p.K.out_cap + ak) * 8, pk_bytes, bar);
+        if (pv_bytes)
+          bulk_g2s(sb32 + SL::kPayV, reinterpret_cast<const unsigned char*>(p.V.out_vals) + (bh * p.V.out_cap + av) * 8, pv_bytes, bar);
       }
     };
 
@@ -279,23 +296,19 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
 
       // ---- outliers --------------------------------------------------------------------------------------
       bool anyK = false, anyV = false;
-      OutlSide ok_, ov_;
-      uint32_t offk = 0, offv = 0, fv_tile = 0, fk_tile = 0;
+      uint32_t offk = 0, offv = 0, fv_tile = 0, fk_tile = 0, nfr = 0;
       if constexpr (OUTL) {
-        const uint32_t* hdr = reinterpret_cast<const uint32_t*>(sb + SL::kHdr);
-        offk = hdr[0]; offv = hdr[1];
+        const uint4 hdr = *reinterpret_cast<const uint4*>(sb + SL::kHdr);
+        offk = hdr.x; offv = hdr.y; nfr = hdr.z;
         uint32_t fk = 0, fv = 0;
-        if (lane < 16 && t0 + lane < t_end) {
-          if (gFlK) fk = reinterpret_cast<const uint32_t*>(sb + SL::kFlK)[lane];
-          if (gFlV) fv = reinterpret_cast<const uint32_t*>(sb + SL::kFlV)[lane];
+        if (hdr.w && lane < 16 && t0 + lane < t_end) {
+          if (hdr.w & 1u) fk = reinterpret_cast<const uint32_t*>(sb + SL::kFlK)[lane];
+          if (hdr.w & 2u) fv = reinterpret_cast<const uint32_t*>(sb + SL::kFlV)[lane];
         }
-        anyK = __ballot_sync(0xffffffffu, fk != 0) != 0;
-        anyV = __ballot_sync(0xffffffffu, fv != 0) != 0;
+        (void)hasFlK; (void)hasFlV;
+        anyK = (hdr.w & 1u) && __ballot_sync(0xffffffffu, fk != 0) != 0;
+        anyV = (hdr.w & 2u) && __ballot_sync(0xffffffffu, fv != 0) != 0;
         fv_tile = fv; fk_tile = fk;
-        // staged entries start at the even entry index at or below the tile's first entry
-        ok_ = ok_seg; ov_ = ov_seg;
-        ok_.stage = reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayK);
-        ov_.stage = reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayV);
       }
 
       // ---- S^T = K Q^T ----------------------------------------------------------------------------------------
@@ -314,6 +327,16 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         mma16816((ks & 1) ? s2 : s, a[0], a[1], a[2], a[3], qb[ks][0], qb[ks][1]);
       });
       if constexpr (OUTL) {
+        // K outliers of a tile that owns fragment records: one shared-memory load and one MMA per record (values
+        // and query in fp16, the precision the codeword path has too)
+        for (uint32_t g = 0; g < nfr; ++g) {
+          const unsigned char* rec = sb + SL::kPayK + g * HQMQ_OFRAG_BYTES;
+          const uint32_t cj = (*reinterpret_cast<const uint32_t*>(rec) >> (8 * j)) & 0xffu;
+          uint2 qv = make_uint2(0u, 0u);
+          if (cj != 0xffu) qv = *reinterpret_cast<const uint2*>(qh16 + r * qstride + 4 * cj);
+          const uint4 a = *reinterpret_cast<const uint4*>(rec + 16 + lane * 16);
+          mma16816(s2, a.x, a.y, a.z, a.w, qv.x, qv.y);
+        }
         if (anyK) {
           // K outliers: their rows decode to 0 (radius code 0), so their scores are added by extra MMA
           // k-slices.  The distinct chunk positions flagged anywhere in the tile are taken four at a time
@@ -321,6 +344,9 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
           // split into an fp16 head and an fp16 remainder so that the product is exact to ~2^-22, and B
           // holds the query values of position c_j.  The result lands in the same accumulators and is
           // scaled with them.
+          // staged entries start at the even entry index at or below the tile's first entry
+          OutlSide ok_;
+          ok_.init(p.K, bh, reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayK));
           const uint32_t pre16 = excl_scan16(__popc(fk_tile), lane);
           uint32_t any_c = __reduce_or_sync(0xffffffffu, fk_tile);
           uint32_t fl[2], pre[2]; float kinv[2];
@@ -340,7 +366,7 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
             }
             uint32_t ahi[4] = {0u, 0u, 0u, 0u}, alo[4] = {0u, 0u, 0u, 0u}, b0 = 0u, b1 = 0u;
             if (cj >= 0) {
-              const uint2 qv = *reinterpret_cast<const uint2*>(qh16 + r * p.d + 4 * cj);
+              const uint2 qv = *reinterpret_cast<const uint2*>(qh16 + r * qstride + 4 * cj);
               b0 = qv.x; b1 = qv.y;
 #pragma unroll
               for (int nt = 0; nt < 2; ++nt) {
@@ -410,7 +436,9 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         // flag words, payload positions and inverse scales of this lane's four tokens (patch path only)
         uint32_t vfl[4] = {0, 0, 0, 0}, vpre[4] = {0, 0, 0, 0};
         float vinv[4] = {0.f, 0.f, 0.f, 0.f};
+        OutlSide ov_;
         if constexpr (PATCH) {
+          ov_.init(p.V, bh, reinterpret_cast<uint2*>(const_cast<unsigned char*>(sb) + SL::kPayV));
           const uint32_t ex = excl_scan16(__popc(fv_tile), lane);
           const float i0 = __fdividef(p.qmaxf, ld.vscale(cur, 0)), i1 = __fdividef(p.qmaxf, ld.vscale(cur, 1));
 #pragma unroll

@@ -65,6 +65,10 @@ int check_packed(const hqmq_packed& p, bool need_flags) {
     if (!is_float_dtype(p.out_dtype) || p.out_cap < 0) return HQMQ_ERR_DTYPE;
     if (((uintptr_t)p.flags & 15) || ((uintptr_t)p.out_vals & 7)) return HQMQ_ERR_ALIGN;
   }
+  if (p.ofrag) {
+    if (!p.flags || !p.ofrag_off || p.ofrag_cap < 0) return HQMQ_ERR_ARG;
+    if (((uintptr_t)p.ofrag & 15) || ((uintptr_t)p.ofrag_off & 3)) return HQMQ_ERR_ALIGN;
+  }
   return HQMQ_OK;
 }
 

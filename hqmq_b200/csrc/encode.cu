@@ -473,6 +473,108 @@ payload_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_sta
 }
 
 
+// ---- fragment records (optional `ofrag` plane) ---------------------------------------------------------
+// Distinct flagged chunk positions of a 16-token block -> records the block owns (0 when it has none,
+// or more than HQMQ_OFRAG_MAX_PER_TILE records would be needed).
+__device__ __forceinline__ int ofrag_records_for(uint32_t any_c) {
+  const int nd = __popc(any_c);
+  const int ng = (nd + 3) >> 2;
+  return ng <= HQMQ_OFRAG_MAX_PER_TILE ? ng : 0;
+}
+
+// One warp per (b, h): record offsets of the blocks this call touches.  Only blocks the call covers
+// completely get records; a block whose records would pass the capacity, and every block after it in this
+// call, gets none.
+__global__ void __launch_bounds__(128)
+ofrag_scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk) {
+  const int bh = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (bh >= dst.B * dst.H) return;
+  const int nb_cap = dst.T_cap / HQMQ_OUT_BLOCK + 1;
+  uint32_t* off = dst.ofrag_off + (int64_t)bh * nb_cap;
+  const uint4* fl = reinterpret_cast<const uint4*>(dst.flags + (int64_t)bh * dst.T_cap);
+  uint32_t run = off[blk0];
+  bool full = false;
+  for (int i0 = 0; i0 < nblk; i0 += 32) {
+    const int i = i0 + lane, ba = blk0 + i;
+    uint32_t cnt = 0;
+    if (i < nblk && ba * HQMQ_OUT_BLOCK >= t_start && (ba + 1) * HQMQ_OUT_BLOCK <= t_start + T_new) {
+      uint32_t any_c = 0;
+#pragma unroll
+      for (int q = 0; q < HQMQ_OUT_BLOCK / 4; ++q) {
+        const uint4 w = fl[(int64_t)ba * (HQMQ_OUT_BLOCK / 4) + q];
+        any_c |= w.x | w.y | w.z | w.w;
+      }
+      cnt = (uint32_t)ofrag_records_for(any_c);
+    }
+    uint32_t incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    incl += run;
+    const bool ok = !full && incl <= (uint32_t)dst.ofrag_cap;
+    const uint32_t last_ok = __reduce_max_sync(0xffffffffu, ok ? incl : run);
+    if (i < nblk) off[ba + 1] = ok ? incl : last_ok;
+    full = full || __any_sync(0xffffffffu, !ok);
+    run = last_ok;
+  }
+}
+
+// One warp per block: writes the block's records (see the layout in include/hqmq_b200.h).
+__global__ void __launch_bounds__(256)
+ofrag_fill_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, int blk0, int nblk) {
+  const int bh = blockIdx.y;
+  const int h = bh % g.H, b = bh / g.H;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (i >= nblk) return;
+  const int ba = blk0 + i;
+  const uint32_t* off = dst.ofrag_off + (int64_t)bh * (dst.T_cap / HQMQ_OUT_BLOCK + 1);
+  const uint32_t o0 = off[ba], o1 = off[ba + 1];
+  if (o1 <= o0) return;
+  const int64_t row0 = (int64_t)bh * dst.T_cap + (int64_t)ba * HQMQ_OUT_BLOCK;
+  const uint32_t fw = lane < HQMQ_OUT_BLOCK ? dst.flags[row0 + lane] : 0u;
+  uint32_t any_c = __reduce_or_sync(0xffffffffu, fw);
+  const int j = lane & 3, r = lane >> 2;
+  uint32_t fl[2]; float inv[2];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    fl[nt] = __shfl_sync(0xffffffffu, fw, nt * 8 + r);
+    inv[nt] = fl[nt] ? (float)g.qmax / load_scale(dst, row0 + nt * 8 + r) : 0.f;
+  }
+  for (uint32_t rec = o0; rec < o1; ++rec) {
+    int cj = -1;
+    uint32_t hdr = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int c = any_c ? __ffs(any_c) - 1 : -1;
+      any_c &= any_c - 1;
+      if (q == j) cj = c;
+      hdr |= (uint32_t)(c & 0xff) << (8 * q);
+    }
+    uint32_t a[4] = {0u, 0u, 0u, 0u};
+    if (cj >= 0) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        if ((fl[nt] >> cj) & 1u) {
+          const int t = ba * HQMQ_OUT_BLOCK + nt * 8 + r - t_start;
+          float v[4];
+          load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * cj, g.x_dtype, v);
+          const __half2 h01 = __floats2half2_rn(v[0] * inv[nt], v[1] * inv[nt]);
+          const __half2 h23 = __floats2half2_rn(v[2] * inv[nt], v[3] * inv[nt]);
+          a[nt] = *reinterpret_cast<const uint32_t*>(&h01);
+          a[2 + nt] = *reinterpret_cast<const uint32_t*>(&h23);
+        }
+      }
+    }
+    unsigned char* recp = dst.ofrag + ((int64_t)bh * dst.ofrag_cap + rec) * HQMQ_OFRAG_BYTES;
+    if (lane == 0) *reinterpret_cast<uint4*>(recp) = make_uint4(hdr, 0u, 0u, 0u);
+    *reinterpret_cast<uint4*>(recp + 16 + lane * 16) = make_uint4(a[0], a[1], a[2], a[3]);
+  }
+}
+
 // ---- look-up table construction ---------------------------------------------------------------------
 // One CTA per (cell, head).  tmp: [H][kLutCells][kLutMaxList] uint16 candidate lists, cnt: [H][kLutCells].
 __global__ void __launch_bounds__(128)
@@ -753,7 +855,14 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
                                                                     maps, a->joint, nullptr, 0, mul);
   }
   HQMQ_LAUNCH_CHECK();
-  if (!med) return HQMQ_OK;
+  if (!med) {
+    // no chunk of this call is flagged: the record offsets of its blocks just carry the running total on
+    if (d.ofrag) {
+      ofrag_scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk);
+      HQMQ_LAUNCH_CHECK();
+    }
+    return HQMQ_OK;
+  }
 
   const uint64_t N = (uint64_t)d.B * a->T_new * d.n_chunks;
   const int64_t per_bh = (int64_t)a->T_new * d.n_chunks;
@@ -780,6 +889,10 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel, ws + wp.blk, wp.blk0, wp.nblk);
   scan_kernel<<<(d.B * d.H + 63) / 64, 64, 0, st>>>(d, a->t_start, a->T_new, ws + wp.blk, wp.blk0, wp.nblk, ws + wp.status);
   payload_kernel<<<dim3((a->T_new + 255) / 256, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start);
+  if (d.ofrag) {
+    ofrag_scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk);
+    ofrag_fill_kernel<<<dim3((wp.nblk + 7) / 8, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, wp.blk0, wp.nblk);
+  }
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }

@@ -29,7 +29,8 @@ class PackedKV:
 
     def __init__(self, B: int, H: int, T_cap: int, n_chunks: int, S: int, radius_bits: int, device,
                  scale_dtype: torch.dtype = torch.bfloat16, with_outliers: bool = False,
-                 out_dtype: torch.dtype = torch.bfloat16, out_cap: Optional[int] = None):
+                 out_dtype: torch.dtype = torch.bfloat16, out_cap: Optional[int] = None,
+                 ofrag: bool = False, ofrag_cap: Optional[int] = None):
         if n_chunks < 1 or n_chunks > 32:
             raise ValueError(f"n_chunks={n_chunks}: the native layout supports d_head <= 128")
         self.B, self.H, self.n_chunks, self.S, self.radius_bits = B, H, n_chunks, S, radius_bits
@@ -52,6 +53,15 @@ class PackedKV:
         else:
             self.out_cap = 0
             self.flags = self.out_vals = self.out_off = self.out_count = None
+        # optional fragment records (see include/hqmq_b200.h): by default room for one record per block
+        self.with_ofrag = bool(ofrag) and with_outliers
+        if self.with_ofrag:
+            self.ofrag_cap = int(ofrag_cap) if ofrag_cap is not None else self.T_cap // _lib.OUT_BLOCK
+            self.ofrag = torch.zeros(B * H * self.ofrag_cap * _lib.OFRAG_BYTES + 16, dtype=torch.uint8, device=dev)
+            self.ofrag_off = torch.zeros(B * H * (self.T_cap // _lib.OUT_BLOCK + 1), dtype=torch.int32, device=dev)
+        else:
+            self.ofrag_cap = 0
+            self.ofrag = self.ofrag_off = None
 
     @property
     def device(self):
@@ -73,7 +83,14 @@ class PackedKV:
         if self.with_outliers:
             p.flags, p.out_vals = self.flags.data_ptr(), self.out_vals.data_ptr()
             p.out_off, p.out_count = self.out_off.data_ptr(), self.out_count.data_ptr()
+        if self.with_ofrag:
+            p.ofrag_cap = self.ofrag_cap
+            p.ofrag, p.ofrag_off = self.ofrag.data_ptr(), self.ofrag_off.data_ptr()
         return p
+
+    def drop_ofrag(self) -> None:
+        """Forget the fragment records: attention then merges K outliers from flags / out_vals."""
+        self.with_ofrag, self.ofrag_cap, self.ofrag, self.ofrag_off = False, 0, None, None
 
     # ---- accounting -------------------------------------------------------------------------
     def n_outliers(self) -> int:

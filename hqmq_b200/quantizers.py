@@ -177,16 +177,22 @@ class HQMQQuantizer(KVQuantizer):
 
     # ---- compressed representation ---------------------------------------------------------------
     def new_cache(self, B: int, T_cap: int, d_head: int, device, scale_dtype=torch.bfloat16,
-                  with_outliers: bool = False, out_dtype=torch.bfloat16, out_cap: Optional[int] = None) -> PackedKV:
+                  with_outliers: bool = False, out_dtype=torch.bfloat16, out_cap: Optional[int] = None,
+                  ofrag: bool = False, ofrag_cap: Optional[int] = None) -> PackedKV:
         if d_head % 4 != 0:
             raise ValueError(f"d_head={d_head} not divisible by 4")
         return PackedKV(B, self.n_heads, T_cap, d_head // 4, self.secondary_size, self.radius_bits, device,
-                        scale_dtype=scale_dtype, with_outliers=with_outliers, out_dtype=out_dtype, out_cap=out_cap)
+                        scale_dtype=scale_dtype, with_outliers=with_outliers, out_dtype=out_dtype, out_cap=out_cap,
+                        ofrag=ofrag, ofrag_cap=ofrag_cap)
 
     def encode(self, x: torch.Tensor, layer_idx: int, kv: int, out: Optional[PackedKV] = None,
                median_mult: Optional[float] = None, scale_dtype: Optional[torch.dtype] = None,
-               search: int = 0, med_out: Optional[torch.Tensor] = None) -> PackedKV:
-        """Encode x (B, H, T_new, d) and append it to ``out`` (a fresh cache when None)."""
+               search: int = 0, med_out: Optional[torch.Tensor] = None, ofrag: Optional[bool] = None) -> PackedKV:
+        """Encode x (B, H, T_new, d) and append it to ``out`` (a fresh cache when None).
+
+        ``ofrag``: also keep the flagged chunks of every complete 16-token block as tensor-core operand
+        records for the decode-attention kernel (K tensors only use them).  Default: on for a fresh K
+        cache with Med3x, off otherwise."""
         why = self._unsupported()
         if why:
             raise NotImplementedError(f"hqmq_b200 accelerates the unit-magnitude linear-radius path only ({why})")
@@ -202,8 +208,10 @@ class HQMQQuantizer(KVQuantizer):
         if out is None:
             sd = scale_dtype or (x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.float32)
             od = x.dtype
+            if ofrag is None:
+                ofrag = kv == 0 and median_mult is not None
             out = self.new_cache(B, T, d, x.device, scale_dtype=sd, with_outliers=median_mult is not None,
-                                 out_dtype=od)
+                                 out_dtype=od, ofrag=bool(ofrag) and median_mult is not None)
         if median_mult is not None and not out.with_outliers:
             raise ValueError("destination cache was created without outlier planes")
         if out.T + T > out.T_cap:

@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define HQMQ_ABI_VERSION 1
+#define HQMQ_ABI_VERSION 2
 
 /* error codes */
 #define HQMQ_OK 0
@@ -55,6 +55,9 @@ extern "C" {
 #define HQMQ_OUT_BLOCK 16
 /* Plane capacities (T_cap) are multiples of this many tokens. */
 #define HQMQ_T_ALIGN 64
+/* Size of one record of the optional `ofrag` plane, and the most records a tile may own. */
+#define HQMQ_OFRAG_BYTES 528
+#define HQMQ_OFRAG_MAX_PER_TILE 2
 
 /*
  * Native compressed layout of one K or V tensor (what the roofline is measured on).
@@ -82,6 +85,21 @@ extern "C" {
  *   out_off  [B][H][T_cap/16 + 1]    number of flagged chunks before each 16-token block
  *   out_count[B][H]                  flagged chunks stored so far
  * Appending tokens never rewrites an earlier row.
+ *
+ * Optional acceleration plane for a K tensor with outliers (no counterpart in the reference; derived
+ * data, never needed to reconstruct the tensor):
+ *   ofrag    [B][H][ofrag_cap][528]  records that hold the flagged chunks of one 16-token block in
+ *          the operand order of the attention kernel's tensor-core instruction, so that their
+ *          scores cost one shared-memory load and one MMA.  A record covers up to four distinct
+ *          chunk positions c_0..c_3 flagged anywhere in the block: bytes 0..3 = c_0..c_3
+ *          (0xFF = unused), bytes 4..15 = 0, then 32 entries of 16 bytes; entry l (row r = l/4,
+ *          position j = l%4) holds eight fp16 values v(r,0) v(r,1) v(r+8,0) v(r+8,1) v(r,2) v(r,3)
+ *          v(r+8,2) v(r+8,3) with v(t,e) = x[token t of the block][4*c_j + e] * qmax / rs[t] if
+ *          chunk c_j of token t is flagged, else 0.
+ *   ofrag_off[B][H][T_cap/16 + 1]    records before each 16-token block.  hqmq_encode writes
+ *          records only for blocks that one call covers completely and that have at most
+ *          4*HQMQ_OFRAG_MAX_PER_TILE distinct flagged positions and fit ofrag_cap; every other
+ *          block owns no record and the attention kernels take its outliers from flags/out_vals.
  */
 typedef struct hqmq_packed {
   uint32_t struct_size;
@@ -94,13 +112,15 @@ typedef struct hqmq_packed {
   int32_t scale_dtype;  /* HQMQ_F16, HQMQ_BF16 or HQMQ_F32: element type of rs */
   int32_t out_dtype;    /* HQMQ_F16, HQMQ_BF16 or HQMQ_F32: element type of out_vals */
   int32_t out_cap;      /* capacity of out_vals per (b,h), in chunks */
-  int32_t reserved;
+  int32_t ofrag_cap;    /* capacity of ofrag per (b,h), in records (0 when ofrag is NULL) */
   uint8_t* codes;
   void* rs;
   uint32_t* flags;
   void* out_vals;
   uint32_t* out_off;
   uint32_t* out_count;
+  uint8_t* ofrag;       /* NULL = no fragment records; 16-byte aligned */
+  uint32_t* ofrag_off;
 } hqmq_packed;
 
 /*

@@ -269,45 +269,63 @@ encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restric
 
 // ---- Med3x: radix select of the two middle order statistics ------------------------------
 // Level 0 histogram (bits 31:21) is accumulated by encode_main_kernel into query slot 0.
-__global__ void select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level, uint64_t N,
-                              float C, float* __restrict__ med_out) {
+__global__ void __launch_bounds__(256)
+select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level, uint64_t N, float C,
+              float* __restrict__ med_out) {
+  __shared__ uint64_t wtot[8];
   const int h = blockIdx.x;
-  const int lane = threadIdx.x;       // launched with one warp
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;   // launched with 256 threads
   uint32_t* st = sel + h * 8;
   const uint64_t lo = (N - 1) / 2, hi = N / 2;
   uint32_t* hl = hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
   const int shift = level == 0 ? 21 : level == 1 ? 10 : 0;
   const int bins = level == 2 ? 1024 : kHistBins;
-  const int per = bins / 32;          // bins per lane
+  const int per = bins / 256;         // bins per thread: 8 or 4
   for (int q = 0; q < 2; ++q) {
     const uint64_t rank = level == 0 ? (q == 0 ? lo : hi) : st[2 * q + 1];
     const uint32_t prefix = level == 0 ? 0u : st[2 * q];
     // level 0 has one histogram (slot 0); deeper levels have one per query
     const uint32_t* hq = hl + (level == 0 ? 0 : q * kHistBins);
+    uint32_t cnt[8];
+#pragma unroll
+    for (int i = 0; i < 8; i += 4) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (i < per) v = *reinterpret_cast<const uint4*>(hq + tid * per + i);
+      cnt[i] = v.x; cnt[i + 1] = v.y; cnt[i + 2] = v.z; cnt[i + 3] = v.w;
+    }
     uint64_t mine = 0;
-    for (int i = 0; i < per; ++i) mine += hq[lane * per + i];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mine += cnt[i];
     uint64_t incl = mine;
     for (int o = 1; o < 32; o <<= 1) {
       const uint64_t y = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += y;
     }
+    __syncthreads();                  // the previous query's readers of wtot are done
+    if (lane == 31) wtot[warp] = incl;
+    __syncthreads();
+    uint64_t base = 0;
+    for (int w = 0; w < warp; ++w) base += wtot[w];
+    incl += base;
     const uint64_t before = incl - mine;
-    // the lane whose segment holds the rank (the last lane takes an out-of-range rank, as the serial scan did)
-    const bool owner = (rank >= before && rank < incl) || (lane == 31 && rank >= incl);
-    __syncwarp();
+    // the thread whose bins hold the rank (the last thread takes an out-of-range rank)
+    const bool owner = (rank >= before && rank < incl) || (tid == 255 && rank >= incl);
     if (owner) {
       uint64_t acc = before; int bin = bins - 1;
-      for (int i = 0; i < per; ++i) {
-        const uint32_t cnt = hq[lane * per + i];
-        if (acc + cnt > rank) { bin = lane * per + i; break; }
-        acc += cnt;
+      bool found = false;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i < per && !found) {
+          if (acc + cnt[i] > rank) { bin = tid * per + i; found = true; }
+          else acc += cnt[i];
+        }
       }
       st[2 * q] = prefix | ((uint32_t)bin << shift);
       st[2 * q + 1] = (uint32_t)(rank - acc);
     }
-    __syncwarp();
   }
-  if (lane != 0) return;
+  __syncthreads();
+  if (tid != 0) return;
   if (level == 2) {
     const float a = __uint_as_float(st[0]), b = __uint_as_float(st[2]);
     float med = (N & 1) ? a : __fsub_rn(b, __fmul_rn(__fsub_rn(b, a), 0.5f));
@@ -367,6 +385,128 @@ hist_kernel(EncGeom g, const void* __restrict__ x, uint32_t* __restrict__ hist, 
   }
 }
 
+// ---- Med3x passes for the common geometry -----------------------------------------------------------------
+// 32 chunks per token (d_head 128), 16-bit inputs, token rows 16-byte aligned: one lane reads two chunks
+// (16 bytes), half a warp reads a token, and every thread keeps four such loads in flight.
+struct Fast32 {
+  const uint16_t* x;
+  int64_t xs_b, xs_h, xs_t;
+  int H, T_new;
+};
+constexpr int kF32Tok = 64;   // tokens per CTA iteration: 8 warps x 2 tokens x 4 loads
+
+template <int DT>
+__device__ __forceinline__ void norms_of_two(const uint4& r, float& n0, float& n1) {
+  float a[4], b[4];
+  a[0] = bits16_to_float(r.x & 0xffff, DT); a[1] = bits16_to_float(r.x >> 16, DT);
+  a[2] = bits16_to_float(r.y & 0xffff, DT); a[3] = bits16_to_float(r.y >> 16, DT);
+  b[0] = bits16_to_float(r.z & 0xffff, DT); b[1] = bits16_to_float(r.z >> 16, DT);
+  b[2] = bits16_to_float(r.w & 0xffff, DT); b[3] = bits16_to_float(r.w >> 16, DT);
+  n0 = chunk_norm(a); n1 = chunk_norm(b);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256)
+hist32_kernel(Fast32 f, uint32_t* __restrict__ hist, const uint32_t* __restrict__ sel, int level) {
+  __shared__ uint32_t sh[2][kHistBins];
+  const int bh = blockIdx.y;
+  const int h = bh % f.H, b = bh / f.H;
+  for (int i = threadIdx.x; i < 2 * kHistBins; i += blockDim.x) (&sh[0][0])[i] = 0;
+  __syncthreads();
+  const uint32_t p0 = sel[h * 8 + 0], p1 = sel[h * 8 + 2];
+  const int hs = level == 1 ? 21 : 10;                   // bits already fixed are above hs
+  const int ds = level == 1 ? 10 : 0;
+  const uint32_t dm = level == 1 ? 0x7ffu : 0x3ffu;
+  const uint32_t q0 = p0 >> hs, q1 = p1 >> hs;
+  const bool same = q0 == q1;                            // both order statistics share the prefix: one histogram
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, l16 = lane & 15;
+  int per = (f.T_new + gridDim.x - 1) / gridDim.x;
+  per = (per + kF32Tok - 1) / kF32Tok * kF32Tok;
+  const int t0 = blockIdx.x * per, t1 = min(f.T_new, t0 + per);
+  const uint16_t* base = f.x + b * f.xs_b + h * f.xs_h + 8 * l16;
+  for (int t = t0 + warp * 2 + (lane >> 4); t < t1; t += kF32Tok) {
+    uint4 r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (t + 16 * u < t1) r[u] = *reinterpret_cast<const uint4*>(base + (int64_t)(t + 16 * u) * f.xs_t);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (t + 16 * u < t1) {
+        float n[2];
+        norms_of_two<DT>(r[u], n[0], n[1]);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t key = __float_as_uint(n[e]);
+          const uint32_t dig = (key >> ds) & dm, top = key >> hs;
+          if (top == q0) atomicAdd(&sh[0][dig], 1u);
+          else if (top == q1) atomicAdd(&sh[1][dig], 1u);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  uint32_t* gh = hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
+  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) {
+    const uint32_t c0 = sh[0][i], c1 = same ? c0 : sh[1][i];
+    if (c0) atomicAdd(&gh[i], c0);
+    if (c1) atomicAdd(&gh[kHistBins + i], c1);
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256)
+flags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, const uint32_t* __restrict__ sel,
+               uint32_t* __restrict__ blk, int blk0, int nblk) {
+  const int bh = blockIdx.y;
+  const int h = bh % f.H, b = bh / f.H;
+  const float thr = __uint_as_float(sel[h * 8 + 6]);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, l16 = lane & 15;
+  const uint32_t halfmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+  int per = (f.T_new + gridDim.x - 1) / gridDim.x;
+  per = (per + kF32Tok - 1) / kF32Tok * kF32Tok;
+  const int t0 = blockIdx.x * per, t1 = min(f.T_new, t0 + per);
+  const uint16_t* base = f.x + b * f.xs_b + h * f.xs_h + 8 * l16;
+  const int cb = ib + rbits;
+  for (int t = t0 + warp * 2 + (lane >> 4); t < t1; t += kF32Tok) {
+    uint4 r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (t + 16 * u < t1) r[u] = *reinterpret_cast<const uint4*>(base + (int64_t)(t + 16 * u) * f.xs_t);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int tu = t + 16 * u;
+      if (tu < t1) {        // uniform over the half warp that shares the token
+        float n[2];
+        norms_of_two<DT>(r[u], n[0], n[1]);
+        const uint32_t m = (n[0] > thr ? 1u : 0u) | (n[1] > thr ? 2u : 0u);
+        const uint32_t word = __reduce_or_sync(halfmask, m << (2 * l16));
+        const int64_t row = (int64_t)bh * dst.T_cap + t_start + tu;
+        if (m) {
+          // A flagged chunk is stored in the side buffer: its radius code in the packed row becomes 0 so
+          // that decoding the row contributes nothing for it.
+          uint32_t* rowp = reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            if ((m >> e) & 1u) {
+              const int c = 2 * l16 + e;
+              const int lo = c * cb + ib, hi = (c + 1) * cb;   // bit range of the radius code
+              const int w0 = lo >> 5, w1 = (hi - 1) >> 5;
+              const uint32_t m0 = ~0u << (lo & 31);
+              const uint32_t m1 = (hi & 31) ? ~(~0u << (hi & 31)) : ~0u;
+              if (w0 == w1) atomicAnd(&rowp[w0], ~(m0 & m1));
+              else { atomicAnd(&rowp[w0], ~m0); atomicAnd(&rowp[w1], ~m1); }
+            }
+          }
+        }
+        if (l16 == 0) {
+          dst.flags[row] = word;
+          if (word) atomicAdd(&blk[(int64_t)bh * (nblk + 1) + ((t_start + tu) / HQMQ_OUT_BLOCK - blk0)], (uint32_t)__popc(word));
+        }
+      }
+    }
+  }
+}
+
 // Flags: one lane group per token; counts flagged chunks per 16-token block of the cache.
 __global__ void __launch_bounds__(256)
 flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, const uint32_t* __restrict__ sel,
@@ -417,24 +557,35 @@ flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start
   }
 }
 
-// Per (b,h): running offsets of the outlier payload for the blocks this call touches.
-__global__ void scan_kernel(hqmq_packed dst, int t_start, int T_new, uint32_t* __restrict__ blk, int blk0, int nblk,
-                            uint32_t* __restrict__ status) {
-  const int bh = blockIdx.x * blockDim.x + threadIdx.x;
+// Per (b,h), one warp: running offsets of the outlier payload for the blocks this call touches.
+__global__ void __launch_bounds__(128)
+scan_kernel(hqmq_packed dst, int t_start, int T_new, uint32_t* __restrict__ blk, int blk0, int nblk,
+            uint32_t* __restrict__ status) {
+  const int bh = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
   if (bh >= dst.B * dst.H) return;
   const int nb_cap = dst.T_cap / HQMQ_OUT_BLOCK + 1;
   uint32_t* off = dst.out_off + (int64_t)bh * nb_cap;
-  uint32_t* cnt = blk + (int64_t)bh * (nblk + 1);
+  const uint32_t* cnt = blk + (int64_t)bh * (nblk + 1);
   uint32_t run = dst.out_count[bh];
-  for (int i = 0; i < nblk; ++i) {
-    const int ba = blk0 + i;
+  for (int i0 = 0; i0 < nblk; i0 += 32) {
+    const int i = i0 + lane;
+    const uint32_t c = i < nblk ? cnt[i] : 0u;
+    uint32_t incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
     // A block that already holds tokens from an earlier call keeps its offset.
-    if (!(i == 0 && (t_start % HQMQ_OUT_BLOCK) != 0)) off[ba] = run;
-    run += cnt[i];
+    if (i < nblk && !(i == 0 && (t_start % HQMQ_OUT_BLOCK) != 0)) off[blk0 + i] = run + incl - c;
+    run += __shfl_sync(0xffffffffu, incl, 31);
   }
-  off[blk0 + nblk] = run;
-  if (run > (uint32_t)dst.out_cap) atomicOr(&status[0], 1u);
-  dst.out_count[bh] = run;
+  if (lane == 0) {
+    off[blk0 + nblk] = run;
+    if (run > (uint32_t)dst.out_cap) atomicOr(&status[0], 1u);
+    dst.out_count[bh] = run;
+  }
 }
 
 // Payload: the original values of every flagged chunk, in (token, chunk) order.
@@ -874,20 +1025,40 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   if (hb < 1) hb = 1;
   uint32_t* hist = ws + wp.hist;
   uint32_t* sel = ws + wp.sel;
-  select_kernel<<<d.H, 32, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr);
-  hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 1);
-  select_kernel<<<d.H, 32, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr);
-  hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 2);
-  select_kernel<<<d.H, 32, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out);
+  // fast passes: d_head 128, 16-bit input, token rows on 16-byte boundaries
+  const bool fast32 = g.n == 32 && is_half_dtype(a->x_dtype) && ((uintptr_t)a->x & 15) == 0 && g.xs_b % 8 == 0 &&
+                      g.xs_h % 8 == 0 && g.xs_t % 8 == 0;
+  Fast32 f32{reinterpret_cast<const uint16_t*>(a->x), g.xs_b, g.xs_h, g.xs_t, d.H, a->T_new};
+  int fgrid = (148 * 16 + bh_count - 1) / bh_count;
+  const int fgrid_max = (a->T_new + kF32Tok - 1) / kF32Tok;
+  if (fgrid > fgrid_max) fgrid = fgrid_max;
+  if (fgrid < 1) fgrid = 1;
+  auto launch_hist = [&](int level) {
+    if (!fast32) hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, level);
+    else if (a->x_dtype == HQMQ_F16) hist32_kernel<HQMQ_F16><<<dim3(fgrid, d.B * d.H), 256, 0, st>>>(f32, hist, sel, level);
+    else hist32_kernel<HQMQ_BF16><<<dim3(fgrid, d.B * d.H), 256, 0, st>>>(f32, hist, sel, level);
+  };
+  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr);
+  launch_hist(1);
+  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr);
+  launch_hist(2);
+  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out);
   HQMQ_LAUNCH_CHECK();
 
-  const int tok_per_fblock = 8 * g.tpw;
-  int fb = (a->T_new + 4 * tok_per_fblock - 1) / (4 * tok_per_fblock);
-  const int fb_cap = (148 * 32 + bh_count - 1) / bh_count;
-  if (fb > fb_cap) fb = fb_cap;
-  if (fb < 1) fb = 1;
-  flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel, ws + wp.blk, wp.blk0, wp.nblk);
-  scan_kernel<<<(d.B * d.H + 63) / 64, 64, 0, st>>>(d, a->t_start, a->T_new, ws + wp.blk, wp.blk0, wp.nblk, ws + wp.status);
+  if (fast32) {
+    if (a->x_dtype == HQMQ_F16)
+      flags32_kernel<HQMQ_F16><<<dim3(fgrid, d.B * d.H), 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, ws + wp.blk, wp.blk0, wp.nblk);
+    else
+      flags32_kernel<HQMQ_BF16><<<dim3(fgrid, d.B * d.H), 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, ws + wp.blk, wp.blk0, wp.nblk);
+  } else {
+    const int tok_per_fblock = 8 * g.tpw;
+    int fb = (a->T_new + 4 * tok_per_fblock - 1) / (4 * tok_per_fblock);
+    const int fb_cap = (148 * 32 + bh_count - 1) / bh_count;
+    if (fb > fb_cap) fb = fb_cap;
+    if (fb < 1) fb = 1;
+    flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel, ws + wp.blk, wp.blk0, wp.nblk);
+  }
+  scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, ws + wp.blk, wp.blk0, wp.nblk, ws + wp.status);
   payload_kernel<<<dim3((a->T_new + 255) / 256, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start);
   if (d.ofrag) {
     ofrag_scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk);

@@ -267,6 +267,170 @@ encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restric
   }
 }
 
+// ---- main pass for the common geometry ------------------------------------------------------------------
+// 32 chunks per token, 16-bit input, look-up-table search, compile-time field layout: one warp per token,
+// one lane per chunk, no run-time geometry in the loop.  Results are the ones encode_main_kernel gives.
+constexpr int kEnc32Threads = 1024;   // one CTA per SM (the tables fill half of shared memory): 32 warps hide the search latency
+constexpr int kEnc32Warps = kEnc32Threads / 32;
+struct NativeMul { uint8_t v[8][24]; };   // native (a << 3 | u) of (axis unit g) * (primary p)
+
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int DT, int IB, int RB>
+__global__ void __launch_bounds__(kEnc32Threads, 1)
+encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
+                     int t_start, uint32_t* __restrict__ hist, Maps24 maps, const float* __restrict__ joint_all,
+                     const uint32_t* __restrict__ lut, int lut_cand_smem, NativeMul nmul) {
+  constexpr int CB = IB + RB;
+  constexpr int RW = 32 * CB / 32;                       // words per row
+  constexpr float qmaxf = (float)((1 << RB) - 1);
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float4* qs = reinterpret_cast<float4*>(smem_raw);
+  uint32_t* rows = reinterpret_cast<uint32_t*>(qs + g.S);            // [warps][kMaxRowWords]
+  uint32_t* shist = rows + kEnc32Warps * kMaxRowWords;                  // [kHistBins]
+  float4* sjoint = reinterpret_cast<float4*>(shist + kHistBins);      // [24 S]
+  uint32_t* soff = reinterpret_cast<uint32_t*>(sjoint + 24 * g.S);     // [kLutCells + 1]
+  uint8_t* snm = reinterpret_cast<uint8_t*>(soff + kLutCells + 4);     // [8][24] (+ padding to 256)
+  uint16_t* scand = reinterpret_cast<uint16_t*>(snm + 256);            // [lut_cand_smem]
+
+  const int bh = blockIdx.y;
+  const int h = bh % g.H, b = bh / g.H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = g.S;
+  {
+    const uint32_t* hdr = lut + (int64_t)h * kLutHdr;
+    const uint16_t* gc = reinterpret_cast<const uint16_t*>(lut + (int64_t)g.H * kLutHdr) + (int64_t)h * kLutCandCap;
+    const uint32_t total = hdr[kLutCells];
+    for (int i = threadIdx.x; i < S; i += blockDim.x) qs[i] = reinterpret_cast<const float4*>(qs_all)[(int64_t)h * S + i];
+    if (hist) for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) shist[i] = 0;
+    for (int i = threadIdx.x; i < 24 * S; i += blockDim.x) sjoint[i] = reinterpret_cast<const float4*>(joint_all)[(int64_t)h * 24 * S + i];
+    for (int i = threadIdx.x; i <= kLutCells; i += blockDim.x) soff[i] = hdr[i];
+    if (threadIdx.x < 192) snm[threadIdx.x] = nmul.v[threadIdx.x / 24][threadIdx.x % 24];
+    const uint32_t* gc32 = reinterpret_cast<const uint32_t*>(gc);
+    uint32_t* sc32 = reinterpret_cast<uint32_t*>(scand);
+    for (uint32_t i = threadIdx.x; i < (total + 1) / 2; i += blockDim.x) sc32[i] = gc32[i];
+  }
+  const float inv_S = 1.0f / (float)S;
+  __syncthreads();
+
+  uint32_t* myrow = rows + warp * kMaxRowWords;
+  const int t_block0 = blockIdx.x * kEnc32Warps * kEncIters;
+  const uint16_t* xp = x + b * g.xs_b + h * g.xs_h + 4 * lane;
+  int t = t_block0 + warp;
+  uint2 raw_n = make_uint2(0u, 0u);
+  if (t < g.T_new) raw_n = *reinterpret_cast<const uint2*>(xp + (int64_t)t * g.xs_t);
+  for (int it = 0; it < kEncIters && t < g.T_new; ++it, t += kEnc32Warps) {
+    const uint2 raw = raw_n;
+    if (it + 1 < kEncIters && t + kEnc32Warps < g.T_new)
+      raw_n = *reinterpret_cast<const uint2*>(xp + (int64_t)(t + kEnc32Warps) * g.xs_t);
+    float v[4];
+    v[0] = bits16_to_float(raw.x & 0xffff, DT); v[1] = bits16_to_float(raw.x >> 16, DT);
+    v[2] = bits16_to_float(raw.y & 0xffff, DT); v[3] = bits16_to_float(raw.y >> 16, DT);
+    const float nrm = chunk_norm(v);
+    const float radius = fmaxf(nrm, 1e-8f);
+    float rmax = radius;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+    const float scale = __fdiv_rn(rmax, qmaxf);
+    // radius code: the quotient is first taken with an approximate reciprocal; only a lane whose quotient
+    // lies close to a rounding boundary repeats it with the IEEE division the contract names
+    float quo = radius * rcp_approx(scale);
+    float rqf = rintf(quo);
+    if (fabsf(quo - rqf) > 0.499f) rqf = rintf(__fdiv_rn(radius, scale));
+    rqf = fminf(fmaxf(rqf, 0.f), qmaxf);
+
+    // ---- nearest codeword ---------------------------------------------------------------------------
+    // (the nearest codeword does not depend on the chunk's length: a cheaply normalised copy keeps the
+    // values in range)
+    const float inv_r = rcp_approx(radius);
+    const float u0 = v[0] * inv_r, u1 = v[1] * inv_r, u2 = v[2] * inv_r, u3 = v[3] * inv_r;
+    int au, sidx;
+    {
+      const float a0 = fabsf(u0), a1 = fabsf(u1), a2 = fabsf(u2), a3 = fabsf(u3);
+      int ax = 0; float am = a0;
+      if (a1 > am) { am = a1; ax = 1; }
+      if (a2 > am) { am = a2; ax = 2; }
+      if (a3 > am) { am = a3; ax = 3; }
+      float v0, v1, v2, v3;
+      if (ax == 0) { v0 = u0; v1 = u1; v2 = u2; v3 = u3; }
+      else if (ax == 1) { v0 = u1; v1 = -u0; v2 = u3; v3 = -u2; }
+      else if (ax == 2) { v0 = u2; v1 = -u3; v2 = -u0; v3 = u1; }
+      else { v0 = u3; v1 = u2; v2 = -u1; v3 = -u0; }
+      const bool neg = v0 < 0.f;
+      if (neg) { v0 = -v0; v1 = -v1; v2 = -v2; v3 = -v3; }
+      uint32_t beg = 0, end = 0;
+      if (am > 0.f) {
+        const float inv = rcp_approx(v0) * (0.5f * kLutN);
+        const int cx = min(kLutN - 1, max(0, (int)fmaf(v1, inv, 0.5f * kLutN)));
+        const int cy = min(kLutN - 1, max(0, (int)fmaf(v2, inv, 0.5f * kLutN)));
+        const int cz = min(kLutN - 1, max(0, (int)fmaf(v3, inv, 0.5f * kLutN)));
+        const int cell = (cx * kLutN + cy) * kLutN + cz;
+        beg = soff[cell]; end = soff[cell + 1];
+      }
+      if (beg == end) {
+        // zero direction (every similarity is 0, the first index wins) or a cell without a list
+        int p = 0; sidx = 0;
+        if (am > 0.f) p = search_exhaustive(qs, S, u0, u1, u2, u3, sidx);
+        au = maps.ref_to_native[p];
+      } else {
+        float best = -2.f; int bk = 0;
+        for (uint32_t e = beg; e < end; e += 4) {
+          const uint2 kk = *reinterpret_cast<const uint2*>(scand + e);
+          const int k0 = kk.x & 0xffff, k1 = kk.x >> 16, k2 = kk.y & 0xffff, k3 = kk.y >> 16;
+          const float4 c0 = sjoint[k0], c1 = sjoint[k1], c2 = sjoint[k2], c3 = sjoint[k3];
+          const float s0 = fmaf(v3, c0.w, fmaf(v2, c0.z, fmaf(v1, c0.y, v0 * c0.x)));
+          const float s1 = fmaf(v3, c1.w, fmaf(v2, c1.z, fmaf(v1, c1.y, v0 * c1.x)));
+          const float s2 = fmaf(v3, c2.w, fmaf(v2, c2.z, fmaf(v1, c2.y, v0 * c2.x)));
+          const float s3 = fmaf(v3, c3.w, fmaf(v2, c3.z, fmaf(v1, c3.y, v0 * c3.x)));
+          if (s0 > best) { best = s0; bk = k0; }
+          if (s1 > best) { best = s1; bk = k1; }
+          if (s2 > best) { best = s2; bk = k2; }
+          if (s3 > best) { best = s3; bk = k3; }
+        }
+        const int pf = (int)(((float)bk + 0.5f) * inv_S);
+        sidx = bk - pf * S;
+        au = snm[(2 * ax + (neg ? 1 : 0)) * 24 + pf];
+      }
+    }
+    const uint32_t ni = (uint32_t)((((au >> 3) * S + sidx) << 3) | (au & 7));
+    const uint32_t f = ni | ((uint32_t)rqf << IB);
+
+    // ---- packed row, scale, flag word ---------------------------------------------------------------------
+    const int64_t row = (int64_t)bh * dst.T_cap + t_start + t;
+    uint32_t* out = reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes);
+    if constexpr (CB == 16) {
+      const uint32_t other = __shfl_xor_sync(0xffffffffu, f, 1);
+      if (!(lane & 1)) out[lane >> 1] = f | (other << 16);
+    } else {
+      if (lane < RW) myrow[lane] = 0;
+      __syncwarp();
+      const int bit = lane * CB, w = bit >> 5, sh = bit & 31;
+      atomicOr(&myrow[w], f << sh);
+      if (sh + CB > 32) atomicOr(&myrow[w + 1], f >> (32 - sh));
+      __syncwarp();
+      if (lane < RW) out[lane] = myrow[lane];
+      __syncwarp();
+    }
+    if (lane == 0) {
+      store_scale(dst, row, rmax);
+      if (dst.flags) dst.flags[row] = 0u;
+    }
+    if (hist) atomicAdd(&shist[__float_as_uint(nrm) >> 21], 1u);
+  }
+  if (hist) {
+    __syncthreads();
+    uint32_t* gh = hist + (int64_t)h * 3 * 2 * kHistBins;  // level 0, query 0
+    for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) {
+      uint32_t cnt = shist[i];
+      if (cnt) atomicAdd(&gh[i], cnt);
+    }
+  }
+}
+
 // ---- Med3x: radix select of the two middle order statistics ------------------------------
 // Level 0 histogram (bits 31:21) is accumulated by encode_main_kernel into query slot 0.
 __global__ void __launch_bounds__(256)
@@ -992,8 +1156,38 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   const size_t smem_lut = smem_base + (size_t)24 * g.S * 16 + (size_t)(kLutCells + 4) * 4 + (size_t)cand_smem * 2;
   const bool use_lut = a->search == 0 && a->lut != nullptr && a->lut_max_cand >= 0 && smem_lut <= 220 * 1024;
   static const Mul8x24 mul = make_mul();
-  if (use_lut) {
-    if ((uintptr_t)a->lut & 15) return HQMQ_ERR_ALIGN;
+  if (use_lut && (uintptr_t)a->lut & 15) return HQMQ_ERR_ALIGN;
+  // specialised kernel: d_head 128, 16-bit input, one of the compiled field layouts
+  const void* fastk = nullptr;
+  if (use_lut && g.n == 32 && is_half_dtype(a->x_dtype)) {
+    const bool h16 = a->x_dtype == HQMQ_F16;
+#define HQMQ_PICK(IB_, RB_)                                                                              \
+    if (g.ib == IB_ && g.rbits == RB_)                                                                     \
+      fastk = h16 ? (const void*)&encode_main32_kernel<HQMQ_F16, IB_, RB_> : (const void*)&encode_main32_kernel<HQMQ_BF16, IB_, RB_>;
+    HQMQ_PICK(10, 3) HQMQ_PICK(12, 4) HQMQ_PICK(13, 6)
+#undef HQMQ_PICK
+  }
+  if (fastk) {
+    static const NativeMul nmul = [] {
+      NativeMul m;
+      const Mul8x24 mm = make_mul();
+      for (int gi = 0; gi < 8; ++gi)
+        for (int pi = 0; pi < 24; ++pi) m.v[gi][pi] = index_maps().ref_to_native[mm.v[gi][pi]];
+      return m;
+    }();
+    const size_t smem_fast = (size_t)g.S * 16 + (size_t)kEnc32Warps * kMaxRowWords * 4 + kHistBins * 4 + (size_t)24 * g.S * 16 +
+                             (size_t)(kLutCells + 4) * 4 + 256 + (size_t)cand_smem * 2;
+    if (smem_fast > 48 * 1024)
+      HQMQ_CHECK_CUDA(cudaFuncSetAttribute(fastk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fast));
+    dim3 fgrid((a->T_new + kEnc32Warps * kEncIters - 1) / (kEnc32Warps * kEncIters), d.B * d.H);
+    const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a->x);
+    uint32_t* hist_arg = med ? ws + wp.hist : nullptr;
+    const uint32_t* lut_arg = reinterpret_cast<const uint32_t*>(a->lut);
+    int t_start_arg = a->t_start;
+    void* kargs[] = {(void*)&g, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&hist_arg, (void*)&maps,
+                     (void*)&a->joint, (void*)&lut_arg, (void*)&cand_smem, (void*)&nmul};
+    HQMQ_CHECK_CUDA(cudaLaunchKernel(fastk, fgrid, dim3(kEnc32Threads), kargs, smem_fast, st));
+  } else if (use_lut) {
     if (smem_lut > 48 * 1024)
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(encode_main_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_lut));
     encode_main_kernel<true><<<grid, kEncThreads, smem_lut, st>>>(g, a->x, a->qs, d, a->t_start, med ? ws + wp.hist : nullptr,

@@ -284,7 +284,7 @@ template <int DT, int IB, int RB>
 __global__ void __launch_bounds__(kEnc32Threads, 1)
 encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
                      int t_start, uint32_t* __restrict__ hist, Maps24 maps, const float* __restrict__ joint_all,
-                     const uint32_t* __restrict__ lut, int lut_cand_smem, NativeMul nmul) {
+                     const uint32_t* __restrict__ lut, int lut_cand_smem, NativeMul nmul, int iters) {
   constexpr int CB = IB + RB;
   constexpr int RW = 32 * CB / 32;                       // words per row
   constexpr float qmaxf = (float)((1 << RB) - 1);
@@ -318,14 +318,14 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
   __syncthreads();
 
   uint32_t* myrow = rows + warp * kMaxRowWords;
-  const int t_block0 = blockIdx.x * kEnc32Warps * kEncIters;
+  const int t_block0 = blockIdx.x * kEnc32Warps * iters;
   const uint16_t* xp = x + b * g.xs_b + h * g.xs_h + 4 * lane;
   int t = t_block0 + warp;
   uint2 raw_n = make_uint2(0u, 0u);
   if (t < g.T_new) raw_n = *reinterpret_cast<const uint2*>(xp + (int64_t)t * g.xs_t);
-  for (int it = 0; it < kEncIters && t < g.T_new; ++it, t += kEnc32Warps) {
+  for (int it = 0; it < iters && t < g.T_new; ++it, t += kEnc32Warps) {
     const uint2 raw = raw_n;
-    if (it + 1 < kEncIters && t + kEnc32Warps < g.T_new)
+    if (it + 1 < iters && t + kEnc32Warps < g.T_new)
       raw_n = *reinterpret_cast<const uint2*>(xp + (int64_t)(t + kEnc32Warps) * g.xs_t);
     float v[4];
     v[0] = bits16_to_float(raw.x & 0xffff, DT); v[1] = bits16_to_float(raw.x >> 16, DT);
@@ -378,8 +378,12 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
         au = maps.ref_to_native[p];
       } else {
         float best = -2.f; int bk = 0;
+        uint2 kk_n = *reinterpret_cast<const uint2*>(scand + beg);
         for (uint32_t e = beg; e < end; e += 4) {
-          const uint2 kk = *reinterpret_cast<const uint2*>(scand + e);
+          // the next four candidate ids are fetched while this step's codewords are evaluated (the read past
+          // the end of the last list stays inside the padded array and is never used)
+          const uint2 kk = kk_n;
+          kk_n = *reinterpret_cast<const uint2*>(scand + e + 4);
           const int k0 = kk.x & 0xffff, k1 = kk.x >> 16, k2 = kk.y & 0xffff, k3 = kk.y >> 16;
           const float4 c0 = sjoint[k0], c1 = sjoint[k1], c2 = sjoint[k2], c3 = sjoint[k3];
           const float s0 = fmaf(v3, c0.w, fmaf(v2, c0.z, fmaf(v1, c0.y, v0 * c0.x)));
@@ -1176,16 +1180,20 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
       return m;
     }();
     const size_t smem_fast = (size_t)g.S * 16 + (size_t)kEnc32Warps * kMaxRowWords * 4 + kHistBins * 4 + (size_t)24 * g.S * 16 +
-                             (size_t)(kLutCells + 4) * 4 + 256 + (size_t)cand_smem * 2;
+                             (size_t)(kLutCells + 4) * 4 + 256 + (size_t)cand_smem * 2 + 16;
+    // tokens per CTA: long enough to amortise loading the tables, short enough to fill the machine twice
+    int iters = (int)(((int64_t)a->T_new * d.B * d.H + (int64_t)2 * 148 * kEnc32Warps - 1) / ((int64_t)2 * 148 * kEnc32Warps));
+    if (iters < 1) iters = 1;
+    if (iters > 64) iters = 64;
     if (smem_fast > 48 * 1024)
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(fastk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fast));
-    dim3 fgrid((a->T_new + kEnc32Warps * kEncIters - 1) / (kEnc32Warps * kEncIters), d.B * d.H);
+    dim3 fgrid((a->T_new + kEnc32Warps * iters - 1) / (kEnc32Warps * iters), d.B * d.H);
     const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a->x);
     uint32_t* hist_arg = med ? ws + wp.hist : nullptr;
     const uint32_t* lut_arg = reinterpret_cast<const uint32_t*>(a->lut);
     int t_start_arg = a->t_start;
     void* kargs[] = {(void*)&g, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&hist_arg, (void*)&maps,
-                     (void*)&a->joint, (void*)&lut_arg, (void*)&cand_smem, (void*)&nmul};
+                     (void*)&a->joint, (void*)&lut_arg, (void*)&cand_smem, (void*)&nmul, (void*)&iters};
     HQMQ_CHECK_CUDA(cudaLaunchKernel(fastk, fgrid, dim3(kEnc32Threads), kargs, smem_fast, st));
   } else if (use_lut) {
     if (smem_lut > 48 * 1024)

@@ -48,7 +48,7 @@ WORKLOADS = {
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read+write of attn_fast_kernel divided by the algorithmic bytes of the same launch, from the ncu
 # capture summarised in profiles/attn_decode_c2.md (batch 4 of the same workload; traffic scales with the tokens)
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.05
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.11
 
 
 def synth(kind, shape, seed, device, dtype):
@@ -403,7 +403,7 @@ def main():
         "gpu_launches": (3 if seq_mode else 2) * args.steps,
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8TBs_nominal": per_gpu_gbs / 8000.0,
-                     "kernel": "attn_fast_kernel (+ combine_kernel, 2 % of the step, inside the same timed region)",
+                     "kernel": "attn_fast_kernel (+ combine_kernel, 3 % of the step, inside the same timed region)",
                      "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * algo_bytes if args.workload == "c2" else None,
                      "traffic_note": "ncu dram bytes of a batch-4 capture scaled by tokens (profiles/attn_decode_c2.md)"},
         "encode": {"tokens_per_s": enc_tokens_per_s * world, "GBps_per_gpu": enc_gbs, "frac_of_peak": enc_gbs / peak,

@@ -33,7 +33,10 @@ constexpr int kTile = 16;
 #ifndef HQMQ_FAST_WARPS_OUTL
 #define HQMQ_FAST_WARPS_OUTL 16
 #endif
-constexpr int kFastWarps = 16, kFastWarpsOutl = HQMQ_FAST_WARPS_OUTL, kSlowWarps = 4;   // warps per CTA of the kernel families
+#ifndef HQMQ_FAST_WARPS
+#define HQMQ_FAST_WARPS 16
+#endif
+constexpr int kFastWarps = HQMQ_FAST_WARPS, kFastWarpsOutl = HQMQ_FAST_WARPS_OUTL, kSlowWarps = 4;   // warps per CTA of the kernel families
 constexpr int kStage = 64;   // outlier payload entries staged per tile and tensor
 static_assert(kTile == HQMQ_OUT_BLOCK, "one outlier-offset entry per KV tile");
 

@@ -132,6 +132,7 @@ def lib():
     L.hqmq_attn_workspace_bytes.argtypes = [C.POINTER(AttnArgs)]
     L.hqmq_attn_decode.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     L.hqmq_attn_decode_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+    L.hqmq_read_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]
     L.hqmq_combine_partials.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     if L.hqmq_abi_version() != ABI_VERSION:
         raise HqmqError("hqmq_b200: library ABI version mismatch; rebuild with `python -m hqmq_b200.build --force`")
@@ -162,6 +163,14 @@ def check_device(device: torch.device) -> None:
 
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
+
+
+def read_status(workspace: torch.Tensor) -> int:
+    """First word of a workspace after synchronising the current stream (see hqmq_read_status)."""
+    st = C.c_uint32(0)
+    with torch.cuda.device(workspace.device):
+        check(lib().hqmq_read_status(workspace.data_ptr(), C.byref(st), stream_ptr()), "hqmq_read_status")
+    return int(st.value)
 
 
 def ref_packed(idx: torch.Tensor, rq: torch.Tensor, rs: torch.Tensor) -> RefPacked:

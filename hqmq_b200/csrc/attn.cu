@@ -90,6 +90,7 @@ struct Plan {
   const void* kernel;
   size_t smem;
   int table_rows, ib, nw, rep_log2;
+  int ppc;   // partials a CTA writes per unit and head: 1 for the staged kernels (merged in shared memory), nw otherwise
   int units, tpu_v, L, P, grid;
   size_t ws_bytes;
 };
@@ -170,6 +171,7 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
     pl.table_rows = a->K_size;
   }
   const bool fast = pl.kernel != nullptr;
+  pl.ppc = fast ? 1 : kSlowWarps;
   if (!pl.kernel) pl.kernel = slow_kernel(n, outl, G > 8);
   if (!pl.kernel) return HQMQ_ERR_UNSUPPORTED;
   const int nheads = G > 8 ? 16 : 8;
@@ -188,7 +190,7 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
     if (!fast) return HQMQ_ERR_UNSUPPORTED;
     // the staged kernel does not fit next to this codebook: use the generic one
     pl.kernel = slow_kernel(n, outl, false);
-    pl.nw = kSlowWarps; pl.rep_log2 = 0;
+    pl.nw = kSlowWarps; pl.rep_log2 = 0; pl.ppc = kSlowWarps;
     pl.smem = (size_t)pl.table_rows * 16 + (outl ? (size_t)8 * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * 8 * 4) : 0);
     if (pl.smem > 226 * 1024) return HQMQ_ERR_UNSUPPORTED;
   }
@@ -216,7 +218,7 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   pl.grid = (int)((total + pl.L - 1) / pl.L);
   pl.P = (pl.tpu_v - 1 + pl.L - 1) / pl.L + 1;
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
-  pl.ws_bytes = 16 + (size_t)rows * pl.P * pl.nw * (a->d + 2) * sizeof(float);
+  pl.ws_bytes = 16 + (size_t)rows * pl.P * pl.ppc * (a->d + 2) * sizeof(float);
   return HQMQ_OK;
 }
 
@@ -287,9 +289,9 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   void* kargs[] = {&p};
   HQMQ_CHECK_CUDA(cudaLaunchKernel(pl.kernel, dim3(pl.grid), dim3(pl.nw * 32), kargs, pl.smem, st));
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
-  combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, (size_t)pl.P * pl.nw * 4, st>>>(
-      p.partials, pl.P * pl.nw, rows, a->d, a->o_dtype, a->O, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
-      a->T_q, p.G, a->B, pl.tpu_v, pl.L, pl.nw, a->partials_only ? a->partials : nullptr, p.status, p.epoch, 0);
+  combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, (size_t)pl.P * pl.ppc * 4, st>>>(
+      p.partials, pl.P * pl.ppc, rows, a->d, a->o_dtype, a->O, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
+      a->T_q, p.G, a->B, pl.tpu_v, pl.L, pl.ppc, a->partials_only ? a->partials : nullptr, p.status, p.epoch, 0);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }

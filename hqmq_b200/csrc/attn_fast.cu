@@ -16,7 +16,8 @@ __global__ void __launch_bounds__(OUTL ? kFastWarpsOutl * 32 : kFastWarps * 32, 
 size_t fast_warp_bytes(int n_chunks, int ib, int rb, bool outl) {
   const size_t row = (size_t)n_chunks * (ib + rb) / 8;
   const size_t stage = 2 * kTile * row + 64 + (outl ? 128 + kSideK + (kPay + 2) * 8 + 16 : 0);
-  return kStages * stage;
+  const size_t merge = (size_t)8 * (4 * n_chunks + 2) * 4;   // one warp's partial during the in-CTA merge
+  return kStages * stage > merge ? kStages * stage : merge;
 }
 
 template <int N, int IB, int RB, bool OUTL>

@@ -215,9 +215,9 @@ struct FastLoader {
       uint32_t pu = *reinterpret_cast<const uint32_t*>(&pair);
       // sign bits of both fields (bits 0 and 16 of the word) into the sign bits of the two halves
       if constexpr (FOLD) pu ^= (word << 15) & 0x80008000u;
-      // broadcast one half to both lanes of the register with a single byte permute
-      const uint32_t bu = __byte_perm(pu, pu, s == 0 ? 0x1010 : 0x3232);
-      rr = *reinterpret_cast<const __half2*>(&bu);
+      // broadcast one half to both lanes (the compiler folds this into the multiply's operand selector)
+      const __half2 p2 = *reinterpret_cast<const __half2*>(&pu);
+      rr = s == 0 ? __low2half2(p2) : __high2half2(p2);
     } else {
       uint32_t v = (s + CB > 32) ? __funnelshift_r(w[a], w[a + 1], s) : (w[a] >> s);
       const __half2 r2 = radius_half2((v >> IB) & ((1u << RB) - 1u));

@@ -77,7 +77,8 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
   unsigned char* after_q = smem_raw + 2 * tbl_bytes + (OUTL ? (size_t)NHEADS * qstride * 2 : 0);
   uint64_t* bars = reinterpret_cast<uint64_t*>(after_q);                                      // [NW][kStages]
   unsigned char* warp_area = after_q + ((NW * kStages * 8 + 15) & ~15);
-  constexpr int WARP_BYTES = kStages * SL::BYTES;
+  // per-warp share of the staging area; it also holds one warp's partial [8 heads][d + 2] during the merge
+  constexpr int WARP_BYTES = kStages * SL::BYTES > NHEADS * (4 * N + 2) * 4 ? kStages * SL::BYTES : NHEADS * (4 * N + 2) * 4;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = lane & 3, r = lane >> 2;
@@ -131,7 +132,7 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
     const int rel_hi = (int)(flat_hi < ubase + p.tpu_v ? flat_hi - ubase : p.tpu_v);
     const int my_lo = tile_lo + rel_lo;
     const int my_hi = min(tile_hi, tile_lo + rel_hi);
-    const int part = ((int)blockIdx.x - (int)(ubase / p.L)) * NW + warp;
+    const int part = (int)blockIdx.x - (int)(ubase / p.L);   // this CTA's slot among the CTAs that share the unit
 
     // ---- Q as B fragments -------------------------------------------------------------------------------
     uint32_t qb[NKS][2];
@@ -489,29 +490,53 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
       }
     }
 
-    // ---- per-warp partial ---------------------------------------------------------------------------------
-    const int n_parts = p.P * NW;
+    // ---- one partial per (CTA, unit, head): the warps' results are merged in shared memory ---------------------
+    // The rings are idle between units (every issued tile was consumed), so their memory holds the warps'
+    // partials [warp][head][d + 2] for the merge.  A warp that gave up on a wait takes the whole CTA out here.
+    if (__syncthreads_or(failed ? 1 : 0)) break;
+    constexpr int PD = 4 * N + 2;
+    float* mp = reinterpret_cast<float*>(warp_area);
+    {
+      float* mine = mp + warp * NHEADS * PD;
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      float l = l_run[e];
-      l += __shfl_xor_sync(0xffffffffu, l, 4);
-      l += __shfl_xor_sync(0xffffffffu, l, 8);
-      l += __shfl_xor_sync(0xffffffffu, l, 16);
-      const int g = 2 * j + e;
-      if (g >= p.G) continue;
-      const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
-      float* dst = p.partials + (row * n_parts + part) * (p.d + 2);
+      for (int e = 0; e < 2; ++e) {
+        float l = l_run[e];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        float* dst = mine + (2 * j + e) * PD;
 #pragma unroll
-      for (int i = 0; i < NOT; ++i) {
-        const int chunk = r * NVG + (i >> 1);
-        if (chunk < N) {
-          dst[4 * chunk + 2 * (i & 1)] = o[i][e];
-          dst[4 * chunk + 2 * (i & 1) + 1] = o[i][2 + e];
+        for (int i = 0; i < NOT; ++i) {
+          const int chunk = r * NVG + (i >> 1);
+          if (chunk < N) {
+            dst[4 * chunk + 2 * (i & 1)] = o[i][e];
+            dst[4 * chunk + 2 * (i & 1) + 1] = o[i][2 + e];
+          }
         }
+        if (r == 0) { dst[4 * N] = m_run[e]; dst[4 * N + 1] = l; }
       }
-      if (r == 0) { dst[p.d] = m_run[e]; dst[p.d + 1] = l; }
     }
-    if (failed) break;
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.G * (4 * N); i += NW * 32) {
+      const int g = i / (4 * N), x = i - g * (4 * N);
+      const float* col = mp + g * PD;
+      float m_star = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) m_star = fmaxf(m_star, col[w * NHEADS * PD + 4 * N]);
+      const float m_use = m_star == -INFINITY ? 0.f : m_star;
+      float acc = 0.f, l_star = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const float wgt = fast_exp2(col[w * NHEADS * PD + 4 * N] - m_use);   // 0 for a warp that saw no key
+        acc = fmaf(col[w * NHEADS * PD + x], wgt, acc);
+        l_star = fmaf(col[w * NHEADS * PD + 4 * N + 1], wgt, l_star);
+      }
+      const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
+      float* dst = p.partials + (row * p.P + part) * PD;
+      dst[x] = acc;
+      if (x == 0) { dst[4 * N] = m_star; dst[4 * N + 1] = l_star; }
+    }
+    __syncthreads();   // the merge is done with the ring memory before the next unit's copies land in it
   }
 }
 

@@ -237,6 +237,13 @@ extern "C" {
 
 int hqmq_abi_version(void) { return HQMQ_ABI_VERSION; }
 
+int hqmq_read_status(const void* workspace, uint32_t* status, void* stream) {
+  if (!workspace || !status) return HQMQ_ERR_ARG;
+  HQMQ_CHECK_CUDA(cudaMemcpyAsync(status, workspace, sizeof(uint32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  HQMQ_CHECK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return HQMQ_OK;
+}
+
 const char* hqmq_strerror(int code) {
   switch (code) {
     case HQMQ_OK: return "ok";

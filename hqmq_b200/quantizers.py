@@ -187,12 +187,14 @@ class HQMQQuantizer(KVQuantizer):
 
     def encode(self, x: torch.Tensor, layer_idx: int, kv: int, out: Optional[PackedKV] = None,
                median_mult: Optional[float] = None, scale_dtype: Optional[torch.dtype] = None,
-               search: int = 0, med_out: Optional[torch.Tensor] = None, ofrag: Optional[bool] = None) -> PackedKV:
+               search: int = 0, med_out: Optional[torch.Tensor] = None, ofrag: Optional[bool] = None,
+               check_status: bool = False) -> PackedKV:
         """Encode x (B, H, T_new, d) and append it to ``out`` (a fresh cache when None).
 
         ``ofrag``: also keep the flagged chunks of every complete 16-token block as tensor-core operand
         records for the decode-attention kernel (K tensors only use them).  Default: on for a fresh K
-        cache with Med3x, off otherwise."""
+        cache with Med3x, off otherwise.  ``check_status``: synchronise and raise if the outlier side buffer
+        overflowed (otherwise the caller may compare ``out_count`` with ``out_cap`` itself)."""
         why = self._unsupported()
         if why:
             raise NotImplementedError(f"hqmq_b200 accelerates the unit-magnitude linear-radius path only ({why})")
@@ -233,6 +235,8 @@ class HQMQQuantizer(KVQuantizer):
             nbytes = L.hqmq_encode_workspace_bytes(C.byref(a))
             ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
             _lib.check(L.hqmq_encode(C.byref(a), ws.data_ptr(), nbytes, _lib.stream_ptr()), "hqmq_encode")
+            if check_status and nbytes and (_lib.read_status(ws) & 1):
+                raise _lib.HqmqError(f"hqmq_b200: outlier side buffer too small (out_cap={out.out_cap} chunks per (b, h))")
         out.T += T
         return out
 

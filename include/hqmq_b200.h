@@ -201,6 +201,18 @@ typedef struct hqmq_encode_args {
 size_t hqmq_encode_workspace_bytes(const hqmq_encode_args* args);
 int hqmq_encode(const hqmq_encode_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Device-detected problems are recorded in the first word of the workspace a call was given, never
+ * printed or trapped on.  This copies that word to the host after synchronising `stream`.
+ *   workspace of hqmq_encode:       bit 0 = the outlier side buffer (out_cap) was too small; rows,
+ *                                   flags and counts are complete, payload entries beyond the
+ *                                   capacity were dropped
+ *   workspace of hqmq_attn_decode:  non-zero = some call on this workspace gave up on a bounded wait
+ *                                   for a staged copy; that call's output rows are NaN
+ * No counterpart in the reference (its kernels have no device-side status).
+ */
+int hqmq_read_status(const void* workspace, uint32_t* status, void* stream);
+
 /* ---- layout conversion ---------------------------------------------------------------- */
 /*
  * native -> reference tuple for tokens [t0, t0+T): idx int32 (B,H,T,n) in reference order,

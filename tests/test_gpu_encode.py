@@ -168,3 +168,24 @@ def test_full_size_properties_config2_slice():
     dense = q.decode(pk, 0, 0, dtype=torch.float32, scale_first=True)
     cos = torch.nn.functional.cosine_similarity(dense.view(-1, 4), x.float().view(-1, 4), dim=-1)
     assert cos.mean() > 0.98
+
+
+def test_side_buffer_overflow_is_reported_not_fatal():
+    """A side buffer that is too small: rows, flags and counts stay complete, the status word of the call's
+    workspace says so (hqmq_read_status), and nothing is written past the capacity."""
+    S, br, C, d, H, B, T = 96, 4, 3.0, 128, 2, 1, 256
+    K = make_kv("hot", (B, H, T, d), seed=9, dtype=torch.bfloat16).cuda()
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, H, S, br, device="cuda"), C)
+    full = q.encode(K, 0, 0)
+    need = int(full.out_count.max())
+    assert need > 64
+    small = q.inner.new_cache(B, T, d, "cuda", scale_dtype=torch.bfloat16, with_outliers=True,
+                              out_dtype=torch.bfloat16, out_cap=64)
+    guard = small.out_vals.clone()
+    with pytest.raises(hqmq.HqmqError, match="side buffer too small"):
+        q.inner.encode(K, 0, 0, out=small, median_mult=C, check_status=True)
+    assert torch.equal(small.flags[:B * H * T], full.flags[:B * H * T])
+    assert torch.equal(small.out_count, full.out_count)
+    n_per = small.out_cap * 4
+    assert torch.equal(small.out_vals[:n_per], full.out_vals[:n_per])          # the entries that fit are the right ones
+    assert torch.equal(small.out_vals[H * n_per:], guard[H * n_per:])            # nothing past the planes

@@ -51,7 +51,7 @@ def test_static_scratch_matches_workspace_entry_point(outliers):
 
 def test_static_scratch_rejects_oversized_problems():
     L = _lib.lib()
-    B, Hq, Hkv, T, d = 256, 64, 8, 64, 64
+    B, Hq, Hkv, T, d = 512, 64, 8, 64, 128
     q = hqmq.HQMQ(1, Hkv, 24, 3, device="cuda")
     Kp = q.new_cache(B, T, d, "cuda")
     Vp = q.new_cache(B, T, d, "cuda")

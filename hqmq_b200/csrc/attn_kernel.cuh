@@ -238,6 +238,45 @@ struct FastLoader {
     cut<GG>(raw.vw[I], idx, rr);
     if constexpr (N % 8 != 0) { if (r * NVG + GG >= N) { idx = 0; rr = __float2half2_rn(0.f); } }
   }
+  // The same, but straight to the byte offset of the codeword in a table whose entries are `stride` bytes
+  // apart (plus this lane's replica offset).  With two 16-bit fields per word the shifts are done by the
+  // multiplier: offset = hi32(masked field * (stride << 16)), radius pair = hi32(masked nibbles << 20), which
+  // keeps them off the half-rate shift/logic pipe.  Used by the full-table (outlier) kernels only: with the
+  // sign-folded table the same change measured 13 % slower.
+  uint32_t mul_lo, mul_hi, lane_off;   // stride (halved for a sign-folded table), the same << 16, replica offset
+  __device__ __forceinline__ void set_table(uint32_t rstride, uint32_t lane_off_) {
+    mul_lo = FOLD ? rstride >> 1 : rstride; mul_hi = mul_lo << 16; lane_off = lane_off_;
+  }
+  static __device__ __forceinline__ uint32_t mad_hi(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+  }
+  template <int F>
+  __device__ __forceinline__ void cut_off(const uint32_t* w, uint32_t& off, __half2& rr) const {
+    if constexpr (CB == 16 && !FOLD) {
+      constexpr int bit = F * CB, a = bit >> 5, s = bit & 31;
+      const uint32_t word = w[a];
+      constexpr uint32_t imask = (1u << IB) - 1u;
+      if constexpr (s == 0) off = (word & imask) * mul_lo + lane_off;
+      else off = mad_hi(word & (imask << 16), mul_hi, lane_off);
+      constexpr uint32_t rmask = (((1u << RB) - 1u) << IB) * 0x10001u;
+      uint32_t bits = mad_hi(word & rmask, 1u << (32 - IB), 0x64006400u);
+      const __half2 pair = __hsub2(*reinterpret_cast<__half2*>(&bits), __float2half2_rn(1024.f));
+      rr = s == 0 ? __low2half2(pair) : __high2half2(pair);
+    } else {
+      uint32_t idx;
+      cut<F>(w, idx, rr);
+      off = idx * (FOLD ? mul_lo * 2u : mul_lo) + lane_off;
+    }
+  }
+  template <int NT, int KS> __device__ __forceinline__ void koff(const Raw& raw, uint32_t& off, __half2& rr) const {
+    cut_off<KS>(raw.kw[NT], off, rr);
+  }
+  template <int I, int GG> __device__ __forceinline__ void voff(const Raw& raw, uint32_t& off, __half2& rr) const {
+    cut_off<GG>(raw.vw[I], off, rr);
+    if constexpr (N % 8 != 0) { if (r * NVG + GG >= N) { off = lane_off; rr = __float2half2_rn(0.f); } }
+  }
   // scale of token nt*8 + r
   __device__ __forceinline__ float kscale(const Raw& raw, int nt) const { return bits16_to_float(raw.rsk[nt], sdt); }
   __device__ __forceinline__ float vscale(const Raw& raw, int nt) const { return bits16_to_float(raw.rsv[nt], sdt); }

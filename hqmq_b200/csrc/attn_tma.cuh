@@ -267,6 +267,7 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
       typename FL::Raw cur;
       FL ld;
       ld.row_bytes = ROW; ld.row_words = ROW / 4; ld.j = j; ld.r = r; ld.sdt = p.K.scale_dtype;
+      ld.set_table(rstride, lane_off);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         const int tr = nt * 8 + r;
@@ -320,8 +321,8 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         static_for<0, 2>([&](auto nt_) {
           constexpr int nt = decltype(nt_)::value;
           uint32_t idx; __half2 rr;
-          ld.template kfield<nt, ks>(cur, idx, rr);
-          const uint2 cw = *reinterpret_cast<const uint2*>(tblK + (idx * rstride + lane_off));
+          ld.template koff<nt, ks>(cur, idx, rr);
+          const uint2 cw = *reinterpret_cast<const uint2*>(tblK + idx);
           a[nt] = hmul2_u32(cw.x, rr);
           a[2 + nt] = hmul2_u32(cw.y, rr);
         });
@@ -456,8 +457,8 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
           static_for<0, 4>([&](auto i_) {
             constexpr int i = decltype(i_)::value;
             uint32_t idx; __half2 rr;
-            ld.template vfield<i, g>(cur, idx, rr);
-            const uint2 cw = *reinterpret_cast<const uint2*>(tblV + (idx * rstride + lane_off));
+            ld.template voff<i, g>(cur, idx, rr);
+            const uint2 cw = *reinterpret_cast<const uint2*>(tblV + idx);
             lo[i] = hmul2_u32(cw.x, rr);
             hi[i] = hmul2_u32(cw.y, rr);
             if constexpr (PATCH) {

@@ -23,6 +23,8 @@ constexpr int kEncWarps = kEncThreads / 32;
 constexpr int kEncIters = 8;      // token groups per block
 constexpr int kHistBins = 2048;   // 11-bit digits: bits [31:21], [20:10], then 10 bits [9:0]
 constexpr int kMaxRowWords = 20;
+constexpr int kBandWords = 4;     // per head: thr_lo bits, thr_hi bits, undecided chunks seen, spare
+constexpr int kUndCap = 4096;     // undecided chunks listed per head; more -> the fix-up re-scans x instead
 
 // ---- nearest-codeword look-up table -------------------------------------------------------------------
 // The unit direction u is first folded by the axis unit g = sign(u_i*) e_i* of its largest component
@@ -57,7 +59,6 @@ struct EncWs {
   uint32_t* status;   // [4]
   uint32_t* hist;     // [H][3 levels][2 queries][kHistBins]
   uint32_t* sel;      // [H][8]: prefix_lo, rank_lo, prefix_hi, rank_hi, a_bits, b_bits, thr_bits, med_bits
-  uint32_t* blk;      // [B*H][nblk_call + 1] flagged chunks per 16-token block of this call
 };
 
 __device__ __forceinline__ void load_chunk(const void* x, int64_t off, int dtype, float v[4]) {
@@ -439,7 +440,7 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
 // Level 0 histogram (bits 31:21) is accumulated by encode_main_kernel into query slot 0.
 __global__ void __launch_bounds__(256)
 select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level, uint64_t N, float C,
-              float* __restrict__ med_out) {
+              float* __restrict__ med_out, uint32_t* __restrict__ band) {
   __shared__ uint64_t wtot[8];
   const int h = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;   // launched with 256 threads
@@ -494,6 +495,12 @@ select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level
   }
   __syncthreads();
   if (tid != 0) return;
+  if (level == 1 && band) {
+    // 22 bits of both order statistics are known: a >= prefix_a, b <= prefix_b | 0x3ff, a <= med <= b, and
+    // thr = fl(med * C) is monotone in med, so it lies in [fl(a_lo * C), fl(b_hi * C)]
+    band[h * kBandWords + 0] = __float_as_uint(__fmul_rn(__uint_as_float(st[0]), C));
+    band[h * kBandWords + 1] = __float_as_uint(__fmul_rn(__uint_as_float(st[2] | 0x3ffu), C));
+  }
   if (level == 2) {
     const float a = __uint_as_float(st[0]), b = __uint_as_float(st[2]);
     float med = (N & 1) ? a : __fsub_rn(b, __fmul_rn(__fsub_rn(b, a), 0.5f));
@@ -621,21 +628,48 @@ hist32_kernel(Fast32 f, uint32_t* __restrict__ hist, const uint32_t* __restrict_
   }
 }
 
+// Clear the radius code of chunk c in a packed row (atomics: other threads may own neighbouring chunks).
+__device__ __forceinline__ void clear_radius(uint32_t* rowp, int c, int ib, int rbits) {
+  const int cb = ib + rbits;
+  const int lo = c * cb + ib, hi = (c + 1) * cb;   // bit range of the radius code
+  const int w0 = lo >> 5, w1 = (hi - 1) >> 5;
+  const uint32_t m0 = ~0u << (lo & 31);
+  const uint32_t m1 = (hi & 31) ? ~(~0u << (hi & 31)) : ~0u;
+  if (w0 == w1) atomicAnd(&rowp[w0], ~(m0 & m1));
+  else { atomicAnd(&rowp[w0], ~m0); atomicAnd(&rowp[w1], ~m1); }
+}
+
+// Flag a chunk found to be an outlier after the provisional pass.
+__device__ __forceinline__ void flag_late(const hqmq_packed& dst, int64_t row, int c, int ib, int rbits) {
+  atomicOr(&dst.flags[row], 1u << c);
+  clear_radius(reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes), c, ib, rbits);
+}
+
+// Last histogram level and the flags in ONE pass over x.  After level 1 the threshold is known to lie in
+// [thr_lo, thr_hi] (a relative width of 2^-13): a chunk above thr_hi is an outlier whatever the last ten
+// bits of the median turn out to be, a chunk at or below thr_lo is not, and the (normally empty) set in
+// between is listed for fixup_list_kernel; if the list overflows, fixup_scan_kernel re-reads x for that head.
+// A flagged chunk is stored in the side buffer: its radius code in the packed row becomes 0 so that decoding
+// the row contributes nothing for it.
 template <int DT>
 __global__ void __launch_bounds__(256)
-flags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, const uint32_t* __restrict__ sel,
-               uint32_t* __restrict__ blk, int blk0, int nblk) {
+histflags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, uint32_t* __restrict__ hist,
+                   const uint32_t* __restrict__ sel, uint32_t* __restrict__ band, uint32_t* __restrict__ und) {
+  __shared__ uint32_t sh[2][1024];
   const int bh = blockIdx.y;
   const int h = bh % f.H, b = bh / f.H;
-  const float thr = __uint_as_float(sel[h * 8 + 6]);
+  for (int i = threadIdx.x; i < 2 * 1024; i += blockDim.x) (&sh[0][0])[i] = 0;
+  __syncthreads();
+  const uint32_t q0 = sel[h * 8 + 0] >> 10, q1 = sel[h * 8 + 2] >> 10;
+  const bool same = q0 == q1;
+  const float thr_lo = __uint_as_float(band[h * kBandWords + 0]), thr_hi = __uint_as_float(band[h * kBandWords + 1]);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, l16 = lane & 15;
-  const uint32_t halfmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
   int per = (f.T_new + gridDim.x - 1) / gridDim.x;
   per = (per + kF32Tok - 1) / kF32Tok * kF32Tok;
   const int t0 = blockIdx.x * per, t1 = min(f.T_new, t0 + per);
   const uint16_t* base = f.x + b * f.xs_b + h * f.xs_h + 8 * l16;
-  const int cb = ib + rbits;
-  for (int t = t0 + warp * 2 + (lane >> 4); t < t1; t += kF32Tok) {
+  for (int tb = t0 + warp * 2; tb < t1; tb += kF32Tok) {      // warp-uniform trip count: the halves shuffle below
+    const int t = tb + (lane >> 4);
     uint4 r[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u)
@@ -643,42 +677,101 @@ flags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, const 
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int tu = t + 16 * u;
-      if (tu < t1) {        // uniform over the half warp that shares the token
+      const bool live = tu < t1;
+      uint32_t m = 0;
+      if (live) {
         float n[2];
         norms_of_two<DT>(r[u], n[0], n[1]);
-        const uint32_t m = (n[0] > thr ? 1u : 0u) | (n[1] > thr ? 2u : 0u);
-        const uint32_t word = __reduce_or_sync(halfmask, m << (2 * l16));
-        const int64_t row = (int64_t)bh * dst.T_cap + t_start + tu;
-        if (m) {
-          // A flagged chunk is stored in the side buffer: its radius code in the packed row becomes 0 so
-          // that decoding the row contributes nothing for it.
-          uint32_t* rowp = reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes);
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            if ((m >> e) & 1u) {
-              const int c = 2 * l16 + e;
-              const int lo = c * cb + ib, hi = (c + 1) * cb;   // bit range of the radius code
-              const int w0 = lo >> 5, w1 = (hi - 1) >> 5;
-              const uint32_t m0 = ~0u << (lo & 31);
-              const uint32_t m1 = (hi & 31) ? ~(~0u << (hi & 31)) : ~0u;
-              if (w0 == w1) atomicAnd(&rowp[w0], ~(m0 & m1));
-              else { atomicAnd(&rowp[w0], ~m0); atomicAnd(&rowp[w1], ~m1); }
-            }
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t key = __float_as_uint(n[e]);
+          const uint32_t top = key >> 10;
+          if (top == q0) atomicAdd(&sh[0][key & 0x3ffu], 1u);
+          else if (top == q1) atomicAdd(&sh[1][key & 0x3ffu], 1u);
+          if (n[e] > thr_hi) m |= 1u << e;
+          else if (n[e] > thr_lo) {
+            const uint32_t pos = atomicAdd(&band[h * kBandWords + 2], 1u);
+            if (pos < (uint32_t)kUndCap) und[(int64_t)h * kUndCap + pos] = (uint32_t)(((int64_t)b * f.T_new + tu) * 32 + 2 * l16 + e);
           }
         }
-        if (l16 == 0) {
-          dst.flags[row] = word;
-          if (word) atomicAdd(&blk[(int64_t)bh * (nblk + 1) + ((t_start + tu) / HQMQ_OUT_BLOCK - blk0)], (uint32_t)__popc(word));
+      }
+      // the token's flag word: OR of the 16 lanes that share it (bits 2*l16 and 2*l16 + 1 each)
+      uint32_t word = m << (2 * l16);
+      word |= __shfl_xor_sync(0xffffffffu, word, 1);
+      word |= __shfl_xor_sync(0xffffffffu, word, 2);
+      word |= __shfl_xor_sync(0xffffffffu, word, 4);
+      word |= __shfl_xor_sync(0xffffffffu, word, 8);
+      if (live) {
+        const int64_t row = (int64_t)bh * dst.T_cap + t_start + tu;
+        if (m) {
+          uint32_t* rowp = reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes);
+          if (m & 1u) clear_radius(rowp, 2 * l16, ib, rbits);
+          if (m & 2u) clear_radius(rowp, 2 * l16 + 1, ib, rbits);
         }
+        if (l16 == 0) dst.flags[row] = word;
       }
     }
   }
+  __syncthreads();
+  uint32_t* gh = hist + ((int64_t)h * 3 + 2) * 2 * kHistBins;
+  for (int i = threadIdx.x; i < 1024; i += blockDim.x) {
+    const uint32_t c0 = sh[0][i], c1 = same ? c0 : sh[1][i];
+    if (c0) atomicAdd(&gh[i], c0);
+    if (c1) atomicAdd(&gh[kHistBins + i], c1);
+  }
 }
 
-// Flags: one lane group per token; counts flagged chunks per 16-token block of the cache.
+// The undecided chunks of one head against the exact threshold (one CTA per head).
+template <int DT>
 __global__ void __launch_bounds__(256)
-flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, const uint32_t* __restrict__ sel,
-             uint32_t* __restrict__ blk, int blk0, int nblk) {
+fixup_list_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, const uint32_t* __restrict__ sel,
+                  const uint32_t* __restrict__ band, const uint32_t* __restrict__ und) {
+  const int h = blockIdx.x;
+  const uint32_t n = band[h * kBandWords + 2];
+  if (n == 0 || n > (uint32_t)kUndCap) return;
+  const float thr = __uint_as_float(sel[h * 8 + 6]);
+  for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const uint32_t e = und[(int64_t)h * kUndCap + i];
+    const int c = e & 31;
+    const int64_t bt = e >> 5;
+    const int b = (int)(bt / f.T_new), t = (int)(bt - (int64_t)b * f.T_new);
+    const uint2 raw = *reinterpret_cast<const uint2*>(f.x + b * f.xs_b + h * f.xs_h + (int64_t)t * f.xs_t + 4 * c);
+    float v[4];
+    v[0] = bits16_to_float(raw.x & 0xffff, DT); v[1] = bits16_to_float(raw.x >> 16, DT);
+    v[2] = bits16_to_float(raw.y & 0xffff, DT); v[3] = bits16_to_float(raw.y >> 16, DT);
+    if (chunk_norm(v) > thr) flag_late(dst, ((int64_t)b * f.H + h) * dst.T_cap + t_start + t, c, ib, rbits);
+  }
+}
+
+// Fallback when a head's list overflowed: re-read x and settle every chunk between the two bounds.
+template <int DT>
+__global__ void __launch_bounds__(256)
+fixup_scan_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, const uint32_t* __restrict__ sel,
+                  const uint32_t* __restrict__ band) {
+  const int bh = blockIdx.y;
+  const int h = bh % f.H, b = bh / f.H;
+  if (band[h * kBandWords + 2] <= (uint32_t)kUndCap) return;
+  const float thr = __uint_as_float(sel[h * 8 + 6]);
+  const float thr_lo = __uint_as_float(band[h * kBandWords + 0]), thr_hi = __uint_as_float(band[h * kBandWords + 1]);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, l16 = lane & 15;
+  int per = (f.T_new + gridDim.x - 1) / gridDim.x;
+  per = (per + kF32Tok - 1) / kF32Tok * kF32Tok;
+  const int t0 = blockIdx.x * per, t1 = min(f.T_new, t0 + per);
+  const uint16_t* base = f.x + b * f.xs_b + h * f.xs_h + 8 * l16;
+  for (int t = t0 + warp * 2 + (lane >> 4); t < t1; t += 16) {
+    const uint4 r = *reinterpret_cast<const uint4*>(base + (int64_t)t * f.xs_t);
+    float n[2];
+    norms_of_two<DT>(r, n[0], n[1]);
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+      if (n[e] > thr_lo && !(n[e] > thr_hi) && n[e] > thr)
+        flag_late(dst, (int64_t)bh * dst.T_cap + t_start + t, 2 * l16 + e, ib, rbits);
+  }
+}
+
+// Flags: one lane group per token.
+__global__ void __launch_bounds__(256)
+flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, const uint32_t* __restrict__ sel) {
   const int bh = blockIdx.y;
   const int h = bh % g.H, b = bh / g.H;
   const float thr = __uint_as_float(sel[h * 8 + 6]);
@@ -717,39 +810,77 @@ flags_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start
     if (t < g.T_new && c == 0) {
       const uint32_t mask = g.npl == 32 ? 0xffffffffu : ((1u << g.npl) - 1u);
       const uint32_t word = (bal >> (sub * g.npl)) & mask;
-      const int ta = t_start + t;
-      dst.flags[(int64_t)bh * dst.T_cap + ta] = word;
-      if (word) atomicAdd(&blk[(int64_t)bh * (nblk + 1) + (ta / HQMQ_OUT_BLOCK - blk0)], (uint32_t)__popc(word));
+      dst.flags[(int64_t)bh * dst.T_cap + t_start + t] = word;
     }
    }
   }
 }
 
-// Per (b,h), one warp: running offsets of the outlier payload for the blocks this call touches.
+// Distinct flagged chunk positions of a 16-token block -> records the block owns (0 when it has none,
+// or more than HQMQ_OFRAG_MAX_PER_TILE records would be needed).
+__device__ __forceinline__ int ofrag_records_for(uint32_t any_c) {
+  const int nd = __popc(any_c);
+  const int ng = (nd + 3) >> 2;
+  return ng <= HQMQ_OFRAG_MAX_PER_TILE ? ng : 0;
+}
+
+// Per (b,h), one warp, one lane per 16-token block of this call: the block's flagged chunks are counted
+// from its flag words and scanned into the payload offsets; with a fragment plane, also the record offsets
+// (only blocks the call covers completely get records; a block whose records would pass the capacity, and
+// every block after it in this call, gets none).  `payload` = 0 on a call without Med3x (nothing flagged).
 __global__ void __launch_bounds__(128)
-scan_kernel(hqmq_packed dst, int t_start, int T_new, uint32_t* __restrict__ blk, int blk0, int nblk,
-            uint32_t* __restrict__ status) {
+scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk, int payload, uint32_t* __restrict__ status) {
   const int bh = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (bh >= dst.B * dst.H) return;
   const int nb_cap = dst.T_cap / HQMQ_OUT_BLOCK + 1;
   uint32_t* off = dst.out_off + (int64_t)bh * nb_cap;
-  const uint32_t* cnt = blk + (int64_t)bh * (nblk + 1);
-  uint32_t run = dst.out_count[bh];
+  uint32_t* foff = dst.ofrag ? dst.ofrag_off + (int64_t)bh * nb_cap : nullptr;
+  const uint32_t* fl = dst.flags + (int64_t)bh * dst.T_cap;
+  uint32_t run = payload ? dst.out_count[bh] : 0u;
+  uint32_t frun = foff ? foff[blk0] : 0u;
+  bool full = false;
+  const int t_end = t_start + T_new;
   for (int i0 = 0; i0 < nblk; i0 += 32) {
-    const int i = i0 + lane;
-    const uint32_t c = i < nblk ? cnt[i] : 0u;
-    uint32_t incl = c;
+    const int i = i0 + lane, ba = blk0 + i;
+    uint32_t c = 0, any_c = 0;
+    if (i < nblk) {
+      const int tb = ba * HQMQ_OUT_BLOCK;
+#pragma unroll
+      for (int q = 0; q < HQMQ_OUT_BLOCK / 4; ++q) {
+        const uint4 w = *reinterpret_cast<const uint4*>(fl + tb + 4 * q);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int t = tb + 4 * q + k;
+          if (t >= t_start && t < t_end) { c += __popc(ww[k]); any_c |= ww[k]; }   // tokens of this call only
+        }
+      }
+    }
+    const bool whole = i < nblk && ba * HQMQ_OUT_BLOCK >= t_start && (ba + 1) * HQMQ_OUT_BLOCK <= t_end;
+    const uint32_t fc = foff && whole ? (uint32_t)ofrag_records_for(any_c) : 0u;
+    uint32_t incl = c, fincl = fc;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
+      const uint32_t fv = __shfl_up_sync(0xffffffffu, fincl, o);
+      if (lane >= o) { incl += v; fincl += fv; }
     }
-    // A block that already holds tokens from an earlier call keeps its offset.
-    if (i < nblk && !(i == 0 && (t_start % HQMQ_OUT_BLOCK) != 0)) off[blk0 + i] = run + incl - c;
-    run += __shfl_sync(0xffffffffu, incl, 31);
+    if (payload) {
+      // A block that already holds tokens from an earlier call keeps its offset.
+      if (i < nblk && !(i == 0 && (t_start % HQMQ_OUT_BLOCK) != 0)) off[ba] = run + incl - c;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (foff) {
+      fincl += frun;
+      const bool ok = !full && fincl <= (uint32_t)dst.ofrag_cap;
+      const uint32_t last_ok = __reduce_max_sync(0xffffffffu, ok ? fincl : frun);
+      if (i < nblk) foff[ba + 1] = ok ? fincl : last_ok;
+      full = full || __any_sync(0xffffffffu, !ok);
+      frun = last_ok;
+    }
   }
-  if (lane == 0) {
+  if (payload && lane == 0) {
     off[blk0 + nblk] = run;
     if (run > (uint32_t)dst.out_cap) atomicOr(&status[0], 1u);
     dst.out_count[bh] = run;
@@ -793,54 +924,6 @@ payload_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_sta
 
 
 // ---- fragment records (optional `ofrag` plane) ---------------------------------------------------------
-// Distinct flagged chunk positions of a 16-token block -> records the block owns (0 when it has none,
-// or more than HQMQ_OFRAG_MAX_PER_TILE records would be needed).
-__device__ __forceinline__ int ofrag_records_for(uint32_t any_c) {
-  const int nd = __popc(any_c);
-  const int ng = (nd + 3) >> 2;
-  return ng <= HQMQ_OFRAG_MAX_PER_TILE ? ng : 0;
-}
-
-// One warp per (b, h): record offsets of the blocks this call touches.  Only blocks the call covers
-// completely get records; a block whose records would pass the capacity, and every block after it in this
-// call, gets none.
-__global__ void __launch_bounds__(128)
-ofrag_scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk) {
-  const int bh = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (bh >= dst.B * dst.H) return;
-  const int nb_cap = dst.T_cap / HQMQ_OUT_BLOCK + 1;
-  uint32_t* off = dst.ofrag_off + (int64_t)bh * nb_cap;
-  const uint4* fl = reinterpret_cast<const uint4*>(dst.flags + (int64_t)bh * dst.T_cap);
-  uint32_t run = off[blk0];
-  bool full = false;
-  for (int i0 = 0; i0 < nblk; i0 += 32) {
-    const int i = i0 + lane, ba = blk0 + i;
-    uint32_t cnt = 0;
-    if (i < nblk && ba * HQMQ_OUT_BLOCK >= t_start && (ba + 1) * HQMQ_OUT_BLOCK <= t_start + T_new) {
-      uint32_t any_c = 0;
-#pragma unroll
-      for (int q = 0; q < HQMQ_OUT_BLOCK / 4; ++q) {
-        const uint4 w = fl[(int64_t)ba * (HQMQ_OUT_BLOCK / 4) + q];
-        any_c |= w.x | w.y | w.z | w.w;
-      }
-      cnt = (uint32_t)ofrag_records_for(any_c);
-    }
-    uint32_t incl = cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
-    }
-    incl += run;
-    const bool ok = !full && incl <= (uint32_t)dst.ofrag_cap;
-    const uint32_t last_ok = __reduce_max_sync(0xffffffffu, ok ? incl : run);
-    if (i < nblk) off[ba + 1] = ok ? incl : last_ok;
-    full = full || __any_sync(0xffffffffu, !ok);
-    run = last_ok;
-  }
-}
-
 // One warp per block: writes the block's records (see the layout in include/hqmq_b200.h).
 __global__ void __launch_bounds__(256)
 ofrag_fill_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, int blk0, int nblk) {
@@ -1045,17 +1128,18 @@ Mul8x24 make_mul() {
 inline size_t lut_bytes(int H) { return (size_t)H * kLutHdr * 4 + (size_t)H * kLutCandCap * 2; }
 inline size_t lut_ws_bytes(int H) { return (size_t)H * kLutCells * 4 + (size_t)H * kLutCells * kLutMaxList * 2; }
 
-struct WsPlan { size_t status, hist, sel, blk, total; int blk0, nblk; };
+struct WsPlan { size_t status, hist, sel, band, und, total; int blk0, nblk; };
 WsPlan plan_ws(const hqmq_encode_args& a) {
   WsPlan w;
-  const int H = a.dst.H, BH = a.dst.B * a.dst.H;
+  const int H = a.dst.H;
   w.blk0 = a.t_start / HQMQ_OUT_BLOCK;
   w.nblk = a.T_new > 0 ? (a.t_start + a.T_new - 1) / HQMQ_OUT_BLOCK - w.blk0 + 1 : 0;
   size_t o = 0;
   w.status = o; o += 4;
   w.hist = o; o += (size_t)H * 3 * 2 * kHistBins;
   w.sel = o; o += (size_t)H * 8;
-  w.blk = o; o += (size_t)BH * (w.nblk + 1);
+  w.band = o; o += (size_t)H * kBandWords;
+  w.und = o; o += (size_t)H * kUndCap;
   w.total = o * sizeof(uint32_t);
   return w;
 }
@@ -1211,7 +1295,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   if (!med) {
     // no chunk of this call is flagged: the record offsets of its blocks just carry the running total on
     if (d.ofrag) {
-      ofrag_scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk);
+      scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, 0, ws + wp.status);
       HQMQ_LAUNCH_CHECK();
     }
     return HQMQ_OK;
@@ -1227,45 +1311,52 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   if (hb < 1) hb = 1;
   uint32_t* hist = ws + wp.hist;
   uint32_t* sel = ws + wp.sel;
-  // fast passes: d_head 128, 16-bit input, token rows on 16-byte boundaries
+  // fast passes: d_head 128, 16-bit input, token rows on 16-byte boundaries (the fused last pass lists
+  // undecided chunks by a 32-bit index over the (batch, token, chunk) grid of a head)
   const bool fast32 = g.n == 32 && is_half_dtype(a->x_dtype) && ((uintptr_t)a->x & 15) == 0 && g.xs_b % 8 == 0 &&
-                      g.xs_h % 8 == 0 && g.xs_t % 8 == 0;
+                      g.xs_h % 8 == 0 && g.xs_t % 8 == 0 && (int64_t)d.B * a->T_new * 32 < ((int64_t)1 << 32);
   Fast32 f32{reinterpret_cast<const uint16_t*>(a->x), g.xs_b, g.xs_h, g.xs_t, d.H, a->T_new};
   int fgrid = (148 * 16 + bh_count - 1) / bh_count;
   const int fgrid_max = (a->T_new + kF32Tok - 1) / kF32Tok;
   if (fgrid > fgrid_max) fgrid = fgrid_max;
   if (fgrid < 1) fgrid = 1;
-  auto launch_hist = [&](int level) {
-    if (!fast32) hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, level);
-    else if (a->x_dtype == HQMQ_F16) hist32_kernel<HQMQ_F16><<<dim3(fgrid, d.B * d.H), 256, 0, st>>>(f32, hist, sel, level);
-    else hist32_kernel<HQMQ_BF16><<<dim3(fgrid, d.B * d.H), 256, 0, st>>>(f32, hist, sel, level);
-  };
-  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr);
-  launch_hist(1);
-  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr);
-  launch_hist(2);
-  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out);
-  HQMQ_LAUNCH_CHECK();
-
+  const dim3 f32_grid(fgrid, d.B * d.H);
+  const bool h16 = a->x_dtype == HQMQ_F16;
+  uint32_t* band = ws + wp.band;
+  uint32_t* und = ws + wp.und;
+  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr, nullptr);
   if (fast32) {
-    if (a->x_dtype == HQMQ_F16)
-      flags32_kernel<HQMQ_F16><<<dim3(fgrid, d.B * d.H), 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, ws + wp.blk, wp.blk0, wp.nblk);
-    else
-      flags32_kernel<HQMQ_BF16><<<dim3(fgrid, d.B * d.H), 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, ws + wp.blk, wp.blk0, wp.nblk);
+    if (h16) hist32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1);
+    else hist32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, band);
+    // last histogram level and provisional flags in one pass, exact threshold, then the (normally empty) fix-up
+    if (h16) histflags32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und);
+    else histflags32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr);
+    if (h16) {
+      fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und);
+      fixup_scan_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band);
+    } else {
+      fixup_list_kernel<HQMQ_BF16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und);
+      fixup_scan_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band);
+    }
   } else {
+    hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 1);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, nullptr);
+    hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 2);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr);
     const int tok_per_fblock = 8 * g.tpw;
     int fb = (a->T_new + 4 * tok_per_fblock - 1) / (4 * tok_per_fblock);
     const int fb_cap = (148 * 32 + bh_count - 1) / bh_count;
     if (fb > fb_cap) fb = fb_cap;
     if (fb < 1) fb = 1;
-    flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel, ws + wp.blk, wp.blk0, wp.nblk);
+    flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel);
   }
-  scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, ws + wp.blk, wp.blk0, wp.nblk, ws + wp.status);
+  HQMQ_LAUNCH_CHECK();
+  scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, 1, ws + wp.status);
   payload_kernel<<<dim3((a->T_new + 255) / 256, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start);
-  if (d.ofrag) {
-    ofrag_scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk);
+  if (d.ofrag)
     ofrag_fill_kernel<<<dim3((wp.nblk + 7) / 8, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, wp.blk0, wp.nblk);
-  }
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }

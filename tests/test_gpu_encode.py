@@ -189,3 +189,42 @@ def test_side_buffer_overflow_is_reported_not_fatal():
     n_per = small.out_cap * 4
     assert torch.equal(small.out_vals[:n_per], full.out_vals[:n_per])          # the entries that fit are the right ones
     assert torch.equal(small.out_vals[H * n_per:], guard[H * n_per:])            # nothing past the planes
+
+
+@pytest.mark.parametrize("T", [256, 4096])
+def test_med3x_chunks_next_to_the_threshold(T):
+    """The 16-bit fast path decides most flags before the last ten bits of the median are known and settles
+    the chunks within 2^-13 of the threshold afterwards (from a list, or by re-reading x when the list
+    overflows: T = 4096).  Norms exactly at the threshold must stay unflagged (strict compare)."""
+    B, H, d, S, br, C = 1, 2, 128, 96, 4, 3.0
+    n = d // 4
+    g = torch.Generator().manual_seed(5)
+    kind = torch.rand(B, H, T, n, generator=g)
+    near, far = (kind >= 0.6) & (kind < 0.8), kind >= 0.8
+    x = torch.zeros(B, H, T, n, 4)
+    x[..., 0] = 1.0                                                    # 60 % of the chunks: norm exactly 1 = the median
+    eps = torch.randint(0, 5, (B, H, T, n), generator=g).float() * 0.01
+    x[..., 0] = torch.where(near, torch.tensor(3.0), x[..., 0])        # norm sqrt(9 + eps^2): 3 or just above
+    x[..., 1] = torch.where(near, eps, x[..., 1])
+    x[..., 0] = torch.where(far, torch.rand(B, H, T, n, generator=g) * 8.0, x[..., 0])
+    x = x.view(B, H, T, d).bfloat16()
+    joint = orc.joint_codebook(orc.secondary_raw(1, H, S, 42)[0, :, 0])
+    enc = orc.encode(x.float(), joint, br, C)
+    assert torch.equal(enc["med"], torch.ones(H))
+    norms = x.float().view(B, H, T, n, 4).norm(dim=-1)
+    band = (norms > 3.0) & (norms < 3.0004)
+    assert int(band.sum()) > (4096 if T == 4096 else 100) * H            # the list really overflows at T = 4096
+    assert enc["flags"][band].all() and not enc["flags"][norms == 3.0].any() and (norms == 3.0).any()
+    q = hqmq.HQMQ(n_layers=1, n_heads=H, secondary_size=S, radius_bits=br, device="cuda", seed=42)
+    med = torch.zeros(H, device="cuda")
+    pk = q.encode(x.cuda(), 0, 0, median_mult=C, scale_dtype=torch.float32, med_out=med)
+    idx, rq, rs, flags = pk.to_reference()
+    assert torch.equal(med.cpu(), enc["med"])
+    assert torch.equal(flags.cpu(), enc["flags"]), "outlier flags differ"
+    assert torch.equal(rq.cpu(), torch.where(enc["flags"], 0, enc["rq"])), "radius codes differ"
+    assert torch.equal(pk.out_count.cpu().view(B, H), enc["flags"].sum(dim=(2, 3)).int())
+    xc = x.view(B, H, T, n, 4)
+    ov = pk.out_vals.cpu()[: B * H * pk.out_cap * 4].view(B, H, pk.out_cap, 4)
+    for h in range(H):
+        want = xc[0, h][enc["flags"][0, h]]
+        assert torch.equal(ov[0, h, : want.shape[0]], want)

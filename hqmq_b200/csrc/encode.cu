@@ -668,6 +668,8 @@ histflags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, ui
   per = (per + kF32Tok - 1) / kF32Tok * kF32Tok;
   const int t0 = blockIdx.x * per, t1 = min(f.T_new, t0 + per);
   const uint16_t* base = f.x + b * f.xs_b + h * f.xs_h + 8 * l16;
+  const bool cb16 = ib + rbits == 16;
+  const uint32_t rmask16 = (0xffffu >> ib) << ib;             // radius bits of a 16-bit field
   for (int tb = t0 + warp * 2; tb < t1; tb += kF32Tok) {      // warp-uniform trip count: the halves shuffle below
     const int t = tb + (lane >> 4);
     uint4 r[4];
@@ -705,8 +707,13 @@ histflags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, ui
         const int64_t row = (int64_t)bh * dst.T_cap + t_start + tu;
         if (m) {
           uint32_t* rowp = reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes);
-          if (m & 1u) clear_radius(rowp, 2 * l16, ib, rbits);
-          if (m & 2u) clear_radius(rowp, 2 * l16 + 1, ib, rbits);
+          if (cb16) {
+            // 16-bit fields: both chunks of this lane live in word l16 of the row, one atomic clears either or both
+            atomicAnd(&rowp[l16], ~(((m & 1u) ? rmask16 : 0u) | ((m & 2u) ? rmask16 << 16 : 0u)));
+          } else {
+            if (m & 1u) clear_radius(rowp, 2 * l16, ib, rbits);
+            if (m & 2u) clear_radius(rowp, 2 * l16 + 1, ib, rbits);
+          }
         }
         if (l16 == 0) dst.flags[row] = word;
       }

@@ -894,58 +894,65 @@ scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk, int pay
   }
 }
 
-// Payload: the original values of every flagged chunk, in (token, chunk) order.
+// Side planes of one 16-token block, one warp per block: the payload (original values of every flagged chunk,
+// in (token, chunk) order) and, for a block that owns fragment records, the records (layout in
+// include/hqmq_b200.h).  Lane l < 16 holds the flag word of token l of the block.
 __global__ void __launch_bounds__(256)
-payload_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start) {
-  const int bh = blockIdx.y;
-  const int h = bh % g.H, b = bh / g.H;
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= g.T_new) return;
-  const int ta = t_start + t;
-  const uint32_t* fl = dst.flags + (int64_t)bh * dst.T_cap;
-  uint32_t word = fl[ta];
-  if (!word) return;
-  const int blk = ta / HQMQ_OUT_BLOCK;
-  uint32_t pos = dst.out_off[(int64_t)bh * (dst.T_cap / HQMQ_OUT_BLOCK + 1) + blk];
-  for (int tt = blk * HQMQ_OUT_BLOCK; tt < ta; ++tt) pos += __popc(fl[tt]);
-  const int esz = dst.out_dtype == HQMQ_F32 ? 4 : 2;
-  unsigned char* base = reinterpret_cast<unsigned char*>(dst.out_vals) + (int64_t)bh * dst.out_cap * 4 * esz;
-  while (word) {
-    const int c = __ffs(word) - 1;
-    word &= word - 1;
-    if (pos < (uint32_t)dst.out_cap) {
-      float v[4];
-      load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
-      if (dst.out_dtype == HQMQ_F32) {
-        *reinterpret_cast<float4*>(base + (int64_t)pos * 16) = make_float4(v[0], v[1], v[2], v[3]);
-      } else {
-        uint2 o;
-        o.x = float_to_bits16(v[0], dst.out_dtype) | ((uint32_t)float_to_bits16(v[1], dst.out_dtype) << 16);
-        o.y = float_to_bits16(v[2], dst.out_dtype) | ((uint32_t)float_to_bits16(v[3], dst.out_dtype) << 16);
-        *reinterpret_cast<uint2*>(base + (int64_t)pos * 8) = o;
-      }
-    }
-    ++pos;
-  }
-}
-
-
-// ---- fragment records (optional `ofrag` plane) ---------------------------------------------------------
-// One warp per block: writes the block's records (see the layout in include/hqmq_b200.h).
-__global__ void __launch_bounds__(256)
-ofrag_fill_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, int blk0, int nblk) {
+side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, int blk0, int nblk) {
   const int bh = blockIdx.y;
   const int h = bh % g.H, b = bh / g.H;
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (i >= nblk) return;
   const int ba = blk0 + i;
-  const uint32_t* off = dst.ofrag_off + (int64_t)bh * (dst.T_cap / HQMQ_OUT_BLOCK + 1);
-  const uint32_t o0 = off[ba], o1 = off[ba + 1];
-  if (o1 <= o0) return;
+  const int nb_cap = dst.T_cap / HQMQ_OUT_BLOCK + 1;
   const int64_t row0 = (int64_t)bh * dst.T_cap + (int64_t)ba * HQMQ_OUT_BLOCK;
   const uint32_t fw = lane < HQMQ_OUT_BLOCK ? dst.flags[row0 + lane] : 0u;
   uint32_t any_c = __reduce_or_sync(0xffffffffu, fw);
+  if (!any_c) return;
+  const int64_t xbase = b * g.xs_b + h * g.xs_h;
+
+  // ---- payload: lane pair (l, l + 16) shares token l; the pair takes the token's flagged chunks alternately ----
+  {
+    uint32_t incl = __popc(fw);
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+      if ((lane & 15) >= o) incl += v;
+    }
+    const uint32_t before = __shfl_sync(0xffffffffu, incl - __popc(fw), lane & 15);   // flagged chunks of earlier tokens
+    uint32_t word = __shfl_sync(0xffffffffu, fw, lane & 15);
+    const int t = ba * HQMQ_OUT_BLOCK + (lane & 15) - t_start;                         // token index within this call
+    if (t >= 0 && t < g.T_new && word) {
+      uint32_t pos = dst.out_off[(int64_t)bh * nb_cap + ba] + before;
+      const int esz = dst.out_dtype == HQMQ_F32 ? 4 : 2;
+      unsigned char* base = reinterpret_cast<unsigned char*>(dst.out_vals) + (int64_t)bh * dst.out_cap * 4 * esz;
+      int k = 0;
+      while (word) {
+        const int c = __ffs(word) - 1;
+        word &= word - 1;
+        if ((k & 1) == (lane >> 4) && pos < (uint32_t)dst.out_cap) {
+          float v[4];
+          load_chunk(x, xbase + t * g.xs_t + 4 * c, g.x_dtype, v);
+          if (dst.out_dtype == HQMQ_F32) {
+            *reinterpret_cast<float4*>(base + (int64_t)pos * 16) = make_float4(v[0], v[1], v[2], v[3]);
+          } else {
+            uint2 o;
+            o.x = float_to_bits16(v[0], dst.out_dtype) | ((uint32_t)float_to_bits16(v[1], dst.out_dtype) << 16);
+            o.y = float_to_bits16(v[2], dst.out_dtype) | ((uint32_t)float_to_bits16(v[3], dst.out_dtype) << 16);
+            *reinterpret_cast<uint2*>(base + (int64_t)pos * 8) = o;
+          }
+        }
+        ++pos; ++k;
+      }
+    }
+  }
+
+  // ---- fragment records --------------------------------------------------------------------------------------
+  if (!dst.ofrag) return;
+  const uint32_t* off = dst.ofrag_off + (int64_t)bh * nb_cap;
+  const uint32_t o0 = off[ba], o1 = off[ba + 1];
+  if (o1 <= o0) return;
   const int j = lane & 3, r = lane >> 2;
   uint32_t fl[2]; float inv[2];
 #pragma unroll
@@ -970,7 +977,7 @@ ofrag_fill_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_
         if ((fl[nt] >> cj) & 1u) {
           const int t = ba * HQMQ_OUT_BLOCK + nt * 8 + r - t_start;
           float v[4];
-          load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * cj, g.x_dtype, v);
+          load_chunk(x, xbase + t * g.xs_t + 4 * cj, g.x_dtype, v);
           const __half2 h01 = __floats2half2_rn(v[0] * inv[nt], v[1] * inv[nt]);
           const __half2 h23 = __floats2half2_rn(v[2] * inv[nt], v[3] * inv[nt]);
           a[nt] = *reinterpret_cast<const uint32_t*>(&h01);
@@ -1361,9 +1368,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   }
   HQMQ_LAUNCH_CHECK();
   scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, 1, ws + wp.status);
-  payload_kernel<<<dim3((a->T_new + 255) / 256, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start);
-  if (d.ofrag)
-    ofrag_fill_kernel<<<dim3((wp.nblk + 7) / 8, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, wp.blk0, wp.nblk);
+  side_kernel<<<dim3((wp.nblk + 7) / 8, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, wp.blk0, wp.nblk);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }

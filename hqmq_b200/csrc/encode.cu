@@ -285,7 +285,8 @@ template <int DT, int IB, int RB>
 __global__ void __launch_bounds__(kEnc32Threads, 1)
 encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
                      int t_start, uint32_t* __restrict__ hist, Maps24 maps, const float* __restrict__ joint_all,
-                     const uint32_t* __restrict__ lut, int lut_cand_smem, NativeMul nmul, int iters) {
+                     const uint32_t* __restrict__ lut, int lut_cand_smem, NativeMul nmul, int iters,
+                     const uint32_t* __restrict__ sel_s) {
   constexpr int CB = IB + RB;
   constexpr int RW = 32 * CB / 32;                       // words per row
   constexpr float qmaxf = (float)((1 << RB) - 1);
@@ -293,7 +294,8 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
   float4* qs = reinterpret_cast<float4*>(smem_raw);
   uint32_t* rows = reinterpret_cast<uint32_t*>(qs + g.S);            // [warps][kMaxRowWords]
   uint32_t* shist = rows + kEnc32Warps * kMaxRowWords;                  // [kHistBins]
-  float4* sjoint = reinterpret_cast<float4*>(shist + kHistBins);      // [24 S]
+  uint32_t* sh1 = shist + kHistBins;                                  // [2][kHistBins]: next digit inside the predicted bins
+  float4* sjoint = reinterpret_cast<float4*>(sh1 + 2 * kHistBins);    // [24 S]
   uint32_t* soff = reinterpret_cast<uint32_t*>(sjoint + 24 * g.S);     // [kLutCells + 1]
   uint8_t* snm = reinterpret_cast<uint8_t*>(soff + kLutCells + 4);     // [8][24] (+ padding to 256)
   uint16_t* scand = reinterpret_cast<uint16_t*>(snm + 256);            // [lut_cand_smem]
@@ -307,7 +309,7 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
     const uint16_t* gc = reinterpret_cast<const uint16_t*>(lut + (int64_t)g.H * kLutHdr) + (int64_t)h * kLutCandCap;
     const uint32_t total = hdr[kLutCells];
     for (int i = threadIdx.x; i < S; i += blockDim.x) qs[i] = reinterpret_cast<const float4*>(qs_all)[(int64_t)h * S + i];
-    if (hist) for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) shist[i] = 0;
+    if (hist) for (int i = threadIdx.x; i < 3 * kHistBins; i += blockDim.x) shist[i] = 0;   // shist and sh1
     for (int i = threadIdx.x; i < 24 * S; i += blockDim.x) sjoint[i] = reinterpret_cast<const float4*>(joint_all)[(int64_t)h * 24 * S + i];
     for (int i = threadIdx.x; i <= kLutCells; i += blockDim.x) soff[i] = hdr[i];
     if (threadIdx.x < 192) snm[threadIdx.x] = nmul.v[threadIdx.x / 24][threadIdx.x % 24];
@@ -316,6 +318,9 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
     for (uint32_t i = threadIdx.x; i < (total + 1) / 2; i += blockDim.x) sc32[i] = gc32[i];
   }
   const float inv_S = 1.0f / (float)S;
+  // Bins (norm bits 31:21) that a sample of the call says hold the two middle order statistics: their next
+  // 11-bit digit is histogrammed here too, which spares a pass over x when the sample was right.
+  const uint32_t pb0 = sel_s ? sel_s[h * 8 + 0] >> 21 : 0xffffffffu, pb1 = sel_s ? sel_s[h * 8 + 2] >> 21 : 0xffffffffu;
   __syncthreads();
 
   uint32_t* myrow = rows + warp * kMaxRowWords;
@@ -424,7 +429,12 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
       store_scale(dst, row, rmax);
       if (dst.flags) dst.flags[row] = 0u;
     }
-    if (hist) atomicAdd(&shist[__float_as_uint(nrm) >> 21], 1u);
+    if (hist) {
+      const uint32_t key = __float_as_uint(nrm), top = key >> 21;
+      atomicAdd(&shist[top], 1u);
+      if (top == pb0) atomicAdd(&sh1[(key >> 10) & 0x7ffu], 1u);
+      else if (top == pb1) atomicAdd(&sh1[kHistBins + ((key >> 10) & 0x7ffu)], 1u);
+    }
   }
   if (hist) {
     __syncthreads();
@@ -433,6 +443,15 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
       uint32_t cnt = shist[i];
       if (cnt) atomicAdd(&gh[i], cnt);
     }
+    if (sel_s) {
+      uint32_t* g1 = gh + 2 * kHistBins;                   // level 1, both queries
+      const bool same = pb0 == pb1;
+      for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) {
+        const uint32_t c0 = sh1[i], c1 = same ? c0 : sh1[kHistBins + i];
+        if (c0) atomicAdd(&g1[i], c0);
+        if (c1) atomicAdd(&g1[kHistBins + i], c1);
+      }
+    }
   }
 }
 
@@ -440,11 +459,15 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
 // Level 0 histogram (bits 31:21) is accumulated by encode_main_kernel into query slot 0.
 __global__ void __launch_bounds__(256)
 select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level, uint64_t N, float C,
-              float* __restrict__ med_out, uint32_t* __restrict__ band) {
+              float* __restrict__ med_out, uint32_t* __restrict__ band, const uint32_t* __restrict__ sel_s,
+              const uint32_t* __restrict__ hist_fb) {
   __shared__ uint64_t wtot[8];
   const int h = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;   // launched with 256 threads
   uint32_t* st = sel + h * 8;
+  // level 1 with a sampled prediction: the main pass filled the level-1 histograms if the sample named the
+  // right bins, else hist32_kernel filled the fallback ones
+  const bool use_fb = level == 1 && sel_s && !(sel_s[h * 8 + 0] == st[0] && sel_s[h * 8 + 2] == st[2]);
   const uint64_t lo = (N - 1) / 2, hi = N / 2;
   uint32_t* hl = hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
   const int shift = level == 0 ? 21 : level == 1 ? 10 : 0;
@@ -454,7 +477,7 @@ select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level
     const uint64_t rank = level == 0 ? (q == 0 ? lo : hi) : st[2 * q + 1];
     const uint32_t prefix = level == 0 ? 0u : st[2 * q];
     // level 0 has one histogram (slot 0); deeper levels have one per query
-    const uint32_t* hq = hl + (level == 0 ? 0 : q * kHistBins);
+    const uint32_t* hq = use_fb ? hist_fb + ((int64_t)h * 2 + q) * kHistBins : hl + (level == 0 ? 0 : q * kHistBins);
     uint32_t cnt[8];
 #pragma unroll
     for (int i = 0; i < 8; i += 4) {
@@ -582,10 +605,13 @@ __device__ __forceinline__ void norms_of_two(const uint4& r, float& n0, float& n
 
 template <int DT>
 __global__ void __launch_bounds__(256)
-hist32_kernel(Fast32 f, uint32_t* __restrict__ hist, const uint32_t* __restrict__ sel, int level) {
+hist32_kernel(Fast32 f, uint32_t* __restrict__ hist, const uint32_t* __restrict__ sel, int level,
+              const uint32_t* __restrict__ sel_s, uint32_t* __restrict__ hist_fb) {
   __shared__ uint32_t sh[2][kHistBins];
   const int bh = blockIdx.y;
   const int h = bh % f.H, b = bh / f.H;
+  // with a sampled prediction this pass is only the fallback: nothing to do when the sample named the right bins
+  if (sel_s && sel_s[h * 8 + 0] == sel[h * 8 + 0] && sel_s[h * 8 + 2] == sel[h * 8 + 2]) return;
   for (int i = threadIdx.x; i < 2 * kHistBins; i += blockDim.x) (&sh[0][0])[i] = 0;
   __syncthreads();
   const uint32_t p0 = sel[h * 8 + 0], p1 = sel[h * 8 + 2];
@@ -620,12 +646,39 @@ hist32_kernel(Fast32 f, uint32_t* __restrict__ hist, const uint32_t* __restrict_
     }
   }
   __syncthreads();
-  uint32_t* gh = hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
+  uint32_t* gh = sel_s ? hist_fb + (int64_t)h * 2 * kHistBins : hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
   for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) {
     const uint32_t c0 = sh[0][i], c1 = same ? c0 : sh[1][i];
     if (c0) atomicAdd(&gh[i], c0);
     if (c1) atomicAdd(&gh[kHistBins + i], c1);
   }
+}
+
+// Level-0 histogram (norm bits 31:21) of every kSampleStride-th token: predicts the bins of the two middle
+// order statistics before the main pass runs.
+constexpr int kSampleStride = 32;
+template <int DT>
+__global__ void __launch_bounds__(256)
+sample32_kernel(Fast32 f, uint32_t* __restrict__ hist_s) {
+  __shared__ uint32_t sh[kHistBins];
+  const int bh = blockIdx.y;
+  const int h = bh % f.H, b = bh / f.H;
+  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, l16 = lane & 15;
+  const int n_s = (f.T_new + kSampleStride - 1) / kSampleStride;       // sampled tokens of this (b, h)
+  const uint16_t* base = f.x + b * f.xs_b + h * f.xs_h + 8 * l16;
+  for (int k = blockIdx.x * 16 + warp * 2 + (lane >> 4); k < n_s; k += gridDim.x * 16) {
+    const uint4 r = *reinterpret_cast<const uint4*>(base + (int64_t)k * kSampleStride * f.xs_t);
+    float n[2];
+    norms_of_two<DT>(r, n[0], n[1]);
+    atomicAdd(&sh[__float_as_uint(n[0]) >> 21], 1u);
+    atomicAdd(&sh[__float_as_uint(n[1]) >> 21], 1u);
+  }
+  __syncthreads();
+  uint32_t* gh = hist_s + (int64_t)h * 3 * 2 * kHistBins;   // laid out like the level-0 slot of the full histograms
+  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x)
+    if (sh[i]) atomicAdd(&gh[i], sh[i]);
 }
 
 // Clear the radius code of chunk c in a packed row (atomics: other threads may own neighbouring chunks).
@@ -1142,7 +1195,7 @@ Mul8x24 make_mul() {
 inline size_t lut_bytes(int H) { return (size_t)H * kLutHdr * 4 + (size_t)H * kLutCandCap * 2; }
 inline size_t lut_ws_bytes(int H) { return (size_t)H * kLutCells * 4 + (size_t)H * kLutCells * kLutMaxList * 2; }
 
-struct WsPlan { size_t status, hist, sel, band, und, total; int blk0, nblk; };
+struct WsPlan { size_t status, hist, sel, band, und, hist_s, sel_s, hist_fb, total; int blk0, nblk; };
 WsPlan plan_ws(const hqmq_encode_args& a) {
   WsPlan w;
   const int H = a.dst.H;
@@ -1154,6 +1207,9 @@ WsPlan plan_ws(const hqmq_encode_args& a) {
   w.sel = o; o += (size_t)H * 8;
   w.band = o; o += (size_t)H * kBandWords;
   w.und = o; o += (size_t)H * kUndCap;
+  w.hist_s = o; o += (size_t)H * 3 * 2 * kHistBins;   // sampled histograms (level-0 slot used)
+  w.sel_s = o; o += (size_t)H * 8;
+  w.hist_fb = o; o += (size_t)H * 2 * kHistBins;      // level 1 when the sample mispredicted
   w.total = o * sizeof(uint32_t);
   return w;
 }
@@ -1257,10 +1313,16 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   cand_smem = (cand_smem + 7) & ~7;
   const size_t smem_lut = smem_base + (size_t)24 * g.S * 16 + (size_t)(kLutCells + 4) * 4 + (size_t)cand_smem * 2;
   const bool use_lut = a->search == 0 && a->lut != nullptr && a->lut_max_cand >= 0 && smem_lut <= 220 * 1024;
+  // fast passes: d_head 128, 16-bit input, token rows on 16-byte boundaries (the fused last pass lists
+  // undecided chunks by a 32-bit index over the (batch, token, chunk) grid of a head)
+  const bool fast32 = g.n == 32 && is_half_dtype(a->x_dtype) && ((uintptr_t)a->x & 15) == 0 && g.xs_b % 8 == 0 &&
+                      g.xs_h % 8 == 0 && g.xs_t % 8 == 0 && (int64_t)d.B * a->T_new * 32 < ((int64_t)1 << 32);
+  Fast32 f32{reinterpret_cast<const uint16_t*>(a->x), g.xs_b, g.xs_h, g.xs_t, d.H, a->T_new};
   static const Mul8x24 mul = make_mul();
   if (use_lut && (uintptr_t)a->lut & 15) return HQMQ_ERR_ALIGN;
   // specialised kernel: d_head 128, 16-bit input, one of the compiled field layouts
   const void* fastk = nullptr;
+  bool predicted = false;
   if (use_lut && g.n == 32 && is_half_dtype(a->x_dtype)) {
     const bool h16 = a->x_dtype == HQMQ_F16;
 #define HQMQ_PICK(IB_, RB_)                                                                              \
@@ -1278,7 +1340,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
       return m;
     }();
     const size_t smem_fast = (size_t)g.S * 16 + (size_t)kEnc32Warps * kMaxRowWords * 4 + kHistBins * 4 + (size_t)24 * g.S * 16 +
-                             (size_t)(kLutCells + 4) * 4 + 256 + (size_t)cand_smem * 2 + 16;
+                             (size_t)(kLutCells + 4) * 4 + 256 + (size_t)cand_smem * 2 + 16 + (size_t)2 * kHistBins * 4;
     // tokens per CTA: long enough to amortise loading the tables, short enough to fill the machine twice
     int iters = (int)(((int64_t)a->T_new * d.B * d.H + (int64_t)2 * 148 * kEnc32Warps - 1) / ((int64_t)2 * 148 * kEnc32Warps));
     if (iters < 1) iters = 1;
@@ -1286,12 +1348,26 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     if (smem_fast > 48 * 1024)
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(fastk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fast));
     dim3 fgrid((a->T_new + kEnc32Warps * iters - 1) / (kEnc32Warps * iters), d.B * d.H);
+    // Med3x: a sample of the tokens predicts which bins hold the two middle order statistics, so that this
+    // pass can histogram their next digit as well (level 1 of the radix select then needs no pass of its own)
+    predicted = med && fast32 && a->T_new >= 1024;
+    if (predicted) {
+      const int n_s = (a->T_new + kSampleStride - 1) / kSampleStride;
+      int gs = (148 * 8 + d.B * d.H - 1) / (d.B * d.H);
+      if (gs > (n_s + 15) / 16) gs = (n_s + 15) / 16;
+      if (gs < 1) gs = 1;
+      if (a->x_dtype == HQMQ_F16) sample32_kernel<HQMQ_F16><<<dim3(gs, d.B * d.H), 256, 0, st>>>(f32, ws + wp.hist_s);
+      else sample32_kernel<HQMQ_BF16><<<dim3(gs, d.B * d.H), 256, 0, st>>>(f32, ws + wp.hist_s);
+      select_kernel<<<d.H, 256, 0, st>>>(ws + wp.hist_s, ws + wp.sel_s, 0, (uint64_t)d.B * n_s * 32, a->median_mult, nullptr,
+                                         nullptr, nullptr, nullptr);
+    }
+    const uint32_t* sel_s_arg = predicted ? ws + wp.sel_s : nullptr;
     const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a->x);
     uint32_t* hist_arg = med ? ws + wp.hist : nullptr;
     const uint32_t* lut_arg = reinterpret_cast<const uint32_t*>(a->lut);
     int t_start_arg = a->t_start;
     void* kargs[] = {(void*)&g, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&hist_arg, (void*)&maps,
-                     (void*)&a->joint, (void*)&lut_arg, (void*)&cand_smem, (void*)&nmul, (void*)&iters};
+                     (void*)&a->joint, (void*)&lut_arg, (void*)&cand_smem, (void*)&nmul, (void*)&iters, (void*)&sel_s_arg};
     HQMQ_CHECK_CUDA(cudaLaunchKernel(fastk, fgrid, dim3(kEnc32Threads), kargs, smem_fast, st));
   } else if (use_lut) {
     if (smem_lut > 48 * 1024)
@@ -1325,11 +1401,6 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   if (hb < 1) hb = 1;
   uint32_t* hist = ws + wp.hist;
   uint32_t* sel = ws + wp.sel;
-  // fast passes: d_head 128, 16-bit input, token rows on 16-byte boundaries (the fused last pass lists
-  // undecided chunks by a 32-bit index over the (batch, token, chunk) grid of a head)
-  const bool fast32 = g.n == 32 && is_half_dtype(a->x_dtype) && ((uintptr_t)a->x & 15) == 0 && g.xs_b % 8 == 0 &&
-                      g.xs_h % 8 == 0 && g.xs_t % 8 == 0 && (int64_t)d.B * a->T_new * 32 < ((int64_t)1 << 32);
-  Fast32 f32{reinterpret_cast<const uint16_t*>(a->x), g.xs_b, g.xs_h, g.xs_t, d.H, a->T_new};
   int fgrid = (148 * 16 + bh_count - 1) / bh_count;
   const int fgrid_max = (a->T_new + kF32Tok - 1) / kF32Tok;
   if (fgrid > fgrid_max) fgrid = fgrid_max;
@@ -1338,15 +1409,18 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   const bool h16 = a->x_dtype == HQMQ_F16;
   uint32_t* band = ws + wp.band;
   uint32_t* und = ws + wp.und;
-  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr, nullptr);
+  const uint32_t* sel_s = predicted ? ws + wp.sel_s : nullptr;
+  uint32_t* hist_fb = ws + wp.hist_fb;
+  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr, nullptr, nullptr, nullptr);
   if (fast32) {
-    if (h16) hist32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1);
-    else hist32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, band);
+    // (with a prediction this launch returns at once unless the sample named the wrong bins)
+    if (h16) hist32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1, sel_s, hist_fb);
+    else hist32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1, sel_s, hist_fb);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, band, sel_s, hist_fb);
     // last histogram level and provisional flags in one pass, exact threshold, then the (normally empty) fix-up
     if (h16) histflags32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und);
     else histflags32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr);
     if (h16) {
       fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und);
       fixup_scan_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band);
@@ -1356,9 +1430,9 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     }
   } else {
     hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 1);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, nullptr);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, nullptr, nullptr, nullptr);
     hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 2);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr);
     const int tok_per_fblock = 8 * g.tpw;
     int fb = (a->T_new + 4 * tok_per_fblock - 1) / (4 * tok_per_fblock);
     const int fb_cap = (148 * 32 + bh_count - 1) / bh_count;

@@ -228,3 +228,27 @@ def test_med3x_chunks_next_to_the_threshold(T):
     for h in range(H):
         want = xc[0, h][enc["flags"][0, h]]
         assert torch.equal(ov[0, h, : want.shape[0]], want)
+
+
+@pytest.mark.parametrize("mislead", [False, True])
+def test_med3x_sampled_prediction_and_its_fallback(mislead):
+    """Long 16-bit calls histogram the second digit of the median inside the main pass, for the bins a sample
+    (every 32nd token) predicts.  With `mislead` the sampled tokens are 100x larger than the rest, the
+    prediction is wrong and the separate pass must take over; either way the integers match the oracle."""
+    B, H, T, d, S, br, C = 1, 2, 2048, 128, 96, 4, 3.0
+    x = make_kv("hot", (B, H, T, d), seed=21, dtype=torch.float32)
+    if mislead:
+        x[:, :, ::32] *= 100.0
+    x = x.bfloat16()
+    joint = orc.joint_codebook(orc.secondary_raw(1, H, S, 42)[0, :, 0])
+    enc = orc.encode(x.float(), joint, br, C)
+    q = hqmq.HQMQ(n_layers=1, n_heads=H, secondary_size=S, radius_bits=br, device="cuda", seed=42)
+    med = torch.zeros(H, device="cuda")
+    pk = q.encode(x.cuda(), 0, 0, median_mult=C, scale_dtype=torch.float32, med_out=med)
+    idx, rq, rs, flags = pk.to_reference()
+    assert torch.equal(med.cpu(), enc["med"]), "median differs"
+    assert torch.equal(flags.cpu(), enc["flags"]), "outlier flags differ"
+    assert torch.equal(rq.cpu(), torch.where(enc["flags"], 0, enc["rq"])), "radius codes differ"
+    assert torch.equal(rs.cpu(), enc["r_max"])
+    n_mis, n_bad = classify_idx(idx, enc, NEAR_TIE)
+    assert n_bad == 0

@@ -48,7 +48,7 @@ WORKLOADS = {
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read+write of attn_fast_kernel divided by the algorithmic bytes of the same launch, from the ncu
 # capture summarised in profiles/attn_decode_c2.md (batch 4 of the same workload; traffic scales with the tokens)
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.11
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.10
 
 
 def synth(kind, shape, seed, device, dtype):

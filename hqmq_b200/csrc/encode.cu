@@ -886,7 +886,7 @@ __device__ __forceinline__ int ofrag_records_for(uint32_t any_c) {
 
 // Per (b,h), one warp, one lane per 16-token block of this call: the block's flagged chunks are counted
 // from its flag words and scanned into the payload offsets; with a fragment plane, also the record offsets
-// (only blocks the call covers completely get records; a block whose records would pass the capacity, and
+// (a block gets records in the call that completes it; a block whose records would pass the capacity, and
 // every block after it in this call, gets none).  `payload` = 0 on a call without Med3x (nothing flagged).
 __global__ void __launch_bounds__(128)
 scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk, int payload, uint32_t* __restrict__ status) {
@@ -913,12 +913,14 @@ scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk, int pay
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int t = tb + 4 * q + k;
-          if (t >= t_start && t < t_end) { c += __popc(ww[k]); any_c |= ww[k]; }   // tokens of this call only
+          if (t >= t_start && t < t_end) c += __popc(ww[k]);   // payload entries: tokens of this call only
+          if (t < t_end) any_c |= ww[k];                         // records: every token the block holds
         }
       }
     }
-    const bool whole = i < nblk && ba * HQMQ_OUT_BLOCK >= t_start && (ba + 1) * HQMQ_OUT_BLOCK <= t_end;
-    const uint32_t fc = foff && whole ? (uint32_t)ofrag_records_for(any_c) : 0u;
+    // a block gets its records in the call that completes it (all 16 tokens present), from flags and payload
+    const bool complete = i < nblk && (ba + 1) * HQMQ_OUT_BLOCK <= t_end;
+    const uint32_t fc = foff && complete ? (uint32_t)ofrag_records_for(any_c) : 0u;
     uint32_t incl = c, fincl = fc;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -966,6 +968,10 @@ side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start,
   const int64_t xbase = b * g.xs_b + h * g.xs_h;
 
   // ---- payload: lane pair (l, l + 16) shares token l; the pair takes the token's flagged chunks alternately ----
+  uint32_t excl16;   // lanes 0..15: flagged chunks of the block's earlier tokens
+  const uint32_t off0 = dst.out_off[(int64_t)bh * nb_cap + ba];
+  const int esz = dst.out_dtype == HQMQ_F32 ? 4 : 2;
+  unsigned char* base = reinterpret_cast<unsigned char*>(dst.out_vals) + (int64_t)bh * dst.out_cap * 4 * esz;
   {
     uint32_t incl = __popc(fw);
 #pragma unroll
@@ -973,13 +979,12 @@ side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start,
       const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
       if ((lane & 15) >= o) incl += v;
     }
-    const uint32_t before = __shfl_sync(0xffffffffu, incl - __popc(fw), lane & 15);   // flagged chunks of earlier tokens
+    excl16 = incl - __popc(fw);
+    const uint32_t before = __shfl_sync(0xffffffffu, excl16, lane & 15);
     uint32_t word = __shfl_sync(0xffffffffu, fw, lane & 15);
     const int t = ba * HQMQ_OUT_BLOCK + (lane & 15) - t_start;                         // token index within this call
     if (t >= 0 && t < g.T_new && word) {
-      uint32_t pos = dst.out_off[(int64_t)bh * nb_cap + ba] + before;
-      const int esz = dst.out_dtype == HQMQ_F32 ? 4 : 2;
-      unsigned char* base = reinterpret_cast<unsigned char*>(dst.out_vals) + (int64_t)bh * dst.out_cap * 4 * esz;
+      uint32_t pos = off0 + before;
       int k = 0;
       while (word) {
         const int c = __ffs(word) - 1;
@@ -1001,16 +1006,20 @@ side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start,
     }
   }
 
-  // ---- fragment records --------------------------------------------------------------------------------------
+  // ---- fragment records: built from the flags and the payload, so that a block filled by several calls
+  // (token-by-token appends) gets them too, in the call that completes it -------------------------------------
   if (!dst.ofrag) return;
   const uint32_t* off = dst.ofrag_off + (int64_t)bh * nb_cap;
   const uint32_t o0 = off[ba], o1 = off[ba + 1];
   if (o1 <= o0) return;
+  __threadfence_block();
+  __syncwarp();            // this call's payload entries of the block were written by other lanes of the warp
   const int j = lane & 3, r = lane >> 2;
-  uint32_t fl[2]; float inv[2];
+  uint32_t fl[2], pre[2]; float inv[2];
 #pragma unroll
   for (int nt = 0; nt < 2; ++nt) {
     fl[nt] = __shfl_sync(0xffffffffu, fw, nt * 8 + r);
+    pre[nt] = __shfl_sync(0xffffffffu, excl16, nt * 8 + r);
     inv[nt] = fl[nt] ? (float)g.qmax / load_scale(dst, row0 + nt * 8 + r) : 0.f;
   }
   for (uint32_t rec = o0; rec < o1; ++rec) {
@@ -1028,9 +1037,18 @@ side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start,
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         if ((fl[nt] >> cj) & 1u) {
-          const int t = ba * HQMQ_OUT_BLOCK + nt * 8 + r - t_start;
-          float v[4];
-          load_chunk(x, xbase + t * g.xs_t + 4 * cj, g.x_dtype, v);
+          const uint32_t pos = off0 + pre[nt] + __popc(fl[nt] & ((1u << cj) - 1u));
+          float v[4] = {0.f, 0.f, 0.f, 0.f};
+          if (pos < (uint32_t)dst.out_cap) {     // (an entry dropped by an overflowing side buffer reads as 0)
+            if (dst.out_dtype == HQMQ_F32) {
+              const float4 f = *reinterpret_cast<const float4*>(base + (int64_t)pos * 16);
+              v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+            } else {
+              const uint2 o = *reinterpret_cast<const uint2*>(base + (int64_t)pos * 8);
+              v[0] = bits16_to_float(o.x & 0xffff, dst.out_dtype); v[1] = bits16_to_float(o.x >> 16, dst.out_dtype);
+              v[2] = bits16_to_float(o.y & 0xffff, dst.out_dtype); v[3] = bits16_to_float(o.y >> 16, dst.out_dtype);
+            }
+          }
           const __half2 h01 = __floats2half2_rn(v[0] * inv[nt], v[1] * inv[nt]);
           const __half2 h23 = __floats2half2_rn(v[2] * inv[nt], v[3] * inv[nt]);
           a[nt] = *reinterpret_cast<const uint32_t*>(&h01);

@@ -96,10 +96,11 @@ extern "C" {
  *          position j = l%4) holds eight fp16 values v(r,0) v(r,1) v(r+8,0) v(r+8,1) v(r,2) v(r,3)
  *          v(r+8,2) v(r+8,3) with v(t,e) = x[token t of the block][4*c_j + e] * qmax / rs[t] if
  *          chunk c_j of token t is flagged, else 0.
- *   ofrag_off[B][H][T_cap/16 + 1]    records before each 16-token block.  hqmq_encode writes
- *          records only for blocks that one call covers completely and that have at most
- *          4*HQMQ_OFRAG_MAX_PER_TILE distinct flagged positions and fit ofrag_cap; every other
- *          block owns no record and the attention kernels take its outliers from flags/out_vals.
+ *   ofrag_off[B][H][T_cap/16 + 1]    records before each 16-token block.  hqmq_encode writes a
+ *          block's records in the call that completes the block (its 16th token), from the flag
+ *          words and out_vals, if the block has at most 4*HQMQ_OFRAG_MAX_PER_TILE distinct flagged
+ *          positions and the records fit ofrag_cap; every other block (the last, incomplete one
+ *          included) owns no record and the attention kernels take its outliers from flags/out_vals.
  */
 typedef struct hqmq_packed {
   uint32_t struct_size;

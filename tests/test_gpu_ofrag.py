@@ -100,7 +100,7 @@ def _attend(Q, Kp, Vp, tk, tv, **kw):
 @pytest.mark.parametrize("kind,T1,T2,cap", [("hot", 600, 0, None), ("hot", 250, 391, None), ("student", 333, 0, None),
                                             ("spiky", 1024, 0, None), ("hot", 640, 0, 7)])
 def test_attention_with_and_without_records(kind, T1, T2, cap):
-    """T2 > 0 appends a second call that starts inside a block: that block owns no record."""
+    """T2 > 0 appends a second call that starts inside a block."""
     S, br, C, d, Hq, Hkv, B = 96, 4, 3.0, 128, 16, 4, 2
     T = T1 + T2
     K = make_kv(kind, (B, Hkv, T, d), seed=51, dtype=torch.bfloat16)
@@ -121,9 +121,16 @@ def test_attention_with_and_without_records(kind, T1, T2, cap):
     off, _ = _planes(Kp)
     n_rec = int(off[..., (T + 15) // 16].sum())
     assert n_rec > 0
-    if T2:   # the block that the second call started in has flagged chunks but no record
+    if T2:   # the block that the second call started in was completed by it: it owns records built from the side buffer
         blk = T1 // 16
-        assert (off[..., blk + 1] == off[..., blk]).all() and kf[:, :, blk * 16:blk * 16 + 16].any()
+        assert (off[..., blk + 1] > off[..., blk]).all() and kf[:, :, blk * 16:blk * 16 + 16].any()
+        _, recs = _planes(Kp)
+        for b in range(B):
+            for h in range(Hkv):
+                eo, er = _expected_records(K[b, h].float().numpy(), kf[b, h].numpy(), ks[b, h].numpy(), 15, 0, T, Kp.ofrag_cap)
+                assert np.array_equal(off[b, h, :len(eo)], eo)
+                for i, rec in enumerate(er):
+                    assert np.array_equal(recs[b, h, i], rec), f"record {i} of (b={b}, h={h})"
     for window in (None, 100):
         if window is not None:
             ref_w = orc.fused_attention(Q, ki, kr, ks, tk["joint"].cpu(), vi.cpu(), vr.cpu(), vs.cpu(),
@@ -141,3 +148,37 @@ def test_attention_with_and_without_records(kind, T1, T2, cap):
     O2 = _attend(Q, Kp, Vp, tk, tv)
     err, r2 = (O2 - ref).abs().max().item(), rel_l2(O2, ref)
     assert err < MAX_ABS * max(1.0, float(ref.abs().max())) and r2 < REL_L2, f"without records: {err:.2e} {r2:.2e}"
+
+
+def test_records_under_token_by_token_appends():
+    """Serving pattern: a prefill call, then one token per call (each call with its own Med3x median).  Every
+    block gets its records in the call that completes it, from flags and side buffer; the last, incomplete
+    block has none and is merged from flags / side buffer by the attention kernel."""
+    S, br, C, d, Hq, Hkv, B, T0, n_app = 96, 4, 3.0, 128, 8, 2, 2, 70, 45
+    T = T0 + n_app
+    K = make_kv("hot", (B, Hkv, T, d), seed=61, dtype=torch.bfloat16)
+    V = make_kv("randn", (B, Hkv, T, d), seed=62, dtype=torch.bfloat16)
+    Q = (torch.randn(B, Hq, 1, d, generator=torch.Generator().manual_seed(63)) / math.sqrt(d)).bfloat16()
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, Hkv, S, br, device="cuda"), C)
+    Kp = q.inner.new_cache(B, T, d, "cuda", scale_dtype=torch.bfloat16, with_outliers=True,
+                           out_dtype=torch.bfloat16, ofrag=True)
+    q.encode(K[:, :, :T0].cuda(), 0, 0, out=Kp)
+    for t in range(T0, T):
+        q.encode(K[:, :, t:t + 1].cuda(), 0, 0, out=Kp)
+    Vp = q.inner.encode(V.cuda(), 0, 1)
+    tk, tv = q.inner.tables(0, 0, "cuda"), q.inner.tables(0, 1, "cuda")
+    ki, kr, ks, kf = (t.cpu() for t in Kp.to_reference())
+    vi, vr, vs, _ = Vp.to_reference()
+    off, recs = _planes(Kp)
+    for b in range(B):
+        for h in range(Hkv):
+            eo, er = _expected_records(K[b, h].float().numpy(), kf[b, h].numpy(), ks[b, h].numpy(), 15, 0, T, Kp.ofrag_cap)
+            assert np.array_equal(off[b, h, :len(eo)], eo), f"offsets of (b={b}, h={h})"
+            for i, rec in enumerate(er):
+                assert np.array_equal(recs[b, h, i], rec), f"record {i} of (b={b}, h={h})"
+            assert len(er) >= T // 16                 # every complete block has hot channels, hence records
+    ref = orc.fused_attention(Q, ki, kr, ks, tk["joint"].cpu(), vi.cpu(), vr.cpu(), vs.cpu(), tv["joint"].cpu(),
+                              15, causal=False, K_flags=kf, K_orig=K)
+    O = _attend(Q, Kp, Vp, tk, tv)
+    err, r2 = (O - ref).abs().max().item(), rel_l2(O, ref)
+    assert err < MAX_ABS * max(1.0, float(ref.abs().max())) and r2 < REL_L2, f"{err:.2e} {r2:.2e}"

@@ -33,7 +33,7 @@ def _fill_q(a: _lib.AttnArgs, Q: torch.Tensor, O: Optional[torch.Tensor]):
 
 def _run(a: _lib.AttnArgs, device):
     L = _lib.lib()
-    with torch.cuda.device(device):
+    with _lib.device_guard(device):
         nbytes = L.hqmq_attn_workspace_bytes(C.byref(a))
         if nbytes == 0:
             # run the validation again to get the error code
@@ -142,7 +142,7 @@ def fused_attention_packed_noalloc(Q: torch.Tensor, K: PackedKV, V: PackedKV, ta
     a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 0.0
     a.K, a.V = K.c_struct(), V.c_struct()
     a.table_K, a.table_V = table_K.data_ptr(), table_V.data_ptr()
-    with torch.cuda.device(Q.device):
+    with _lib.device_guard(Q.device):
         _lib.check(_lib.lib().hqmq_attn_decode_static(C.byref(a), _lib.stream_ptr()), "hqmq_attn_decode_static")
     return out
 

@@ -268,6 +268,193 @@ encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restric
   }
 }
 
+// ---- small calls (decode-time appends) ------------------------------------------------------------------
+// One CTA per head does the whole call: norms, per-token scale, nearest codeword (tables read straight from
+// global memory: they sit in L2 and a handful of chunks per thread do not pay for staging them), the exact
+// median by rank counting in shared memory, flags, packed rows.  It replaces the main pass, the three select
+// levels and the flag pass by one launch when a head has at most kSmallMax chunks in the call; the offset
+// scan and the side-plane kernel follow as usual.  Same arithmetic as the large-call kernels.
+constexpr int kSmallMax = 2048;          // chunks per head and call
+constexpr int kSmallThreads = 1024;
+constexpr int kSmallTok = 512;           // tokens per head and call (kSmallMax / 4 chunks)
+
+__global__ void __launch_bounds__(kSmallThreads)
+encode_small_kernel(EncGeom g, const void* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
+                    int t_start, Maps24 maps, const float* __restrict__ joint_all, const uint32_t* __restrict__ lut,
+                    Mul8x24 mul, float C, float* __restrict__ med_out) {
+  __shared__ uint32_t keys[kSmallMax];                    // norm bits of every chunk of the head
+  __shared__ uint32_t tokmax[kSmallTok];                  // bits of the largest radius of a token
+  __shared__ uint32_t tokflags[kSmallTok];
+  __shared__ uint32_t rows[kSmallTok / 8][kMaxRowWords];   // packed rows, 64 tokens at a time
+  const int h = blockIdx.x;
+  const int n = g.n, per_b = g.T_new * n;                 // chunks of one batch entry
+  const int N = g.B * per_b, n_tok = g.B * g.T_new;
+  const int S = g.S;
+  const float inv_S = 1.0f / (float)S;
+  const bool med = C > 0.f;
+  const float qmaxf = (float)g.qmax;
+  for (int i = threadIdx.x; i < n_tok; i += blockDim.x) { tokmax[i] = 0u; tokflags[i] = 0u; }
+  __syncthreads();
+
+  const uint32_t* hdr = lut ? lut + (int64_t)h * kLutHdr : nullptr;
+  const bool use_lut = hdr && hdr[kLutCells + 1] == 1u;
+  const uint16_t* cand = lut ? reinterpret_cast<const uint16_t*>(lut + (int64_t)g.H * kLutHdr) + (int64_t)h * kLutCandCap : nullptr;
+  const float4* joint = reinterpret_cast<const float4*>(joint_all) + (int64_t)h * 24 * S;
+  const float4* qs = reinterpret_cast<const float4*>(qs_all) + (int64_t)h * S;
+
+  // ---- phase A: norms, token maxima, nearest codewords ------------------------------------------------------
+  float nrm[2], radius[2];
+  uint32_t ni[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int i = threadIdx.x + k * kSmallThreads;
+    nrm[k] = 0.f; radius[k] = 0.f; ni[k] = 0u;
+    if (i < N) {
+      const int b = i / per_b, r = i - b * per_b, t = r / n, c = r - t * n;
+      float v[4];
+      load_chunk(x, b * g.xs_b + h * g.xs_h + t * g.xs_t + 4 * c, g.x_dtype, v);
+      nrm[k] = chunk_norm(v);
+      radius[k] = fmaxf(nrm[k], 1e-8f);
+      keys[i] = __float_as_uint(nrm[k]);
+      atomicMax(&tokmax[b * g.T_new + t], __float_as_uint(radius[k]));   // positive floats order like their bits
+      const float inv_r = __frcp_rn(radius[k]);
+      const float u0 = v[0] * inv_r, u1 = v[1] * inv_r, u2 = v[2] * inv_r, u3 = v[3] * inv_r;
+      int sidx, p;
+      if (use_lut) p = search_lut(joint, hdr, cand, qs, S, inv_S, u0, u1, u2, u3, mul, sidx);
+      else p = search_exhaustive(qs, S, u0, u1, u2, u3, sidx);
+      const int au = maps.ref_to_native[p];
+      ni[k] = (uint32_t)((((au >> 3) * S + sidx) << 3) | (au & 7));
+    }
+  }
+  __syncthreads();
+
+  // ---- phase B: the two middle order statistics: radix select (4 x 8 bits) of the lower one in shared memory,
+  // the upper one is the same value or the next larger key ------------------------------------------------------
+  float thr = 0.f;
+  if (med) {
+    __shared__ uint32_t shist[256];
+    __shared__ uint32_t s_state[4];       // prefix, rank, keys <= a, smallest key > a
+    const uint32_t lo = (uint32_t)((N - 1) / 2), hi = (uint32_t)(N / 2);
+    uint32_t prefix = 0u, rank = lo;
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (threadIdx.x < 256) shist[threadIdx.x] = 0u;
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int i = threadIdx.x + k * kSmallThreads;
+        if (i < N) {
+          const uint32_t key = keys[i];
+          if (pass == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&shist[(key >> shift) & 0xffu], 1u);
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        uint32_t c8[8], mine = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { c8[q] = shist[lane * 8 + q]; mine += c8[q]; }
+        uint32_t incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += v;
+        }
+        const uint32_t before = incl - mine;
+        if (rank >= before && rank < incl) {      // exactly one lane: the rank is below the number of matching keys
+          uint32_t acc = before; int digit = lane * 8 + 7;
+          bool found = false;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (!found) {
+              if (acc + c8[q] > rank) { digit = lane * 8 + q; found = true; }
+              else acc += c8[q];
+            }
+          }
+          s_state[0] = prefix | ((uint32_t)digit << shift);
+          s_state[1] = rank - acc;
+        }
+      }
+      __syncthreads();
+      prefix = s_state[0]; rank = s_state[1];
+    }
+    const uint32_t a_bits = prefix;
+    if (threadIdx.x == 0) { s_state[2] = 0u; s_state[3] = 0xffffffffu; }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = threadIdx.x + k * kSmallThreads;
+      if (i < N) {
+        const uint32_t key = keys[i];
+        if (key <= a_bits) atomicAdd(&s_state[2], 1u);
+        else atomicMin(&s_state[3], key);
+      }
+    }
+    __syncthreads();
+    const uint32_t b_bits = s_state[2] > hi ? a_bits : s_state[3];
+    const float a = __uint_as_float(a_bits), b2 = __uint_as_float(b_bits);
+    const float m = (N & 1) ? a : __fsub_rn(b2, __fmul_rn(__fsub_rn(b2, a), 0.5f));
+    thr = __fmul_rn(m, C);
+    if (threadIdx.x == 0 && med_out) med_out[h] = m;
+  }
+
+  // ---- phase C: radius codes, flags -------------------------------------------------------------------------
+  uint32_t field[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int i = threadIdx.x + k * kSmallThreads;
+    field[k] = 0u;
+    if (i < N) {
+      const int b = i / per_b, r = i - b * per_b, t = r / n, c = r - t * n;
+      const float rmax = fmaxf(__uint_as_float(tokmax[b * g.T_new + t]), 1e-8f);
+      const float scale = __fdiv_rn(rmax, qmaxf);
+      float rqf = rintf(__fdiv_rn(radius[k], scale));
+      rqf = fminf(fmaxf(rqf, 0.f), qmaxf);
+      if (med && nrm[k] > thr) {
+        atomicOr(&tokflags[b * g.T_new + t], 1u << c);
+        rqf = 0.f;          // a flagged chunk is stored in the side buffer: its radius code in the row is 0
+      }
+      field[k] = ni[k] | ((uint32_t)rqf << g.ib);
+    }
+  }
+  __syncthreads();
+
+  // ---- phase D: packed rows, 64 tokens at a time; scales and flag words ---------------------------------------
+  const int cb = g.ib + g.rbits, rw = dst.row_bytes >> 2;
+  for (int tok0 = 0; tok0 < n_tok; tok0 += kSmallTok / 8) {
+    for (int w = threadIdx.x; w < (kSmallTok / 8) * kMaxRowWords; w += blockDim.x) (&rows[0][0])[w] = 0u;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = threadIdx.x + k * kSmallThreads;
+      if (i < N) {
+        const int b = i / per_b, r = i - b * per_b, t = r / n, c = r - t * n;
+        const int tok = b * g.T_new + t - tok0;
+        if (tok >= 0 && tok < kSmallTok / 8) {
+          const int bit = c * cb, w = bit >> 5, sh = bit & 31;
+          atomicOr(&rows[tok][w], field[k] << sh);
+          if (sh + cb > 32) atomicOr(&rows[tok][w + 1], field[k] >> (32 - sh));
+        }
+      }
+    }
+    __syncthreads();
+    const int cnt = min(kSmallTok / 8, n_tok - tok0);
+    for (int w = threadIdx.x; w < cnt * rw; w += blockDim.x) {
+      const int tok = tok0 + w / rw, ww = w - (w / rw) * rw;
+      const int b = tok / g.T_new, t = tok - b * g.T_new;
+      const int64_t row = ((int64_t)b * g.H + h) * dst.T_cap + t_start + t;
+      reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes)[ww] = rows[tok - tok0][ww];
+    }
+    __syncthreads();
+  }
+  for (int tok = threadIdx.x; tok < n_tok; tok += blockDim.x) {
+    const int b = tok / g.T_new, t = tok - b * g.T_new;
+    const int64_t row = ((int64_t)b * g.H + h) * dst.T_cap + t_start + t;
+    store_scale(dst, row, fmaxf(__uint_as_float(tokmax[tok]), 1e-8f));
+    if (dst.flags) dst.flags[row] = tokflags[tok];
+  }
+}
+
 // ---- main pass for the common geometry ------------------------------------------------------------------
 // 32 chunks per token, 16-bit input, look-up-table search, compile-time field layout: one warp per token,
 // one lane per chunk, no run-time geometry in the loop.  Results are the ones encode_main_kernel gives.
@@ -1318,9 +1505,25 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   g.xs_b = a->x_stride[0]; g.xs_h = a->x_stride[1]; g.xs_t = a->x_stride[2];
 
   uint32_t* ws = reinterpret_cast<uint32_t*>(workspace);
-  HQMQ_CHECK_CUDA(cudaMemsetAsync(ws, 0, wp.total, st));
   Maps24 maps;
   memcpy(maps.ref_to_native, index_maps().ref_to_native, 24);
+
+  // Small calls (decode-time appends): one kernel per head does main pass, median and flags at once.
+  if ((int64_t)d.B * a->T_new * g.n <= kSmallMax && (int64_t)d.B * a->T_new <= kSmallTok) {
+    static const Mul8x24 mul_s = make_mul();
+    const bool lut_ok = a->search == 0 && a->lut != nullptr && a->lut_max_cand >= 0;
+    if (lut_ok && ((uintptr_t)a->lut & 15)) return HQMQ_ERR_ALIGN;
+    HQMQ_CHECK_CUDA(cudaMemsetAsync(ws, 0, 16, st));      // the status word
+    encode_small_kernel<<<d.H, kSmallThreads, 0, st>>>(g, a->x, a->qs, d, a->t_start, maps, a->joint,
+                                                        lut_ok ? reinterpret_cast<const uint32_t*>(a->lut) : nullptr, mul_s,
+                                                        a->median_mult, a->med_out);
+    if (med || d.ofrag)
+      scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, med ? 1 : 0, ws + wp.status);
+    if (med) side_kernel<<<dim3((wp.nblk + 7) / 8, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, wp.blk0, wp.nblk);
+    HQMQ_LAUNCH_CHECK();
+    return HQMQ_OK;
+  }
+  HQMQ_CHECK_CUDA(cudaMemsetAsync(ws, 0, wp.total, st));
 
   const int tok_per_block = kEncWarps * g.tpw * kEncIters;
   dim3 grid((a->T_new + tok_per_block - 1) / tok_per_block, d.B * d.H);

@@ -231,7 +231,7 @@ class HQMQQuantizer(KVQuantizer):
         a.med_out = med_out.data_ptr() if med_out is not None else None
         a.lut, a.lut_max_cand = tb["lut"].data_ptr(), tb["lut_max_cand"]
         L = _lib.lib()
-        with torch.cuda.device(x.device):
+        with _lib.device_guard(x.device):
             nbytes = L.hqmq_encode_workspace_bytes(C.byref(a))
             ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
             _lib.check(L.hqmq_encode(C.byref(a), ws.data_ptr(), nbytes, _lib.stream_ptr()), "hqmq_encode")
@@ -302,18 +302,25 @@ class HQMQQuantizer(KVQuantizer):
 
 
 class _OutlierStats:
-    """Running outlier rate kept as device counters; read (and synchronised) only on demand."""
+    """Running outlier rate kept as device counters; read (and synchronised) only on demand.  A call costs one
+    small device copy (the cache's cumulative counters after the call); the per-call count is the difference
+    to the previous snapshot of the same cache, taken when the statistics are read."""
+
+    _MAX_PENDING = 1024
 
     def __init__(self):
-        self._pending = []          # (flagged-count tensor, n_chunks_total)
+        self._pending = []          # (counters after the call, counters before it or None, n_chunks_total)
         self._rate, self._n = 0.0, 0
 
-    def push(self, count_tensor: torch.Tensor, total: int):
-        self._pending.append((count_tensor, total))
+    def push(self, after: torch.Tensor, before: Optional[torch.Tensor], total: int):
+        self._pending.append((after, before, total))
+        if len(self._pending) >= self._MAX_PENDING:
+            self._sync()
 
     def _sync(self):
-        for cnt, total in self._pending:
-            rate = float(cnt.sum().item()) / max(1, total)
+        for after, before, total in self._pending:
+            cnt = float(after.sum().item()) - (float(before.sum().item()) if before is not None else 0.0)
+            rate = cnt / max(1, total)
             self._rate = (self._rate * self._n + rate) / (self._n + 1)
             self._n += 1
         self._pending.clear()
@@ -366,10 +373,14 @@ class OutlierAwareHQMQQuantizer(KVQuantizer):
 
     def encode(self, x, layer_idx, kv, out: Optional[PackedKV] = None, **kw) -> PackedKV:
         self._check_mode()
-        n_before = None if out is None else out.out_count.clone()
+        # the cache's counters before this call: the snapshot taken after the previous call on the same cache
+        before = getattr(out, "_count_snapshot", None) if out is not None else None
+        if out is not None and before is None and out.T > 0:
+            before = out.out_count.clone()
         pk = self.inner.encode(x, layer_idx, kv, out=out, median_mult=self.median_mult, **kw)
-        cnt = pk.out_count.clone() if n_before is None else pk.out_count - n_before
-        self._stats.push(cnt, x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4))
+        after = pk.out_count.clone()
+        pk._count_snapshot = after
+        self._stats.push(after, before, x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4))
         return pk
 
     def decode(self, packed, layer_idx, kv, **kw):
@@ -379,7 +390,7 @@ class OutlierAwareHQMQQuantizer(KVQuantizer):
         self._check_mode()
         out = self.inner._qdq(x, layer_idx, kv, median_mult=self.median_mult)
         pk = self.inner._last_packed
-        self._stats.push(pk.out_count.clone(), x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4))
+        self._stats.push(pk.out_count.clone(), None, x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4))
         return out
 
     def quantize_K(self, k, layer_idx):

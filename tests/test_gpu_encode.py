@@ -252,3 +252,23 @@ def test_med3x_sampled_prediction_and_its_fallback(mislead):
     assert torch.equal(rs.cpu(), enc["r_max"])
     n_mis, n_bad = classify_idx(idx, enc, NEAR_TIE)
     assert n_bad == 0
+
+
+@pytest.mark.parametrize("shape,S,br", [((2, 2, 32, 128), 96, 4), ((16, 2, 1, 128), 96, 4), ((64, 2, 2, 64), 24, 3),
+                                        ((3, 1, 7, 48), 192, 6), ((1, 1, 1, 4), 24, 3)])
+@pytest.mark.parametrize("C", [None, 3.0])
+def test_small_calls_one_kernel_per_head(shape, S, br, C):
+    """Calls with at most 2048 chunks per head (decode-time appends) run main pass, median and flags in one
+    kernel per head; same integers as the oracle, and the same as the 16-bit input gives."""
+    B, H, T, d = shape
+    x = make_kv("spiky" if d >= 16 else "randn", shape, seed=31)
+    if d >= 16:
+        x[:, :, :, :4] *= 6.0                           # one hot chunk per token: flagged by Med3x
+    _encode_and_compare(x, S, br, C)
+    x16 = x.bfloat16()
+    q = hqmq.HQMQ(n_layers=2, n_heads=H, secondary_size=S, radius_bits=br, device="cuda")
+    a = q.encode(x16.cuda(), 0, 0, median_mult=C, scale_dtype=torch.float32).to_reference()
+    b = q.encode(x16.float().cuda(), 0, 0, median_mult=C, scale_dtype=torch.float32).to_reference()
+    for u, v in zip(a, b):
+        if u is not None:
+            assert torch.equal(u, v)

@@ -286,6 +286,21 @@ def main():
     enc_gbs = (enc_in_bytes + algo_bytes) / sum(enc_times) / 1e9
     outl_frac = [(pk.n_outliers() / (B * Hkv * T * (d // 4))) if Cm is not None else 0.0 for pk in caches]
 
+    # decode-time append: one token per sequence and call into a small cache, through the public encode()
+    ap_cache = inner.new_cache(B, 256, d, dev, scale_dtype=dtype, with_outliers=Cm is not None, out_dtype=dtype,
+                               ofrag=Cm is not None)
+    ap_x = [synth(w["kk"], (B, Hkv, 1, d), 2000 + i, dev, dtype) for i in range(4)]
+    quant.encode(synth(w["kk"], (B, Hkv, 64, d), 1999, dev, dtype), 0, 0, out=ap_cache)
+    for i in range(16):
+        quant.encode(ap_x[i % 4], 0, 0, out=ap_cache)
+    torch.cuda.synchronize()
+    t_ap = time.perf_counter()
+    for i in range(128):
+        quant.encode(ap_x[i % 4], 0, 0, out=ap_cache)
+    torch.cuda.synchronize()
+    append_us = (time.perf_counter() - t_ap) / 128 * 1e6
+    del ap_cache, ap_x
+
     # ---- one decode step through the C ABI, descriptors built once -------------------------------------
     Qh = (torch.randn(B, Hq, 1, d, generator=torch.Generator().manual_seed(7 + rank)) / math.sqrt(d)).to(dtype).pin_memory()
     Oh = torch.empty(B, Hq, 1, d, dtype=dtype).pin_memory()
@@ -407,7 +422,7 @@ def main():
                      "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * algo_bytes if args.workload == "c2" else None,
                      "traffic_note": "ncu dram bytes of a batch-4 capture scaled by tokens (profiles/attn_decode_c2.md)"},
         "encode": {"tokens_per_s": enc_tokens_per_s * world, "GBps_per_gpu": enc_gbs, "frac_of_peak": enc_gbs / peak,
-                   "tokens": B * T, "seconds_K_V": enc_times,
+                   "tokens": B * T, "seconds_K_V": enc_times, "append_one_token_us_per_call": append_us,
                    "note": "one call per tensor over the whole (B, H_kv, T, d) input, Med3x median per call; median of 3 timed calls after 1 warm-up call"},
         "clocks": clocks,
     }

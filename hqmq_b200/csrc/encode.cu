@@ -1071,65 +1071,106 @@ __device__ __forceinline__ int ofrag_records_for(uint32_t any_c) {
   return ng <= HQMQ_OFRAG_MAX_PER_TILE ? ng : 0;
 }
 
-// Per (b,h), one warp, one lane per 16-token block of this call: the block's flagged chunks are counted
-// from its flag words and scanned into the payload offsets; with a fragment plane, also the record offsets
-// (a block gets records in the call that completes it; a block whose records would pass the capacity, and
-// every block after it in this call, gets none).  `payload` = 0 on a call without Med3x (nothing flagged).
-__global__ void __launch_bounds__(128)
+// Per (b,h), one CTA of 8 warps, one lane per 16-token block of this call: the block's flagged chunks are
+// counted from its flag words and scanned into the payload offsets; with a fragment plane, also the record
+// offsets (a block gets records in the call that completes it; a block whose records would pass the capacity,
+// and every block after it in this call, gets none: the running total is monotone, so that is every block
+// whose inclusive total exceeds the capacity).  `payload` = 0 on a call without Med3x (nothing flagged).
+constexpr int kScanWarps = 8;
+constexpr int kScanIters = 16;     // blocks per lane: up to 8 * 32 * 16 = 4096 blocks (64 k tokens) in one sweep
+__global__ void __launch_bounds__(kScanWarps * 32)
 scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk, int payload, uint32_t* __restrict__ status) {
-  const int bh = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (bh >= dst.B * dst.H) return;
+  __shared__ uint32_t w_tot[kScanWarps], w_ftot[kScanWarps], s_last_ok[kScanWarps];
+  const int bh = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nb_cap = dst.T_cap / HQMQ_OUT_BLOCK + 1;
   uint32_t* off = dst.out_off + (int64_t)bh * nb_cap;
   uint32_t* foff = dst.ofrag ? dst.ofrag_off + (int64_t)bh * nb_cap : nullptr;
   const uint32_t* fl = dst.flags + (int64_t)bh * dst.T_cap;
   uint32_t run = payload ? dst.out_count[bh] : 0u;
   uint32_t frun = foff ? foff[blk0] : 0u;
-  bool full = false;
   const int t_end = t_start + T_new;
-  for (int i0 = 0; i0 < nblk; i0 += 32) {
-    const int i = i0 + lane, ba = blk0 + i;
-    uint32_t c = 0, any_c = 0;
-    if (i < nblk) {
-      const int tb = ba * HQMQ_OUT_BLOCK;
+  const int sweep = kScanWarps * 32 * kScanIters;
+  bool full = false;       // a block of an earlier sweep did not fit the record capacity
+  for (int s0 = 0; s0 < nblk; s0 += sweep) {
+    // warp w owns the contiguous blocks [s0 + w*32*kScanIters, ...): lane-major inside an iteration
+    uint32_t c[kScanIters], fc[kScanIters];
+    uint32_t wsum = 0, wfsum = 0;
 #pragma unroll
-      for (int q = 0; q < HQMQ_OUT_BLOCK / 4; ++q) {
-        const uint4 w = *reinterpret_cast<const uint4*>(fl + tb + 4 * q);
-        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    for (int it = 0; it < kScanIters; ++it) {
+      const int i = s0 + (warp * kScanIters + it) * 32 + lane, ba = blk0 + i;
+      uint32_t cc = 0, any_c = 0;
+      if (i < nblk) {
+        const int tb = ba * HQMQ_OUT_BLOCK;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int t = tb + 4 * q + k;
-          if (t >= t_start && t < t_end) c += __popc(ww[k]);   // payload entries: tokens of this call only
-          if (t < t_end) any_c |= ww[k];                         // records: every token the block holds
+        for (int q = 0; q < HQMQ_OUT_BLOCK / 4; ++q) {
+          const uint4 w = *reinterpret_cast<const uint4*>(fl + tb + 4 * q);
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int t = tb + 4 * q + k;
+            if (t >= t_start && t < t_end) cc += __popc(ww[k]);   // payload entries: tokens of this call only
+            if (t < t_end) any_c |= ww[k];                          // records: every token the block holds
+          }
         }
       }
+      // a block gets its records in the call that completes it (all 16 tokens present), from flags and payload
+      const bool complete = i < nblk && (ba + 1) * HQMQ_OUT_BLOCK <= t_end;
+      c[it] = cc;
+      fc[it] = foff && complete ? (uint32_t)ofrag_records_for(any_c) : 0u;
+      wsum += cc; wfsum += fc[it];
     }
-    // a block gets its records in the call that completes it (all 16 tokens present), from flags and payload
-    const bool complete = i < nblk && (ba + 1) * HQMQ_OUT_BLOCK <= t_end;
-    const uint32_t fc = foff && complete ? (uint32_t)ofrag_records_for(any_c) : 0u;
-    uint32_t incl = c, fincl = fc;
+    wsum = __reduce_add_sync(0xffffffffu, wsum);
+    wfsum = __reduce_add_sync(0xffffffffu, wfsum);
+    if (lane == 0) { w_tot[warp] = wsum; w_ftot[warp] = wfsum; }
+    __syncthreads();
+    uint32_t base = run, fbase = frun, all = 0, fall = 0;
+    for (int w = 0; w < kScanWarps; ++w) {
+      if (w < warp) { base += w_tot[w]; fbase += w_ftot[w]; }
+      all += w_tot[w]; fall += w_ftot[w];
+    }
+    uint32_t my_last_ok = frun;      // largest inclusive record total within the capacity seen by this warp
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-      const uint32_t fv = __shfl_up_sync(0xffffffffu, fincl, o);
-      if (lane >= o) { incl += v; fincl += fv; }
-    }
-    if (payload) {
-      // A block that already holds tokens from an earlier call keeps its offset.
-      if (i < nblk && !(i == 0 && (t_start % HQMQ_OUT_BLOCK) != 0)) off[ba] = run + incl - c;
-      run += __shfl_sync(0xffffffffu, incl, 31);
+    for (int it = 0; it < kScanIters; ++it) {
+      const int i = s0 + (warp * kScanIters + it) * 32 + lane, ba = blk0 + i;
+      uint32_t incl = c[it], fincl = fc[it];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+        const uint32_t fv = __shfl_up_sync(0xffffffffu, fincl, o);
+        if (lane >= o) { incl += v; fincl += fv; }
+      }
+      if (payload) {
+        // A block that already holds tokens from an earlier call keeps its offset.
+        if (i < nblk && !(i == 0 && (t_start % HQMQ_OUT_BLOCK) != 0)) off[ba] = base + incl - c[it];
+        base += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (foff) {
+        fincl += fbase;
+        const bool ok = !full && fincl <= (uint32_t)dst.ofrag_cap;
+        fc[it] = ok ? fincl : 0xffffffffu;      // reused: the inclusive total, or "over the capacity"
+        if (ok && i < nblk) my_last_ok = max(my_last_ok, fincl);
+        fbase = __shfl_sync(0xffffffffu, fincl, 31);
+      }
     }
     if (foff) {
-      fincl += frun;
-      const bool ok = !full && fincl <= (uint32_t)dst.ofrag_cap;
-      const uint32_t last_ok = __reduce_max_sync(0xffffffffu, ok ? fincl : frun);
-      if (i < nblk) foff[ba + 1] = ok ? fincl : last_ok;
-      full = full || __any_sync(0xffffffffu, !ok);
+      my_last_ok = __reduce_max_sync(0xffffffffu, my_last_ok);
+      if (lane == 0) s_last_ok[warp] = my_last_ok;
+      __syncthreads();
+      uint32_t last_ok = frun;
+      for (int w = 0; w < kScanWarps; ++w) last_ok = max(last_ok, s_last_ok[w]);
+#pragma unroll
+      for (int it = 0; it < kScanIters; ++it) {
+        const int i = s0 + (warp * kScanIters + it) * 32 + lane;
+        if (i < nblk) foff[blk0 + i + 1] = fc[it] != 0xffffffffu ? fc[it] : last_ok;
+      }
+      full = full || frun + fall > last_ok;   // some block of this sweep was over the capacity
       frun = last_ok;
     }
+    run += all;
+    __syncthreads();      // w_tot / s_last_ok are rewritten by the next sweep
   }
-  if (payload && lane == 0) {
+  if (payload && threadIdx.x == 0) {
     off[blk0 + nblk] = run;
     if (run > (uint32_t)dst.out_cap) atomicOr(&status[0], 1u);
     dst.out_count[bh] = run;
@@ -1518,7 +1559,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
                                                         lut_ok ? reinterpret_cast<const uint32_t*>(a->lut) : nullptr, mul_s,
                                                         a->median_mult, a->med_out);
     if (med || d.ofrag)
-      scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, med ? 1 : 0, ws + wp.status);
+      scan_kernel<<<d.B * d.H, kScanWarps * 32, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, med ? 1 : 0, ws + wp.status);
     if (med) side_kernel<<<dim3((wp.nblk + 7) / 8, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, wp.blk0, wp.nblk);
     HQMQ_LAUNCH_CHECK();
     return HQMQ_OK;
@@ -1606,7 +1647,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   if (!med) {
     // no chunk of this call is flagged: the record offsets of its blocks just carry the running total on
     if (d.ofrag) {
-      scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, 0, ws + wp.status);
+      scan_kernel<<<d.B * d.H, kScanWarps * 32, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, 0, ws + wp.status);
       HQMQ_LAUNCH_CHECK();
     }
     return HQMQ_OK;
@@ -1662,7 +1703,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel);
   }
   HQMQ_LAUNCH_CHECK();
-  scan_kernel<<<(d.B * d.H + 3) / 4, 128, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, 1, ws + wp.status);
+  scan_kernel<<<d.B * d.H, kScanWarps * 32, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, 1, ws + wp.status);
   side_kernel<<<dim3((wp.nblk + 7) / 8, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, wp.blk0, wp.nblk);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;

@@ -1606,7 +1606,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     // tokens per CTA: long enough to amortise loading the tables, short enough to fill the machine twice
     int iters = (int)(((int64_t)a->T_new * d.B * d.H + (int64_t)2 * 148 * kEnc32Warps - 1) / ((int64_t)2 * 148 * kEnc32Warps));
     if (iters < 1) iters = 1;
-    if (iters > 64) iters = 64;
+    if (iters > 128) iters = 128;
     if (smem_fast > 48 * 1024)
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(fastk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fast));
     dim3 fgrid((a->T_new + kEnc32Warps * iters - 1) / (kEnc32Warps * iters), d.B * d.H);
@@ -1663,7 +1663,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   if (hb < 1) hb = 1;
   uint32_t* hist = ws + wp.hist;
   uint32_t* sel = ws + wp.sel;
-  int fgrid = (148 * 16 + bh_count - 1) / bh_count;
+  int fgrid = (148 * 32 + bh_count - 1) / bh_count;
   const int fgrid_max = (a->T_new + kF32Tok - 1) / kF32Tok;
   if (fgrid > fgrid_max) fgrid = fgrid_max;
   if (fgrid < 1) fgrid = 1;

@@ -49,6 +49,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read+write of attn_fast_kernel divided by the algorithmic bytes of the same launch, from the ncu
 # capture summarised in profiles/attn_decode_c2.md (batch 4 of the same workload; traffic scales with the tokens)
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.10
+L2_BYTES = 126e6     # B200 L2; a cache within twice this size is timed with a flush before every step
 
 
 def synth(kind, shape, seed, device, dtype):
@@ -166,6 +167,32 @@ def cpu_port_run(w, sample_T, reps, threads=None):
                 threads=torch.get_num_threads())
 
 
+def dense_sdpa_us(B, Hq, Hkv, T, d, dtype, dev, reps=10):
+    """Device time of torch's scaled_dot_product_attention (library kernel) for the same decode step over an
+    UNcompressed 16-bit cache of the same shape: the number a reader compares the compressed path with.
+    Random dense K/V (the values do not change the time); K/V are (B, H_kv, T, d) and the query heads of a
+    group are folded into the query length, so the cache is read once per KV head like in the compressed path."""
+    import torch.nn.functional as F
+    G = Hq // Hkv
+    K = torch.randn(B, Hkv, T, d, device=dev, dtype=dtype)
+    V = torch.randn(B, Hkv, T, d, device=dev, dtype=dtype)
+    Q = torch.randn(B, Hkv, G, d, device=dev, dtype=dtype)
+    for _ in range(3):
+        F.scaled_dot_product_attention(Q, K, V)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        F.scaled_dot_product_attention(Q, K, V)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / reps * 1e3
+    return {"us_per_step": us, "bytes": 2 * K.numel() * K.element_size(), "GBps": 2 * K.numel() * K.element_size() / us / 1e3,
+            "what": "torch scaled_dot_product_attention over a dense 16-bit cache of the same shape (query heads of a "
+                    "KV group as query rows); the cache exceeds L2" if 2 * K.numel() * K.element_size() > 2 * L2_BYTES else
+                    "torch scaled_dot_product_attention over a dense 16-bit cache of the same shape; cache within twice L2, not flushed"}
+
+
 def run_reference_arm(args, w, rank, world):
     """--impl reference: the reference's CPU implementation of the path (its torch restatement under
     oracle/, since the Python reference itself does not travel to the GPU box), all host threads, on a
@@ -210,6 +237,10 @@ def main():
     ap.add_argument("--no-med3x", action="store_true", help="encode without outlier extraction")
     ap.add_argument("--no-ofrag", action="store_true",
                     help="K cache without fragment records (attention merges K outliers from flags / side buffer)")
+    ap.add_argument("--push", action="store_true",
+                    help="with --seq-split: exchange the partials by direct stores into the peers' memory (NVLink, "
+                         "CUDA-IPC mapped buffers, bounded wait on local flag words) instead of an NCCL all_gather")
+    ap.add_argument("--no-dense", action="store_true", help="skip the dense 16-bit SDPA comparison line")
     ap.add_argument("--seq-split", action="store_true",
                     help="with N > 1: split ONE cache by sequence across the ranks (flash-decoding over NVLink: "
                          "partials + all_gather + merge) instead of giving every rank its own batch shard")
@@ -326,12 +357,15 @@ def main():
         ws_bytes = L.hqmq_attn_workspace_bytes(C.byref(a))
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream()
+    px = hd.PushExchange(B * Hq, d, dev) if seq_mode and args.push else None
 
     def step():
         rc = L.hqmq_attn_decode(C.byref(a), ws.data_ptr(), ws_bytes, stream.cuda_stream)
         if rc:
             raise RuntimeError(L.hqmq_strerror(rc).decode())
-        if seq_mode:
+        if px is not None:
+            px.step(part, Od)
+        elif seq_mode:
             dist.all_gather_into_tensor(allp.view(world * B, Hq, 1, d + 2), part)
             rc = L.hqmq_combine_partials(allp.data_ptr(), world, B * Hq, d, 1, _lib.dtype_enum(dtype), Od.data_ptr(),
                                          stream.cuda_stream)
@@ -343,35 +377,64 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if px is not None:
+        # the pushed exchange must reproduce the all_gather exchange bit for bit (same blocks, same merge order)
+        step()
+        pushed = Od.clone()
+        px_keep, px = px, None
+        step()
+        px = px_keep
+        torch.cuda.synchronize()
+        px.check()
+        if not torch.equal(pushed, Od):
+            raise RuntimeError("pushed exchange and all_gather exchange disagree")
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
-    # the timed region: exactly `steps` steps between barriers; the cache (>= 100 MB) exceeds what L2 keeps
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # the timed region: exactly `steps` steps between barriers.  A cache of more than twice the L2 size cannot
+    # stay in it; for a smaller one a 256 MiB buffer is rewritten before every timed step (outside the step's
+    # own pair of events), so that every step reads its cache from HBM.
+    need_flush = algo_bytes <= 2 * L2_BYTES
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if need_flush else None
+
+    def timed(n, one_step):
+        """Device seconds of n steps: one event pair around the loop, or one per step when L2 is flushed between."""
+        if flush_buf is None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(n):
+                one_step()
+            e1.record(stream)
+            barrier()
+            return e0.elapsed_time(e1) * 1e-3
+        pairs = []
+        for i in range(n):
+            flush_buf.fill_(i & 255)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            one_step()
+            e1.record(stream)
+            pairs.append((e0, e1))
+        barrier()
+        return sum(a_.elapsed_time(b_) for a_, b_ in pairs) * 1e-3
+
     barrier()
-    ev0.record(stream)
-    for _ in range(args.steps):
-        step()
-    ev1.record(stream)
-    barrier()
-    dev_s = ev0.elapsed_time(ev1) * 1e-3
+    dev_s = timed(args.steps, step)
+
     # e2e: host queries -> device, attention, output -> host, every step
-    for _ in range(3):
-        Qd.copy_(Qh, non_blocking=True); step(); Oh.copy_(Od, non_blocking=True)
-    barrier()
-    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev2.record(stream)
-    for _ in range(args.steps):
+    def e2e_step():
         Qd.copy_(Qh, non_blocking=True)
         step()
         Oh.copy_(Od, non_blocking=True)
         stream.synchronize()        # the caller consumes the output before the next token
-    ev3.record(stream)
+
+    for _ in range(3):
+        e2e_step()
     barrier()
-    e2e_s = ev2.elapsed_time(ev3) * 1e-3
+    e2e_s = timed(args.steps, e2e_step)
     # a short timed region can fall between two nvidia-smi samples: keep the same step running (untimed)
     # until the sampler has seen the GPU under this load
     t_probe = time.perf_counter()
@@ -382,6 +445,9 @@ def main():
     barrier()
     clocks = sampler.stop() if rank == 0 else None
 
+    if px is not None:
+        px.check()
+        px.close()
     t = torch.tensor([dev_s, e2e_s], device=dev, dtype=torch.float64)
     tot_bytes = torch.tensor([float(algo_bytes)], device=dev, dtype=torch.float64)
     if dist is not None:
@@ -407,15 +473,16 @@ def main():
                    "q_heads": Hq, "kv_heads": Hkv, "d_head": d, "context": T, "S": S, "radius_bits": br,
                    "median_mult": Cm, "outlier_fraction_K_V": outl_frac,
                    "k_fragment_records": bool(Kp.with_ofrag),
-                   "sharding": f"sequence x{world} (context {T_full} total, partials all_gather + merge)" if seq_mode else f"batch x{world}",
-                   "l2": "compressed cache per GPU exceeds L2 (inputs larger than L2, no flush needed)"
-                   if algo_bytes > 2 * 126e6 else "cache smaller than 2x L2: numbers include L2 hits"},
+                   "sharding": (f"sequence x{world} (context {T_full} total, partials pushed into the peers' memory + local merge)" if px is not None
+                                else f"sequence x{world} (context {T_full} total, partials all_gather + merge)") if seq_mode else f"batch x{world}",
+                   "l2": "compressed cache per GPU exceeds twice the L2 size (inputs larger than L2, no flush needed)"
+                   if not need_flush else "cache within twice the L2 size: 256 MiB rewritten before every timed step (L2 flushed)"},
         "compressed_bytes_per_step": total_bytes,
         "fp16_cache_bytes_equiv": 2 * 2 * B * Hkv * T * d * world,
         "e2e": {"value": total_bytes / (e2e_s / args.steps) / 1e9, "unit": "GB/s",
                 "us_per_step": e2e_s / args.steps * 1e6,
                 "h2d_bytes_per_step": Qh.numel() * Qh.element_size(), "d2h_bytes_per_step": Oh.numel() * Oh.element_size()},
-        "gpu_launches": (3 if seq_mode else 2) * args.steps,
+        "gpu_launches": (5 if px is not None else 3 if seq_mode else 2) * args.steps,
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8TBs_nominal": per_gpu_gbs / 8000.0,
                      "kernel": "attn_fast_kernel (+ combine_kernel, 3 % of the step, inside the same timed region)",
@@ -426,6 +493,11 @@ def main():
                    "note": "one call per tensor over the whole (B, H_kv, T, d) input, Med3x median per call; median of 3 timed calls after 1 warm-up call"},
         "clocks": clocks,
     }
+    if not args.no_dense and world == 1:
+        try:
+            line["dense_sdpa"] = dense_sdpa_us(B, Hq, Hkv, T, d, dtype, dev)
+        except Exception as e:      # a comparison line only: never lose the bench line to it
+            line["dense_sdpa"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     if not args.no_cpu_baseline:
         sample_T = min(T, 4096)
         info = cpu_port_run(w, sample_T, reps=3)

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("HQMQ_B200_LIB") or os.path.join(HERE, "libhqmq_b200.so")
 
 F32, F16, BF16, I32, I16, I8, U8, I64 = range(8)
-ABI_VERSION = 2
+ABI_VERSION = 3
 OUT_BLOCK = 16
 OFRAG_BYTES = 528
 T_ALIGN = 64
@@ -65,7 +65,7 @@ class EncodeArgs(C.Structure):
         ("struct_size", C.c_uint32), ("x_dtype", C.c_int32), ("x", C.c_void_p), ("x_stride", C.c_int64 * 3),
         ("T_new", C.c_int32), ("t_start", C.c_int32), ("qs", C.c_void_p), ("joint", C.c_void_p),
         ("median_mult", C.c_float), ("search", C.c_int32), ("dst", Packed), ("med_out", C.c_void_p),
-        ("lut", C.c_void_p), ("lut_max_cand", C.c_int32), ("reserved", C.c_int32),
+        ("lut", C.c_void_p), ("lut_max_cand", C.c_int32), ("reserved", C.c_int32), ("med_in", C.c_void_p),
     ]
 
 
@@ -90,6 +90,16 @@ class AttnArgs(C.Structure):
         ("K", Packed), ("V", Packed), ("table_K", C.c_void_p), ("table_V", C.c_void_p),
         ("K_ref", RefPacked), ("V_ref", RefPacked), ("joint_dtype", C.c_int32), ("K_size", C.c_int32),
         ("joint_K", C.c_void_p), ("joint_V", C.c_void_p), ("partials", C.c_void_p),
+    ]
+
+
+EXCHANGE_MAX_RANKS = 16
+
+
+class Exchange(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("world", C.c_int32), ("rank", C.c_int32), ("reserved", C.c_int32),
+        ("block_floats", C.c_int64), ("recv", C.c_void_p * EXCHANGE_MAX_RANKS), ("flags", C.c_void_p * EXCHANGE_MAX_RANKS),
     ]
 
 
@@ -124,6 +134,10 @@ def lib():
     L.hqmq_encode_workspace_bytes.restype = C.c_size_t
     L.hqmq_encode_workspace_bytes.argtypes = [C.POINTER(EncodeArgs)]
     L.hqmq_encode.argtypes = [C.POINTER(EncodeArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    L.hqmq_med3x_state_bytes.restype = C.c_size_t
+    L.hqmq_med3x_state_bytes.argtypes = [C.c_int]
+    L.hqmq_med3x_hist.argtypes = [C.POINTER(EncodeArgs), C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    L.hqmq_med3x_select.argtypes = [C.c_int, C.c_int, C.c_uint64, C.c_float, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
     L.hqmq_unpack.argtypes = [C.POINTER(Packed), C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                               C.c_void_p]
     L.hqmq_pack.argtypes = [C.POINTER(RefPacked), C.c_int, C.POINTER(Packed), C.c_int, C.c_void_p]
@@ -132,6 +146,12 @@ def lib():
     L.hqmq_attn_workspace_bytes.argtypes = [C.POINTER(AttnArgs)]
     L.hqmq_attn_decode.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     L.hqmq_attn_decode_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+    L.hqmq_exchange_recv_bytes.restype = C.c_size_t
+    L.hqmq_exchange_recv_bytes.argtypes = [C.c_int, C.c_int64]
+    L.hqmq_exchange_flag_bytes.restype = C.c_size_t
+    L.hqmq_exchange_flag_bytes.argtypes = [C.c_int]
+    L.hqmq_exchange_push.argtypes = [C.POINTER(Exchange), C.c_void_p, C.c_uint32, C.c_void_p]
+    L.hqmq_exchange_wait.argtypes = [C.POINTER(Exchange), C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
     L.hqmq_read_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]
     L.hqmq_combine_partials.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     if L.hqmq_abi_version() != ABI_VERSION:

@@ -258,6 +258,7 @@ const char* hqmq_strerror(int code) {
     case HQMQ_ERR_CAPACITY: return "packed cache or outlier buffer capacity exceeded";
     case HQMQ_ERR_STATIC_SCRATCH:
       return "the problem needs more scratch than the library's built-in buffer; call hqmq_attn_decode with a workspace";
+    case HQMQ_ERR_TIMEOUT: return "a bounded device-side wait ran out";
     default: return "unknown error";
   }
 }

@@ -733,9 +733,11 @@ hist_kernel(EncGeom g, const void* __restrict__ x, uint32_t* __restrict__ hist, 
   for (int i = threadIdx.x; i < 2 * kHistBins; i += blockDim.x) (&sh[0][0])[i] = 0;
   __syncthreads();
   const uint32_t p0 = sel[h * 8 + 0], p1 = sel[h * 8 + 2];
-  const int hs = level == 1 ? 21 : 10;                   // bits already fixed are above hs
-  const int ds = level == 1 ? 10 : 0;
-  const uint32_t dm = level == 1 ? 0x7ffu : 0x3ffu;
+  // level 0 (used when the histograms of several GPUs are summed between the levels): nothing is fixed yet; a
+  // norm has sign bit 0 and `sel` starts zeroed, so comparing bit 31 alone lets every key through
+  const int hs = level == 0 ? 31 : level == 1 ? 21 : 10;   // bits already fixed are above hs
+  const int ds = level == 0 ? 21 : level == 1 ? 10 : 0;
+  const uint32_t dm = level == 2 ? 0x3ffu : 0x7ffu;
   const int64_t total = (int64_t)g.T_new * g.n;
   const int64_t per_block = (total + gridDim.x - 1) / gridDim.x;
   const int64_t i0 = blockIdx.x * per_block, i1 = min(total, i0 + per_block);
@@ -802,9 +804,11 @@ hist32_kernel(Fast32 f, uint32_t* __restrict__ hist, const uint32_t* __restrict_
   for (int i = threadIdx.x; i < 2 * kHistBins; i += blockDim.x) (&sh[0][0])[i] = 0;
   __syncthreads();
   const uint32_t p0 = sel[h * 8 + 0], p1 = sel[h * 8 + 2];
-  const int hs = level == 1 ? 21 : 10;                   // bits already fixed are above hs
-  const int ds = level == 1 ? 10 : 0;
-  const uint32_t dm = level == 1 ? 0x7ffu : 0x3ffu;
+  // level 0 (used when the histograms of several GPUs are summed between the levels): nothing is fixed yet; a
+  // norm has sign bit 0 and `sel` starts zeroed, so comparing bit 31 alone lets every key through
+  const int hs = level == 0 ? 31 : level == 1 ? 21 : 10;   // bits already fixed are above hs
+  const int ds = level == 0 ? 21 : level == 1 ? 10 : 0;
+  const uint32_t dm = level == 2 ? 0x3ffu : 0x7ffu;
   const uint32_t q0 = p0 >> hs, q1 = p1 >> hs;
   const bool same = q0 == q1;                            // both order statistics share the prefix: one histogram
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, l16 = lane & 15;
@@ -1468,7 +1472,7 @@ using namespace hqmq;
 
 static int validate_encode(const hqmq_encode_args* a) {
   if (!a || a->struct_size != sizeof(hqmq_encode_args)) return HQMQ_ERR_ARG;
-  if (!a->x || !a->qs || !a->joint) return HQMQ_ERR_ARG;
+  if ((!a->x && a->T_new != 0) || !a->qs || !a->joint) return HQMQ_ERR_ARG;   // an empty input has no address
   if (!is_float_dtype(a->x_dtype)) return HQMQ_ERR_DTYPE;
   const bool med = a->median_mult > 0.f;
   int rc = check_packed(a->dst, med);
@@ -1521,6 +1525,70 @@ extern "C" int hqmq_encode_lut_max_candidates(const void* lut, int H, int* max_c
   return HQMQ_OK;
 }
 
+// ---- Med3x median of a head whose batch entries live on several GPUs ---------------------------------------
+// State: [H][3 levels][2 queries][kHistBins] histograms, then [H][8] select words (the layout select_kernel uses).
+namespace hqmq {
+namespace {
+inline size_t med3x_state_words(int H) { return (size_t)H * 3 * 2 * kHistBins + (size_t)H * 8; }
+
+__global__ void thr_from_median_kernel(const float* __restrict__ med_in, float C, int H, uint32_t* __restrict__ sel,
+                                       float* __restrict__ med_out) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  const float med = med_in[h];
+  sel[h * 8 + 6] = __float_as_uint(__fmul_rn(med, C));   // thr = med * C in fp32, like the local select
+  sel[h * 8 + 7] = __float_as_uint(med);
+  if (med_out) med_out[h] = med;
+}
+}  // namespace
+}  // namespace hqmq
+using namespace hqmq;
+
+extern "C" size_t hqmq_med3x_state_bytes(int H) { return H < 1 ? 0 : med3x_state_words(H) * 4; }
+
+extern "C" int hqmq_med3x_hist(const hqmq_encode_args* a, int level, void* state, size_t state_bytes, void* stream) {
+  int rc = validate_encode(a);
+  if (rc) return rc;
+  if (level < 0 || level > 2) return HQMQ_ERR_ARG;
+  const hqmq_packed& d = a->dst;
+  if (!state || state_bytes < med3x_state_words(d.H) * 4) return HQMQ_ERR_WORKSPACE;
+  if ((uintptr_t)state & 15) return HQMQ_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint32_t* hist = reinterpret_cast<uint32_t*>(state);
+  uint32_t* sel = hist + (size_t)d.H * 3 * 2 * kHistBins;
+  if (level == 0) HQMQ_CHECK_CUDA(cudaMemsetAsync(state, 0, med3x_state_words(d.H) * 4, st));
+  if (a->T_new == 0) return HQMQ_OK;     // this GPU holds none of the head's tokens: its histograms stay zero
+  EncGeom g;
+  g.B = d.B; g.H = d.H; g.T_new = a->T_new; g.n = d.n_chunks;
+  g.npl = 1; while (g.npl < g.n) g.npl <<= 1;
+  g.tpw = 32 / g.npl;
+  g.S = d.S; g.ib = idx_bits_for(d.S); g.rbits = d.radius_bits; g.qmax = (1 << d.radius_bits) - 1;
+  g.x_dtype = a->x_dtype;
+  g.xs_b = a->x_stride[0]; g.xs_h = a->x_stride[1]; g.xs_t = a->x_stride[2];
+  const int bh_count = d.B * d.H;
+  const int64_t per_bh = (int64_t)a->T_new * d.n_chunks;
+  int hb = (148 * 16 + bh_count - 1) / bh_count;
+  const int hb_max = (int)((per_bh + 256 * 16 - 1) / (256 * 16));
+  if (hb > hb_max) hb = hb_max;
+  if (hb < 1) hb = 1;
+  hist_kernel<<<dim3(hb, bh_count), 256, 0, st>>>(g, a->x, hist, sel, level);
+  HQMQ_LAUNCH_CHECK();
+  return HQMQ_OK;
+}
+
+extern "C" int hqmq_med3x_select(int H, int level, uint64_t n_total, float median_mult, void* state, size_t state_bytes,
+                                 float* med_out, void* stream) {
+  if (H < 1 || level < 0 || level > 2 || n_total < 1 || !(median_mult > 0.f)) return HQMQ_ERR_ARG;
+  if (!state || state_bytes < med3x_state_words(H) * 4) return HQMQ_ERR_WORKSPACE;
+  if ((uintptr_t)state & 15) return HQMQ_ERR_ALIGN;
+  uint32_t* hist = reinterpret_cast<uint32_t*>(state);
+  uint32_t* sel = hist + (size_t)H * 3 * 2 * kHistBins;
+  select_kernel<<<H, 256, 0, (cudaStream_t)stream>>>(hist, sel, level, n_total, median_mult, level == 2 ? med_out : nullptr,
+                                                     nullptr, nullptr, nullptr);
+  HQMQ_LAUNCH_CHECK();
+  return HQMQ_OK;
+}
+
 extern "C" size_t hqmq_encode_workspace_bytes(const hqmq_encode_args* a) {
   if (validate_encode(a) != HQMQ_OK) return 0;
   return plan_ws(*a).total;
@@ -1529,10 +1597,10 @@ extern "C" size_t hqmq_encode_workspace_bytes(const hqmq_encode_args* a) {
 extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t workspace_bytes, void* stream) {
   int rc = validate_encode(a);
   if (rc) return rc;
+  if (a->T_new == 0) return HQMQ_OK;   // appending nothing: the planes stay as they are, no workspace needed
   const WsPlan wp = plan_ws(*a);
   if (!workspace || workspace_bytes < wp.total) return HQMQ_ERR_WORKSPACE;
   if ((uintptr_t)workspace & 15) return HQMQ_ERR_ALIGN;
-  if (a->T_new == 0) return HQMQ_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const hqmq_packed& d = a->dst;
   const bool med = a->median_mult > 0.f;
@@ -1550,7 +1618,8 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   memcpy(maps.ref_to_native, index_maps().ref_to_native, 24);
 
   // Small calls (decode-time appends): one kernel per head does main pass, median and flags at once.
-  if ((int64_t)d.B * a->T_new * g.n <= kSmallMax && (int64_t)d.B * a->T_new <= kSmallTok) {
+  const bool ext_med = med && a->med_in != nullptr;   // the median comes from the caller (batch of a head split over GPUs)
+  if (!ext_med && (int64_t)d.B * a->T_new * g.n <= kSmallMax && (int64_t)d.B * a->T_new <= kSmallTok) {
     static const Mul8x24 mul_s = make_mul();
     const bool lut_ok = a->search == 0 && a->lut != nullptr && a->lut_max_cand >= 0;
     if (lut_ok && ((uintptr_t)a->lut & 15)) return HQMQ_ERR_ALIGN;
@@ -1612,7 +1681,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     dim3 fgrid((a->T_new + kEnc32Warps * iters - 1) / (kEnc32Warps * iters), d.B * d.H);
     // Med3x: a sample of the tokens predicts which bins hold the two middle order statistics, so that this
     // pass can histogram their next digit as well (level 1 of the radix select then needs no pass of its own)
-    predicted = med && fast32 && a->T_new >= 1024;
+    predicted = med && !ext_med && fast32 && a->T_new >= 1024;
     if (predicted) {
       const int n_s = (a->T_new + kSampleStride - 1) / kSampleStride;
       int gs = (148 * 8 + d.B * d.H - 1) / (d.B * d.H);
@@ -1625,7 +1694,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     }
     const uint32_t* sel_s_arg = predicted ? ws + wp.sel_s : nullptr;
     const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a->x);
-    uint32_t* hist_arg = med ? ws + wp.hist : nullptr;
+    uint32_t* hist_arg = med && !ext_med ? ws + wp.hist : nullptr;
     const uint32_t* lut_arg = reinterpret_cast<const uint32_t*>(a->lut);
     int t_start_arg = a->t_start;
     void* kargs[] = {(void*)&g, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&hist_arg, (void*)&maps,
@@ -1634,13 +1703,13 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   } else if (use_lut) {
     if (smem_lut > 48 * 1024)
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(encode_main_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_lut));
-    encode_main_kernel<true><<<grid, kEncThreads, smem_lut, st>>>(g, a->x, a->qs, d, a->t_start, med ? ws + wp.hist : nullptr,
+    encode_main_kernel<true><<<grid, kEncThreads, smem_lut, st>>>(g, a->x, a->qs, d, a->t_start, med && !ext_med ? ws + wp.hist : nullptr,
                                                                   maps, a->joint, reinterpret_cast<const uint32_t*>(a->lut),
                                                                   cand_smem, mul);
   } else {
     if (smem_base > 48 * 1024)
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(encode_main_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_base));
-    encode_main_kernel<false><<<grid, kEncThreads, smem_base, st>>>(g, a->x, a->qs, d, a->t_start, med ? ws + wp.hist : nullptr,
+    encode_main_kernel<false><<<grid, kEncThreads, smem_base, st>>>(g, a->x, a->qs, d, a->t_start, med && !ext_med ? ws + wp.hist : nullptr,
                                                                     maps, a->joint, nullptr, 0, mul);
   }
   HQMQ_LAUNCH_CHECK();
@@ -1673,6 +1742,16 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   uint32_t* und = ws + wp.und;
   const uint32_t* sel_s = predicted ? ws + wp.sel_s : nullptr;
   uint32_t* hist_fb = ws + wp.hist_fb;
+  if (ext_med) {
+    // threshold from the caller's medians, then the plain flag pass (any geometry)
+    thr_from_median_kernel<<<(d.H + 63) / 64, 64, 0, st>>>(a->med_in, a->median_mult, d.H, sel, a->med_out);
+    const int tok_per_fblock = 8 * g.tpw;
+    int fb = (a->T_new + 4 * tok_per_fblock - 1) / (4 * tok_per_fblock);
+    const int fb_cap = (148 * 32 + bh_count - 1) / bh_count;
+    if (fb > fb_cap) fb = fb_cap;
+    if (fb < 1) fb = 1;
+    flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel);
+  } else {
   select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr, nullptr, nullptr, nullptr);
   if (fast32) {
     // (with a prediction this launch returns at once unless the sample named the wrong bins)
@@ -1701,6 +1780,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     if (fb > fb_cap) fb = fb_cap;
     if (fb < 1) fb = 1;
     flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel);
+  }
   }
   HQMQ_LAUNCH_CHECK();
   scan_kernel<<<d.B * d.H, kScanWarps * 32, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, 1, ws + wp.status);

@@ -1,0 +1,110 @@
+// Exchange of sequence-split attention partials between GPUs by direct stores over NVLink.
+//
+// When one long context is split by sequence over N GPUs, every GPU ends a decode step with one block of
+// un-normalised partial results (o[d], m, l per query head: 17 KB at 32 heads x d 128) that every other GPU
+// needs before it can merge.  An all_gather does that with a collective launch on every rank; here each rank
+// instead WRITES its block into slot `rank` of every peer's receive buffer (peer-mapped pointers, plain
+// vectorised stores), then publishes a per-step epoch word with a system-scope release store.  The consumer
+// polls only its OWN memory, with a bounded number of polls; a wait that runs out records the missing ranks
+// in a status word and returns, so the context stays usable and the host can report the failure.
+//
+// No load ever targets a peer's memory, nothing is multicast, and no kernel of one GPU waits for another
+// kernel of the SAME GPU: the producer of every flag a kernel polls runs on a different device.
+#include <cuda_runtime.h>
+
+#include "../../include/hqmq_b200.h"
+#include "common.cuh"
+
+namespace hqmq {
+namespace {
+
+constexpr uint32_t kDefaultPolls = 1u << 22;     // x >= 100 ns of sleep per poll: gives up after roughly a second
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// One CTA per destination rank (this rank's own receive buffer included).
+__global__ void __launch_bounds__(256)
+push_kernel(hqmq_exchange x, const float* __restrict__ local, uint32_t epoch) {
+  const int p = blockIdx.x;
+  const int par = (int)(epoch & 1u);
+  float* dst = x.recv[p] + ((int64_t)par * x.world + x.rank) * x.block_floats;
+  const int64_t n4 = x.block_floats >> 2;
+  const float4* s4 = reinterpret_cast<const float4*>(local);
+  float4* d4 = reinterpret_cast<float4*>(dst);
+  for (int64_t i = threadIdx.x; i < n4; i += blockDim.x) d4[i] = s4[i];
+  for (int64_t i = (n4 << 2) + threadIdx.x; i < x.block_floats; i += blockDim.x) dst[i] = local[i];
+  __threadfence_system();          // every thread's stores are visible system-wide before the epoch word is
+  __syncthreads();
+  if (threadIdx.x == 0) st_release_sys(x.flags[p] + par * x.world + x.rank, epoch);
+}
+
+// One CTA; thread r waits for rank r's epoch word in this GPU's own memory.
+__global__ void __launch_bounds__(32)
+wait_kernel(hqmq_exchange x, uint32_t epoch, uint32_t max_polls, uint32_t* __restrict__ status) {
+  const int r = threadIdx.x;
+  const int par = (int)(epoch & 1u);
+  bool missing = false;
+  if (r < x.world) {
+    const uint32_t* f = x.flags[x.rank] + par * x.world + r;
+    uint32_t polls = 0;
+    while (ld_acquire_sys(f) != epoch) {
+      if (++polls >= max_polls) { missing = true; break; }
+      __nanosleep(100);
+    }
+  }
+  const uint32_t miss = __ballot_sync(0xffffffffu, missing);
+  if (r == 0 && miss) atomicOr(status, miss);     // bit r = rank r's block of this step never arrived
+}
+
+int validate(const hqmq_exchange* x) {
+  if (!x || x->struct_size != sizeof(hqmq_exchange)) return HQMQ_ERR_ARG;
+  if (x->world < 1 || x->world > HQMQ_EXCHANGE_MAX_RANKS || x->rank < 0 || x->rank >= x->world) return HQMQ_ERR_ARG;
+  if (x->block_floats < 1) return HQMQ_ERR_SHAPE;
+  for (int p = 0; p < x->world; ++p) {
+    if (!x->recv[p] || !x->flags[p]) return HQMQ_ERR_ARG;
+    if (((uintptr_t)x->recv[p] & 15) || ((uintptr_t)x->flags[p] & 3)) return HQMQ_ERR_ALIGN;
+  }
+  if (x->block_floats % 4) return HQMQ_ERR_ALIGN;   // every slot starts on a 16-byte boundary
+  return HQMQ_OK;
+}
+
+}  // namespace
+}  // namespace hqmq
+using namespace hqmq;
+
+extern "C" size_t hqmq_exchange_recv_bytes(int world, int64_t block_floats) {
+  if (world < 1 || world > HQMQ_EXCHANGE_MAX_RANKS || block_floats < 1) return 0;
+  return (size_t)2 * world * block_floats * sizeof(float);
+}
+
+extern "C" size_t hqmq_exchange_flag_bytes(int world) {
+  if (world < 1 || world > HQMQ_EXCHANGE_MAX_RANKS) return 0;
+  return (size_t)2 * world * sizeof(uint32_t);
+}
+
+extern "C" int hqmq_exchange_push(const hqmq_exchange* x, const float* local, uint32_t epoch, void* stream) {
+  int rc = validate(x);
+  if (rc) return rc;
+  if (!local || epoch == 0) return HQMQ_ERR_ARG;
+  if ((uintptr_t)local & 15) return HQMQ_ERR_ALIGN;
+  push_kernel<<<x->world, 256, 0, (cudaStream_t)stream>>>(*x, local, epoch);
+  HQMQ_LAUNCH_CHECK();
+  return HQMQ_OK;
+}
+
+extern "C" int hqmq_exchange_wait(const hqmq_exchange* x, uint32_t epoch, uint32_t max_polls, uint32_t* status,
+                                  void* stream) {
+  int rc = validate(x);
+  if (rc) return rc;
+  if (!status || epoch == 0) return HQMQ_ERR_ARG;
+  wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(*x, epoch, max_polls ? max_polls : kDefaultPolls, status);
+  HQMQ_LAUNCH_CHECK();
+  return HQMQ_OK;
+}

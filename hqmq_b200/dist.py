@@ -2,11 +2,15 @@
 
 The reference is single-GPU.  Both halves shard without any data-path collective over the units
 (batch, KV head): the encoder's Med3x median couples only the batch entries of one head, and decode
-attention is independent per (batch, KV head).  Only two exchanges exist:
+attention is independent per (batch, KV head).  Three exchanges exist:
   * gathering the attention outputs of KV-head shards (an all_gather of (B, H_q/N, 1, d) tensors), and
   * for a cache split by SEQUENCE across GPUs (one very long context), merging the per-GPU partial
     results (o[d], m, l) of each query head: one all_gather of (B, H_q, 1, d+2) fp32 followed by the
-    library's merge kernel.
+    library's merge kernel, and
+  * for a head whose BATCH entries are spread over several GPUs (more GPUs than KV heads): the encoder's
+    Med3x median must still be the one over every batch entry of the head, so the three histogram levels
+    of its radix select are summed over those GPUs (three all_reduce of 16 KB per head; integer sums, so
+    every GPU derives identical bits).
 """
 from __future__ import annotations
 
@@ -75,3 +79,150 @@ def seq_parallel_attention(Q: torch.Tensor, K_local, V_local, table_K, table_V, 
                            partials=part)
     allp = gather_partials(part, group)
     return combine_partials(allp, out_dtype or Q.dtype)
+
+
+HIST_BINS = 2048      # bins per radix-select histogram of the library (two histograms per level and head)
+
+
+def summed_radix_select(hist_level, level_view, select_level, group=None) -> None:
+    """The exchange pattern of a median over values that live on several ranks: for each of the three digit
+    levels, ``hist_level(level)`` histograms this rank's values into its own state, the level's counters
+    (``level_view(level)``, an integer tensor view of that state) are summed over the ranks of ``group``, and
+    ``select_level(level)`` narrows the search on the summed counters -- identically on every rank."""
+    for level in range(3):
+        hist_level(level)
+        view = level_view(level)
+        tmp = view.contiguous()
+        dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=group)
+        if tmp.data_ptr() != view.data_ptr():
+            view.copy_(tmp)
+        select_level(level)
+
+
+def split_batch_median(quant, x: torch.Tensor, layer_idx: int, kv: int, out, group=None,
+                       n_total: Optional[int] = None) -> torch.Tensor:
+    """Med3x medians (H,) fp32 of the chunk norms of x over ALL ranks of ``group``: every rank passes its own
+    batch entries of the same H heads (same T_new not required; a rank may hold none).  ``quant`` is the
+    outlier-aware wrapper, ``out`` the cache the following ``encode(..., med_in=...)`` call will append to.
+    ``n_total`` = chunk norms per head over all ranks (computed with one more all_reduce when not given)."""
+    import ctypes as C
+    from . import _lib
+    inner, mult = quant.inner, float(quant.median_mult)
+    B, H, T, d = x.shape
+    if x.stride(-1) != 1 or any(s % 4 for s in x.stride()[:3]):
+        x = x.contiguous()
+    L = _lib.lib()
+    dev = x.device
+    a = inner._enc_args(x, layer_idx, kv, out, mult)
+    nbytes = L.hqmq_med3x_state_bytes(H)
+    state = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    hist = state[: H * 3 * 2 * HIST_BINS * 4].view(torch.int32).view(H, 3, 2, HIST_BINS)
+    med = torch.empty(H, dtype=torch.float32, device=dev)
+    if n_total is None:
+        n = torch.tensor([B * T * (d // 4)], dtype=torch.int64, device=dev)
+        dist.all_reduce(n, op=dist.ReduceOp.SUM, group=group)
+        n_total = int(n.item())
+
+    def hist_level(level):
+        with _lib.device_guard(dev):
+            _lib.check(L.hqmq_med3x_hist(C.byref(a), level, state.data_ptr(), nbytes, _lib.stream_ptr()), "hqmq_med3x_hist")
+
+    def select_level(level):
+        with _lib.device_guard(dev):
+            _lib.check(L.hqmq_med3x_select(H, level, n_total, mult, state.data_ptr(), nbytes, med.data_ptr(),
+                                           _lib.stream_ptr()), "hqmq_med3x_select")
+
+    summed_radix_select(hist_level, lambda level: hist[:, level], select_level, group)
+    return med
+
+
+def encode_split_batch(quant, x: torch.Tensor, layer_idx: int, kv: int, out=None, group=None, **kw):
+    """``quant.encode`` for a rank that holds only some batch entries of its heads: the Med3x threshold is the
+    one the reference would take over the whole batch (src/quantizers/outlier_aware.py:63-72).  Every rank of
+    ``group`` must make the call."""
+    inner = quant.inner
+    B, H, T, d = x.shape
+    if out is None:
+        sd = x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.float32
+        out = inner.new_cache(B, max(T, 1), d, x.device, scale_dtype=sd, with_outliers=True, out_dtype=x.dtype,
+                              ofrag=kv == 0)
+    med = split_batch_median(quant, x, layer_idx, kv, out, group)
+    return quant.encode(x, layer_idx, kv, out=out, med_in=med, **kw)
+
+
+class PushExchange:
+    """Sequence-split partials exchanged by direct stores into the peers' memory (see hqmq_exchange in
+    include/hqmq_b200.h) instead of an all_gather: one small kernel per step stores this rank's block into
+    every peer, one polls this GPU's own flag words, then the usual merge runs on the local receive buffer.
+
+    Set-up (collective over ``group``, once): every rank allocates its receive buffer and flag words, exports
+    them with CUDA IPC through torch's tensor sharing, and maps the peers' ones.  ``rows`` = B * H_q * T_q
+    rows of d + 2 floats per rank.  All ranks must call ``step`` the same number of times."""
+
+    def __init__(self, rows: int, d: int, device, group=None, max_polls: int = 0):
+        import ctypes as C
+        from torch.multiprocessing.reductions import reduce_tensor
+        from . import _lib
+        self.group, self.rows, self.d = group, rows, d
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.block = rows * (d + 2)
+        if self.block % 4:
+            raise ValueError(f"rows * (d + 2) = {self.block} must be a multiple of 4 (16-byte slots)")
+        if self.world > _lib.EXCHANGE_MAX_RANKS:
+            raise ValueError(f"at most {_lib.EXCHANGE_MAX_RANKS} ranks")
+        L = _lib.lib()
+        dev = torch.device(device)
+        self.recv = torch.zeros(L.hqmq_exchange_recv_bytes(self.world, self.block) // 4, dtype=torch.float32, device=dev)
+        self.flags = torch.zeros(L.hqmq_exchange_flag_bytes(self.world) // 4, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize(dev)
+        mine = tuple(reduce_tensor(t) for t in (self.recv, self.flags))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._peers = []                       # the mapped tensors stay alive with this object
+        x = _lib.Exchange()
+        x.struct_size = C.sizeof(_lib.Exchange)
+        x.world, x.rank, x.block_floats = self.world, self.rank, self.block
+        for p, shared in enumerate(everyone):
+            if p == self.rank:
+                r, f = self.recv, self.flags
+            else:
+                (fn_r, args_r), (fn_f, args_f) = shared
+                r, f = fn_r(*args_r), fn_f(*args_f)
+                self._peers.append((r, f))
+            x.recv[p], x.flags[p] = r.data_ptr(), f.data_ptr()
+        self.x, self.max_polls, self.epoch = x, max_polls, 0
+        dist.barrier(group=group)              # every rank has mapped every buffer before anyone stores into one
+
+    def step(self, part: torch.Tensor, out: torch.Tensor) -> None:
+        """Enqueue on the current stream: push ``part`` (rows, d + 2 fp32, contiguous) to all ranks, wait for all
+        ranks' blocks of this step, merge them into ``out`` (rows, d)."""
+        import ctypes as C
+        from . import _lib
+        L = _lib.lib()
+        if part.dtype != torch.float32 or part.numel() != self.block or not part.is_contiguous():
+            raise ValueError("part must be contiguous fp32 with rows * (d + 2) elements")
+        self.epoch += 1
+        st = _lib.stream_ptr()
+        _lib.check(L.hqmq_exchange_push(C.byref(self.x), part.data_ptr(), self.epoch, st), "hqmq_exchange_push")
+        _lib.check(L.hqmq_exchange_wait(C.byref(self.x), self.epoch, self.max_polls, self.status.data_ptr(), st),
+                   "hqmq_exchange_wait")
+        src = self.recv.data_ptr() + (self.epoch & 1) * self.world * self.block * 4
+        _lib.check(L.hqmq_combine_partials(src, self.world, self.rows, self.d, 1, _lib.dtype_enum(out.dtype),
+                                           out.data_ptr(), st), "hqmq_combine_partials")
+
+    def check(self) -> None:
+        """Synchronise and raise if a wait ran out since the last check (bit r of the status = rank r missing)."""
+        from . import _lib
+        s = int(self.status.item()) & 0xffffffff
+        if s:
+            self.status.zero_()
+            missing = [r for r in range(self.world) if s >> r & 1]
+            raise _lib.HqmqError(f"hqmq_b200: exchange timed out waiting for the partials of ranks {missing} (-11)")
+
+    def close(self) -> None:
+        """Collective: nobody unmaps a buffer that a peer may still store into."""
+        torch.cuda.synchronize(self.recv.device)
+        dist.barrier(group=self.group)
+        self._peers.clear()
+        dist.barrier(group=self.group)

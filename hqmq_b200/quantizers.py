@@ -185,16 +185,42 @@ class HQMQQuantizer(KVQuantizer):
                         scale_dtype=scale_dtype, with_outliers=with_outliers, out_dtype=out_dtype, out_cap=out_cap,
                         ofrag=ofrag, ofrag_cap=ofrag_cap)
 
+    def _enc_args(self, x, layer_idx, kv, out, median_mult=None, search=0, med_out=None, med_in=None):
+        """The hqmq_encode_args of one call (x already validated and laid out, ``out`` the destination cache)."""
+        tb = self.tables(layer_idx, kv, x.device)
+        B, H, T, d = x.shape
+        a = _lib.EncodeArgs()
+        a.struct_size = C.sizeof(_lib.EncodeArgs)
+        a.x_dtype, a.x = _lib.dtype_enum(x.dtype), x.data_ptr()
+        a.x_stride = (C.c_int64 * 3)(*x.stride()[:3])
+        a.T_new, a.t_start = T, out.T
+        a.qs, a.joint = tb["qs"].data_ptr(), tb["joint"].data_ptr()
+        a.median_mult = float(median_mult) if median_mult is not None else 0.0
+        a.search = search
+        a.dst = out.c_struct()
+        a.med_out = med_out.data_ptr() if med_out is not None else None
+        if med_in is not None:
+            if median_mult is None:
+                raise ValueError("med_in needs a median multiplier (Med3x encode)")
+            if med_in.dtype != torch.float32 or med_in.numel() != H or med_in.device != x.device or not med_in.is_contiguous():
+                raise ValueError("med_in must be a contiguous (H,) fp32 tensor on the device of x")
+            a.med_in = med_in.data_ptr()
+        a.lut, a.lut_max_cand = tb["lut"].data_ptr(), tb["lut_max_cand"]
+        a._keep = (x, tb, out, med_out, med_in)     # the struct holds raw addresses: keep their owners alive with it
+        return a
+
     def encode(self, x: torch.Tensor, layer_idx: int, kv: int, out: Optional[PackedKV] = None,
                median_mult: Optional[float] = None, scale_dtype: Optional[torch.dtype] = None,
                search: int = 0, med_out: Optional[torch.Tensor] = None, ofrag: Optional[bool] = None,
-               check_status: bool = False) -> PackedKV:
+               check_status: bool = False, med_in: Optional[torch.Tensor] = None) -> PackedKV:
         """Encode x (B, H, T_new, d) and append it to ``out`` (a fresh cache when None).
 
         ``ofrag``: also keep the flagged chunks of every complete 16-token block as tensor-core operand
         records for the decode-attention kernel (K tensors only use them).  Default: on for a fresh K
         cache with Med3x, off otherwise.  ``check_status``: synchronise and raise if the outlier side buffer
-        overflowed (otherwise the caller may compare ``out_count`` with ``out_cap`` itself)."""
+        overflowed (otherwise the caller may compare ``out_count`` with ``out_cap`` itself).  ``med_in``: (H,) fp32
+        medians to flag against instead of this call's own (``hqmq_b200.dist.split_batch_median`` computes them
+        when the batch entries of a head are spread over several GPUs)."""
         why = self._unsupported()
         if why:
             raise NotImplementedError(f"hqmq_b200 accelerates the unit-magnitude linear-radius path only ({why})")
@@ -218,18 +244,9 @@ class HQMQQuantizer(KVQuantizer):
             raise ValueError("destination cache was created without outlier planes")
         if out.T + T > out.T_cap:
             raise _lib.HqmqError(f"hqmq_b200: cache capacity {out.T_cap} exceeded ({out.T} + {T})")
-        tb = self.tables(layer_idx, kv, x.device)
-        a = _lib.EncodeArgs()
-        a.struct_size = C.sizeof(_lib.EncodeArgs)
-        a.x_dtype, a.x = _lib.dtype_enum(x.dtype), x.data_ptr()
-        a.x_stride = (C.c_int64 * 3)(*x.stride()[:3])
-        a.T_new, a.t_start = T, out.T
-        a.qs, a.joint = tb["qs"].data_ptr(), tb["joint"].data_ptr()
-        a.median_mult = float(median_mult) if median_mult is not None else 0.0
-        a.search = search
-        a.dst = out.c_struct()
-        a.med_out = med_out.data_ptr() if med_out is not None else None
-        a.lut, a.lut_max_cand = tb["lut"].data_ptr(), tb["lut_max_cand"]
+        if T == 0:              # appending nothing leaves the cache as it is (an empty tensor has no address to pass)
+            return out
+        a = self._enc_args(x, layer_idx, kv, out, median_mult, search, med_out, med_in)
         L = _lib.lib()
         with _lib.device_guard(x.device):
             nbytes = L.hqmq_encode_workspace_bytes(C.byref(a))

@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define HQMQ_ABI_VERSION 2
+#define HQMQ_ABI_VERSION 3
 
 /* error codes */
 #define HQMQ_OK 0
@@ -40,6 +40,7 @@ extern "C" {
 #define HQMQ_ERR_UNSUPPORTED (-8)
 #define HQMQ_ERR_CAPACITY (-9)    /* packed cache or outlier side buffer too small */
 #define HQMQ_ERR_STATIC_SCRATCH (-10) /* needs more scratch than the library's built-in buffer holds */
+#define HQMQ_ERR_TIMEOUT (-11)    /* a bounded device-side wait ran out (reported by the host layer from a status word) */
 
 /* element types */
 #define HQMQ_F32 0
@@ -190,6 +191,8 @@ typedef struct hqmq_encode_args {
   const void* lut;          /* optional nearest-codeword table of this codebook (hqmq_encode_lut_build) */
   int32_t lut_max_cand;     /* hqmq_encode_lut_max_candidates() of `lut` (0 = unknown, assume the capacity) */
   int32_t reserved;
+  const float* med_in;      /* optional (H,) fp32, device: per-head medians to use instead of this call's own; for a
+                               head whose batch entries are spread over several GPUs (hqmq_med3x_hist / _select) */
 } hqmq_encode_args;
 
 /*
@@ -202,6 +205,25 @@ typedef struct hqmq_encode_args {
 size_t hqmq_encode_workspace_bytes(const hqmq_encode_args* args);
 int hqmq_encode(const hqmq_encode_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Med3x median of heads whose batch entries live on SEVERAL GPUs.  The reference takes the median over every
+ * batch entry of a head in one call (src/quantizers/outlier_aware.py:63-72); when the batch of a head is
+ * partitioned across GPUs, the same number comes from a three-level radix select whose histograms are summed
+ * across those GPUs between the levels (integer sums, so every GPU derives identical bits):
+ *     for level in 0, 1, 2:
+ *         hqmq_med3x_hist(args, level, state, ...)        -- histogram of this GPU's chunk norms (level 0 clears state)
+ *         sum the 2 * 2048 uint32 words at  state + ((h * 3 + level) * 2 * 2048) * 4  of every head h over the GPUs
+ *                                                        (ncclAllReduce; a sum over the whole histogram area is as good)
+ *         hqmq_med3x_select(H, level, n_total, C, state, ..., med_out)   -- n_total = chunk norms per head over all GPUs
+ *     hqmq_encode(args with med_in = med_out, ...)
+ * `state` is hqmq_med3x_state_bytes(H) bytes of device memory, 16-byte aligned, owned by the caller.  Only x,
+ * x_dtype, x_stride, T_new and the geometry fields of dst (B, H, n_chunks, S, radius_bits) of `args` are read
+ * by hqmq_med3x_hist.  The reference has no multi-GPU path; these have no counterpart there.
+ */
+size_t hqmq_med3x_state_bytes(int H);
+int hqmq_med3x_hist(const hqmq_encode_args* args, int level, void* state, size_t state_bytes, void* stream);
+int hqmq_med3x_select(int H, int level, uint64_t n_total, float median_mult, void* state, size_t state_bytes,
+                      float* med_out, void* stream);
 /*
  * Device-detected problems are recorded in the first word of the workspace a call was given, never
  * printed or trapped on.  This copies that word to the host after synchronising `stream`.
@@ -318,6 +340,47 @@ int hqmq_attn_decode_static(const hqmq_attn_args* args, void* stream);
 int hqmq_combine_partials(const float* parts, int n_parts, int64_t rows, int d, int part_major, int out_dtype,
                           void* out, void* stream);
 
+/* ---- exchange of sequence-split partials over NVLink by direct stores ------------------------------------ */
+/*
+ * For one long context split by sequence over `world` GPUs (one process each): instead of an all_gather of
+ * the per-GPU partial blocks (partials_only output of hqmq_attn_decode, rows * (d + 2) floats), every rank
+ * stores its block into slot `rank` of every peer's receive buffer through peer-mapped pointers and then
+ * publishes the step's epoch in the peer's flag words; the receiver waits on its OWN memory only.  No
+ * counterpart in the reference (it is single-GPU).
+ *
+ *   recv[p]   address, in THIS process, of rank p's receive buffer: float[2][world][block_floats]
+ *             (hqmq_exchange_recv_bytes; 16-byte aligned; two halves used alternately by epoch parity, so a
+ *             rank that is one step ahead never overwrites a block that is still being merged)
+ *   flags[p]  address, in this process, of rank p's flag words: uint32[2][world], zero before first use
+ *   recv[rank] / flags[rank] are this rank's own buffers; the others are the peers' (cudaIpc or any other
+ *   peer mapping; peer access must be enabled).  block_floats must be a multiple of 4.
+ *
+ * Per step, with epoch = 1, 2, 3, ... (the same on every rank, never 0), on the rank's stream:
+ *     hqmq_attn_decode(partials_only = 1)                      -> local block
+ *     hqmq_exchange_push(x, local, epoch, stream)              -> stores into all world receive buffers
+ *     hqmq_exchange_wait(x, epoch, max_polls, status, stream)  -> returns on the GPU when every rank's epoch
+ *                                                                 word arrived, or after max_polls polls
+ *                                                                 (0 = default, about a second): then bit r of
+ *                                                                 *status (device uint32, caller-zeroed) is set
+ *                                                                 for every rank r whose block is missing
+ *     hqmq_combine_partials(recv[rank] + (epoch & 1) * world * block_floats, world, rows, d, 1, ...)
+ * A non-zero status after synchronising means the output of that step is invalid (HQMQ_ERR_TIMEOUT in the
+ * host layer); nothing hangs.  The kernels of one GPU never wait for each other; do not run two ranks of one
+ * exchange on the same GPU concurrently.
+ */
+#define HQMQ_EXCHANGE_MAX_RANKS 16
+typedef struct hqmq_exchange {
+  uint32_t struct_size;
+  int32_t world, rank;
+  int32_t reserved;
+  int64_t block_floats;
+  float* recv[HQMQ_EXCHANGE_MAX_RANKS];
+  uint32_t* flags[HQMQ_EXCHANGE_MAX_RANKS];
+} hqmq_exchange;
+size_t hqmq_exchange_recv_bytes(int world, int64_t block_floats);
+size_t hqmq_exchange_flag_bytes(int world);
+int hqmq_exchange_push(const hqmq_exchange* x, const float* local, uint32_t epoch, void* stream);
+int hqmq_exchange_wait(const hqmq_exchange* x, uint32_t epoch, uint32_t max_polls, uint32_t* status, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -78,3 +78,55 @@ def test_sequence_split_gather_and_merge_two_ranks():
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def _radix_worker(rank, world, port, ret):
+    """Two ranks hold different values of the same three 'heads'; a numpy stand-in of the library's histogram
+    and select steps drives hd.summed_radix_select, whose result must be torch.quantile of the union."""
+    sys.path.insert(0, ROOT)
+    import numpy as np
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        H, counts = 3, (700, 1301)                       # uneven shares, odd total
+        g = torch.Generator().manual_seed(5)
+        allv = [torch.randn(H, c, generator=g).abs() * (1 + 10 * (torch.rand(H, c, generator=g) < 0.05)) for c in counts]
+        mine = allv[rank].numpy().view(np.uint32)        # non-negative floats order like their bit patterns
+        n_total = sum(counts)
+        hist = torch.zeros(H, 3, 2, hd.HIST_BINS, dtype=torch.int32)
+        prefix = np.zeros((H, 2), dtype=np.uint32)
+        rank_in = np.array([[(n_total - 1) // 2, n_total // 2]] * H, dtype=np.int64)
+        shifts, masks, fixed = (21, 10, 0), (0x7ff, 0x7ff, 0x3ff), (32, 21, 10)
+
+        def hist_level(level):
+            for h in range(H):
+                for q in range(2):
+                    keys = mine[h].astype(np.uint64)
+                    sel = keys >> fixed[level] == np.uint64(prefix[h, q]) >> np.uint64(fixed[level]) if level else np.ones(keys.shape, bool)
+                    dig = ((keys[sel] >> np.uint64(shifts[level])) & np.uint64(masks[level])).astype(np.int64)
+                    hist[h, level, q] = torch.from_numpy(np.bincount(dig, minlength=hd.HIST_BINS).astype(np.int32))
+
+        def select_level(level):
+            for h in range(H):
+                for q in range(2):
+                    cum = np.cumsum(hist[h, level, q].numpy().astype(np.int64))
+                    b = int(np.searchsorted(cum, rank_in[h, q], side="right"))
+                    rank_in[h, q] -= cum[b - 1] if b else 0
+                    prefix[h, q] |= np.uint32(b << shifts[level])
+
+        hd.summed_radix_select(hist_level, lambda level: hist[:, level], select_level)
+        a, b = torch.from_numpy(prefix.view(np.float32).copy()).unbind(1)
+        med = a if n_total % 2 else b - (b - a) * 0.5
+        want = torch.quantile(torch.cat(allv, 1), 0.5, dim=1)
+        ret[rank] = bool(torch.equal(med, want))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_median_over_values_spread_across_two_ranks():
+    world = 2
+    port = 31500 + os.getpid() % 2000
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_radix_worker, args=(world, port, ret), nprocs=world, join=True)
+        assert dict(ret) == {0: True, 1: True}

@@ -156,3 +156,45 @@ def test_bad_arguments_raise():
     q = hqmq.HQMQ(1, 2, device="cuda")
     with pytest.raises(ValueError):
         q.quantize_K(torch.randn(1, 2, 4, 18).cuda(), 0)
+
+
+def test_empty_cache_and_empty_append():
+    """Edge cases: attention over a cache that holds no token gives zeros (no key carries weight) instead of
+    failing, and an append of zero tokens leaves the cache as it was."""
+    S, br, d, Hq, Hkv, B = 24, 3, 64, 4, 2, 2
+    q = hqmq.HQMQ(1, Hkv, S, br, device="cuda")
+    Kp = q.new_cache(B, 64, d, "cuda")
+    Vp = q.new_cache(B, 64, d, "cuda")
+    tk, tv = q.tables(0, 0, "cuda"), q.tables(0, 1, "cuda")
+    Q = torch.randn(B, Hq, 1, d, device="cuda").half()
+    O = torch.full(Q.shape, 7.0, dtype=torch.float32, device="cuda")
+    hqmq.fused_attention_packed(Q, Kp, Vp, tk["table16"], tv["table16"], out=O)
+    assert torch.equal(O, torch.zeros_like(O))
+    x = make_kv("randn", (B, Hkv, 20, d), seed=3, dtype=torch.float16).cuda()
+    q.encode(x, 0, 0, out=Kp)
+    before = (Kp.codes.clone(), Kp.rs.clone(), Kp.T)
+    q.encode(x[:, :, :0], 0, 0, out=Kp)
+    assert Kp.T == before[2] and torch.equal(Kp.codes, before[0]) and torch.equal(Kp.rs, before[1])
+
+
+def test_large_codebook_generic_kernels():
+    """A codebook far larger than the benchmark ones (S = 512: 12288 codewords, 14 index bits, fields that are
+    not a multiple of 8 bits): the encoder's exhaustive / table search and the generic attention kernel."""
+    S, br, C, d, Hq, Hkv, T, B = 512, 2, 3.0, 32, 4, 2, 40, 1
+    K = make_kv("spiky", (B, Hkv, T, d), seed=71)
+    V = make_kv("randn", (B, Hkv, T, d), seed=72)
+    Q = torch.randn(B, Hq, 1, d, generator=torch.Generator().manual_seed(73)) / math.sqrt(d)
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, Hkv, S, br, device="cuda"), C)
+    Kp, Vp = q.encode(K.cuda(), 0, 0, scale_dtype=torch.float16), q.encode(V.cuda(), 0, 1, scale_dtype=torch.float16)
+    tk, tv = q.inner.tables(0, 0, "cuda"), q.inner.tables(0, 1, "cuda")
+    joint = orc.joint_codebook(orc.secondary_raw(1, Hkv, S, 42)[0, :, 0])
+    enc = orc.encode(K, joint, br, C)
+    ki, kr, ks, kf = (t.cpu() for t in Kp.to_reference())
+    vi, vr, vs, vf = (t.cpu() for t in Vp.to_reference())
+    assert torch.equal(kf, enc["flags"]) and torch.equal(kr, torch.where(enc["flags"], 0, enc["rq"]))
+    assert int(((ki != enc["idx"]) & (enc["gap"] >= 1e-6)).sum()) == 0
+    O = torch.empty(Q.shape, dtype=torch.float32, device="cuda")
+    hqmq.fused_attention_packed(Q.cuda(), Kp, Vp, tk["table16"], tv["table16"], out=O)
+    ref = orc.fused_attention(Q, ki, kr, ks, tk["joint"].cpu(), vi, vr, vs, tv["joint"].cpu(), (1 << br) - 1,
+                              causal=False, K_flags=kf, K_orig=K, V_flags=vf, V_orig=V)
+    _check(O, ref, "S=512")

@@ -272,3 +272,60 @@ def test_small_calls_one_kernel_per_head(shape, S, br, C):
     for u, v in zip(a, b):
         if u is not None:
             assert torch.equal(u, v)
+
+
+@pytest.mark.parametrize("shape,dtype,S,br", [((4, 2, 160, 128), torch.bfloat16, 96, 4), ((3, 3, 96, 64), torch.float32, 24, 3)])
+def test_split_batch_median_and_encode_match_the_whole_batch(shape, dtype, S, br):
+    """A head whose batch entries sit on two GPUs: the per-level histograms of the two parts, summed (what the
+    all_reduce between the levels does; here both parts live on one device and the sum is a tensor add), must
+    select the median of the whole batch bit for bit, and encoding each part against that median must give the
+    rows, flags and payload of the whole-batch call."""
+    import ctypes as C
+    from hqmq_b200 import _lib
+    from hqmq_b200.dist import HIST_BINS
+    B, H, T, d = shape
+    Cm = 3.0
+    x = make_kv("spiky", shape, seed=311, dtype=dtype).cuda()
+    inner = hqmq.HQMQ(1, H, S, br, device="cuda")
+    quant = hqmq.with_outlier_extraction(inner, Cm)
+    med_ref = torch.zeros(H, device="cuda")
+    whole = quant.encode(x, 0, 0, med_out=med_ref, scale_dtype=torch.float32)
+    assert whole.n_outliers() > 0
+    parts = [x[:1], x[1:]]                       # uneven on purpose
+    L = _lib.lib()
+    nbytes = L.hqmq_med3x_state_bytes(H)
+    sd = torch.float32
+    caches = [inner.new_cache(p.shape[0], T, d, "cuda", scale_dtype=sd, with_outliers=True, out_dtype=dtype, ofrag=True)
+              for p in parts]
+    args = [inner._enc_args(p, 0, 0, c, Cm) for p, c in zip(parts, caches)]
+    states = [torch.empty(nbytes, dtype=torch.uint8, device="cuda") for _ in parts]
+    hists = [s[: H * 3 * 2 * HIST_BINS * 4].view(torch.int32).view(H, 3, 2, HIST_BINS) for s in states]
+    meds = [torch.zeros(H, device="cuda") for _ in parts]
+    n_total = B * T * (d // 4)
+    for level in range(3):
+        for a, s in zip(args, states):
+            _lib.check(L.hqmq_med3x_hist(C.byref(a), level, s.data_ptr(), nbytes, _lib.stream_ptr()), "hist")
+        total = hists[0][:, level] + hists[1][:, level]
+        for h_ in hists:
+            h_[:, level] = total
+        for s, m in zip(states, meds):
+            _lib.check(L.hqmq_med3x_select(H, level, n_total, Cm, s.data_ptr(), nbytes, m.data_ptr(), _lib.stream_ptr()), "select")
+    torch.cuda.synchronize()
+    assert torch.equal(meds[0], med_ref) and torch.equal(meds[1], med_ref)
+    b0 = 0
+    for p, c, m in zip(parts, caches, meds):
+        got_med = torch.zeros(H, device="cuda")
+        quant.encode(p, 0, 0, out=c, med_in=m, med_out=got_med)
+        assert torch.equal(got_med, med_ref)
+        nb = p.shape[0]
+        for got, want in zip(c.to_reference(), whole.to_reference()):
+            assert torch.equal(got, want[b0:b0 + nb])
+        cw = whole.out_count.view(B, H)[b0:b0 + nb]
+        assert torch.equal(c.out_count.view(nb, H), cw)
+        ov_w = whole.out_vals[: B * H * whole.out_cap * 4].view(B, H, whole.out_cap, 4)[b0:b0 + nb]
+        ov_c = c.out_vals[: nb * H * c.out_cap * 4].view(nb, H, c.out_cap, 4)
+        for b in range(nb):
+            for h in range(H):
+                k = int(cw[b, h])
+                assert torch.equal(ov_c[b, h, :k], ov_w[b, h, :k])
+        b0 += nb

@@ -18,6 +18,7 @@ from .attention import fused_hqmq_attention as fused_attention
 from .attention import fused_hqmq_attention_dequant_sdpa as fused_attention_reference
 from ._lib import HqmqError  # noqa: F401
 from .packed import PackedKV  # noqa: F401
+from .cache import PackedKVCache  # noqa: F401
 from .quantizers import HQMQQuantizer as HQMQ
 from .quantizers import KVQuantizer  # noqa: F401
 from .quantizers import OutlierAwareGenericQuantizer, OutlierAwareHQMQQuantizer
@@ -58,6 +59,6 @@ __all__ = [
     "HQMQ", "PaddedHQMQ", "OutlierAwareHQMQQuantizer", "OutlierAwareGenericQuantizer",
     "fused_attention", "fused_attention_reference", "with_outlier_extraction", "device_info",
     "kernels_ada", "kernels_hopper", "kernels_blackwell",
-    "PackedKV", "fused_attention_packed", "combine_partials", "decode_dequant", "HqmqError",
+    "PackedKV", "PackedKVCache", "fused_attention_packed", "combine_partials", "decode_dequant", "HqmqError",
 ]
 __version__ = "0.1.0"

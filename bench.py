@@ -44,6 +44,10 @@ WORKLOADS = {
                     desc="long-context single sequence, s24_r3 + Med3x"),
     "c5_layer": dict(B=64, Hq=64, Hkv=8, d=64, T=16384, S=96, br=4, C=3.0, kk="onehot", vk="onehot", dtype="bf16",
                      desc="gpt-oss-20b-shaped full-attention layer, s96_r4 + Med3x"),
+    "c5_model": dict(B=64, Hq=64, Hkv=8, d=64, T=16384, S=96, br=4, C=3.0, kk="onehot", vk="onehot", dtype="bf16",
+                     layers=24, window=128,
+                     desc="gpt-oss-20b-shaped attention stack: 24 layers alternating full and 128-token sliding-window "
+                          "attention, per step a one-token append-encode and a decode attention in every layer"),
 }
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read+write of attn_fast_kernel divided by the algorithmic bytes of the same launch, from the ncu
@@ -193,6 +197,123 @@ def dense_sdpa_us(B, Hq, Hkv, T, d, dtype, dev, reps=10):
                     "torch scaled_dot_product_attention over a dense 16-bit cache of the same shape; cache within twice L2, not flushed"}
 
 
+def run_model_sweep(args, w, rank, world, local):
+    """Whole-stack decode step (BASELINE config 5): every layer appends one new token per sequence to its
+    compressed cache (K and V, own Med3x median per call) and attends over it -- all tokens in even layers, the
+    last `window` in odd ones.  With N ranks the KV heads (and their query heads) are split N ways (strong scaling:
+    a fixed job), with no data-path collective.  Reports us per step and the compressed bytes the step reads."""
+    import hqmq_b200 as hqmq
+    from hqmq_b200 import dist as hd
+    from hqmq_b200.cache import PackedKVCache
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+        dist = dist_
+        dist.init_process_group("nccl", device_id=dev)
+    B, Hq, Hkv, d, T, S, br, Cm, NL, win = (w[k] for k in ("B", "Hq", "Hkv", "d", "T", "S", "br", "C", "layers", "window"))
+    _, hs = hd.kv_head_shard(B, Hkv, world, rank)
+    h0, h1 = hs.start, hs.stop
+    Hl, G = h1 - h0, Hq // Hkv
+    dtype = torch.bfloat16
+    full = hqmq.HQMQ(n_layers=NL, n_heads=Hkv, secondary_size=S, radius_bits=br, device=dev, seed=42)
+    inner = hqmq.HQMQ(n_layers=NL, n_heads=Hl, secondary_size=S, radius_bits=br, device=dev, seed=42)
+    inner.secondary_raw.data = full.secondary_raw.data[:, h0:h1].clone()     # this rank's heads of the same codebooks
+    quant = hqmq.with_outlier_extraction(inner, Cm)
+    n_steps = max(3, args.warmup) + 2 * args.steps + 8
+    cache = PackedKVCache(quant, max_tokens=T + n_steps, sliding_window={l: win for l in range(1, NL, 2)})
+    for l in range(NL):
+        # a sliding-window layer only ever reads its last `win` tokens: a short prompt gives the same step
+        Tl = T if l % 2 == 0 else 2 * win
+        k = synth(w["kk"], (B, Hkv, Tl, d), 3000 + l, dev, dtype)[:, h0:h1]
+        v = synth(w["vk"], (B, Hkv, Tl, d), 4000 + l, dev, dtype)[:, h0:h1]
+        cache.update(k, v, l)
+        del k, v
+    cache.check()
+    new = [(synth(w["kk"], (B, Hkv, 1, d), 5000 + i, dev, dtype)[:, h0:h1].contiguous(),
+            synth(w["vk"], (B, Hkv, 1, d), 6000 + i, dev, dtype)[:, h0:h1].contiguous()) for i in range(4)]
+    Q = (torch.randn(NL, B, Hl * G, 1, d, generator=torch.Generator().manual_seed(11 + rank)) / math.sqrt(d)).to(dtype).to(dev)
+    O = torch.empty_like(Q)
+    counter = [0]
+
+    def step():
+        i = counter[0] = counter[0] + 1
+        for l in range(NL):
+            k, v = new[(i + l) % 4]
+            cache.update(k, v, l)
+            cache.attend(Q[l], l, out=O[l])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    stream = torch.cuda.current_stream()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    barrier()
+    dev_s = ev0.elapsed_time(ev1) * 1e-3
+    # e2e: the step's queries come from pinned host memory and its outputs go back, with a sync per step
+    Qh, Oh = Q.cpu().pin_memory(), torch.empty(O.shape, dtype=dtype).pin_memory()
+    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev2.record(stream)
+    for _ in range(args.steps):
+        Q.copy_(Qh, non_blocking=True)
+        step()
+        Oh.copy_(O, non_blocking=True)
+        stream.synchronize()
+    ev3.record(stream)
+    barrier()
+    e2e_s = ev2.elapsed_time(ev3) * 1e-3
+    clocks = sampler.stop() if rank == 0 else None
+    cache.check()
+    read_bytes = 0
+    for l in range(NL):
+        Kp, Vp = cache._layers[l]
+        vis = Kp.T if l % 2 == 0 else win
+        for pk in (Kp, Vp):
+            read_bytes += pk.algorithmic_bytes(T=vis, n_out=int(pk.n_outliers() * vis / max(pk.T, 1)))
+    t = torch.tensor([dev_s, e2e_s], device=dev, dtype=torch.float64)
+    tb = torch.tensor([float(read_bytes)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tb, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        step_s, e2e_step = float(t[0]) / args.steps, float(t[1]) / args.steps
+        peak, peak_kind = hbm_peak()
+        gbs = float(tb[0]) / step_s / 1e9
+        print(json.dumps({
+            "metric": "decode step over the whole attention stack: us per step (append-encode + attention in every layer)",
+            "value": step_s * 1e6, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": step_s * 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 mma / f32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "desc": w["desc"], "batch": B, "q_heads": Hq, "kv_heads": Hkv, "d_head": d,
+                       "context": T, "layers": NL, "window": win, "S": S, "radius_bits": br, "median_mult": Cm,
+                       "sharding": f"KV heads x{world} ({Hl} per GPU)",
+                       "l2": "the compressed caches read per step exceed L2 many times over (no flush needed)"},
+            "compressed_bytes_read_per_step": float(tb[0]), "achieved_GBps_all_gpus": gbs,
+            "e2e": {"value": e2e_step * 1e6, "unit": "us", "h2d_bytes_per_step": Qh.numel() * Qh.element_size(),
+                    "d2h_bytes_per_step": Oh.numel() * Oh.element_size()},
+            "gpu_launches_note": "per layer and step: 2 append-encode calls of 3 kernels each, attention + merge kernel",
+            "gpu_launches": NL * 8 * args.steps,
+            "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
+                         "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "note": "whole step (host-bound appends included), not one kernel"},
+            "clocks": clocks}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_reference_arm(args, w, rank, world):
     """--impl reference: the reference's CPU implementation of the path (its torch restatement under
     oracle/, since the Python reference itself does not travel to the GPU box), all host threads, on a
@@ -258,6 +379,9 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args, w, rank, world)
+        return
+    if "layers" in w:
+        run_model_sweep(args, w, rank, world, local)
         return
 
     import hqmq_b200 as hqmq

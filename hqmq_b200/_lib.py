@@ -150,6 +150,11 @@ def lib():
     L.hqmq_exchange_recv_bytes.argtypes = [C.c_int, C.c_int64]
     L.hqmq_exchange_flag_bytes.restype = C.c_size_t
     L.hqmq_exchange_flag_bytes.argtypes = [C.c_int]
+    L.hqmq_exchange_enable_peer.argtypes = [C.c_int]
+    L.hqmq_exchange_verify.argtypes = [C.POINTER(Exchange)]
+    L.hqmq_exchange_ipc_export.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
+    L.hqmq_exchange_ipc_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    L.hqmq_exchange_ipc_close.argtypes = [C.c_void_p]
     L.hqmq_exchange_push.argtypes = [C.POINTER(Exchange), C.c_void_p, C.c_uint32, C.c_void_p]
     L.hqmq_exchange_wait.argtypes = [C.POINTER(Exchange), C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
     L.hqmq_read_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]

@@ -10,10 +10,13 @@
 //
 // No load ever targets a peer's memory, nothing is multicast, and no kernel of one GPU waits for another
 // kernel of the SAME GPU: the producer of every flag a kernel polls runs on a different device.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "../../include/hqmq_b200.h"
 #include "common.cuh"
+
+#include <cstring>
 
 namespace hqmq {
 namespace {
@@ -87,6 +90,77 @@ extern "C" size_t hqmq_exchange_recv_bytes(int world, int64_t block_floats) {
 extern "C" size_t hqmq_exchange_flag_bytes(int world) {
   if (world < 1 || world > HQMQ_EXCHANGE_MAX_RANKS) return 0;
   return (size_t)2 * world * sizeof(uint32_t);
+}
+
+extern "C" int hqmq_exchange_enable_peer(int peer_device) {
+  int cur = -1, can = 0;
+  HQMQ_CHECK_CUDA(cudaGetDevice(&cur));
+  if (peer_device == cur) return HQMQ_OK;
+  if (cudaDeviceCanAccessPeer(&can, cur, peer_device) != cudaSuccess) { cudaGetLastError(); return HQMQ_ERR_ARG; }
+  if (!can) return HQMQ_ERR_UNSUPPORTED;
+  const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); return HQMQ_OK; }   // clear the sticky-free error
+  return e == cudaSuccess ? HQMQ_OK : HQMQ_ERR_CUDA;
+}
+
+// ---- mapping a peer process's receive buffer ---------------------------------------------------------------
+// An IPC mapping is made "into the current device's address space": a mapping opened with the buffer's OWN
+// device current (what a tensor-sharing layer does, because it wants to use the tensor on that device) is not
+// reachable by kernels of another device of the same process, peer access or not.  So the buffer is opened
+// here with the ACCESSING device current and cudaIpcMemLazyEnablePeerAccess, the pattern collective libraries use.
+extern "C" int hqmq_exchange_ipc_export(const void* ptr, unsigned char* handle64, int64_t* offset) {
+  if (!ptr || !handle64 || !offset) return HQMQ_ERR_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == HQMQ_IPC_HANDLE_BYTES, "IPC handle size");
+  // the handle names the whole allocation the address lies in; its start comes from the driver
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
+      q != cudaDriverEntryPointSuccess) { cudaGetLastError(); return HQMQ_ERR_CUDA; }
+  CUdeviceptr base = 0; size_t size = 0;
+  if (reinterpret_cast<RangeFn>(fn)(&base, &size, (CUdeviceptr)(uintptr_t)ptr) != CUDA_SUCCESS || !base) return HQMQ_ERR_ARG;
+  cudaIpcMemHandle_t h;
+  HQMQ_CHECK_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>((uintptr_t)base)));
+  memcpy(handle64, &h, sizeof(h));
+  *offset = (int64_t)((uintptr_t)ptr - (uintptr_t)base);
+  return HQMQ_OK;
+}
+
+extern "C" int hqmq_exchange_ipc_open(const unsigned char* handle64, void** base_out) {
+  if (!handle64 || !base_out) return HQMQ_ERR_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* base = nullptr;
+  if (cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess || !base) { cudaGetLastError(); return HQMQ_ERR_CUDA; }
+  *base_out = base;
+  return HQMQ_OK;
+}
+
+extern "C" int hqmq_exchange_ipc_close(void* base) {
+  if (!base) return HQMQ_ERR_ARG;
+  HQMQ_CHECK_CUDA(cudaIpcCloseMemHandle(base));
+  return HQMQ_OK;
+}
+
+extern "C" int hqmq_exchange_verify(const hqmq_exchange* x) {
+  int rc = validate(x);
+  if (rc) return rc;
+  int cur = -1;
+  HQMQ_CHECK_CUDA(cudaGetDevice(&cur));
+  for (int p = 0; p < x->world; ++p) {
+    const void* ptrs[2] = {x->recv[p], x->flags[p]};
+    for (const void* q : ptrs) {
+      // a host address or an unmapped one would fault in the kernel: refuse it here
+      cudaPointerAttributes at;
+      if (cudaPointerGetAttributes(&at, q) != cudaSuccess || at.type != cudaMemoryTypeDevice) { cudaGetLastError(); return HQMQ_ERR_ARG; }
+      if (p == x->rank && at.device != cur) return HQMQ_ERR_ARG;    // the own buffers live on the current device
+      if (at.device != cur) {
+        rc = hqmq_exchange_enable_peer(at.device);
+        if (rc) return rc;
+      }
+    }
+  }
+  return HQMQ_OK;
 }
 
 extern "C" int hqmq_exchange_push(const hqmq_exchange* x, const float* local, uint32_t epoch, void* stream) {

@@ -155,13 +155,13 @@ class PushExchange:
     include/hqmq_b200.h) instead of an all_gather: one small kernel per step stores this rank's block into
     every peer, one polls this GPU's own flag words, then the usual merge runs on the local receive buffer.
 
-    Set-up (collective over ``group``, once): every rank allocates its receive buffer and flag words, exports
-    them with CUDA IPC through torch's tensor sharing, and maps the peers' ones.  ``rows`` = B * H_q * T_q
-    rows of d + 2 floats per rank.  All ranks must call ``step`` the same number of times."""
+    Set-up (collective over ``group``, once): every rank allocates one buffer (receive slots + flag words),
+    exports its CUDA IPC handle, and maps every peer's buffer with ITS OWN device current, so that its kernels
+    can store into them.  ``rows`` = B * H_q * T_q rows of d + 2 floats per rank.  All ranks must call
+    ``step`` the same number of times; ``close`` is collective too."""
 
     def __init__(self, rows: int, d: int, device, group=None, max_polls: int = 0):
         import ctypes as C
-        from torch.multiprocessing.reductions import reduce_tensor
         from . import _lib
         self.group, self.rows, self.d = group, rows, d
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
@@ -171,26 +171,35 @@ class PushExchange:
         if self.world > _lib.EXCHANGE_MAX_RANKS:
             raise ValueError(f"at most {_lib.EXCHANGE_MAX_RANKS} ranks")
         L = _lib.lib()
-        dev = torch.device(device)
-        self.recv = torch.zeros(L.hqmq_exchange_recv_bytes(self.world, self.block) // 4, dtype=torch.float32, device=dev)
-        self.flags = torch.zeros(L.hqmq_exchange_flag_bytes(self.world) // 4, dtype=torch.int32, device=dev)
+        dev = self.device = torch.device(device)
+        recv_bytes, flag_bytes = L.hqmq_exchange_recv_bytes(self.world, self.block), L.hqmq_exchange_flag_bytes(self.world)
+        self.buf = torch.zeros(recv_bytes + flag_bytes, dtype=torch.uint8, device=dev)     # one allocation, one handle
+        self.recv = self.buf[:recv_bytes].view(torch.float32)
+        self.flags = self.buf[recv_bytes:].view(torch.int32)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         torch.cuda.synchronize(dev)
-        mine = tuple(reduce_tensor(t) for t in (self.recv, self.flags))
+        handle, off = (C.c_ubyte * 64)(), C.c_int64(0)
+        with _lib.device_guard(dev):
+            _lib.check(L.hqmq_exchange_ipc_export(self.buf.data_ptr(), handle, C.byref(off)), "hqmq_exchange_ipc_export")
         everyone = [None] * self.world
-        dist.all_gather_object(everyone, mine, group=group)
-        self._peers = []                       # the mapped tensors stay alive with this object
+        dist.all_gather_object(everyone, (bytes(handle), int(off.value)), group=group)
+        self._opened = []                      # peers' mapped allocations, closed in close()
         x = _lib.Exchange()
         x.struct_size = C.sizeof(_lib.Exchange)
         x.world, x.rank, x.block_floats = self.world, self.rank, self.block
-        for p, shared in enumerate(everyone):
+        for p, (h, o) in enumerate(everyone):
             if p == self.rank:
-                r, f = self.recv, self.flags
+                base = self.buf.data_ptr()
             else:
-                (fn_r, args_r), (fn_f, args_f) = shared
-                r, f = fn_r(*args_r), fn_f(*args_f)
-                self._peers.append((r, f))
-            x.recv[p], x.flags[p] = r.data_ptr(), f.data_ptr()
+                mapped = C.c_void_p()
+                with _lib.device_guard(dev):
+                    _lib.check(L.hqmq_exchange_ipc_open((C.c_ubyte * 64).from_buffer_copy(h), C.byref(mapped)),
+                               "hqmq_exchange_ipc_open")
+                self._opened.append(mapped.value)
+                base = mapped.value + o
+            x.recv[p], x.flags[p] = base, base + recv_bytes
+        with _lib.device_guard(dev):
+            _lib.check(L.hqmq_exchange_verify(C.byref(x)), "hqmq_exchange_verify")
         self.x, self.max_polls, self.epoch = x, max_polls, 0
         dist.barrier(group=group)              # every rank has mapped every buffer before anyone stores into one
 
@@ -222,7 +231,11 @@ class PushExchange:
 
     def close(self) -> None:
         """Collective: nobody unmaps a buffer that a peer may still store into."""
-        torch.cuda.synchronize(self.recv.device)
+        from . import _lib
+        torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
-        self._peers.clear()
+        with _lib.device_guard(self.device):
+            for base in self._opened:
+                _lib.check(_lib.lib().hqmq_exchange_ipc_close(base), "hqmq_exchange_ipc_close")
+        self._opened = []
         dist.barrier(group=self.group)

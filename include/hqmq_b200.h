@@ -353,7 +353,7 @@ int hqmq_combine_partials(const float* parts, int n_parts, int64_t rows, int d, 
  *             rank that is one step ahead never overwrites a block that is still being merged)
  *   flags[p]  address, in this process, of rank p's flag words: uint32[2][world], zero before first use
  *   recv[rank] / flags[rank] are this rank's own buffers; the others are the peers' (cudaIpc or any other
- *   peer mapping; peer access must be enabled).  block_floats must be a multiple of 4.
+ *   peer mapping; peer access must be enabled: hqmq_exchange_enable_peer).  block_floats must be a multiple of 4.
  *
  * Per step, with epoch = 1, 2, 3, ... (the same on every rank, never 0), on the rank's stream:
  *     hqmq_attn_decode(partials_only = 1)                      -> local block
@@ -377,6 +377,21 @@ typedef struct hqmq_exchange {
   float* recv[HQMQ_EXCHANGE_MAX_RANKS];
   uint32_t* flags[HQMQ_EXCHANGE_MAX_RANKS];
 } hqmq_exchange;
+/* Lets kernels of the CURRENT device store into memory that lives on `peer_device` (cudaDeviceEnablePeerAccess;
+ * an IPC mapping opened with the peer's device current does not enable it by itself).  Once per peer, at set-up. */
+int hqmq_exchange_enable_peer(int peer_device);
+/* Mapping the peers' buffers (one process per GPU).  export: the 64-byte CUDA IPC handle of the allocation that
+ * holds `ptr`, and ptr's byte offset in it; send both to the peers by any host channel.  open: map a peer's
+ * allocation for stores from the CURRENT device (open it with the device current whose kernels will store into
+ * it -- a mapping opened with the buffer's own device current is not reachable from another device); the
+ * buffer is at base + offset.  One open per handle and process; close after a barrier, at tear-down. */
+#define HQMQ_IPC_HANDLE_BYTES 64
+int hqmq_exchange_ipc_export(const void* ptr, unsigned char* handle64, int64_t* offset);
+int hqmq_exchange_ipc_open(const unsigned char* handle64, void** base_out);
+int hqmq_exchange_ipc_close(void* base);
+/* Set-up check, once: every address of `x` is device memory known to this process, the own buffers live on the
+ * current device, and peer access to every other buffer's device is (made) enabled. */
+int hqmq_exchange_verify(const hqmq_exchange* x);
 size_t hqmq_exchange_recv_bytes(int world, int64_t block_floats);
 size_t hqmq_exchange_flag_bytes(int world);
 int hqmq_exchange_push(const hqmq_exchange* x, const float* local, uint32_t epoch, void* stream);

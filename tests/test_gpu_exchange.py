@@ -84,3 +84,12 @@ def test_exchange_arguments_are_validated():
     xs[0].block_floats = 6
     assert L.hqmq_exchange_push(C.byref(xs[0]), recv[0].data_ptr(), 1, None) == -4      # slots off 16-byte boundaries
     assert L.hqmq_exchange_recv_bytes(17, 8) == 0 and L.hqmq_exchange_flag_bytes(2) == 16
+    xs[0].block_floats = 8
+    assert L.hqmq_exchange_verify(C.byref(xs[0])) == 0 and L.hqmq_exchange_enable_peer(torch.cuda.current_device()) == 0
+    handle, off = (C.c_ubyte * 64)(), C.c_int64(-1)
+    assert L.hqmq_exchange_ipc_export(recv[0].data_ptr() + 16, handle, C.byref(off)) == 0      # an interior address
+    assert off.value >= 16 and off.value % 16 == 0 and any(handle)
+    assert L.hqmq_exchange_ipc_export(None, handle, C.byref(off)) == -1
+    host = (C.c_float * 64)()
+    xs[0].recv[1] = C.addressof(host)                                                    # not device memory
+    assert L.hqmq_exchange_verify(C.byref(xs[0])) in (-1, -4)

@@ -283,7 +283,7 @@ def run_model_sweep(args, w, rank, world, local):
         vis = Kp.T if l % 2 == 0 else win
         for pk in (Kp, Vp):
             read_bytes += pk.algorithmic_bytes(T=vis, n_out=int(pk.n_outliers() * vis / max(pk.T, 1)))
-    t = torch.tensor([dev_s, e2e_s], device=dev, dtype=torch.float64)
+    t = torch.tensor([dev_s, e2e_s, local_s or 0.0], device=dev, dtype=torch.float64)
     tb = torch.tensor([float(read_bytes)], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -559,6 +559,17 @@ def main():
         e2e_step()
     barrier()
     e2e_s = timed(args.steps, e2e_step)
+    # sequence split: the same steps without the exchange and the merge, so that their cost can be split out
+    local_s = None
+    if seq_mode:
+        def local_step():
+            rc = L.hqmq_attn_decode(C.byref(a), ws.data_ptr(), ws_bytes, stream.cuda_stream)
+            if rc:
+                raise RuntimeError(L.hqmq_strerror(rc).decode())
+        for _ in range(3):
+            local_step()
+        barrier()
+        local_s = timed(args.steps, local_step)
     # a short timed region can fall between two nvidia-smi samples: keep the same step running (untimed)
     # until the sampler has seen the GPU under this load
     t_probe = time.perf_counter()
@@ -577,7 +588,7 @@ def main():
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot_bytes, op=dist.ReduceOp.SUM)
-    dev_s, e2e_s = float(t[0]), float(t[1])
+    dev_s, e2e_s, local_s = float(t[0]), float(t[1]), float(t[2])
     total_bytes = float(tot_bytes[0])
     if rank != 0:
         if dist is not None:
@@ -617,6 +628,11 @@ def main():
                    "note": "one call per tensor over the whole (B, H_kv, T, d) input, Med3x median per call; median of 3 timed calls after 1 warm-up call"},
         "clocks": clocks,
     }
+    if seq_mode:
+        line["seq_split"] = {"local_attention_us": local_s / args.steps * 1e6,
+                             "exchange_and_merge_us": (dev_s - local_s) / args.steps * 1e6,
+                             "exchange": "pushed stores + bounded wait" if args.push else "NCCL all_gather",
+                             "note": "max over ranks of each; local = the attention kernel writing its partial block"}
     if not args.no_dense and world == 1:
         try:
             line["dense_sdpa"] = dense_sdpa_us(B, Hq, Hkv, T, d, dtype, dev)

@@ -283,7 +283,7 @@ def run_model_sweep(args, w, rank, world, local):
         vis = Kp.T if l % 2 == 0 else win
         for pk in (Kp, Vp):
             read_bytes += pk.algorithmic_bytes(T=vis, n_out=int(pk.n_outliers() * vis / max(pk.T, 1)))
-    t = torch.tensor([dev_s, e2e_s, local_s or 0.0], device=dev, dtype=torch.float64)
+    t = torch.tensor([dev_s, e2e_s], device=dev, dtype=torch.float64)
     tb = torch.tensor([float(read_bytes)], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -583,7 +583,7 @@ def main():
     if px is not None:
         px.check()
         px.close()
-    t = torch.tensor([dev_s, e2e_s], device=dev, dtype=torch.float64)
+    t = torch.tensor([dev_s, e2e_s, local_s or 0.0], device=dev, dtype=torch.float64)
     tot_bytes = torch.tensor([float(algo_bytes)], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

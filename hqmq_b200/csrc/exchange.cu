@@ -21,7 +21,7 @@
 namespace hqmq {
 namespace {
 
-constexpr uint32_t kDefaultPolls = 1u << 22;     // x >= 100 ns of sleep per poll: gives up after roughly a second
+constexpr uint32_t kDefaultPolls = 1u << 19;     // a poll is a system-scope load (~1 us) + 100 ns of sleep: gives up after roughly a second
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

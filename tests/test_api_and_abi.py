@@ -142,3 +142,16 @@ def test_validation_returns_error_codes_without_launching(built_lib):
     assert L.hqmq_codebook_tables(None, 1, 24, None, None) == -1
     p = _lib.Packed()
     assert L.hqmq_unpack(C.byref(p), 0, 1, None, None, None, None, None) == -1
+
+
+def test_packed_cache_has_no_cpu_path(built_lib):
+    """The cache mirrors the reference cache's update() call but never falls back: CPU tensors raise."""
+    import hqmq_b200 as hqmq
+    from hqmq_b200.cache import PackedKVCache
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, 2, 24, 3, device="cpu"), 3.0)
+    cache = PackedKVCache(q, max_tokens=64, sliding_window={1: 16})
+    with pytest.raises(_lib.HqmqError):
+        cache.update(torch.randn(1, 2, 4, 16), torch.randn(1, 2, 4, 16), 0)
+    with pytest.raises(ValueError):
+        cache.update(torch.randn(1, 2, 4, 16), torch.randn(1, 2, 5, 16), 0)
+    assert cache.get_seq_length(0) == 0 and cache.get_seq_length(3) == 0 and cache.compressed_bytes() >= 0

@@ -559,6 +559,20 @@ def main():
         e2e_step()
     barrier()
     e2e_s = timed(args.steps, e2e_step)
+    # spread of single steps: each of up to 50 steps between its own pair of events (after a flush where one applies)
+    def per_step_us(n):
+        pairs = []
+        for i in range(n):
+            if flush_buf is not None:
+                flush_buf.fill_(i & 255)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            step()
+            e1.record(stream)
+            pairs.append((e0, e1))
+        barrier()
+        return sorted(a_.elapsed_time(b_) * 1e3 for a_, b_ in pairs)
+    spread = per_step_us(min(args.steps, 50))
     # sequence split: the same steps without the exchange and the merge, so that their cost can be split out
     local_s = None
     if seq_mode:
@@ -612,6 +626,7 @@ def main():
                                 else f"sequence x{world} (context {T_full} total, partials all_gather + merge)") if seq_mode else f"batch x{world}",
                    "l2": "compressed cache per GPU exceeds twice the L2 size (inputs larger than L2, no flush needed)"
                    if not need_flush else "cache within twice the L2 size: 256 MiB rewritten before every timed step (L2 flushed)"},
+        "us_per_step_median_min_rank0": [spread[len(spread) // 2], spread[0]],
         "compressed_bytes_per_step": total_bytes,
         "fp16_cache_bytes_equiv": 2 * 2 * B * Hkv * T * d * world,
         "e2e": {"value": total_bytes / (e2e_s / args.steps) / 1e9, "unit": "GB/s",

@@ -216,9 +216,10 @@ int hqmq_encode(const hqmq_encode_args* args, void* workspace, size_t workspace_
  *                                                        (ncclAllReduce; a sum over the whole histogram area is as good)
  *         hqmq_med3x_select(H, level, n_total, C, state, ..., med_out)   -- n_total = chunk norms per head over all GPUs
  *     hqmq_encode(args with med_in = med_out, ...)
- * `state` is hqmq_med3x_state_bytes(H) bytes of device memory, 16-byte aligned, owned by the caller.  Only x,
- * x_dtype, x_stride, T_new and the geometry fields of dst (B, H, n_chunks, S, radius_bits) of `args` are read
- * by hqmq_med3x_hist.  The reference has no multi-GPU path; these have no counterpart there.
+ * `state` is hqmq_med3x_state_bytes(H) bytes of device memory, 16-byte aligned, owned by the caller.  `args` is
+ * the struct of the hqmq_encode call that follows and is validated like it; hqmq_med3x_hist reads x and the
+ * geometry only and writes nothing but `state`.  A GPU that holds no token of the heads (T_new = 0) still takes
+ * part in the sums.  The reference has no multi-GPU path; these have no counterpart there.
  */
 size_t hqmq_med3x_state_bytes(int H);
 int hqmq_med3x_hist(const hqmq_encode_args* args, int level, void* state, size_t state_bytes, void* stream);

@@ -138,8 +138,9 @@ def cpu_port_run(w, sample_T, reps, threads=None):
     the workload's distribution.  Returns seconds per decode step, encode seconds, and the sample's
     algorithmic bytes."""
     from oracle import hqmq_oracle as orc
-    if threads:
-        torch.set_num_threads(threads)
+    # all host threads of this process's CPU set, also under torchrun (which exports OMP_NUM_THREADS=1)
+    avail = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(threads or max(1, avail))
     Hkv, Hq, d, S, br, Cm = w["Hkv"], w["Hq"], w["d"], w["S"], w["br"], w["C"]
     dtype = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
     K = synth(w["kk"], (1, Hkv, sample_T, d), 1002, "cpu", dtype)

@@ -10,8 +10,7 @@ import os
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# HQMQ_B200_LIB points at another build of the same library (used to compare kernel variants)
-LIB_PATH = os.environ.get("HQMQ_B200_LIB") or os.path.join(HERE, "libhqmq_b200.so")
+LIB_PATH = os.path.join(HERE, "libhqmq_b200.so")
 
 F32, F16, BF16, I32, I16, I8, U8, I64 = range(8)
 ABI_VERSION = 3
@@ -146,6 +145,7 @@ def lib():
     L.hqmq_attn_workspace_bytes.argtypes = [C.POINTER(AttnArgs)]
     L.hqmq_attn_decode.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     L.hqmq_attn_decode_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+    L.hqmq_attn_static_status.argtypes = [C.POINTER(C.c_uint32), C.c_void_p]
     L.hqmq_exchange_recv_bytes.restype = C.c_size_t
     L.hqmq_exchange_recv_bytes.argtypes = [C.c_int, C.c_int64]
     L.hqmq_exchange_flag_bytes.restype = C.c_size_t

@@ -1,5 +1,8 @@
 // Decode attention: host side (validation, work decomposition, launch), the generic kernels (any
 // field width, reference layout, G up to 16) and the partial-merge kernel.
+#include <atomic>
+#include <mutex>
+
 #include "attn_kernel.cuh"
 
 namespace hqmq {
@@ -7,6 +10,11 @@ namespace attn {
 
 const void* fast_kernel(int n_chunks, int ib, int rb, bool outl);
 size_t fast_warp_bytes(int n_chunks, int ib, int rb, bool outl);
+bool ring_kernel(int n_chunks, int ib, int rb, bool outl, RingKernelInfo& k);
+size_t ring_smem_total(int table_rows, int repk_log2, int repv_log2, int d, bool outl, int stages, int merge_slots,
+                       size_t stage_bytes);
+constexpr int kRingMinKeys = 1024;       // shorter key ranges keep the per-warp staging rings
+constexpr size_t kSmemLimit = 226 * 1024;
 constexpr int kFastStages = 2;   // must equal kStages of the staged kernels
 constexpr int kFastQPad = 8;     // must equal kQPad of the staged kernels
 
@@ -90,6 +98,8 @@ struct Plan {
   const void* kernel;
   size_t smem;
   int table_rows, ib, nw, rep_log2;
+  int threads;                             // threads per CTA (the ring kernels add a producer warp to their nw consumers)
+  int repv_log2, ring_stages, merge_slots; // ring kernels only
   int ppc;   // partials a CTA writes per unit and head: 1 for the staged kernels (merged in shared memory), nw otherwise
   int units, tpu_v, L, P, grid;
   size_t ws_bytes;
@@ -132,13 +142,17 @@ static int validate_attn(const hqmq_attn_args* a) {
   return HQMQ_OK;
 }
 
-// Resident CTAs of `kernel` on the current device (cached per kernel and shared-memory size).
+// Resident CTAs of `kernel` on the current device (cached per kernel, shared-memory size and device).  The first
+// query of a (kernel, size, device) also raises the kernel's dynamic shared-memory limit, so a launch never has to.
+// Guarded by a mutex: host threads that serve different GPUs call into the library concurrently.
 static int resident_ctas(const void* kernel, size_t smem, int threads) {
   struct Entry { const void* k; size_t smem; int dev; int val; };
-  static Entry cache[64];
+  static Entry cache[128];
   static int n_cache = 0;
+  static std::mutex mu;
   int dev = 0;
   cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
   for (int i = 0; i < n_cache; ++i)
     if (cache[i].k == kernel && cache[i].smem == smem && cache[i].dev == dev) return cache[i].val;
   int sms = 0, occ = 0;
@@ -147,7 +161,7 @@ static int resident_ctas(const void* kernel, size_t smem, int threads) {
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem) != cudaSuccess || occ < 1) occ = 1;
   cudaGetLastError();
   const int val = (sms > 0 ? sms : 148) * occ;
-  if (n_cache < 64) cache[n_cache++] = {kernel, smem, dev, val};
+  if (n_cache < 128) cache[n_cache++] = {kernel, smem, dev, val};
   return val;
 }
 
@@ -174,6 +188,30 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   pl.ppc = fast ? 1 : kSlowWarps;
   if (!pl.kernel) pl.kernel = slow_kernel(n, outl, G > 8);
   if (!pl.kernel) return HQMQ_ERR_UNSUPPORTED;
+  pl.threads = pl.nw * 32;
+  pl.repv_log2 = pl.ring_stages = pl.merge_slots = 0;
+  const int keys = a->window > 0 ? (a->window < a->T_kv ? a->window : a->T_kv) : a->T_kv;
+  // Long key ranges: the kernels with one CTA-wide staging ring.  Shared memory goes first to the replication
+  // of the sign-folded tables (K at least as much as V), then to merge slots, then to a third ring stage.
+  RingKernelInfo rk;
+  bool ring = false;
+  if (fast && keys >= kRingMinKeys && ring_kernel(n, pl.ib, a->K.radius_bits, outl, rk)) {
+    for (int rsum = 8; rsum >= 0 && !ring; --rsum) {
+      const int rk_log2 = (rsum + 1) / 2, rv_log2 = rsum / 2;
+      if (ring_smem_total(pl.table_rows, rk_log2, rv_log2, a->d, outl, 2, 1, rk.stage_bytes) > kSmemLimit) continue;
+      ring = true;
+      pl.rep_log2 = rk_log2; pl.repv_log2 = rv_log2; pl.ring_stages = 2; pl.merge_slots = 1;
+      for (int ms : {5, 3})
+        if (ring_smem_total(pl.table_rows, rk_log2, rv_log2, a->d, outl, 2, ms, rk.stage_bytes) <= kSmemLimit) { pl.merge_slots = ms; break; }
+      if (ring_smem_total(pl.table_rows, rk_log2, rv_log2, a->d, outl, 3, pl.merge_slots, rk.stage_bytes) <= kSmemLimit) pl.ring_stages = 3;
+    }
+  }
+  if (ring) {
+    pl.kernel = rk.fn;
+    pl.nw = kRingWarpsHost;
+    pl.threads = (kRingWarpsHost + 1) * 32;
+    pl.smem = ring_smem_total(pl.table_rows, pl.rep_log2, pl.repv_log2, a->d, outl, pl.ring_stages, pl.merge_slots, rk.stage_bytes);
+  } else {
   const int nheads = G > 8 ? 16 : 8;
   size_t extra = outl ? (size_t)nheads * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * nheads * 4) : 0;
   if (fast)
@@ -186,27 +224,30 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   if (fast)
     while (pl.rep_log2 < 4 && (tbl_unit << (pl.rep_log2 + 1)) + extra <= 224 * 1024) ++pl.rep_log2;
   pl.smem = (tbl_unit << pl.rep_log2) + extra;
-  if (pl.smem > 226 * 1024) {
+  if (pl.smem > kSmemLimit) {
     if (!fast) return HQMQ_ERR_UNSUPPORTED;
     // the staged kernel does not fit next to this codebook: use the generic one
     pl.kernel = slow_kernel(n, outl, false);
     pl.nw = kSlowWarps; pl.rep_log2 = 0; pl.ppc = kSlowWarps;
+    pl.threads = pl.nw * 32;
     pl.smem = (size_t)pl.table_rows * 16 + (outl ? (size_t)8 * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * 8 * 4) : 0);
-    if (pl.smem > 226 * 1024) return HQMQ_ERR_UNSUPPORTED;
+    if (pl.smem > kSmemLimit) return HQMQ_ERR_UNSUPPORTED;
+  }
   }
 
   // tiles a unit can have (a window may straddle one extra tile)
-  const int keys = a->window > 0 ? (a->window < a->T_kv ? a->window : a->T_kv) : a->T_kv;
   int tpu = (keys + kTile - 1) / kTile + (a->window > 0 ? 1 : 0);
   if (tpu < 1) tpu = 1;
   pl.units = a->B * a->T_q * a->H_kv;
+  // (asked on every path: the first query of a kernel also raises its dynamic shared-memory limit)
+  int slots = query_device ? resident_ctas(pl.kernel, pl.smem, pl.threads) : 148;
+  if (slots < 1) slots = 1;
   if (a->kv_splits > 0) {
     int splits = a->kv_splits < tpu ? a->kv_splits : tpu;
     pl.L = (tpu + splits - 1) / splits;
     pl.tpu_v = pl.L * splits;
   } else {
     // equal pieces of the flat tile sequence, one per resident CTA; at least one tile per warp
-    const int slots = query_device ? resident_ctas(pl.kernel, pl.smem, pl.nw * 32) : 148;
     pl.tpu_v = tpu;
     const int64_t total = (int64_t)pl.units * tpu;
     int64_t L = (total + slots - 1) / slots;
@@ -268,13 +309,14 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   p.sscale = scale * 1.4426950408889634f / (float)a->r_qmax;
   p.qscale = scale * 1.4426950408889634f;
   p.nw = pl.nw; p.rep_log2 = pl.rep_log2;
+  p.repv_log2 = pl.repv_log2; p.ring_stages = pl.ring_stages; p.merge_slots = pl.merge_slots;
   p.vscale = 1.0f / (float)a->r_qmax;
   p.qmaxf = (float)a->r_qmax;
   p.units = pl.units; p.tpu_v = pl.tpu_v; p.L = pl.L; p.P = pl.P;
   p.Q = a->Q; p.q_dtype = a->q_dtype; p.qs_b = a->q_stride[0]; p.qs_h = a->q_stride[1]; p.qs_t = a->q_stride[2];
-  static uint32_t epoch_counter = 0x5eed0000u;
+  static std::atomic<uint32_t> epoch_counter{0x5eed0000u};
   p.status = reinterpret_cast<uint32_t*>(workspace);
-  p.epoch = ++epoch_counter;
+  p.epoch = epoch_counter.fetch_add(1u, std::memory_order_relaxed) + 1u;
   p.partials = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 16);
   p.layout = a->layout;
   p.table_rows = pl.table_rows;
@@ -284,10 +326,9 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   } else {
     p.Kr = a->K_ref; p.Vr = a->V_ref; p.jK = a->joint_K; p.jV = a->joint_V; p.j_dtype = a->joint_dtype;
   }
-  if (pl.smem > 48 * 1024)
-    HQMQ_CHECK_CUDA(cudaFuncSetAttribute(pl.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+  // (the kernel's dynamic shared-memory limit was raised when the plan asked for its occupancy: resident_ctas)
   void* kargs[] = {&p};
-  HQMQ_CHECK_CUDA(cudaLaunchKernel(pl.kernel, dim3(pl.grid), dim3(pl.nw * 32), kargs, pl.smem, st));
+  HQMQ_CHECK_CUDA(cudaLaunchKernel(pl.kernel, dim3(pl.grid), dim3(pl.threads), kargs, pl.smem, st));
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
   combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, (size_t)pl.P * pl.ppc * 4, st>>>(
       p.partials, pl.P * pl.ppc, rows, a->d, a->o_dtype, a->O, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,
@@ -327,7 +368,19 @@ extern "C" int hqmq_attn_decode_static(const hqmq_attn_args* a, void* stream) {
     if (cudaGetSymbolAddress(&ptr, g_attn_static_scratch) != cudaSuccess || !ptr) return HQMQ_ERR_CUDA;
     __atomic_store_n(&g_static_scratch_ptr[dev], ptr, __ATOMIC_RELEASE);
   }
-  // Nothing in the scratch has to start at zero: every partial that is read was written by this call, and
-  // the give-up word is compared with a per-call epoch.
+  // Of everything in the scratch only the give-up word has to start at zero: every partial that is read was
+  // written by this call.  The word is cleared on the stream ahead of the kernels, so that after the call it
+  // tells about this call alone (also when the call is replayed from a captured graph with its epoch baked in).
+  HQMQ_CHECK_CUDA(cudaMemsetAsync(ptr, 0, 16, (cudaStream_t)stream));
   return hqmq_attn_decode(a, ptr, (size_t)HQMQ_ATTN_STATIC_SCRATCH_BYTES, stream);
+}
+
+extern "C" int hqmq_attn_static_status(uint32_t* status, void* stream) {
+  if (!status) return HQMQ_ERR_ARG;
+  int dev = -1;
+  HQMQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return HQMQ_ERR_UNSUPPORTED;
+  void* ptr = __atomic_load_n(&g_static_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) { *status = 0; return HQMQ_OK; }   // no static call was made on this device yet
+  return hqmq_read_status(ptr, status, stream);
 }

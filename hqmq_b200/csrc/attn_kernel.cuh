@@ -49,6 +49,9 @@ struct AttnParams {
   float qmaxf;
   int nw;        // warps per CTA
   int rep_log2;  // the codeword tables are replicated 2^rep_log2 times, interleaved entry by entry
+  int repv_log2;      // ring kernels: replication of the V table (rep_log2 is then the K table's)
+  int ring_stages;    // ring kernels: stages of the CTA-wide staging ring
+  int merge_slots;    // ring kernels: warps whose partials are merged per round at the end of a unit
   // flat tile space: units * tpu_v virtual tiles, L per CTA; a unit is touched by at most P CTAs
   int units, tpu_v, L, P;
   const void* Q; int q_dtype; int64_t qs_b, qs_h, qs_t;
@@ -63,6 +66,10 @@ struct AttnParams {
   uint32_t* status;   // a kernel that gave up on a bounded wait stores `epoch` here; the merge kernel then emits NaN
   uint32_t epoch;
 };
+
+// A ring kernel (attn_ring.cu) and the bytes of one of its stages.
+struct RingKernelInfo { const void* fn; size_t stage_bytes; };
+constexpr int kRingWarpsHost = 15;   // consumer warps of the ring kernels (one more warp produces)
 
 // Key range [beg, end) of query position tq and the tiles that cover it.
 __host__ __device__ inline void key_range(int Tkv, int causal, int window, int tq, int& beg, int& end) {
@@ -368,7 +375,9 @@ struct OutlRaw { uint32_t fk, fv, offk, offv; uint2 pk[kStage / 32], pv[kStage /
 
 struct OutlSide {
   const uint32_t* flags; const uint32_t* off; const unsigned char* vals; int dtype; uint2* stage;
+  uint32_t cap;   // entries the (b,h) side buffer holds; an entry at or beyond it was dropped by the encoder and reads as 0
   __device__ __forceinline__ void init(const hqmq_packed& pk, int64_t bh, uint2* stage_) {
+    cap = (uint32_t)pk.out_cap;
     flags = pk.flags ? pk.flags + bh * pk.T_cap : nullptr;
     off = pk.flags ? pk.out_off + bh * (pk.T_cap / HQMQ_OUT_BLOCK + 1) : nullptr;
     dtype = pk.out_dtype;
@@ -377,6 +386,7 @@ struct OutlSide {
   }
   // original values of payload entry `pos` (tile-relative index `rel`)
   __device__ __forceinline__ float4 loadf(uint32_t pos, uint32_t rel) const {
+    if (pos >= cap) return make_float4(0.f, 0.f, 0.f, 0.f);
     if (dtype == HQMQ_F32) return *reinterpret_cast<const float4*>(vals + (int64_t)pos * 16);
     const uint2 v = rel < (uint32_t)kStage ? stage[rel] : *reinterpret_cast<const uint2*>(vals + (int64_t)pos * 8);
     const float2 a = pair16_to_float2(v.x, dtype), b = pair16_to_float2(v.y, dtype);
@@ -385,7 +395,9 @@ struct OutlSide {
   // the same scaled by `inv`, as two half2 registers
   __device__ __forceinline__ void load(uint32_t pos, uint32_t rel, float inv, uint32_t& lo, uint32_t& hi) const {
     float x0, x1, x2, x3;
-    if (dtype == HQMQ_F32) {
+    if (pos >= cap) {
+      x0 = x1 = x2 = x3 = 0.f;
+    } else if (dtype == HQMQ_F32) {
       const float4 v = *reinterpret_cast<const float4*>(vals + (int64_t)pos * 16);
       x0 = v.x; x1 = v.y; x2 = v.z; x3 = v.w;
     } else {
@@ -545,8 +557,8 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
       for (int q = 0; q < kStage / 32; ++q) {
         const uint32_t e = q * 32 + lane;
         oo.pk[q] = make_uint2(0, 0); oo.pv[q] = make_uint2(0, 0);
-        if (ok_.dtype != HQMQ_F32 && k0 + e < k1) oo.pk[q] = *reinterpret_cast<const uint2*>(ok_.vals + (int64_t)(k0 + e) * 8);
-        if (ov_.dtype != HQMQ_F32 && v0 + e < v1) oo.pv[q] = *reinterpret_cast<const uint2*>(ov_.vals + (int64_t)(v0 + e) * 8);
+        if (ok_.dtype != HQMQ_F32 && k0 + e < k1 && k0 + e < ok_.cap) oo.pk[q] = *reinterpret_cast<const uint2*>(ok_.vals + (int64_t)(k0 + e) * 8);
+        if (ov_.dtype != HQMQ_F32 && v0 + e < v1 && v0 + e < ov_.cap) oo.pv[q] = *reinterpret_cast<const uint2*>(ov_.vals + (int64_t)(v0 + e) * 8);
       }
     };
     auto fetch_off = [&](int tl, uint32_t& k0, uint32_t& k1, uint32_t& v0, uint32_t& v1) {

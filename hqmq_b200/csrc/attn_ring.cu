@@ -1,0 +1,41 @@
+// Decode-attention kernels with one CTA-wide staging ring (long key ranges), native layouts with a compile-time
+// field layout: (index bits, radius bits) = (10,3) s24_r3, (12,4) s96_r4, (13,6) s192_r6; d_head 64 or 128; G <= 8.
+#include "attn_ring.cuh"
+
+namespace hqmq {
+namespace attn {
+
+template <int N, int IB, int RB, bool OUTL>
+__global__ void __launch_bounds__(kRingThreads, 1) attn_ring_kernel(const AttnParams p) {
+  attn_ring_body<N, IB, RB, OUTL>(p);
+}
+
+template <int N, int IB, int RB, bool OUTL>
+static void fill(RingKernelInfo& k) {
+  k.fn = reinterpret_cast<const void*>(&attn_ring_kernel<N, IB, RB, OUTL>);
+  k.stage_bytes = RingLayout<N, IB, RB, OUTL>::BYTES;
+}
+
+template <int N, bool OUTL>
+static bool pick(int ib, int rb, RingKernelInfo& k) {
+  if (ib == 10 && rb == 3) { fill<N, 10, 3, OUTL>(k); return true; }
+  if (ib == 12 && rb == 4) { fill<N, 12, 4, OUTL>(k); return true; }
+  if (ib == 13 && rb == 6) { fill<N, 13, 6, OUTL>(k); return true; }
+  return false;
+}
+
+// Kernel for (n_chunks, idx bits, radius bits, outliers); false when no specialisation exists.
+bool ring_kernel(int n_chunks, int ib, int rb, bool outl, RingKernelInfo& k) {
+  if ((n_chunks * (ib + rb)) % 32) return false;   // rows must be whole words without padding
+  if (n_chunks == 32) return outl ? pick<32, true>(ib, rb, k) : pick<32, false>(ib, rb, k);
+  if (n_chunks == 16) return outl ? pick<16, true>(ib, rb, k) : pick<16, false>(ib, rb, k);
+  return false;
+}
+
+size_t ring_smem_total(int table_rows, int repk_log2, int repv_log2, int d, bool outl, int stages, int merge_slots,
+                       size_t stage_bytes) {
+  return ring_smem(table_rows, repk_log2, repv_log2, d, outl, stages, merge_slots, stage_bytes).total;
+}
+
+}  // namespace attn
+}  // namespace hqmq

@@ -197,8 +197,11 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         } else if (nk1 > nk0) {
           flk = true; bytes += 64;
           if (stageK) {
+            // (entries at or beyond out_cap were dropped by the encoder: nothing of them is copied, they read as 0)
             ak = nk0 & ~1u;
             uint32_t n = nk1 - ak; if (n > kPay + 1) n = kPay + 1;
+            const uint32_t room = ak < (uint32_t)p.K.out_cap ? (uint32_t)p.K.out_cap - ak : 0u;
+            if (n > room) n = room;
             pk_bytes = ((n + 1) & ~1u) * 8; bytes += pk_bytes;
           }
         }
@@ -207,6 +210,8 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
           if (stageV) {
             av = nv0 & ~1u;
             uint32_t n = nv1 - av; if (n > kPay + 1) n = kPay + 1;
+            const uint32_t room = av < (uint32_t)p.V.out_cap ? (uint32_t)p.V.out_cap - av : 0u;
+            if (n > room) n = room;
             pv_bytes = ((n + 1) & ~1u) * 8; bytes += pv_bytes;
           }
         }

@@ -63,7 +63,8 @@ int check_packed(const hqmq_packed& p, bool need_flags) {
   if (need_flags || p.flags) {
     if (!p.flags || !p.out_vals || !p.out_off || !p.out_count) return HQMQ_ERR_ARG;
     if (!is_float_dtype(p.out_dtype) || p.out_cap < 0) return HQMQ_ERR_DTYPE;
-    if (((uintptr_t)p.flags & 15) || ((uintptr_t)p.out_vals & 7)) return HQMQ_ERR_ALIGN;
+    // payload entries are read as one 8-byte (16-bit values) or 16-byte (fp32 values) load
+    if (((uintptr_t)p.flags & 15) || ((uintptr_t)p.out_vals & (p.out_dtype == HQMQ_F32 ? 15 : 7))) return HQMQ_ERR_ALIGN;
   }
   if (p.ofrag) {
     if (!p.flags || !p.ofrag_off || p.ofrag_cap < 0) return HQMQ_ERR_ARG;
@@ -132,7 +133,7 @@ __global__ void pack_kernel(hqmq_ref_packed s, int T, hqmq_packed p, int t_start
   int64_t bh = tok / T;
   int h = (int)(bh % p.H), b = (int)(bh / p.H);
   const int n = p.n_chunks, ib = idx_bits_for(p.S), cb = ib + p.radius_bits;
-  uint32_t words[20];
+  uint32_t words[25];   // up to 32 chunks x (16 index + 8 radius) bits = 24 words
   const int nw = p.row_bytes / 4;
   for (int w = 0; w < nw; ++w) words[w] = 0;
   int64_t ib0 = b * s.idx_stride[0] + h * s.idx_stride[1] + t * s.idx_stride[2];
@@ -188,9 +189,10 @@ __global__ void dequant_native_kernel(hqmq_packed p, int t0, int T, const float*
   const int ib = idx_bits_for(p.S), cb = ib + p.radius_bits;
   float v[4];
   if (merge && p.flags && ((p.flags[row] >> c) & 1u)) {
+    // an entry beyond the side buffer's capacity was dropped by the encoder: it reads as 0
     uint32_t slot = outlier_slot(p, bh, t0 + t, c);
     const int64_t o = ((int64_t)bh * p.out_cap + slot) * 4;
-    for (int e = 0; e < 4; ++e) v[e] = load_float(p.out_vals, o + e, p.out_dtype);
+    for (int e = 0; e < 4; ++e) v[e] = slot < (uint32_t)p.out_cap ? load_float(p.out_vals, o + e, p.out_dtype) : 0.f;
   } else {
     const uint32_t* rowp = reinterpret_cast<const uint32_t*>(p.codes + row * p.row_bytes);
     uint32_t f = row_field(rowp, c, cb);

@@ -109,6 +109,7 @@ def split_batch_median(quant, x: torch.Tensor, layer_idx: int, kv: int, out, gro
     from . import _lib
     inner, mult = quant.inner, float(quant.median_mult)
     B, H, T, d = x.shape
+    inner._check_dst(x, out)
     if x.stride(-1) != 1 or any(s % 4 for s in x.stride()[:3]):
         x = x.contiguous()
     L = _lib.lib()

@@ -185,6 +185,18 @@ class HQMQQuantizer(KVQuantizer):
                         scale_dtype=scale_dtype, with_outliers=with_outliers, out_dtype=out_dtype, out_cap=out_cap,
                         ofrag=ofrag, ofrag_cap=ofrag_cap)
 
+    def _check_dst(self, x: torch.Tensor, out: PackedKV):
+        """The library takes batch, heads and chunks per token from the destination planes: x must have that geometry."""
+        B, H, _, d = x.shape
+        if (B, H, d // 4) != (out.B, out.H, out.n_chunks) or d % 4:
+            raise ValueError(f"x of shape {tuple(x.shape)} does not match the destination cache "
+                             f"(B={out.B}, H={out.H}, d_head={out.n_chunks * 4})")
+        if out.S != self.secondary_size or out.radius_bits != self.radius_bits:
+            raise ValueError(f"destination cache is s{out.S}_r{out.radius_bits}, quantizer is "
+                             f"s{self.secondary_size}_r{self.radius_bits}")
+        if out.device != x.device:
+            raise ValueError(f"x is on {x.device}, the destination cache on {out.device}")
+
     def _enc_args(self, x, layer_idx, kv, out, median_mult=None, search=0, med_out=None, med_in=None):
         """The hqmq_encode_args of one call (x already validated and laid out, ``out`` the destination cache)."""
         tb = self.tables(layer_idx, kv, x.device)
@@ -240,6 +252,7 @@ class HQMQQuantizer(KVQuantizer):
                 ofrag = kv == 0 and median_mult is not None
             out = self.new_cache(B, T, d, x.device, scale_dtype=sd, with_outliers=median_mult is not None,
                                  out_dtype=od, ofrag=bool(ofrag) and median_mult is not None)
+        self._check_dst(x, out)
         if median_mult is not None and not out.with_outliers:
             raise ValueError("destination cache was created without outlier planes")
         if out.T + T > out.T_cap:

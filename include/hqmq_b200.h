@@ -328,9 +328,15 @@ int hqmq_attn_decode(const hqmq_attn_args* args, void* workspace, size_t workspa
  *   - All calls on a device share the one buffer, and it keeps what the previous call left.  Nothing in it
  *     needs clearing between calls (every value read was written by the same call), but two calls that
  *     overlap on the GPU -- different streams, or graphs replayed concurrently -- race on it: serialise them.
+ *   - The one word that must start at zero, the give-up word of the bounded waits, is cleared on `stream`
+ *     at the start of every call.  hqmq_attn_static_status() synchronises `stream` and returns that word of
+ *     the current device's buffer: non-zero = the most recent call on this device gave up on a bounded wait
+ *     for a staged copy and its output rows are NaN (the same meaning hqmq_read_status has for a caller's
+ *     workspace).  Call it with the same device current.
  */
 #define HQMQ_ATTN_STATIC_SCRATCH_BYTES (16u << 20)
 int hqmq_attn_decode_static(const hqmq_attn_args* args, void* stream);
+int hqmq_attn_static_status(uint32_t* status, void* stream);
 
 /*
  * Merge n_parts partial results (o[d], m, l per row, as written with partials_only; m is the maximum

@@ -10,7 +10,7 @@ namespace attn {
 
 const void* fast_kernel(int n_chunks, int ib, int rb, bool outl);
 size_t fast_warp_bytes(int n_chunks, int ib, int rb, bool outl);
-bool ring_kernel(int n_chunks, int ib, int rb, bool outl, RingKernelInfo& k);
+bool ring_kernel(int n_chunks, int ib, int rb, bool outl, int scale_dtype, RingKernelInfo& k);
 size_t ring_smem_total(int table_rows, int repk_log2, int repv_log2, int d, bool outl, int stages, int merge_slots,
                        size_t stage_bytes);
 constexpr int kRingMinKeys = 1024;       // shorter key ranges keep the per-warp staging rings
@@ -191,19 +191,24 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   pl.threads = pl.nw * 32;
   pl.repv_log2 = pl.ring_stages = pl.merge_slots = 0;
   const int keys = a->window > 0 ? (a->window < a->T_kv ? a->window : a->T_kv) : a->T_kv;
-  // Long key ranges: the kernels with one CTA-wide staging ring.  Shared memory goes first to the replication
-  // of the sign-folded tables (K at least as much as V), then to merge slots, then to a third ring stage.
+  // Long key ranges: the kernels with one CTA-wide staging ring.  The kernels are bound by shared-memory bandwidth
+  // (the random 8-byte codeword gathers), so shared memory goes first to the replication of the sign-folded tables
+  // (K at least as much as V) next to a two-stage ring, then to a third stage, then to merge slots (measured: a
+  // third stage bought nothing where it cost a table replica).
   RingKernelInfo rk;
   bool ring = false;
-  if (fast && keys >= kRingMinKeys && ring_kernel(n, pl.ib, a->K.radius_bits, outl, rk)) {
-    for (int rsum = 8; rsum >= 0 && !ring; --rsum) {
-      const int rk_log2 = (rsum + 1) / 2, rv_log2 = rsum / 2;
-      if (ring_smem_total(pl.table_rows, rk_log2, rv_log2, a->d, outl, 2, 1, rk.stage_bytes) > kSmemLimit) continue;
+  if (fast && keys >= kRingMinKeys && ring_kernel(n, pl.ib, a->K.radius_bits, outl, a->K.scale_dtype, rk)) {
+    auto fits = [&](int rsum, int ns, int ms) {
+      return ring_smem_total(pl.table_rows, (rsum + 1) / 2, rsum / 2, a->d, outl, ns, ms, rk.stage_bytes) <= kSmemLimit;
+    };
+    if (fits(0, 2, 1)) {
+      int rsum = 0;
+      while (rsum < 8 && fits(rsum + 1, 2, 1)) ++rsum;
       ring = true;
-      pl.rep_log2 = rk_log2; pl.repv_log2 = rv_log2; pl.ring_stages = 2; pl.merge_slots = 1;
+      pl.rep_log2 = (rsum + 1) / 2; pl.repv_log2 = rsum / 2; pl.ring_stages = 2; pl.merge_slots = 1;
+      while (pl.ring_stages < 4 && fits(rsum, pl.ring_stages + 1, 1)) ++pl.ring_stages;
       for (int ms : {5, 3})
-        if (ring_smem_total(pl.table_rows, rk_log2, rv_log2, a->d, outl, 2, ms, rk.stage_bytes) <= kSmemLimit) { pl.merge_slots = ms; break; }
-      if (ring_smem_total(pl.table_rows, rk_log2, rv_log2, a->d, outl, 3, pl.merge_slots, rk.stage_bytes) <= kSmemLimit) pl.ring_stages = 3;
+        if (fits(rsum, pl.ring_stages, ms)) { pl.merge_slots = ms; break; }
     }
   }
   if (ring) {

@@ -5,30 +5,33 @@
 namespace hqmq {
 namespace attn {
 
-template <int N, int IB, int RB, bool OUTL>
+// SDT: element type of the per-token scale planes (HQMQ_F16 or HQMQ_BF16), fixed at compile time like the field layout.
+template <int N, int IB, int RB, bool OUTL, int SDT>
 __global__ void __launch_bounds__(kRingThreads, 1) attn_ring_kernel(const AttnParams p) {
-  attn_ring_body<N, IB, RB, OUTL>(p);
+  attn_ring_body<N, IB, RB, OUTL, SDT>(p);
 }
 
 template <int N, int IB, int RB, bool OUTL>
-static void fill(RingKernelInfo& k) {
-  k.fn = reinterpret_cast<const void*>(&attn_ring_kernel<N, IB, RB, OUTL>);
+static void fill(int sdt, RingKernelInfo& k) {
+  k.fn = sdt == HQMQ_F16 ? reinterpret_cast<const void*>(&attn_ring_kernel<N, IB, RB, OUTL, HQMQ_F16>)
+                         : reinterpret_cast<const void*>(&attn_ring_kernel<N, IB, RB, OUTL, HQMQ_BF16>);
   k.stage_bytes = RingLayout<N, IB, RB, OUTL>::BYTES;
 }
 
 template <int N, bool OUTL>
-static bool pick(int ib, int rb, RingKernelInfo& k) {
-  if (ib == 10 && rb == 3) { fill<N, 10, 3, OUTL>(k); return true; }
-  if (ib == 12 && rb == 4) { fill<N, 12, 4, OUTL>(k); return true; }
-  if (ib == 13 && rb == 6) { fill<N, 13, 6, OUTL>(k); return true; }
+static bool pick(int ib, int rb, int sdt, RingKernelInfo& k) {
+  if (ib == 10 && rb == 3) { fill<N, 10, 3, OUTL>(sdt, k); return true; }
+  if (ib == 12 && rb == 4) { fill<N, 12, 4, OUTL>(sdt, k); return true; }
+  if (ib == 13 && rb == 6) { fill<N, 13, 6, OUTL>(sdt, k); return true; }
   return false;
 }
 
-// Kernel for (n_chunks, idx bits, radius bits, outliers); false when no specialisation exists.
-bool ring_kernel(int n_chunks, int ib, int rb, bool outl, RingKernelInfo& k) {
+// Kernel for (n_chunks, idx bits, radius bits, outliers, scale dtype); false when no specialisation exists.
+bool ring_kernel(int n_chunks, int ib, int rb, bool outl, int scale_dtype, RingKernelInfo& k) {
   if ((n_chunks * (ib + rb)) % 32) return false;   // rows must be whole words without padding
-  if (n_chunks == 32) return outl ? pick<32, true>(ib, rb, k) : pick<32, false>(ib, rb, k);
-  if (n_chunks == 16) return outl ? pick<16, true>(ib, rb, k) : pick<16, false>(ib, rb, k);
+  if (scale_dtype != HQMQ_F16 && scale_dtype != HQMQ_BF16) return false;
+  if (n_chunks == 32) return outl ? pick<32, true>(ib, rb, scale_dtype, k) : pick<32, false>(ib, rb, scale_dtype, k);
+  if (n_chunks == 16) return outl ? pick<16, true>(ib, rb, scale_dtype, k) : pick<16, false>(ib, rb, scale_dtype, k);
   return false;
 }
 

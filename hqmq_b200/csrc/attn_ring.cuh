@@ -53,7 +53,7 @@ struct RingLayout {
 
 // What the host must know about the kernel's shared memory (the device derives the same offsets).
 struct RingSmem {
-  size_t tblK, tblV, q, bars, merge, ring, total;
+  size_t tblK, tblV, q, vinfo, bars, merge, ring, total;
 };
 __host__ __device__ inline RingSmem ring_smem(int table_rows, int repk_log2, int repv_log2, int d, bool outl, int stages,
                                                int merge_slots, size_t stage_bytes) {
@@ -63,6 +63,7 @@ __host__ __device__ inline RingSmem ring_smem(int table_rows, int repk_log2, int
   s.tblV = o; o += (size_t)(table_rows >> 1) * (8u << repv_log2);
   s.q = o; o += outl ? (size_t)8 * (d + kQPad) * 2 : 0;
   o = (o + 15) & ~(size_t)15;
+  s.vinfo = o; o += outl ? (size_t)kRingWarps * kTile * 16 : 0;   // per warp and token: V flag word, entries before it, qmax / rs
   s.bars = o; o += 64;                                   // full[4], empty[4]
   // merge area: m[warps][8], l[warps][8], weight[warps][8], m*[8], l*[8], abort word, then `merge_slots` slots of [8][d] floats
   s.merge = o; o += (size_t)(3 * kRingWarps * 8 + 16 + 4) * 4 + (size_t)merge_slots * 8 * d * 4;
@@ -72,6 +73,11 @@ __host__ __device__ inline RingSmem ring_smem(int table_rows, int repk_log2, int
   return s;
 }
 
+__device__ __forceinline__ float rcp_fast(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -106,17 +112,27 @@ __device__ __forceinline__ UnitPiece unit_piece(const AttnParams& p, int u, int6
   return q;
 }
 
-// Bounded wait on an mbarrier phase; gives up when the limit is reached or another warp already gave up.
+// Bounded wait on an mbarrier phase.  Each try may suspend the thread in hardware for up to kRingSuspendNs (it is
+// woken as soon as the phase completes), so a waiting warp costs a handful of instructions instead of a spin loop;
+// kRingWaitTries of them bound the wait to about a second.  Gives up early when another warp already gave up.
+constexpr uint32_t kRingSuspendNs = 10u * 1000u * 1000u;
+constexpr uint32_t kRingWaitTries = 100u;
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(kRingSuspendNs) : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word) {
-  uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if (++spins > kWaitLimit) return false;
-    if ((spins & 1023u) == 0 && *abort_word) return false;
+  uint32_t tries = 0;
+  while (!mbar_try_wait_suspend(bar, parity)) {
+    if (++tries > kRingWaitTries || *abort_word) return false;
   }
   return true;
 }
 
-template <int N, int IB, int RB, bool OUTL>
+template <int N, int IB, int RB, bool OUTL, int SDT>
 __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
   using G_ = Geo<N>;
   using FL = FastLoader<N, IB, RB, true>;
@@ -130,6 +146,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
   unsigned char* tblK = smem_raw + sl.tblK;
   unsigned char* tblV = smem_raw + sl.tblV;
   __half* qh16 = reinterpret_cast<__half*>(smem_raw + sl.q);
+  uint4* vinfo = reinterpret_cast<uint4*>(smem_raw + sl.vinfo);     // [warp][16 tokens] (OUTL)
   constexpr int qstride = D + kQPad;
   const uint32_t bar_full = smem_u32(smem_raw + sl.bars), bar_empty = bar_full + 32;
   float* m_s = reinterpret_cast<float*>(smem_raw + sl.merge);      // [16][8]
@@ -160,23 +177,53 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
     const bool hasFlK = OUTL && p.K.flags != nullptr, hasFlV = OUTL && p.V.flags != nullptr;
     const bool stageK = hasFlK && p.K.out_dtype != HQMQ_F32, stageV = hasFlV && p.V.out_dtype != HQMQ_F32;
     const bool hasFr = hasFlK && p.K.ofrag != nullptr;
-    for (int u = u_first; ok && (int64_t)u * p.tpu_v < flat_hi; ++u) {
-      const UnitPiece up = unit_piece(p, u, flat_lo, flat_hi);
-      const int64_t bh = (int64_t)up.b * p.Hkv + up.h;
-      for (int tile0 = up.my_lo; tile0 < up.my_hi; tile0 += kRingTiles, ++gs) {
+    // The stages of this CTA's piece, in order: (unit, first tile).  A unit without tiles in the piece has none.
+    struct StageIt { int u, tile0; bool valid; UnitPiece up; };
+    auto seek = [&](StageIt& it) {          // first unit from it.u on that has tiles here
+      it.valid = false;
+      for (; (int64_t)it.u * p.tpu_v < flat_hi; ++it.u) {
+        it.up = unit_piece(p, it.u, flat_lo, flat_hi);
+        if (it.up.my_lo < it.up.my_hi) { it.tile0 = it.up.my_lo; it.valid = true; break; }
+      }
+    };
+    auto advance = [&](StageIt& it) {
+      it.tile0 += kRingTiles;
+      if (it.tile0 >= it.up.my_hi) { ++it.u; seek(it); }
+    };
+    // side ranges of a stage's tiles: lane l holds the offsets before tile l of the stage (l <= tiles of the stage)
+    auto load_side = [&](const StageIt& it, uint32_t& kOff, uint32_t& vOff, uint32_t& fOff) {
+      kOff = vOff = fOff = 0;
+      if constexpr (OUTL) {
+        if (it.valid) {
+          const int nt_ = min(kRingTiles, it.up.my_hi - it.tile0);
+          if (lane <= nt_) {
+            const int64_t bh_ = (int64_t)it.up.b * p.Hkv + it.up.h;
+            const int64_t nb = bh_ * (p.K.T_cap / HQMQ_OUT_BLOCK + 1) + it.tile0 + lane;
+            if (hasFlK) kOff = p.K.out_off[nb];
+            if (hasFr) fOff = p.K.ofrag_off[nb];
+            if (hasFlV) vOff = p.V.out_off[bh_ * (p.V.T_cap / HQMQ_OUT_BLOCK + 1) + it.tile0 + lane];
+          }
+        }
+      }
+    };
+    StageIt cur;
+    cur.u = u_first;
+    seek(cur);
+    uint32_t kOff, vOff, fOff;
+    load_side(cur, kOff, vOff, fOff);
+    for (; ok && cur.valid; ++gs) {
+      {
+        const UnitPiece& up = cur.up;
+        const int tile0 = cur.tile0;
+        const int64_t bh = (int64_t)up.b * p.Hkv + up.h;
         const int nt = min(kRingTiles, up.my_hi - tile0);
         const int buf = gs % NS;
         unsigned char* sb = ring + (size_t)buf * RL::BYTES;
-        // side ranges of the stage's tiles (global loads issued before the wait for the buffer)
-        uint32_t kOff = 0, vOff = 0, fOff = 0;
-        if constexpr (OUTL) {
-          if (lane <= nt) {
-            const int64_t nb = bh * (p.K.T_cap / HQMQ_OUT_BLOCK + 1) + tile0 + lane;
-            if (hasFlK) kOff = p.K.out_off[nb];
-            if (hasFr) fOff = p.K.ofrag_off[nb];
-            if (hasFlV) vOff = p.V.out_off[bh * (p.V.T_cap / HQMQ_OUT_BLOCK + 1) + tile0 + lane];
-          }
-        }
+        // the next stage's side ranges are fetched now (global loads in flight across the wait and the issue below)
+        StageIt nxt = cur;
+        advance(nxt);
+        uint32_t kOffN, vOffN, fOffN;
+        load_side(nxt, kOffN, vOffN, fOffN);
         if (gs >= (uint32_t)NS) {
           ok = ring_wait(bar_empty + 8 * buf, ((gs / NS) - 1u) & 1u, abort_word);
           ok = __all_sync(0xffffffffu, ok);
@@ -238,6 +285,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
             if (nR) bulk_g2s(sb32 + RL::kSideK, p.K.ofrag + (bh * p.K.ofrag_cap + f0) * HQMQ_OFRAG_BYTES, nR * HQMQ_OFRAG_BYTES, bar);
           }
         }
+        cur = nxt; kOff = kOffN; vOff = vOffN; fOff = fOffN;
       }
     }
     if (!ok) {
@@ -265,7 +313,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
   bool failed = false;
   int cur_h = -1;
   FL ld;
-  ld.row_bytes = ROW; ld.row_words = ROW / 4; ld.j = j; ld.r = r; ld.sdt = p.K.scale_dtype;
+  ld.row_bytes = ROW; ld.row_words = ROW / 4; ld.j = j; ld.r = r; ld.sdt = SDT;
 
   for (int u = u_first; (int64_t)u * p.tpu_v < flat_hi; ++u) {
     const UnitPiece up = unit_piece(p, u, flat_lo, flat_hi);
@@ -320,32 +368,39 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
     for (int tile0 = up.my_lo; tile0 < up.my_hi && !failed; tile0 += kRingTiles, ++gs) {
       const int buf = gs % NS;
       const int tile = tile0 + warp;
+      // Every warp waits for the stage, also one without a tile in it (the last, partial stage of a piece): its
+      // arrival on the "empty" barrier below must fall into THIS stage's phase, and only a completed "full" phase
+      // proves that the producer has seen the previous use of the buffer released by all warps.
+      if (!ring_wait(bar_full + 8 * buf, (gs / NS) & 1u, abort_word)) failed = true;
+      failed = __any_sync(0xffffffffu, failed);
+      if (failed) {
+        if (lane == 0) { *abort_word = 1u; *p.status = p.epoch; }
+        break;
+      }
       if (tile < up.my_hi) {
-        if (!ring_wait(bar_full + 8 * buf, (gs / NS) & 1u, abort_word)) failed = true;
-        failed = __any_sync(0xffffffffu, failed);
-        if (failed) {
-          if (lane == 0) { *abort_word = 1u; *p.status = p.epoch; }
-          break;
-        }
         const unsigned char* sb = ring + (size_t)buf * RL::BYTES;
         const int t0 = tile * kTile;
         const bool edge = t0 < t_beg || t0 + kTile > t_end;
         const unsigned char* kc = sb + RL::kK + warp * (kTile * ROW);
         const unsigned char* vc = sb + RL::kV + warp * (kTile * ROW);
 
+        // The tile, compiled twice: EDGE = false for a tile that lies wholly inside the key range (no masks, no
+        // bounds on the rows), EDGE = true for the first / last tile of a range.
+        auto tile_body = [&](auto edge_c) {
+        constexpr bool EDGE = decltype(edge_c)::value;
         // ---- this lane's fields and scales ------------------------------------------------------------------
         typename FL::Raw cur;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
           const int tr = nt * 8 + r;
-          ld.template load_span<FL::KW, FL::LK>(cur.kw[nt], kc + tr * ROW, j, !edge || t0 + tr < t_end);
+          ld.template load_span<FL::KW, FL::LK>(cur.kw[nt], kc + tr * ROW, j, !EDGE || t0 + tr < t_end);
           cur.rsk[nt] = reinterpret_cast<const uint16_t*>(sb + RL::kRsK)[warp * kTile + tr];
           cur.rsv[nt] = reinterpret_cast<const uint16_t*>(sb + RL::kRsV)[warp * kTile + tr];
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int tr = 2 * j + (i & 1) + (i >> 1) * 8;
-          ld.template load_span<FL::VW, FL::LV>(cur.vw[i], vc + tr * ROW, r, !edge || t0 + tr < t_end);
+          ld.template load_span<FL::VW, FL::LV>(cur.vw[i], vc + tr * ROW, r, !EDGE || t0 + tr < t_end);
         }
         float ksc[2], vsc[2];
 #pragma unroll
@@ -354,7 +409,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
           vsc[nt] = ld.vscale(cur, nt) * p.vscale;
         }
         bool okt[2] = {true, true};
-        if (edge) {
+        if constexpr (EDGE) {
 #pragma unroll
           for (int nt = 0; nt < 2; ++nt) {
             const int t = t0 + nt * 8 + r;
@@ -382,29 +437,21 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
         // ---- K outliers ----------------------------------------------------------------------------------------
         float corr[4] = {0.f, 0.f, 0.f, 0.f};   // additions to the scaled scores (this lane's tokens r, r+8 x heads 2j, 2j+1)
         uint4 th0 = make_uint4(0u, 0u, 0u, 0u), sh0 = make_uint4(0u, 0u, 0u, 0u);
-        uint32_t stage_bits = 0, rec0 = 0, nrec_staged = 0;
         if constexpr (OUTL) {
-          th0 = *reinterpret_cast<const uint4*>(sb + RL::kTileHdr + warp * 32);           // k0, k1, v0, v1
+          th0 = *reinterpret_cast<const uint4*>(sb + RL::kTileHdr + warp * 32);                  // k0, k1, v0, v1
           const uint2 fr = *reinterpret_cast<const uint2*>(sb + RL::kTileHdr + warp * 32 + 16);   // f0, f1
-          sh0 = *reinterpret_cast<const uint4*>(sb + RL::kStageHdr);                        // ak, nK, av, nV
-          const uint4 sh1 = *reinterpret_cast<const uint4*>(sb + RL::kStageHdr + 16);      // rec0, nR, bits
-          rec0 = sh1.x; nrec_staged = sh1.y; stage_bits = sh1.z;
+          sh0 = *reinterpret_cast<const uint4*>(sb + RL::kStageHdr);                               // ak, nK, av, nV
+          const uint2 sh1 = *reinterpret_cast<const uint2*>(sb + RL::kStageHdr + 16);             // first staged record, count
           if (fr.y > fr.x) {
             // fragment records: one 16-byte load per lane and one MMA per record (values and query in fp16,
             // the precision of the codeword path)
             uint32_t n = fr.y - fr.x; if (n > HQMQ_OFRAG_MAX_PER_TILE) n = HQMQ_OFRAG_MAX_PER_TILE;
             for (uint32_t g = 0; g < n; ++g) {
-              const uint32_t ri = fr.x + g - rec0;        // index among the staged records
-              uint32_t hdr; uint4 a;
-              if (ri < nrec_staged) {
-                const unsigned char* rec = sb + RL::kSideK + ri * HQMQ_OFRAG_BYTES;
-                hdr = *reinterpret_cast<const uint32_t*>(rec);
-                a = *reinterpret_cast<const uint4*>(rec + 16 + lane * 16);
-              } else {
-                const unsigned char* rec = p.K.ofrag + (bh * p.K.ofrag_cap + fr.x + g) * HQMQ_OFRAG_BYTES;
-                hdr = *reinterpret_cast<const uint32_t*>(rec);
-                a = *reinterpret_cast<const uint4*>(rec + 16 + lane * 16);
-              }
+              const uint32_t ri = fr.x + g - sh1.x;        // index among the staged records
+              const unsigned char* rec = ri < sh1.y ? sb + RL::kSideK + ri * HQMQ_OFRAG_BYTES
+                                                    : p.K.ofrag + (bh * p.K.ofrag_cap + fr.x + g) * HQMQ_OFRAG_BYTES;
+              const uint32_t hdr = *reinterpret_cast<const uint32_t*>(rec);
+              const uint4 a = *reinterpret_cast<const uint4*>(rec + 16 + lane * 16);
               const uint32_t cj = (hdr >> (8 * j)) & 0xffu;
               uint2 qv = make_uint2(0u, 0u);
               if (cj != 0xffu) qv = *reinterpret_cast<const uint2*>(qh16 + r * qstride + 4 * cj);
@@ -452,23 +499,28 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
         for (int x = 0; x < 4; ++x) s[x] += s2[x];
 
         // ---- scale, mask, online softmax ---------------------------------------------------------------------
-        bool grew = false;
-        float mx[2];
+        // The reference exponent m_run of a head only has to bound the scores from above by a margin that keeps
+        // 2^(s - m_run) and its sums in range; it is raised (and the accumulators rescaled) only when some score
+        // of the tile exceeds it by more than kSlack, which after the first tiles of a range is rare.  The cross-lane
+        // maximum (three shuffles per head) is taken only then.
+        constexpr float kSlack = 4.f;
+        float loc[2];
+        bool need = false;
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          s[e] = okt[0] ? fmaf(s[e], ksc[0], corr[e] * p.qscale) : -INFINITY;
-          s[2 + e] = okt[1] ? fmaf(s[2 + e], ksc[1], corr[2 + e] * p.qscale) : -INFINITY;
-          float m = fmaxf(s[e], s[2 + e]);
-          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
-          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
-          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
-          mx[e] = m;
-          grew |= m > m_run[e];
+          s[e] = (!EDGE || okt[0]) ? fmaf(s[e], ksc[0], corr[e] * p.qscale) : -INFINITY;
+          s[2 + e] = (!EDGE || okt[1]) ? fmaf(s[2 + e], ksc[1], corr[2 + e] * p.qscale) : -INFINITY;
+          loc[e] = fmaxf(s[e], s[2 + e]);
+          need |= loc[e] > m_run[e] + kSlack;
         }
-        if (__any_sync(0xffffffffu, grew)) {
+        if (__any_sync(0xffffffffu, need)) {
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const float m_new = fmaxf(m_run[e], mx[e]);
+            float m = loc[e];
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+            const float m_new = fmaxf(m_run[e], m);
             const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run[e] - m_new);
             m_run[e] = m_new;
             l_run[e] *= alpha;
@@ -476,41 +528,106 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
             for (int i = 0; i < NOT; ++i) { o[i][e] *= alpha; o[i][2 + e] *= alpha; }
           }
         }
+        // P goes to the tensor cores as fp16(p * rs_V / qmax).  The weights that are summed into l (and that weigh the
+        // V outliers below) are those rounded products divided by the same scale again, so numerator and denominator
+        // of the output use one and the same set of weights: the rounding of P cancels instead of adding 2^-11 of
+        // relative error to an output that a single key dominates.
         float pe[4];
         uint32_t pb[2];
+        {
+          float praw[4];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float m_use = m_run[e] == -INFINITY ? 0.f : m_run[e];
-          pe[e] = fast_exp2(s[e] - m_use);
-          pe[2 + e] = fast_exp2(s[2 + e] - m_use);
-          l_run[e] += pe[e] + pe[2 + e];
+          for (int e = 0; e < 2; ++e) {
+            const float m_use = m_run[e] == -INFINITY ? 0.f : m_run[e];
+            praw[e] = fast_exp2(s[e] - m_use);
+            praw[2 + e] = fast_exp2(s[2 + e] - m_use);
+          }
+          const __half2 h0 = __floats2half2_rn(praw[0] * vsc[0], praw[1] * vsc[0]);
+          const __half2 h1 = __floats2half2_rn(praw[2] * vsc[1], praw[3] * vsc[1]);
+          const float iv0 = vsc[0] > 0.f ? rcp_fast(vsc[0]) : 0.f, iv1 = vsc[1] > 0.f ? rcp_fast(vsc[1]) : 0.f;
+          const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+          pe[0] = f0.x * iv0; pe[1] = f0.y * iv0; pe[2] = f1.x * iv1; pe[3] = f1.y * iv1;
+          l_run[0] += pe[0] + pe[2];
+          l_run[1] += pe[1] + pe[3];
+          pb[0] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h0));
+          pb[1] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h1));
         }
-        pb[0] = movmatrix_trans(pack_half2(pe[0] * vsc[0], pe[1] * vsc[0]));
-        pb[1] = movmatrix_trans(pack_half2(pe[2] * vsc[1], pe[3] * vsc[1]));
 
         // ---- O^T += V^T P^T -----------------------------------------------------------------------------------
-        static_for<0, NVG>([&](auto g_) {
-          constexpr int g = decltype(g_)::value;
-          uint32_t lo[4], hi[4];
-          static_for<0, 4>([&](auto i_) {
-            constexpr int i = decltype(i_)::value;
-            uint32_t idx; __half2 rr;
-            FL::template cut<g>(cur.vw[i], idx, rr);
-            const uint2 cw = *reinterpret_cast<const uint2*>(tblV + (idx * strideV + laneoffV));
-            lo[i] = hmul2_u32(cw.x, rr);
-            hi[i] = hmul2_u32(cw.y, rr);
+        // A tile with many flagged V chunks (a hot channel: one per token) patches them into the decoded fragments on
+        // the way (x * qmax / rs in place of the zero the codeword path gives); a tile with a few takes the additive
+        // fp32 correction below, which costs nothing when there is none.
+        // (compiled for d_head 64 only: in the d_head 128 kernels the second copy of the loop costs registers that the
+        //  common path needs -- measured 3 to 15 % of a step -- so there a dense tile takes the additive correction too)
+        constexpr bool kPatchV = OUTL && N == 16;
+        const bool dense_v = kPatchV && th0.w - th0.z > 5u;
+        auto v_side = [&](auto patch_) {
+          constexpr bool PATCH = decltype(patch_)::value;
+          if constexpr (PATCH) {
+            // per token of the tile: flag word, flagged chunks of the tile's earlier tokens, qmax / rs -- parked in
+            // shared memory and fetched per gather, so that the patch keeps no registers alive across the loop
+            uint32_t fw = 0;
+            float inv = 0.f;
+            if (lane < kTile) {
+              if (t0 + lane < t_end) fw = reinterpret_cast<const uint32_t*>(sb + RL::kFlV)[warp * kTile + lane];
+              inv = __fdividef(p.qmaxf, bits16_to_float(reinterpret_cast<const uint16_t*>(sb + RL::kRsV)[warp * kTile + lane], SDT));
+            }
+            const uint32_t ex = excl_scan16(__popc(fw), lane);
+            if (lane < kTile) vinfo[warp * kTile + lane] = make_uint4(fw, ex, __float_as_uint(inv), 0u);
+            __syncwarp();
+          }
+          static_for<0, NVG>([&](auto g_) {
+            constexpr int g = decltype(g_)::value;
+            uint32_t lo[4], hi[4];
+            static_for<0, 4>([&](auto i_) {
+              constexpr int i = decltype(i_)::value;
+              uint32_t idx; __half2 rr;
+              FL::template cut<g>(cur.vw[i], idx, rr);
+              const uint2 cw = *reinterpret_cast<const uint2*>(tblV + (idx * strideV + laneoffV));
+              lo[i] = hmul2_u32(cw.x, rr);
+              hi[i] = hmul2_u32(cw.y, rr);
+              if constexpr (PATCH) {
+                const int c = r * NVG + g;
+                const uint4 ti = vinfo[warp * kTile + 2 * j + (i & 1) + (i >> 1) * 8];
+                if ((ti.x >> c) & 1u) {
+                  const uint32_t e = th0.z + ti.y + __popc(ti.x & ((1u << c) - 1u));
+                  const float vi = __uint_as_float(ti.z);
+                  float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
+                  if (e < (uint32_t)p.V.out_cap) {
+                    if (p.V.out_dtype == HQMQ_F32) {
+                      const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.V.out_vals) + (bh * p.V.out_cap + e) * 4);
+                      x0 = v.x; x1 = v.y; x2 = v.z; x3 = v.w;
+                    } else {
+                      const uint32_t rel = e - sh0.z;
+                      const uint2 v = rel < sh0.w ? reinterpret_cast<const uint2*>(sb + RL::kPayV)[rel]
+                                                  : reinterpret_cast<const uint2*>(p.V.out_vals)[bh * p.V.out_cap + e];
+                      const float2 a = pair16_to_float2(v.x, p.V.out_dtype), bb = pair16_to_float2(v.y, p.V.out_dtype);
+                      x0 = a.x; x1 = a.y; x2 = bb.x; x3 = bb.y;
+                    }
+                  }
+                  lo[i] = pack_half2(x0 * vi, x1 * vi);
+                  hi[i] = pack_half2(x2 * vi, x3 * vi);
+                }
+              }
+            });
+            const uint32_t a0 = __byte_perm(lo[0], lo[1], 0x5410), a1 = __byte_perm(lo[0], lo[1], 0x7632);
+            const uint32_t a2 = __byte_perm(lo[2], lo[3], 0x5410), a3 = __byte_perm(lo[2], lo[3], 0x7632);
+            const uint32_t c0 = __byte_perm(hi[0], hi[1], 0x5410), c1 = __byte_perm(hi[0], hi[1], 0x7632);
+            const uint32_t c2 = __byte_perm(hi[2], hi[3], 0x5410), c3 = __byte_perm(hi[2], hi[3], 0x7632);
+            mma16816(o[2 * g], a0, a1, a2, a3, pb[0], pb[1]);
+            mma16816(o[2 * g + 1], c0, c1, c2, c3, pb[0], pb[1]);
           });
-          const uint32_t a0 = __byte_perm(lo[0], lo[1], 0x5410), a1 = __byte_perm(lo[0], lo[1], 0x7632);
-          const uint32_t a2 = __byte_perm(lo[2], lo[3], 0x5410), a3 = __byte_perm(lo[2], lo[3], 0x7632);
-          const uint32_t c0 = __byte_perm(hi[0], hi[1], 0x5410), c1 = __byte_perm(hi[0], hi[1], 0x7632);
-          const uint32_t c2 = __byte_perm(hi[2], hi[3], 0x5410), c3 = __byte_perm(hi[2], hi[3], 0x7632);
-          mma16816(o[2 * g], a0, a1, a2, a3, pb[0], pb[1]);
-          mma16816(o[2 * g + 1], c0, c1, c2, c3, pb[0], pb[1]);
-        });
+        };
+        if constexpr (kPatchV) {
+          if (dense_v) v_side(std::true_type{});
+          else v_side(std::false_type{});
+        } else {
+          v_side(std::false_type{});
+        }
 
         // ---- V outliers: o[g][4c + e] += P[t][g] * x[e] for every flagged chunk (t, c), in fp32 ------------------
         if constexpr (OUTL) {
-          if (th0.w > th0.z) {
+          if (th0.w > th0.z && !dense_v) {
             uint32_t fw = 0;
             if (lane < kTile && t0 + lane < t_end) fw = reinterpret_cast<const uint32_t*>(sb + RL::kFlV)[warp * kTile + lane];
             uint32_t tm = __ballot_sync(0xffffffffu, fw != 0u);
@@ -554,8 +671,10 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
               }
             }
           }
-          (void)stage_bits;
         }
+        };   // tile_body
+        if (edge) tile_body(std::true_type{});
+        else tile_body(std::false_type{});
         __syncwarp();   // every lane is done with the stage before lane 0 releases it
       }
       if (lane == 0) mbar_arrive(bar_empty + 8 * buf);

@@ -36,6 +36,7 @@ class PackedKV:
         self.B, self.H, self.n_chunks, self.S, self.radius_bits = B, H, n_chunks, S, radius_bits
         self.T_cap = max(_lib.T_ALIGN, ((T_cap + _lib.T_ALIGN - 1) // _lib.T_ALIGN) * _lib.T_ALIGN)
         self.T = 0
+        self._enc_cache = {}      # argument structs of repeated small encode calls (see HQMQQuantizer.encode)
         self.row_bytes = row_bytes(n_chunks, S, radius_bits)
         self.scale_dtype, self.out_dtype = scale_dtype, out_dtype
         dev = torch.device(device)
@@ -91,6 +92,7 @@ class PackedKV:
     def drop_ofrag(self) -> None:
         """Forget the fragment records: attention then merges K outliers from flags / out_vals."""
         self.with_ofrag, self.ofrag_cap, self.ofrag, self.ofrag_off = False, 0, None, None
+        self._enc_cache.clear()
 
     # ---- accounting -------------------------------------------------------------------------
     def n_outliers(self) -> int:
@@ -141,3 +143,122 @@ class PackedKV:
         _lib.check(_lib.lib().hqmq_pack(C.byref(src), T, C.byref(p), 0, _lib.stream_ptr()), "hqmq_pack")
         out.T = T
         return out
+
+    # ---- on-disk / wire format -----------------------------------------------------------------------
+    # The reference keeps no compressed representation at all; its bit accounting (experiments/18_memory.py:22-35,
+    # README.md:77-83: code bits + 16-bit scale per token, with outlier extraction one flag bit per chunk and the
+    # original 16-bit values of every flagged chunk) is what a stored cache has to honour.  A file is
+    #     magic "HQMQKV1\0" | uint32 header length | JSON header, padded with spaces to a multiple of 16 bytes |
+    #     codes [B][H][T][row_bytes] | rs [B][H][T] | flags [B][H][T] (uint16 for d_head <= 64, else uint32) |
+    #     out_count [B][H] uint32 | payload: the out_count[b][h] entries of every (b, h) in order, 4 values each
+    # i.e. the native planes cut to the T tokens held, so the body is exactly algorithmic_bytes() plus the B*H
+    # counters.  Derived data (block offsets, fragment records) is not stored: offsets are rebuilt on load; a loaded
+    # cache has no fragment records (attention then merges its outliers from flags and payload).
+    MAGIC = b"HQMQKV1\x00"
+
+    def save(self, file, meta: Optional[dict] = None) -> int:
+        """Write the T tokens held to ``file`` (a path or a binary file object).  ``meta``: what the planes do not
+        know about themselves and a reader needs to rebuild the codebooks (for example {"C": 3.0, "seed": 42,
+        "layer": 0, "kv": 0}); it is stored in the header as given.  Returns the number of bytes written."""
+        import json
+        B, H, T, n = self.B, self.H, self.T, self.n_chunks
+        hdr = {"format": 1, "S": self.S, "radius_bits": self.radius_bits, "d_head": 4 * n, "H_kv": H, "B": B, "T": T,
+               "row_bytes": self.row_bytes, "scale_dtype": str(self.scale_dtype).replace("torch.", ""),
+               "outliers": bool(self.with_outliers), "out_dtype": str(self.out_dtype).replace("torch.", ""),
+               "flag_bytes": (2 if n <= 16 else 4) if self.with_outliers else 0, "meta": meta or {}}
+        hb = json.dumps(hdr, sort_keys=True).encode()
+        hb += b" " * (-(len(self.MAGIC) + 4 + len(hb)) % 16)
+        rows = self.codes[:B * H * self.T_cap * self.row_bytes].view(B, H, self.T_cap, self.row_bytes)[:, :, :T]
+        rs = self.rs[:B * H * self.T_cap].view(B, H, self.T_cap)[:, :, :T].contiguous().cpu()
+        parts = [self.MAGIC, len(hb).to_bytes(4, "little"), hb, rows.contiguous().cpu().numpy().tobytes(),
+                 rs.view(torch.int16 if rs.element_size() == 2 else torch.int32).numpy().tobytes()]
+        if self.with_outliers:
+            fl = self.flags[:B * H * self.T_cap].view(B, H, self.T_cap)[:, :, :T].contiguous().cpu()
+            parts.append((fl.to(torch.int16) if n <= 16 else fl).numpy().tobytes())
+            cnt = self.out_count.cpu()
+            parts.append(cnt.numpy().tobytes())
+            vals = self.out_vals[:B * H * self.out_cap * 4].view(B * H, self.out_cap, 4).cpu()
+            vbits = vals.view(torch.int16 if vals.element_size() == 2 else torch.int32)
+            for bh in range(B * H):
+                k = min(int(cnt[bh]), self.out_cap)
+                parts.append(vbits[bh, :k].numpy().tobytes())
+                if k < int(cnt[bh]):            # entries the side buffer had dropped read as zeros, like everywhere else
+                    parts.append(bytes((int(cnt[bh]) - k) * 4 * vals.element_size()))
+        blob = b"".join(parts)
+        if hasattr(file, "write"):
+            file.write(blob)
+        else:
+            with open(file, "wb") as f:
+                f.write(blob)
+        return len(blob)
+
+    @classmethod
+    def load(cls, file, device, T_cap: Optional[int] = None, out_cap: Optional[int] = None):
+        """Read a cache written by ``save`` onto ``device``.  Returns (PackedKV, meta).  ``T_cap`` / ``out_cap``:
+        capacities of the new planes (defaults: what the file holds), for a cache that will be appended to."""
+        import json
+        import numpy as np
+        blob = file.read() if hasattr(file, "read") else open(file, "rb").read()
+        if blob[:8] != cls.MAGIC:
+            raise ValueError("not a packed HQMQ cache (bad magic)")
+        hl = int.from_bytes(blob[8:12], "little")
+        hdr = json.loads(blob[12:12 + hl].decode())
+        if hdr.get("format") != 1:
+            raise ValueError(f"unsupported packed-cache format {hdr.get('format')}")
+        B, H, T, n = hdr["B"], hdr["H_kv"], hdr["T"], hdr["d_head"] // 4
+        sdt, odt = getattr(torch, hdr["scale_dtype"]), getattr(torch, hdr["out_dtype"])
+        pos = 12 + hl
+
+        def take(nbytes, np_dtype):
+            nonlocal pos
+            if pos + nbytes > len(blob):
+                raise ValueError("packed-cache file is truncated")
+            a = np.frombuffer(blob, dtype=np_dtype, count=nbytes // np.dtype(np_dtype).itemsize, offset=pos)
+            pos += nbytes
+            return torch.from_numpy(a.copy())
+
+        rows = take(B * H * T * hdr["row_bytes"], np.uint8).view(B, H, T, hdr["row_bytes"])
+        sb = 4 if sdt == torch.float32 else 2
+        rs = take(B * H * T * sb, np.int16 if sb == 2 else np.int32).view(sdt).view(B, H, T)
+        cnt = fl = payload = None
+        if hdr["outliers"]:
+            fb = hdr["flag_bytes"]
+            fl = take(B * H * T * fb, np.uint16 if fb == 2 else np.int32).to(torch.int32).view(B, H, T)
+            cnt = take(B * H * 4, np.int32)
+            vb = 4 if odt == torch.float32 else 2
+            payload = take(int(cnt.sum()) * 4 * vb, np.int16 if vb == 2 else np.int32).view(odt).view(-1, 4)
+        if pos != len(blob):
+            raise ValueError("packed-cache file has trailing bytes")
+        need_cap = int(cnt.max()) if cnt is not None and cnt.numel() else 0
+        out = cls(B, H, max(T_cap or T, T, 1), n, hdr["S"], hdr["radius_bits"], device, scale_dtype=sdt,
+                  with_outliers=hdr["outliers"], out_dtype=odt, out_cap=max(out_cap or 0, need_cap, 2) if hdr["outliers"] else None)
+        if out.row_bytes != hdr["row_bytes"]:
+            raise ValueError("row size in the file does not match the geometry in its header")
+        dev = out.device
+        out.codes[:B * H * out.T_cap * out.row_bytes].view(B, H, out.T_cap, out.row_bytes)[:, :, :T] = rows.to(dev)
+        out.rs[:B * H * out.T_cap].view(B, H, out.T_cap)[:, :, :T] = rs.to(dev)
+        if hdr["outliers"]:
+            fl = fl.to(dev)
+            out.flags[:B * H * out.T_cap].view(B, H, out.T_cap)[:, :, :T] = fl
+            out.out_count.copy_(cnt.to(dev))
+            vals = out.out_vals[:B * H * out.out_cap * 4].view(B * H, out.out_cap, 4)
+            o = 0
+            for bh in range(B * H):
+                k = int(cnt[bh])
+                vals[bh, :k] = payload[o:o + k].to(dev)
+                o += k
+            # entries before every 16-token block: popcount of the flag words, summed per block, scanned
+            pc = torch.zeros_like(fl)
+            for k in range(32):
+                pc += (fl >> k) & 1
+            nb = out.T_cap // _lib.OUT_BLOCK
+            per_blk = torch.zeros(B * H, nb, dtype=torch.int64, device=dev)
+            tb = (T + _lib.OUT_BLOCK - 1) // _lib.OUT_BLOCK
+            padded = torch.zeros(B * H, tb * _lib.OUT_BLOCK, dtype=torch.int64, device=dev)
+            padded[:, :T] = pc.view(B * H, T)
+            per_blk[:, :tb] = padded.view(B * H, tb, _lib.OUT_BLOCK).sum(-1)
+            off = torch.zeros(B * H, nb + 1, dtype=torch.int64, device=dev)
+            off[:, 1:] = per_blk.cumsum(-1)
+            out.out_off.copy_(off.to(torch.int32).view(-1))
+        out.T = T
+        return out, hdr.get("meta", {})

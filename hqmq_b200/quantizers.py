@@ -233,6 +233,23 @@ class HQMQQuantizer(KVQuantizer):
         overflowed (otherwise the caller may compare ``out_count`` with ``out_cap`` itself).  ``med_in``: (H,) fp32
         medians to flag against instead of this call's own (``hqmq_b200.dist.split_batch_median`` computes them
         when the batch entries of a head are spread over several GPUs)."""
+        # Decode-time appends repeat one small call shape on one cache: the argument struct and the workspace of
+        # such a call are kept with the cache, and a repeat only patches the input address and the write position
+        # (calls on one cache are ordered on a stream anyway, since they append to the same planes).
+        fast_key = None
+        if out is not None and med_out is None and med_in is None and not check_status and x.dim() == 4 and x.shape[2] <= 64:
+            fast_key = (id(self), layer_idx, kv, tuple(x.shape), x.dtype, x.stride(), median_mult, search)
+            hit = out._enc_cache.get(fast_key)
+            if hit is not None:
+                a, ws, nbytes = hit
+                T = x.shape[2]
+                if out.T + T > out.T_cap:
+                    raise _lib.HqmqError(f"hqmq_b200: cache capacity {out.T_cap} exceeded ({out.T} + {T})")
+                a.x, a.t_start = x.data_ptr(), out.T
+                with _lib.device_guard(x.device):
+                    _lib.check(_lib.lib().hqmq_encode(C.byref(a), ws.data_ptr(), nbytes, _lib.stream_ptr()), "hqmq_encode")
+                out.T += T
+                return out
         why = self._unsupported()
         if why:
             raise NotImplementedError(f"hqmq_b200 accelerates the unit-magnitude linear-radius path only ({why})")
@@ -243,6 +260,7 @@ class HQMQQuantizer(KVQuantizer):
             raise ValueError(f"d_head={d} not divisible by 4")
         if H != self.n_heads:
             raise ValueError(f"x has {H} heads, quantizer has {self.n_heads}")
+        x_given = x
         if x.stride(-1) != 1 or any(s % 4 for s in x.stride()[:3]):
             x = x.contiguous()
         if out is None:
@@ -267,6 +285,9 @@ class HQMQQuantizer(KVQuantizer):
             _lib.check(L.hqmq_encode(C.byref(a), ws.data_ptr(), nbytes, _lib.stream_ptr()), "hqmq_encode")
             if check_status and nbytes and (_lib.read_status(ws) & 1):
                 raise _lib.HqmqError(f"hqmq_b200: outlier side buffer too small (out_cap={out.out_cap} chunks per (b, h))")
+        if fast_key is not None and x is x_given:
+            a._keep = (a._keep[1], out)          # the tables and the planes, not the input tensor of this call
+            out._enc_cache[fast_key] = (a, ws, nbytes)
         out.T += T
         return out
 
@@ -332,33 +353,62 @@ class HQMQQuantizer(KVQuantizer):
 
 
 class _OutlierStats:
-    """Running outlier rate kept as device counters; read (and synchronised) only on demand.  A call costs one
-    small device copy (the cache's cumulative counters after the call); the per-call count is the difference
-    to the previous snapshot of the same cache, taken when the statistics are read."""
-
-    _MAX_PENDING = 1024
+    """Running mean of the per-call outlier rates (what the reference's wrapper keeps in ``_observed_outlier_rate``),
+    from the caches' device counters, read (and synchronised) only on demand.  A call costs no device work: every
+    cache remembers how many calls of which size it took since its counters were last read, and the flagged chunks
+    of those calls are the growth of its counters.  Calls of one size on one cache share their growth evenly (exact
+    for the sum of their rates, which is all a mean needs)."""
 
     def __init__(self):
-        self._pending = []          # (counters after the call, counters before it or None, n_chunks_total)
-        self._rate, self._n = 0.0, 0
+        self._caches = []           # caches with calls that were not accounted yet
+        self._counts = []           # (0-d device tensor: flagged chunks of one finished call, chunks of that call)
+        self._sum_rates, self._n = 0.0, 0   # sum of the per-call rates, number of calls
 
-    def push(self, after: torch.Tensor, before: Optional[torch.Tensor], total: int):
-        self._pending.append((after, before, total))
-        if len(self._pending) >= self._MAX_PENDING:
+    def begin(self, pk, total_chunks: int):
+        """Before a call appends to ``pk`` (None: a fresh cache).  Calls of another size are accounted first."""
+        if pk is None:
+            return
+        st = getattr(pk, "_stat_pending", None)
+        if st is not None and st[1] != total_chunks:
+            self._account(pk)
+        elif st is None and pk.T > 0 and not hasattr(pk, "_stat_base"):
+            pk._stat_base = float(pk.out_count.sum().item())      # a cache filled elsewhere: count from what it holds
+
+    def end(self, pk, total_chunks: int):
+        st = getattr(pk, "_stat_pending", None)
+        if st is None:
+            st = pk._stat_pending = [0, total_chunks]
+            self._caches.append(pk)
+        st[0] += 1
+
+    def _account(self, pk):
+        n_calls, total = pk._stat_pending
+        pk._stat_pending = None
+        now = float(pk.out_count.sum().item())
+        self._sum_rates += (now - getattr(pk, "_stat_base", 0.0)) / max(1, total)
+        self._n += n_calls
+        pk._stat_base = now
+
+    def push_count(self, count: torch.Tensor, total_chunks: int):
+        """A finished one-shot call (fake-quant): only its count is kept, not its cache."""
+        self._counts.append((count, total_chunks))
+        if len(self._counts) >= 1024:
             self._sync()
 
     def _sync(self):
-        for after, before, total in self._pending:
-            cnt = float(after.sum().item()) - (float(before.sum().item()) if before is not None else 0.0)
-            rate = cnt / max(1, total)
-            self._rate = (self._rate * self._n + rate) / (self._n + 1)
+        for pk in self._caches:
+            if getattr(pk, "_stat_pending", None) is not None:
+                self._account(pk)
+        self._caches = []
+        for count, total in self._counts:
+            self._sum_rates += float(count.item()) / max(1, total)
             self._n += 1
-        self._pending.clear()
+        self._counts = []
 
     @property
     def rate(self):
         self._sync()
-        return self._rate
+        return self._sum_rates / self._n if self._n else 0.0
 
     @property
     def n(self):
@@ -403,14 +453,12 @@ class OutlierAwareHQMQQuantizer(KVQuantizer):
 
     def encode(self, x, layer_idx, kv, out: Optional[PackedKV] = None, **kw) -> PackedKV:
         self._check_mode()
-        # the cache's counters before this call: the snapshot taken after the previous call on the same cache
-        before = getattr(out, "_count_snapshot", None) if out is not None else None
-        if out is not None and before is None and out.T > 0:
-            before = out.out_count.clone()
+        total = x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4)
+        if total:
+            self._stats.begin(out, total)
         pk = self.inner.encode(x, layer_idx, kv, out=out, median_mult=self.median_mult, **kw)
-        after = pk.out_count.clone()
-        pk._count_snapshot = after
-        self._stats.push(after, before, x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4))
+        if total:
+            self._stats.end(pk, total)
         return pk
 
     def decode(self, packed, layer_idx, kv, **kw):
@@ -419,8 +467,8 @@ class OutlierAwareHQMQQuantizer(KVQuantizer):
     def _qdq(self, x, layer_idx, kv):
         self._check_mode()
         out = self.inner._qdq(x, layer_idx, kv, median_mult=self.median_mult)
-        pk = self.inner._last_packed
-        self._stats.push(pk.out_count.clone(), None, x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4))
+        if x.shape[0] and x.shape[2]:
+            self._stats.push_count(self.inner._last_packed.out_count.sum(), x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4))
         return out
 
     def quantize_K(self, k, layer_idx):

@@ -55,3 +55,64 @@ def test_prompt_then_token_appends_over_two_layers_with_a_sliding_window():
         ref = torch.softmax(Q.half().float() @ Kw.transpose(-1, -2) / math.sqrt(d), -1) @ Vw
         assert float((O.cpu() - ref).abs().max()) < 2e-3 and _rel_l2(O.cpu(), ref) < 1e-3, l
     assert cache.compressed_bytes() > 0
+
+
+def test_packed_cache_file_round_trip(tmp_path):
+    """The on-disk format: the native planes cut to the tokens held, so the body is the algorithmic byte count
+    (plus one counter per (batch, head)); a loaded cache decodes and attends exactly like the one that was saved."""
+    import math
+    S, br, C, d, Hq, Hkv, T, B = 96, 4, 3.0, 128, 8, 2, 1500, 2
+    K = make_kv("hot", (B, Hkv, T, d), seed=91, dtype=torch.bfloat16)
+    V = make_kv("spiky", (B, Hkv, T, d), seed=92, dtype=torch.bfloat16)
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, Hkv, S, br, device="cuda"), C)
+    Kp, Vp = q.encode(K.cuda(), 0, 0), q.encode(V.cuda(), 0, 1)
+    tk, tv = q.inner.tables(0, 0, "cuda"), q.inner.tables(0, 1, "cuda")
+    Q = (torch.randn(B, Hq, 1, d, generator=torch.Generator().manual_seed(93)) / math.sqrt(d)).bfloat16().cuda()
+    loaded = []
+    for name, pk, kv in (("k.hqmq", Kp, 0), ("v.hqmq", Vp, 1)):
+        path = tmp_path / name
+        n = pk.save(str(path), meta={"C": C, "seed": 42, "layer": 0, "kv": kv})
+        blob = path.read_bytes()
+        hdr_len = 12 + int.from_bytes(blob[8:12], "little")
+        assert n == len(blob) == hdr_len + pk.algorithmic_bytes() + 4 * B * Hkv
+        back, meta = hqmq.PackedKV.load(str(path), "cuda", T_cap=T + 64)
+        assert meta == {"C": C, "seed": 42, "layer": 0, "kv": kv} and back.T == T
+        for g, w in zip(back.to_reference(), pk.to_reference()):
+            assert torch.equal(g, w)
+        assert torch.equal(q.decode(back, 0, kv, dtype=torch.float32), q.decode(pk, 0, kv, dtype=torch.float32))
+        loaded.append(back)
+    # the loaded K cache has no fragment records: same result through the flag / payload path, within the tolerance
+    O1 = torch.empty(Q.shape, dtype=torch.float32, device="cuda")
+    O2 = torch.empty_like(O1)
+    hqmq.fused_attention_packed(Q, Kp, Vp, tk["table16"], tv["table16"], out=O1)
+    hqmq.fused_attention_packed(Q, loaded[0], loaded[1], tk["table16"], tv["table16"], out=O2)
+    assert (O1 - O2).abs().max().item() < 2e-3
+    # and it can be appended to
+    more = make_kv("hot", (B, Hkv, 16, d), seed=94, dtype=torch.bfloat16).cuda()
+    q.encode(more, 0, 0, out=loaded[0])
+    assert loaded[0].T == T + 16
+    with pytest.raises(ValueError):
+        hqmq.PackedKV.load(_truncated(tmp_path / "k.hqmq"), "cuda")
+
+
+def _truncated(path):
+    import io
+    return io.BytesIO(path.read_bytes()[:-10])
+
+
+def test_padded_head_dim_matches_the_oracle():
+    """PaddedHQMQ (head dims that are not a multiple of 4: zero-pad, quantise, truncate; src/quantizers/hqmq_padded.py:51-71)
+    through the CUDA encoder and dequant: bit-identical to the oracle's fake-quant of the padded tensor, truncated."""
+    from oracle import hqmq_oracle as orc
+    S, br, Hkv, T, B, d = 24, 3, 2, 70, 2, 45
+    x = torch.randn(B, Hkv, T, d, generator=torch.Generator().manual_seed(95))
+    pq = hqmq.PaddedHQMQ(n_layers=1, n_heads=Hkv, d_head=d, secondary_size=S, radius_bits=br, device="cuda")
+    assert (pq.d_head_padded, pq.pad_count) == (48, 3)
+    got = pq.quantize_K(x.cuda(), 0).cpu()
+    assert got.shape == x.shape
+    joint = orc.joint_codebook(orc.secondary_raw(1, Hkv, S, 42)[0, :, 0])
+    xp = torch.nn.functional.pad(x, (0, 3))
+    enc = orc.encode(xp, joint, br, None)
+    want = orc.fake_quant(xp, joint, br, None, enc=enc)[..., :d]
+    near_tie = (enc["gap"] < 1e-6).unsqueeze(-1).expand(B, Hkv, T, 12, 4).reshape(B, Hkv, T, 48)[..., :d]
+    assert torch.equal(got[~near_tie], want[~near_tie])

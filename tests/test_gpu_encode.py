@@ -137,11 +137,32 @@ def test_encode_append_keeps_earlier_rows_and_offsets():
     assert abs(q._observed_outlier_rate - np.mean([float(e["flags"].float().mean()) for e in encs])) < 1e-6
 
 
-def test_exhaustive_and_default_search_agree():
-    x = make_kv("hot", (1, 2, 64, 128), seed=33)
-    a = _encode_and_compare(x, 96, 4, None, search=0)[1].to_reference()[0]
-    b = _encode_and_compare(x, 96, 4, None, search=1)[1].to_reference()[0]
-    assert (a != b).float().mean().item() < 1e-3
+@pytest.mark.parametrize("S,br", [(24, 3), (96, 4), (192, 6)])
+@pytest.mark.parametrize("kind", ["randn", "hot", "spiky"])
+def test_exhaustive_and_default_search_agree(S, br, kind):
+    """The look-up-table search against the exhaustive closed-form scan on a million chunks per case (GPU against
+    GPU); every chunk on which they disagree is then put to the oracle, and a disagreement is allowed only where
+    the oracle's two best similarities differ by less than 1e-6 (a documented near-tie)."""
+    B, H, T, d = 4, 8, 1024, 128
+    x = make_kv(kind, (B, H, T, d), seed=500 + S, dtype=torch.bfloat16)
+    q = hqmq.HQMQ(1, H, S, br, device="cuda")
+    a = q.encode(x.cuda(), 0, 0, search=0).to_reference()[0].cpu()
+    b = q.encode(x.cuda(), 0, 0, search=1).to_reference()[0].cpu()
+    diff = a != b
+    assert diff.float().mean().item() < 2e-3
+    raw = orc.secondary_raw(1, H, S, 42)
+    joint = orc.joint_codebook(raw[0, :, 0])
+    xc = x.float().view(B, H, T, d // 4, 4)
+    for h in range(H):
+        m = diff[:, h]
+        if not m.any():
+            continue
+        chunks = xc[:, h][m].reshape(1, 1, -1, 4)            # every disagreeing chunk as a one-chunk token
+        enc = orc.encode(chunks, joint[h:h + 1], br, None)
+        gap, want = enc["gap"].reshape(-1), enc["idx"].reshape(-1)
+        for got in (a[:, h][m], b[:, h][m]):
+            bad = (got.to(torch.int32) != want) & (gap >= 1e-6)
+            assert int(bad.sum()) == 0, f"S={S} {kind} head {h}: {int(bad.sum())} indices differ from the oracle outside near-ties"
 
 
 def test_full_size_properties_config2_slice():
@@ -154,12 +175,13 @@ def test_full_size_properties_config2_slice():
     pk = q.encode(x, 0, 0, scale_dtype=torch.float32, med_out=med)
     idx, rq, rs, flags = pk.to_reference()
     xf = x.float().view(1, 2, 32768, 32, 4)
-    nrm = xf.norm(dim=-1)
+    sq = xf * xf          # the contract's norm: separate IEEE multiplies and adds in this order, then one square root
+    nrm = (((sq[..., 0] + sq[..., 1]) + sq[..., 2]) + sq[..., 3]).sqrt()
     # median property: at least half of the norms are <= med and at least half are >= med
     for h in range(2):
         v = nrm[0, h].reshape(-1)
         assert (v <= med[h]).float().mean() >= 0.5 and (v >= med[h]).float().mean() >= 0.5
-        assert torch.equal(flags[0, h], nrm[0, h] > med[h] * C) or (flags[0, h] != (nrm[0, h] > med[h] * C)).sum() <= 2
+        assert torch.equal(flags[0, h], nrm[0, h] > med[h] * C)
     assert int(rq.max()) == 15 and int(rq.min()) >= 0
     assert (torch.where(flags, 15, rq).max(dim=-1).values == 15).all()   # the token's largest chunk codes qmax (or is flagged)
     assert int(idx.max()) < 24 * S and int(idx.min()) >= 0

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libhqmq_b200.so")
 
 F32, F16, BF16, I32, I16, I8, U8, I64 = range(8)
-ABI_VERSION = 3
+ABI_VERSION = 4
 OUT_BLOCK = 16
 OFRAG_BYTES = 528
 T_ALIGN = 64
@@ -64,7 +64,7 @@ class EncodeArgs(C.Structure):
         ("struct_size", C.c_uint32), ("x_dtype", C.c_int32), ("x", C.c_void_p), ("x_stride", C.c_int64 * 3),
         ("T_new", C.c_int32), ("t_start", C.c_int32), ("qs", C.c_void_p), ("joint", C.c_void_p),
         ("median_mult", C.c_float), ("search", C.c_int32), ("dst", Packed), ("med_out", C.c_void_p),
-        ("lut", C.c_void_p), ("lut_max_cand", C.c_int32), ("reserved", C.c_int32), ("med_in", C.c_void_p),
+        ("lut", C.c_void_p), ("lut_footprint", C.c_int32), ("reserved", C.c_int32), ("med_in", C.c_void_p),
     ]
 
 
@@ -129,7 +129,7 @@ def lib():
     L.hqmq_encode_lut_workspace_bytes.argtypes = [C.c_int, C.c_int]
     L.hqmq_encode_lut_build.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t,
                                         C.c_void_p]
-    L.hqmq_encode_lut_max_candidates.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.c_void_p]
+    L.hqmq_encode_lut_footprint.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.c_void_p]
     L.hqmq_encode_workspace_bytes.restype = C.c_size_t
     L.hqmq_encode_workspace_bytes.argtypes = [C.POINTER(EncodeArgs)]
     L.hqmq_encode.argtypes = [C.POINTER(EncodeArgs), C.c_void_p, C.c_size_t, C.c_void_p]

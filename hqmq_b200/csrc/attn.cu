@@ -100,6 +100,7 @@ struct Plan {
   int table_rows, ib, nw, rep_log2;
   int threads;                             // threads per CTA (the ring kernels add a producer warp to their nw consumers)
   int repv_log2, ring_stages, merge_slots; // ring kernels only
+  size_t ticket_bytes;                     // ring kernels: one ticket word per unit between the status word and the partials
   int ppc;   // partials a CTA writes per unit and head: 1 for the staged kernels (merged in shared memory), nw otherwise
   int units, tpu_v, L, P, grid;
   size_t ws_bytes;
@@ -264,7 +265,8 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   pl.grid = (int)((total + pl.L - 1) / pl.L);
   pl.P = (pl.tpu_v - 1 + pl.L - 1) / pl.L + 1;
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
-  pl.ws_bytes = 16 + (size_t)rows * pl.P * pl.ppc * (a->d + 2) * sizeof(float);
+  pl.ticket_bytes = pl.ring_stages ? (((size_t)pl.units * 4 + 15) & ~(size_t)15) : 0;
+  pl.ws_bytes = 16 + pl.ticket_bytes + (size_t)rows * pl.P * pl.ppc * (a->d + 2) * sizeof(float);
   return HQMQ_OK;
 }
 
@@ -322,7 +324,12 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   static std::atomic<uint32_t> epoch_counter{0x5eed0000u};
   p.status = reinterpret_cast<uint32_t*>(workspace);
   p.epoch = epoch_counter.fetch_add(1u, std::memory_order_relaxed) + 1u;
-  p.partials = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 16);
+  p.tickets = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(workspace) + 16);
+  p.partials = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 16 + pl.ticket_bytes);
+  p.O = a->O; p.o_dtype = a->o_dtype; p.os_b = a->o_stride[0]; p.os_h = a->o_stride[1]; p.os_t = a->o_stride[2];
+  p.merged = a->partials_only ? a->partials : nullptr;
+  const bool fused_merge = pl.ring_stages > 0;   // the ring kernels merge a unit's partials themselves (last CTA of the unit)
+  if (fused_merge) HQMQ_CHECK_CUDA(cudaMemsetAsync(p.tickets, 0, pl.ticket_bytes, st));
   p.layout = a->layout;
   p.table_rows = pl.table_rows;
   p.ib = pl.ib;
@@ -334,6 +341,7 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   // (the kernel's dynamic shared-memory limit was raised when the plan asked for its occupancy: resident_ctas)
   void* kargs[] = {&p};
   HQMQ_CHECK_CUDA(cudaLaunchKernel(pl.kernel, dim3(pl.grid), dim3(pl.threads), kargs, pl.smem, st));
+  if (fused_merge) { HQMQ_LAUNCH_CHECK(); return HQMQ_OK; }
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
   combine_kernel<<<(unsigned)rows, a->d < 128 ? 64 : 128, (size_t)pl.P * pl.ppc * 4, st>>>(
       p.partials, pl.P * pl.ppc, rows, a->d, a->o_dtype, a->O, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->H_q,

@@ -65,6 +65,10 @@ struct AttnParams {
   const void* jK; const void* jV; int j_dtype;
   uint32_t* status;   // a kernel that gave up on a bounded wait stores `epoch` here; the merge kernel then emits NaN
   uint32_t epoch;
+  // ring kernels: the merge over the CTAs of a unit is done by the last of them to finish (one ticket per unit)
+  uint32_t* tickets;  // [units], zero at launch
+  void* O; int o_dtype; int64_t os_b, os_h, os_t;
+  float* merged;      // partials_only: one merged (o[d], m, l) per row instead of O
 };
 
 // A ring kernel (attn_ring.cu) and the bytes of one of its stages.

@@ -154,6 +154,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
   float* w_s = l_s + kRingWarps * 8;                                // [16][8]
   float* ms_s = w_s + kRingWarps * 8;                               // [8] m*, [8] l*
   volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(ms_s + 16);
+  volatile uint32_t* last_s = abort_word + 1;                       // "this CTA drew the unit's last ticket"
   float* slots = ms_s + 20;                                         // [merge_slots][8][D]
   unsigned char* ring = smem_raw + sl.ring;
 
@@ -739,16 +740,69 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
         }
         consumer_bar();
       }
+      // ---- across the CTAs that share the unit: the last one to finish merges all of their partials ----------------
+      // (no CTA waits for another: a ticket per unit counts arrivals, and whoever draws the last one does the merge)
+      const int64_t ubase = (int64_t)u * p.tpu_v;
+      const int c0 = (int)(ubase / p.L), n_ctas = (int)((ubase + p.tpu_v - 1) / p.L) - c0 + 1;
+      auto emit = [&](int g, int x, float v, float m_star, float l_star) {
+        const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
+        if (p.merged) {
+          p.merged[row * (D + 2) + x] = v;
+          if (x == 0) { p.merged[row * (D + 2) + D] = m_star; p.merged[row * (D + 2) + D + 1] = l_star; }
+        } else {
+          store_float(p.O, (int64_t)b * p.os_b + (int64_t)(h * p.G + g) * p.os_h + (int64_t)tq * p.os_t + x,
+                      l_star > 0.f ? v / l_star : 0.f, p.o_dtype);
+        }
+      };
+      if (n_ctas == 1) {
 #pragma unroll
-      for (int q = 0; q < PER; ++q) {
-        const int i = threadIdx.x + q * kRingConsumerThreads;
-        if (i < 8 * D) {
-          const int g = i / D, x = i - g * D;
-          if (g < p.G) {
-            const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
-            float* dst = p.partials + (row * p.P + up.part) * (D + 2);
-            dst[x] = acc[q];
-            if (x == 0) { dst[D] = ms_s[g]; dst[D + 1] = ms_s[8 + g]; }
+        for (int q = 0; q < PER; ++q) {
+          const int i = threadIdx.x + q * kRingConsumerThreads;
+          if (i < 8 * D) {
+            const int g = i / D, x = i - g * D;
+            if (g < p.G) emit(g, x, acc[q], ms_s[g], ms_s[8 + g]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < PER; ++q) {
+          const int i = threadIdx.x + q * kRingConsumerThreads;
+          if (i < 8 * D) {
+            const int g = i / D, x = i - g * D;
+            if (g < p.G) {
+              const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
+              float* dst = p.partials + (row * p.P + up.part) * (D + 2);
+              dst[x] = acc[q];
+              if (x == 0) { dst[D] = ms_s[g]; dst[D + 1] = ms_s[8 + g]; }
+            }
+          }
+        }
+        __threadfence();                      // this CTA's partial is visible device-wide before its ticket is drawn
+        consumer_bar();
+        if (threadIdx.x == 0) *last_s = atomicAdd(&p.tickets[u], 1u) == (uint32_t)(n_ctas - 1) ? 1u : 0u;
+        consumer_bar();
+        if (*last_s) {
+          __threadfence();
+#pragma unroll
+          for (int q = 0; q < PER; ++q) {
+            const int i = threadIdx.x + q * kRingConsumerThreads;
+            if (i < 8 * D) {
+              const int g = i / D, x = i - g * D;
+              if (g < p.G) {
+                const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
+                const float* base = p.partials + row * p.P * (D + 2);
+                float m_star = -INFINITY;
+                for (int c = 0; c < n_ctas; ++c) m_star = fmaxf(m_star, __ldcg(base + c * (D + 2) + D));
+                const float m_use = m_star == -INFINITY ? 0.f : m_star;
+                float v = 0.f, l_star = 0.f;
+                for (int c = 0; c < n_ctas; ++c) {
+                  const float wgt = fast_exp2(__ldcg(base + c * (D + 2) + D) - m_use);
+                  v = fmaf(__ldcg(base + c * (D + 2) + x), wgt, v);
+                  l_star = fmaf(__ldcg(base + c * (D + 2) + D + 1), wgt, l_star);
+                }
+                emit(g, x, v, m_star, l_star);
+              }
+            }
           }
         }
       }

@@ -27,23 +27,36 @@ constexpr int kBandWords = 4;     // per head: thr_lo bits, thr_hi bits, undecid
 constexpr int kUndCap = 4096;     // undecided chunks listed per head; more -> the fix-up re-scans x instead
 
 // ---- nearest-codeword look-up table -------------------------------------------------------------------
-// The unit direction u is first folded by the axis unit g = sign(u_i*) e_i* of its largest component
-// (v = conj(g) * u, an exact signed permutation), which makes v0 the largest component and positive; the
-// joint codebook is invariant under left multiplication by the 8 axis units, so the nearest codeword of
-// u is g times the nearest codeword of v.  v is located in a grid over w = (v1,v2,v3)/v0 in [-1,1]^3 with
-// kLutN cells per axis; each cell lists every codeword that can be the nearest one for some direction in
-// the cell (all k not beaten over the whole cell by the winner at the cell's centre: the comparison of two
-// codewords is linear in w, so its maximum over the box is attained at a corner).  Only the listed
-// codewords are evaluated, with the same fp32 dot product an exhaustive scan of the joint table would use.
-constexpr int kLutN = 16;
-constexpr int kLutCells = kLutN * kLutN * kLutN;
-constexpr int kLutHdr = kLutCells + 4;      // per head: offsets[kLutCells + 1], valid flag, padding
-constexpr int kLutCandCap = 49152;          // candidate entries per head
-constexpr int kLutMaxList = 64;             // longest list a cell may have; longer -> exhaustive search there
+// The joint codebook {p * q_s} is invariant under left multiplication by any of the 24 Hurwitz units g, so the
+// unit direction u is first FOLDED by its nearest unit: v = conj(g) * u lies in the Voronoi cell of 1 among the 24
+// units, which in the coordinates w = (v1, v2, v3) / v0 is the octahedron |w1| + |w2| + |w3| <= 1, and the nearest
+// codeword of u is g times the nearest codeword of v (a 24 x 24 index table).  (Folding by the nearest unit is
+// closed form: the larger of the largest |u_i| and (|u0|+|u1|+|u2|+|u3|)/2 names it; conj(g) * u is a signed
+// permutation for an axis unit and sums of differences of the |u_i| for a half-integer unit.)
+// A grid of n cells per axis covers the octahedron (only the cells that meet it are stored: a row table over
+// (cx, cy) gives the first stored cz and where the row's cells start).  Each cell names every codeword that can be
+// the nearest one for some direction in the (slightly grown) cell: all k not beaten over the whole cell by the
+// winner at the cell's centre, minus those beaten over the whole cell by another listed one -- the comparison of
+// two codewords is linear in w, so its extreme over the box is at a corner.  A cell with ONE possible winner stores
+// it in its own word (no similarity is evaluated at all); the others point at a list, padded to groups of four,
+// which is evaluated with the same fp32 dot product an exhaustive scan of the joint table would use.  At n = 48
+// and S = 96 a list holds 1.9 codewords on average (8 at most) and 98 % of the lists are one group.
+constexpr int kLutNMax = 48;
+constexpr int kLutRows = kLutNMax * kLutNMax;
+constexpr int kLutCellCap = 24576;          // stored cells (23.4 k at n = 48)
+constexpr int kLutCandCap = 65532;          // candidate entries per head (list offsets / 4 are 15-bit cell words)
+constexpr int kLutMaxList = 16;             // longest list a cell may have; longer -> exhaustive search there
 constexpr float kLutBoxEps = 1e-5f;         // the boxes are grown by this much (cell assignment rounding)
 constexpr float kLutMargin = 1e-5f;         // a codeword is dropped only if it loses by more than this
+// device layout of a table (bytes): global header {n, n_cells, ...} | rows[kLutRows] uint32 = base (20 bits) |
+// first stored cz (6) | stored cells of the row (6) | per head: {total candidates, valid, -, -} uint32, then
+// cells[kLutCellCap] uint16 (0xFFFF: exhaustive; bit 15: the single winner in bits 0..14; else list offset / 4),
+// cands[kLutCandCap] uint16 (bit 15 of a group's first entry marks the list's last group)
+constexpr size_t kLutOffRows = 32;
+constexpr size_t kLutOffHeads = kLutOffRows + (size_t)kLutRows * 4;
+constexpr size_t kLutHeadBytes = 16 + (size_t)kLutCellCap * 2 + (size_t)kLutCandCap * 2;
 
-struct Mul8x24 { uint8_t v[8][24]; };      // index of (axis unit g) * (primary p)
+struct Mul24 { uint8_t v[24][24]; };       // reference index of (unit g) * (primary p)
 
 struct Maps24 { uint8_t ref_to_native[24]; };
 
@@ -116,63 +129,139 @@ __device__ __forceinline__ int search_exhaustive(const float4* __restrict__ qs, 
   return bp;
 }
 
-// Nearest codeword through the look-up table.  Returns the reference primary index and the secondary.
-__device__ __forceinline__ int search_lut(const float4* __restrict__ joint, const uint32_t* __restrict__ off,
-                                          const uint16_t* __restrict__ cand, const float4* __restrict__ qs, int S,
-                                          float inv_S, float u0, float u1, float u2, float u3, const Mul8x24& mul,
-                                          int& best_s) {
+// A table as a kernel sees it (global or shared memory).
+struct LutView {
+  const uint32_t* rows; const uint16_t* cells; const uint16_t* cands;
+  const uint8_t* nm;     // [24][24]: (fold unit g, primary p of the folded winner) -> primary of g * p, in the form the caller wants
+  int n; float hn;       // cells per axis, n / 2
+};
+
+__device__ __forceinline__ float xor_sign(float x, uint32_t sign_bits) { return __uint_as_float(__float_as_uint(x) ^ sign_bits); }
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Nearest codeword of the direction u through the table: writes nm[g][p'] and the secondary index, returns
+// false when the chunk has to take the exhaustive search (zero direction, a cell without a list).
+__device__ __forceinline__ bool search_fold24(const float4* __restrict__ joint, const LutView& L, int S, float inv_S,
+                                              float u0, float u1, float u2, float u3, int& prim, int& sidx) {
   const float a0 = fabsf(u0), a1 = fabsf(u1), a2 = fabsf(u2), a3 = fabsf(u3);
   int ax = 0; float am = a0;
   if (a1 > am) { am = a1; ax = 1; }
   if (a2 > am) { am = a2; ax = 2; }
   if (a3 > am) { am = a3; ax = 3; }
-  if (!(am > 0.f)) { best_s = 0; return 0; }   // zero direction: every similarity is 0, the first index wins
-  float v0, v1, v2, v3;
-  if (ax == 0) { v0 = u0; v1 = u1; v2 = u2; v3 = u3; }
-  else if (ax == 1) { v0 = u1; v1 = -u0; v2 = u3; v3 = -u2; }
-  else if (ax == 2) { v0 = u2; v1 = -u3; v2 = -u0; v3 = u1; }
-  else { v0 = u3; v1 = u2; v2 = -u1; v3 = -u0; }
-  const bool neg = v0 < 0.f;
-  if (neg) { v0 = -v0; v1 = -v1; v2 = -v2; v3 = -v3; }
-  const float inv = __frcp_rn(v0);
-  const int cx = min(kLutN - 1, max(0, (int)((v1 * inv + 1.f) * (0.5f * kLutN))));
-  const int cy = min(kLutN - 1, max(0, (int)((v2 * inv + 1.f) * (0.5f * kLutN))));
-  const int cz = min(kLutN - 1, max(0, (int)((v3 * inv + 1.f) * (0.5f * kLutN))));
-  const int cell = (cx * kLutN + cy) * kLutN + cz;
-  const uint32_t beg = off[cell], end = off[cell + 1];
-  if (beg == end) return search_exhaustive(qs, S, u0, u1, u2, u3, best_s);
-  // lists are padded to a multiple of four entries (the last one repeated), four evaluated per step
-  float best = -2.f; int bk = 0;
-  for (uint32_t e = beg; e < end; e += 4) {
-    const uint2 kk = *reinterpret_cast<const uint2*>(cand + e);
-    const int k0 = kk.x & 0xffff, k1 = kk.x >> 16, k2 = kk.y & 0xffff, k3 = kk.y >> 16;
-    const float4 c0 = joint[k0], c1 = joint[k1], c2 = joint[k2], c3 = joint[k3];
-    const float s0 = fmaf(v3, c0.w, fmaf(v2, c0.z, fmaf(v1, c0.y, v0 * c0.x)));
-    const float s1 = fmaf(v3, c1.w, fmaf(v2, c1.z, fmaf(v1, c1.y, v0 * c1.x)));
-    const float s2 = fmaf(v3, c2.w, fmaf(v2, c2.z, fmaf(v1, c2.y, v0 * c2.x)));
-    const float s3 = fmaf(v3, c3.w, fmaf(v2, c3.z, fmaf(v1, c3.y, v0 * c3.x)));
-    if (s0 > best) { best = s0; bk = k0; }
-    if (s1 > best) { best = s1; bk = k1; }
-    if (s2 > best) { best = s2; bk = k2; }
-    if (s3 > best) { best = s3; bk = k3; }
+  if (!(am > 0.f)) return false;
+  const float hs = ((a0 + a1) + a2) + a3;          // twice the similarity of the nearest half-integer unit
+  int gp; float v0, v1, v2, v3;
+  if (hs > 2.f * am) {
+    // g = (s0, s1, s2, s3) / 2 with s_i = sign(u_i); 2 conj(g) u in terms of the |u_i|
+    const uint32_t b0 = __float_as_uint(u0), b1 = __float_as_uint(u1), b2 = __float_as_uint(u2), b3 = __float_as_uint(u3);
+    gp = 8 + (int)(((b0 >> 31) << 3) | ((b1 >> 31) << 2) | ((b2 >> 31) << 1) | (b3 >> 31));
+    v0 = hs;
+    v1 = xor_sign(a1 - a0, (b0 ^ b1) & 0x80000000u) + xor_sign(a2 - a3, (b2 ^ b3) & 0x80000000u);
+    v2 = xor_sign(a2 - a0, (b0 ^ b2) & 0x80000000u) + xor_sign(a3 - a1, (b1 ^ b3) & 0x80000000u);
+    v3 = xor_sign(a3 - a0, (b0 ^ b3) & 0x80000000u) + xor_sign(a1 - a2, (b1 ^ b2) & 0x80000000u);
+  } else {
+    if (ax == 0) { v0 = u0; v1 = u1; v2 = u2; v3 = u3; }
+    else if (ax == 1) { v0 = u1; v1 = -u0; v2 = u3; v3 = -u2; }
+    else if (ax == 2) { v0 = u2; v1 = -u3; v2 = -u0; v3 = u1; }
+    else { v0 = u3; v1 = u2; v2 = -u1; v3 = -u0; }
+    const bool neg = v0 < 0.f;
+    if (neg) { v0 = -v0; v1 = -v1; v2 = -v2; v3 = -v3; }
+    gp = 2 * ax + (neg ? 1 : 0);
+  }
+  const float inv = rcp_approx(v0) * L.hn;
+  const int cx = min(L.n - 1, max(0, (int)fmaf(v1, inv, L.hn)));
+  const int cy = min(L.n - 1, max(0, (int)fmaf(v2, inv, L.hn)));
+  const int cz = (int)fmaf(v3, inv, L.hn);
+  const uint32_t row = L.rows[cx * L.n + cy];
+  const int zcnt = (int)(row >> 26);
+  if (zcnt == 0) return false;
+  const int zc = min(zcnt - 1, max(0, cz - (int)((row >> 20) & 63u)));
+  const uint32_t cw = L.cells[(row & 0xfffffu) + zc];
+  if (cw == 0xffffu) return false;
+  int bk;
+  if (cw & 0x8000u) {
+    bk = (int)(cw & 0x7fffu);
+  } else {
+    float best = -3.f;
+    bk = 0;
+    const uint16_t* e = L.cands + cw * 4u;
+    for (;;) {
+      const uint2 kk = *reinterpret_cast<const uint2*>(e);
+      const int k0 = kk.x & 0x7fff, k1 = kk.x >> 16, k2 = kk.y & 0xffff, k3 = kk.y >> 16;
+      const float4 c0 = joint[k0], c1 = joint[k1], c2 = joint[k2], c3 = joint[k3];
+      const float s0 = fmaf(v3, c0.w, fmaf(v2, c0.z, fmaf(v1, c0.y, v0 * c0.x)));
+      const float s1 = fmaf(v3, c1.w, fmaf(v2, c1.z, fmaf(v1, c1.y, v0 * c1.x)));
+      const float s2 = fmaf(v3, c2.w, fmaf(v2, c2.z, fmaf(v1, c2.y, v0 * c2.x)));
+      const float s3 = fmaf(v3, c3.w, fmaf(v2, c3.z, fmaf(v1, c3.y, v0 * c3.x)));
+      if (s0 > best) { best = s0; bk = k0; }
+      if (s1 > best) { best = s1; bk = k1; }
+      if (s2 > best) { best = s2; bk = k2; }
+      if (s3 > best) { best = s3; bk = k3; }
+      if (kk.x & 0x8000u) break;
+      e += 4;
+    }
   }
   const int pf = (int)(((float)bk + 0.5f) * inv_S);
-  best_s = bk - pf * S;
-  return mul.v[2 * ax + (neg ? 1 : 0)][pf];
+  sidx = bk - pf * S;
+  prim = L.nm[gp * 24 + pf];
+  return true;
+}
+
+// Bytes of shared memory a kernel needs for a table of n cells per axis, n_cells stored cells and n_cand candidates.
+__host__ __device__ inline size_t lut_smem_bytes(int n, int n_cells, int n_cand) {
+  return (size_t)n * n * 4 + (((size_t)n_cells * 2 + 15) & ~(size_t)15) + (((size_t)n_cand * 2 + 15) & ~(size_t)15) + 576;
+}
+// Copy head h's table into shared memory at `dst` (all threads of the CTA; the caller synchronises) and return the view.
+__device__ __forceinline__ LutView lut_to_smem(const unsigned char* __restrict__ lut, int h, unsigned char* dst,
+                                               const Mul24& nm) {
+  const uint32_t* gh = reinterpret_cast<const uint32_t*>(lut);
+  const int n = (int)gh[0], n_cells = (int)gh[1];
+  const unsigned char* head = lut + kLutOffHeads + (size_t)h * kLutHeadBytes;
+  const uint32_t total = reinterpret_cast<const uint32_t*>(head)[0];
+  uint32_t* rows = reinterpret_cast<uint32_t*>(dst);
+  uint16_t* cells = reinterpret_cast<uint16_t*>(dst + (size_t)n * n * 4);
+  uint16_t* cands = reinterpret_cast<uint16_t*>(dst + (size_t)n * n * 4 + (((size_t)n_cells * 2 + 15) & ~(size_t)15));
+  uint8_t* snm = reinterpret_cast<uint8_t*>(cands) + (((size_t)total * 2 + 15) & ~(size_t)15);
+  const uint32_t* grows = reinterpret_cast<const uint32_t*>(lut + kLutOffRows);
+  for (int i = threadIdx.x; i < n * n; i += blockDim.x) rows[i] = grows[i];
+  const uint32_t* gc = reinterpret_cast<const uint32_t*>(head + 16);
+  for (int i = threadIdx.x; i < (n_cells + 1) / 2; i += blockDim.x) reinterpret_cast<uint32_t*>(cells)[i] = gc[i];
+  const uint32_t* gd = reinterpret_cast<const uint32_t*>(head + 16 + (size_t)kLutCellCap * 2);
+  for (uint32_t i = threadIdx.x; i < (total + 1) / 2; i += blockDim.x) reinterpret_cast<uint32_t*>(cands)[i] = gd[i];
+  for (int i = threadIdx.x; i < 576; i += blockDim.x) snm[i] = nm.v[i / 24][i % 24];
+  LutView L;
+  L.rows = rows; L.cells = cells; L.cands = cands; L.nm = snm; L.n = n; L.hn = 0.5f * (float)n;
+  return L;
+}
+// The same table read in place from global memory (small calls).
+__device__ __forceinline__ LutView lut_global(const unsigned char* __restrict__ lut, int h, const uint8_t* nm) {
+  const uint32_t* gh = reinterpret_cast<const uint32_t*>(lut);
+  const unsigned char* head = lut + kLutOffHeads + (size_t)h * kLutHeadBytes;
+  LutView L;
+  L.rows = reinterpret_cast<const uint32_t*>(lut + kLutOffRows);
+  L.cells = reinterpret_cast<const uint16_t*>(head + 16);
+  L.cands = reinterpret_cast<const uint16_t*>(head + 16 + (size_t)kLutCellCap * 2);
+  L.nm = nm; L.n = (int)gh[0]; L.hn = 0.5f * (float)L.n;
+  return L;
+}
+__device__ __forceinline__ bool lut_head_valid(const unsigned char* __restrict__ lut, int h) {
+  return reinterpret_cast<const uint32_t*>(lut + kLutOffHeads + (size_t)h * kLutHeadBytes)[1] == 1u;
 }
 
 template <bool LUT>
 __global__ void __launch_bounds__(kEncThreads)
 encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
                    int t_start, uint32_t* __restrict__ hist, Maps24 maps, const float* __restrict__ joint_all,
-                   const uint32_t* __restrict__ lut, int lut_cand_smem, Mul8x24 mul) {
+                   const unsigned char* __restrict__ lut, Mul24 nmul) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float4* qs = reinterpret_cast<float4*>(smem_raw);
   uint32_t* rows = reinterpret_cast<uint32_t*>(qs + g.S);            // [warps][tpw][kMaxRowWords]
   uint32_t* shist = rows + kEncWarps * g.tpw * kMaxRowWords;          // [kHistBins]
-  float4* sjoint = reinterpret_cast<float4*>(shist + kHistBins);      // LUT: [24 S]
-  uint32_t* soff = reinterpret_cast<uint32_t*>(sjoint + 24 * g.S);     // LUT: [kLutCells + 1]
-  uint16_t* scand = reinterpret_cast<uint16_t*>(soff + kLutCells + 4); // LUT: [lut_cand_smem]
+  float4* sjoint = reinterpret_cast<float4*>(shist + kHistBins);      // LUT: [24 S], then the table of the head
 
   const int bh = blockIdx.y;
   const int h = bh % g.H, b = bh / g.H;
@@ -180,17 +269,12 @@ encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restric
   for (int i = threadIdx.x; i < g.S; i += blockDim.x) qs[i] = reinterpret_cast<const float4*>(qs_all)[(int64_t)h * g.S + i];
   if (hist) for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) shist[i] = 0;
   bool use_lut = false;
+  LutView L = {};
   if constexpr (LUT) {
-    const uint32_t* hdr = lut + (int64_t)h * kLutHdr;
-    const uint16_t* gc = reinterpret_cast<const uint16_t*>(lut + (int64_t)g.H * kLutHdr) + (int64_t)h * kLutCandCap;
-    const uint32_t total = hdr[kLutCells];
-    use_lut = hdr[kLutCells + 1] == 1u && total <= (uint32_t)lut_cand_smem;
+    use_lut = lut_head_valid(lut, h);
     if (use_lut) {
       for (int i = threadIdx.x; i < 24 * g.S; i += blockDim.x) sjoint[i] = reinterpret_cast<const float4*>(joint_all)[(int64_t)h * 24 * g.S + i];
-      for (int i = threadIdx.x; i <= kLutCells; i += blockDim.x) soff[i] = hdr[i];
-      const uint32_t* gc32 = reinterpret_cast<const uint32_t*>(gc);
-      uint32_t* sc32 = reinterpret_cast<uint32_t*>(scand);
-      for (uint32_t i = threadIdx.x; i < (total + 1) / 2; i += blockDim.x) sc32[i] = gc32[i];
+      L = lut_to_smem(lut, h, reinterpret_cast<unsigned char*>(sjoint + 24 * g.S), nmul);
     }
   }
   const float inv_S = 1.0f / (float)g.S;
@@ -235,10 +319,9 @@ encode_main_kernel(EncGeom g, const void* __restrict__ x, const float* __restric
       // normalised copy (keeps the values in range) instead of the reference's exact x / radius
       const float inv_r = __frcp_rn(radius);
       const float u0 = v[0] * inv_r, u1 = v[1] * inv_r, u2 = v[2] * inv_r, u3 = v[3] * inv_r;
-      int s, p;
-      if (LUT && use_lut) p = search_lut(sjoint, soff, scand, qs, g.S, inv_S, u0, u1, u2, u3, mul, s);
-      else p = search_exhaustive(qs, g.S, u0, u1, u2, u3, s);
-      const int au = maps.ref_to_native[p];
+      int s, au;
+      if (!(LUT && use_lut && search_fold24(sjoint, L, g.S, inv_S, u0, u1, u2, u3, au, s)))
+        au = maps.ref_to_native[search_exhaustive(qs, g.S, u0, u1, u2, u3, s)];
       const uint32_t ni = (uint32_t)((((au >> 3) * g.S + s) << 3) | (au & 7));
       const uint32_t f = ni | ((uint32_t)rqf << g.ib);
       const int bit = c * cb, w = bit >> 5, sh = bit & 31;
@@ -280,8 +363,8 @@ constexpr int kSmallTok = 512;           // tokens per head and call (kSmallMax 
 
 __global__ void __launch_bounds__(kSmallThreads)
 encode_small_kernel(EncGeom g, const void* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
-                    int t_start, Maps24 maps, const float* __restrict__ joint_all, const uint32_t* __restrict__ lut,
-                    Mul8x24 mul, float C, float* __restrict__ med_out) {
+                    int t_start, Maps24 maps, const float* __restrict__ joint_all, const unsigned char* __restrict__ lut,
+                    const uint8_t* __restrict__ nmul_dev, float C, float* __restrict__ med_out) {
   __shared__ uint32_t keys[kSmallMax];                    // norm bits of every chunk of the head
   __shared__ uint32_t tokmax[kSmallTok];                  // bits of the largest radius of a token
   __shared__ uint32_t tokflags[kSmallTok];
@@ -296,9 +379,9 @@ encode_small_kernel(EncGeom g, const void* __restrict__ x, const float* __restri
   for (int i = threadIdx.x; i < n_tok; i += blockDim.x) { tokmax[i] = 0u; tokflags[i] = 0u; }
   __syncthreads();
 
-  const uint32_t* hdr = lut ? lut + (int64_t)h * kLutHdr : nullptr;
-  const bool use_lut = hdr && hdr[kLutCells + 1] == 1u;
-  const uint16_t* cand = lut ? reinterpret_cast<const uint16_t*>(lut + (int64_t)g.H * kLutHdr) + (int64_t)h * kLutCandCap : nullptr;
+  const bool use_lut = lut && lut_head_valid(lut, h);
+  LutView L = {};
+  if (use_lut) L = lut_global(lut, h, nmul_dev);
   const float4* joint = reinterpret_cast<const float4*>(joint_all) + (int64_t)h * 24 * S;
   const float4* qs = reinterpret_cast<const float4*>(qs_all) + (int64_t)h * S;
 
@@ -319,10 +402,9 @@ encode_small_kernel(EncGeom g, const void* __restrict__ x, const float* __restri
       atomicMax(&tokmax[b * g.T_new + t], __float_as_uint(radius[k]));   // positive floats order like their bits
       const float inv_r = __frcp_rn(radius[k]);
       const float u0 = v[0] * inv_r, u1 = v[1] * inv_r, u2 = v[2] * inv_r, u3 = v[3] * inv_r;
-      int sidx, p;
-      if (use_lut) p = search_lut(joint, hdr, cand, qs, S, inv_S, u0, u1, u2, u3, mul, sidx);
-      else p = search_exhaustive(qs, S, u0, u1, u2, u3, sidx);
-      const int au = maps.ref_to_native[p];
+      int sidx, au;
+      if (!(use_lut && search_fold24(joint, L, S, inv_S, u0, u1, u2, u3, au, sidx)))
+        au = maps.ref_to_native[search_exhaustive(qs, S, u0, u1, u2, u3, sidx)];
       ni[k] = (uint32_t)((((au >> 3) * S + sidx) << 3) | (au & 7));
     }
   }
@@ -460,19 +542,11 @@ encode_small_kernel(EncGeom g, const void* __restrict__ x, const float* __restri
 // one lane per chunk, no run-time geometry in the loop.  Results are the ones encode_main_kernel gives.
 constexpr int kEnc32Threads = 1024;   // one CTA per SM (the tables fill half of shared memory): 32 warps hide the search latency
 constexpr int kEnc32Warps = kEnc32Threads / 32;
-struct NativeMul { uint8_t v[8][24]; };   // native (a << 3 | u) of (axis unit g) * (primary p)
-
-__device__ __forceinline__ float rcp_approx(float x) {
-  float y;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 template <int DT, int IB, int RB>
 __global__ void __launch_bounds__(kEnc32Threads, 1)
 encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
                      int t_start, uint32_t* __restrict__ hist, Maps24 maps, const float* __restrict__ joint_all,
-                     const uint32_t* __restrict__ lut, int lut_cand_smem, NativeMul nmul, int iters,
+                     const unsigned char* __restrict__ lut, Mul24 nmul, int iters,
                      const uint32_t* __restrict__ sel_s) {
   constexpr int CB = IB + RB;
   constexpr int RW = 32 * CB / 32;                       // words per row
@@ -482,28 +556,16 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
   uint32_t* rows = reinterpret_cast<uint32_t*>(qs + g.S);            // [warps][kMaxRowWords]
   uint32_t* shist = rows + kEnc32Warps * kMaxRowWords;                  // [kHistBins]
   uint32_t* sh1 = shist + kHistBins;                                  // [2][kHistBins]: next digit inside the predicted bins
-  float4* sjoint = reinterpret_cast<float4*>(sh1 + 2 * kHistBins);    // [24 S]
-  uint32_t* soff = reinterpret_cast<uint32_t*>(sjoint + 24 * g.S);     // [kLutCells + 1]
-  uint8_t* snm = reinterpret_cast<uint8_t*>(soff + kLutCells + 4);     // [8][24] (+ padding to 256)
-  uint16_t* scand = reinterpret_cast<uint16_t*>(snm + 256);            // [lut_cand_smem]
+  float4* sjoint = reinterpret_cast<float4*>(sh1 + 2 * kHistBins);    // [24 S], then the look-up table of the head
 
   const int bh = blockIdx.y;
   const int h = bh % g.H, b = bh / g.H;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = g.S;
-  {
-    const uint32_t* hdr = lut + (int64_t)h * kLutHdr;
-    const uint16_t* gc = reinterpret_cast<const uint16_t*>(lut + (int64_t)g.H * kLutHdr) + (int64_t)h * kLutCandCap;
-    const uint32_t total = hdr[kLutCells];
-    for (int i = threadIdx.x; i < S; i += blockDim.x) qs[i] = reinterpret_cast<const float4*>(qs_all)[(int64_t)h * S + i];
-    if (hist) for (int i = threadIdx.x; i < 3 * kHistBins; i += blockDim.x) shist[i] = 0;   // shist and sh1
-    for (int i = threadIdx.x; i < 24 * S; i += blockDim.x) sjoint[i] = reinterpret_cast<const float4*>(joint_all)[(int64_t)h * 24 * S + i];
-    for (int i = threadIdx.x; i <= kLutCells; i += blockDim.x) soff[i] = hdr[i];
-    if (threadIdx.x < 192) snm[threadIdx.x] = nmul.v[threadIdx.x / 24][threadIdx.x % 24];
-    const uint32_t* gc32 = reinterpret_cast<const uint32_t*>(gc);
-    uint32_t* sc32 = reinterpret_cast<uint32_t*>(scand);
-    for (uint32_t i = threadIdx.x; i < (total + 1) / 2; i += blockDim.x) sc32[i] = gc32[i];
-  }
+  for (int i = threadIdx.x; i < S; i += blockDim.x) qs[i] = reinterpret_cast<const float4*>(qs_all)[(int64_t)h * S + i];
+  if (hist) for (int i = threadIdx.x; i < 3 * kHistBins; i += blockDim.x) shist[i] = 0;   // shist and sh1
+  for (int i = threadIdx.x; i < 24 * S; i += blockDim.x) sjoint[i] = reinterpret_cast<const float4*>(joint_all)[(int64_t)h * 24 * S + i];
+  const LutView L = lut_to_smem(lut, h, reinterpret_cast<unsigned char*>(sjoint + 24 * S), nmul);
   const float inv_S = 1.0f / (float)S;
   // Bins (norm bits 31:21) that a sample of the call says hold the two middle order statistics: their next
   // 11-bit digit is histogrammed here too, which spares a pass over x when the sample was right.
@@ -542,56 +604,11 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
     const float inv_r = rcp_approx(radius);
     const float u0 = v[0] * inv_r, u1 = v[1] * inv_r, u2 = v[2] * inv_r, u3 = v[3] * inv_r;
     int au, sidx;
-    {
-      const float a0 = fabsf(u0), a1 = fabsf(u1), a2 = fabsf(u2), a3 = fabsf(u3);
-      int ax = 0; float am = a0;
-      if (a1 > am) { am = a1; ax = 1; }
-      if (a2 > am) { am = a2; ax = 2; }
-      if (a3 > am) { am = a3; ax = 3; }
-      float v0, v1, v2, v3;
-      if (ax == 0) { v0 = u0; v1 = u1; v2 = u2; v3 = u3; }
-      else if (ax == 1) { v0 = u1; v1 = -u0; v2 = u3; v3 = -u2; }
-      else if (ax == 2) { v0 = u2; v1 = -u3; v2 = -u0; v3 = u1; }
-      else { v0 = u3; v1 = u2; v2 = -u1; v3 = -u0; }
-      const bool neg = v0 < 0.f;
-      if (neg) { v0 = -v0; v1 = -v1; v2 = -v2; v3 = -v3; }
-      uint32_t beg = 0, end = 0;
-      if (am > 0.f) {
-        const float inv = rcp_approx(v0) * (0.5f * kLutN);
-        const int cx = min(kLutN - 1, max(0, (int)fmaf(v1, inv, 0.5f * kLutN)));
-        const int cy = min(kLutN - 1, max(0, (int)fmaf(v2, inv, 0.5f * kLutN)));
-        const int cz = min(kLutN - 1, max(0, (int)fmaf(v3, inv, 0.5f * kLutN)));
-        const int cell = (cx * kLutN + cy) * kLutN + cz;
-        beg = soff[cell]; end = soff[cell + 1];
-      }
-      if (beg == end) {
-        // zero direction (every similarity is 0, the first index wins) or a cell without a list
-        int p = 0; sidx = 0;
-        if (am > 0.f) p = search_exhaustive(qs, S, u0, u1, u2, u3, sidx);
-        au = maps.ref_to_native[p];
-      } else {
-        float best = -2.f; int bk = 0;
-        uint2 kk_n = *reinterpret_cast<const uint2*>(scand + beg);
-        for (uint32_t e = beg; e < end; e += 4) {
-          // the next four candidate ids are fetched while this step's codewords are evaluated (the read past
-          // the end of the last list stays inside the padded array and is never used)
-          const uint2 kk = kk_n;
-          kk_n = *reinterpret_cast<const uint2*>(scand + e + 4);
-          const int k0 = kk.x & 0xffff, k1 = kk.x >> 16, k2 = kk.y & 0xffff, k3 = kk.y >> 16;
-          const float4 c0 = sjoint[k0], c1 = sjoint[k1], c2 = sjoint[k2], c3 = sjoint[k3];
-          const float s0 = fmaf(v3, c0.w, fmaf(v2, c0.z, fmaf(v1, c0.y, v0 * c0.x)));
-          const float s1 = fmaf(v3, c1.w, fmaf(v2, c1.z, fmaf(v1, c1.y, v0 * c1.x)));
-          const float s2 = fmaf(v3, c2.w, fmaf(v2, c2.z, fmaf(v1, c2.y, v0 * c2.x)));
-          const float s3 = fmaf(v3, c3.w, fmaf(v2, c3.z, fmaf(v1, c3.y, v0 * c3.x)));
-          if (s0 > best) { best = s0; bk = k0; }
-          if (s1 > best) { best = s1; bk = k1; }
-          if (s2 > best) { best = s2; bk = k2; }
-          if (s3 > best) { best = s3; bk = k3; }
-        }
-        const int pf = (int)(((float)bk + 0.5f) * inv_S);
-        sidx = bk - pf * S;
-        au = snm[(2 * ax + (neg ? 1 : 0)) * 24 + pf];
-      }
+    if (!search_fold24(sjoint, L, S, inv_S, u0, u1, u2, u3, au, sidx)) {
+      // zero direction (every similarity is 0, the first index wins) or a cell without a list
+      int p = 0; sidx = 0;
+      if (fmaxf(fmaxf(fabsf(u0), fabsf(u1)), fmaxf(fabsf(u2), fabsf(u3))) > 0.f) p = search_exhaustive(qs, S, u0, u1, u2, u3, sidx);
+      au = maps.ref_to_native[p];
     }
     const uint32_t ni = (uint32_t)((((au >> 3) * S + sidx) << 3) | (au & 7));
     const uint32_t f = ni | ((uint32_t)rqf << IB);
@@ -1295,134 +1312,187 @@ side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start,
 }
 
 // ---- look-up table construction ---------------------------------------------------------------------
-// One CTA per (cell, head).  tmp: [H][kLutCells][kLutMaxList] uint16 candidate lists, cnt: [H][kLutCells].
+// Geometry (the same for every head): per (cx, cy) column the stored cz range = the cells whose grown box meets
+// the octahedron |w1| + |w2| + |w3| <= 1, and the index of the column's first cell.
+__device__ __forceinline__ float min_abs_over(float lo, float hi) { return (lo <= 0.f && hi >= 0.f) ? 0.f : fminf(fabsf(lo), fabsf(hi)); }
+__global__ void __launch_bounds__(1024) lut_rows_kernel(int n, uint32_t* __restrict__ ghdr, uint32_t* __restrict__ rows) {
+  __shared__ uint32_t s_cnt[kLutRows], s_min[kLutRows];
+  const float step = 2.0f / (float)n;
+  for (int col = threadIdx.x; col < n * n; col += blockDim.x) {
+    const int cx = col / n, cy = col - cx * n;
+    const float m1 = min_abs_over(cx * step - 1.f - kLutBoxEps, (cx + 1) * step - 1.f + kLutBoxEps);
+    const float m2 = min_abs_over(cy * step - 1.f - kLutBoxEps, (cy + 1) * step - 1.f + kLutBoxEps);
+    const float lim = 1.f + kLutBoxEps - m1 - m2;
+    int zmin = n, zmax = -1;
+    for (int cz = 0; cz < n; ++cz) {
+      const float m3 = min_abs_over(cz * step - 1.f - kLutBoxEps, (cz + 1) * step - 1.f + kLutBoxEps);
+      if (m3 <= lim) { zmin = min(zmin, cz); zmax = max(zmax, cz); }
+    }
+    s_cnt[col] = zmax >= zmin ? (uint32_t)(zmax - zmin + 1) : 0u;
+    s_min[col] = zmax >= zmin ? (uint32_t)zmin : 0u;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t run = 0;
+    for (int col = 0; col < n * n; ++col) {
+      rows[col] = run | (s_min[col] << 20) | (s_cnt[col] << 26);
+      run += s_cnt[col];
+    }
+    ghdr[0] = (uint32_t)n; ghdr[1] = run; ghdr[2] = ghdr[3] = 0u;
+  }
+}
+
+// One CTA per ((cx, cy) column, head), walking the column's stored cells.  tmp: [H][kLutCellCap][kLutMaxList] uint16
+// candidate lists (ascending), cnt: [H][kLutCellCap] list lengths (0 = too long: exhaustive search in that cell).
 __global__ void __launch_bounds__(128)
-lut_cells_kernel(const float* __restrict__ joint_all, int S, uint16_t* __restrict__ tmp, uint32_t* __restrict__ cnt) {
+lut_cells_kernel(const float* __restrict__ joint_all, int S, int n, const uint32_t* __restrict__ rows,
+                 uint16_t* __restrict__ tmp, uint32_t* __restrict__ cnt) {
   __shared__ float s_best[4];
   __shared__ int s_bk[4];
   __shared__ int s_n;
   __shared__ uint16_t s_list[kLutMaxList];
-  const int cell = blockIdx.x, h = blockIdx.y, K = 24 * S;
-  const float4* joint = reinterpret_cast<const float4*>(joint_all) + (int64_t)h * K;
-  const int cz = cell % kLutN, cy = (cell / kLutN) % kLutN, cx = cell / (kLutN * kLutN);
-  const float step = 2.0f / kLutN;
-  const float w1 = (cx + 0.5f) * step - 1.f, w2 = (cy + 0.5f) * step - 1.f, w3 = (cz + 0.5f) * step - 1.f;
-  const float hh = 0.5f * step + kLutBoxEps;
-  // winner at the centre of the cell
-  float best = -1e30f; int bk = 0;
-  for (int k = threadIdx.x; k < K; k += blockDim.x) {
-    const float4 c = joint[k];
-    const float sim = c.x + w1 * c.y + w2 * c.z + w3 * c.w;
-    if (sim > best) { best = sim; bk = k; }
-  }
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-    const int ok = __shfl_xor_sync(0xffffffffu, bk, o);
-    if (ob > best || (ob == best && ok < bk)) { best = ob; bk = ok; }
-  }
-  if ((threadIdx.x & 31) == 0) { s_best[threadIdx.x >> 5] = best; s_bk[threadIdx.x >> 5] = bk; }
-  if (threadIdx.x == 0) s_n = 0;
-  __syncthreads();
-  best = s_best[0]; bk = s_bk[0];
-  for (int i = 1; i < 4; ++i)
-    if (s_best[i] > best || (s_best[i] == best && s_bk[i] < bk)) { best = s_best[i]; bk = s_bk[i]; }
-  const float4 cs = joint[bk];
-  // every codeword that is not beaten by the centre's winner over the whole (grown) box
-  for (int k = threadIdx.x; k < K; k += blockDim.x) {
-    const float4 c = joint[k];
-    const float d0 = c.x - cs.x, d1 = c.y - cs.y, d2 = c.z - cs.z, d3 = c.w - cs.w;
-    const float ub = d0 + d1 * w1 + d2 * w2 + d3 * w3 + hh * (fabsf(d1) + fabsf(d2) + fabsf(d3));
-    if (ub >= -kLutMargin) {
-      const int pos = atomicAdd(&s_n, 1);
-      if (pos < kLutMaxList) s_list[pos] = (uint16_t)k;
-    }
-  }
-  __syncthreads();
   __shared__ float4 s_cw[kLutMaxList];
   __shared__ unsigned char s_drop[kLutMaxList];
-  int n = s_n;
-  if (n > kLutMaxList) n = 0;         // too long: this cell falls back to the exhaustive search
-  if (threadIdx.x == 0) {
-    for (int i = 1; i < n; ++i) {     // ascending order makes the table reproducible
-      const uint16_t v = s_list[i];
-      int q = i - 1;
-      while (q >= 0 && s_list[q] > v) { s_list[q + 1] = s_list[q]; --q; }
-      s_list[q + 1] = v;
+  const int col = blockIdx.x, h = blockIdx.y, K = 24 * S;
+  const float4* joint = reinterpret_cast<const float4*>(joint_all) + (int64_t)h * K;
+  const uint32_t row = rows[col];
+  const int zcnt = (int)(row >> 26), zmin = (int)((row >> 20) & 63u), base = (int)(row & 0xfffffu);
+  const int cx = col / n, cy = col - cx * n;
+  const float step = 2.0f / (float)n;
+  const float w1 = (cx + 0.5f) * step - 1.f, w2 = (cy + 0.5f) * step - 1.f;
+  const float hh = 0.5f * step + kLutBoxEps;
+  for (int zc = 0; zc < zcnt; ++zc) {
+    const int cell = base + zc;
+    const float w3 = (zmin + zc + 0.5f) * step - 1.f;
+    // winner at the centre of the cell
+    float best = -1e30f; int bk = 0;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+      const float4 c = joint[k];
+      const float sim = c.x + w1 * c.y + w2 * c.z + w3 * c.w;
+      if (sim > best) { best = sim; bk = k; }
     }
-  }
-  __syncthreads();
-  if (threadIdx.x < n) s_cw[threadIdx.x] = joint[s_list[threadIdx.x]];
-  __syncthreads();
-  // second filter: drop a codeword that loses to some OTHER listed codeword over the whole box
-  if (threadIdx.x < n) {
-    const float4 ci = s_cw[threadIdx.x];
-    bool drop = false;
-    for (int q = 0; q < n && !drop; ++q) {
-      if (q == threadIdx.x) continue;
-      const float4 cq = s_cw[q];
-      const float d0 = ci.x - cq.x, d1 = ci.y - cq.y, d2 = ci.z - cq.z, d3 = ci.w - cq.w;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int ok = __shfl_xor_sync(0xffffffffu, bk, o);
+      if (ob > best || (ob == best && ok < bk)) { best = ob; bk = ok; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_best[threadIdx.x >> 5] = best; s_bk[threadIdx.x >> 5] = bk; }
+    if (threadIdx.x == 0) s_n = 0;
+    __syncthreads();
+    best = s_best[0]; bk = s_bk[0];
+    for (int i = 1; i < 4; ++i)
+      if (s_best[i] > best || (s_best[i] == best && s_bk[i] < bk)) { best = s_best[i]; bk = s_bk[i]; }
+    const float4 cs = joint[bk];
+    // every codeword that is not beaten by the centre's winner over the whole (grown) box
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+      const float4 c = joint[k];
+      const float d0 = c.x - cs.x, d1 = c.y - cs.y, d2 = c.z - cs.z, d3 = c.w - cs.w;
       const float ub = d0 + d1 * w1 + d2 * w2 + d3 * w3 + hh * (fabsf(d1) + fabsf(d2) + fabsf(d3));
-      drop = ub < -kLutMargin;
+      if (ub >= -kLutMargin) {
+        const int pos = atomicAdd(&s_n, 1);
+        if (pos < kLutMaxList) s_list[pos] = (uint16_t)k;
+      }
     }
-    s_drop[threadIdx.x] = drop ? 1 : 0;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint16_t* dst = tmp + ((int64_t)h * kLutCells + cell) * kLutMaxList;
-    int m = 0;
-    for (int i = 0; i < n; ++i)
-      if (!s_drop[i]) dst[m++] = s_list[i];
-    while (m & 3) { dst[m] = dst[m - 1]; ++m; }   // pad to a multiple of four (n <= 64 keeps m <= 64)
-    cnt[(int64_t)h * kLutCells + cell] = (uint32_t)m;
+    __syncthreads();
+    int m = s_n;
+    if (m > kLutMaxList) m = 0;         // too long: this cell falls back to the exhaustive search
+    if (threadIdx.x == 0) {
+      for (int i = 1; i < m; ++i) {     // ascending order makes the table reproducible
+        const uint16_t v = s_list[i];
+        int q = i - 1;
+        while (q >= 0 && s_list[q] > v) { s_list[q + 1] = s_list[q]; --q; }
+        s_list[q + 1] = v;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < m) s_cw[threadIdx.x] = joint[s_list[threadIdx.x]];
+    __syncthreads();
+    // second filter: drop a codeword that loses to some OTHER listed codeword over the whole box
+    if (threadIdx.x < m) {
+      const float4 ci = s_cw[threadIdx.x];
+      bool drop = false;
+      for (int q = 0; q < m && !drop; ++q) {
+        if (q == threadIdx.x) continue;
+        const float4 cq = s_cw[q];
+        const float d0 = ci.x - cq.x, d1 = ci.y - cq.y, d2 = ci.z - cq.z, d3 = ci.w - cq.w;
+        const float ub = d0 + d1 * w1 + d2 * w2 + d3 * w3 + hh * (fabsf(d1) + fabsf(d2) + fabsf(d3));
+        drop = ub < -kLutMargin;
+      }
+      s_drop[threadIdx.x] = drop ? 1 : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint16_t* dst = tmp + ((int64_t)h * kLutCellCap + cell) * kLutMaxList;
+      int q = 0;
+      for (int i = 0; i < m; ++i)
+        if (!s_drop[i]) dst[q++] = s_list[i];
+      cnt[(int64_t)h * kLutCellCap + cell] = (uint32_t)q;
+    }
+    __syncthreads();
   }
 }
 
-// Per head: exclusive scan of the list lengths -> offsets; valid flag = the lists fit the capacity.
-__global__ void __launch_bounds__(1024) lut_scan_kernel(const uint32_t* __restrict__ cnt, uint32_t* __restrict__ lut) {
+// Per head: cell words and the padded candidate lists.  A list of one needs no entry; longer ones are padded to a
+// multiple of four with their last codeword, and the first entry of a list's last group carries bit 15.
+__global__ void __launch_bounds__(1024)
+lut_pack_kernel(const uint16_t* __restrict__ tmp, const uint32_t* __restrict__ cnt, unsigned char* __restrict__ lut, int S) {
   __shared__ uint32_t s_sum[1024];
   const int h = blockIdx.x;
-  constexpr int PER = kLutCells / 1024;
-  uint32_t loc[PER], tot = 0;
-  for (int i = 0; i < PER; ++i) { loc[i] = cnt[(int64_t)h * kLutCells + threadIdx.x * PER + i]; tot += loc[i]; }
+  const uint32_t* gh = reinterpret_cast<const uint32_t*>(lut);
+  const int n_cells = (int)gh[1];
+  unsigned char* head = lut + kLutOffHeads + (size_t)h * kLutHeadBytes;
+  uint16_t* cells = reinterpret_cast<uint16_t*>(head + 16);
+  uint16_t* cands = reinterpret_cast<uint16_t*>(head + 16 + (size_t)kLutCellCap * 2);
+  const int per = (n_cells + 1023) / 1024;
+  const int c0 = threadIdx.x * per, c1 = min(n_cells, c0 + per);
+  uint32_t tot = 0;
+  for (int c = c0; c < c1; ++c) {
+    const uint32_t m = cnt[(int64_t)h * kLutCellCap + c];
+    tot += m > 1 ? (m + 3u) & ~3u : 0u;
+  }
   s_sum[threadIdx.x] = tot;
   __syncthreads();
   for (int o = 1; o < 1024; o <<= 1) {
-    uint32_t v = threadIdx.x >= o ? s_sum[threadIdx.x - o] : 0;
+    const uint32_t v = threadIdx.x >= o ? s_sum[threadIdx.x - o] : 0;
     __syncthreads();
     s_sum[threadIdx.x] += v;
     __syncthreads();
   }
+  const uint32_t total = s_sum[1023];
+  const bool valid = total <= (uint32_t)kLutCandCap && n_cells <= kLutCellCap && 24 * S < 32768;
+  if (threadIdx.x == 0) {
+    uint32_t* hh = reinterpret_cast<uint32_t*>(head);
+    hh[0] = valid ? total : 0u; hh[1] = valid ? 1u : 0u; hh[2] = hh[3] = 0u;
+  }
+  if (!valid) return;
   uint32_t run = s_sum[threadIdx.x] - tot;
-  uint32_t* hdr = lut + (int64_t)h * kLutHdr;
-  for (int i = 0; i < PER; ++i) { hdr[threadIdx.x * PER + i] = run; run += loc[i]; }
-  if (threadIdx.x == 1023) {
-    hdr[kLutCells] = run;
-    hdr[kLutCells + 1] = run <= (uint32_t)kLutCandCap ? 1u : 0u;
+  for (int c = c0; c < c1; ++c) {
+    const uint32_t m = cnt[(int64_t)h * kLutCellCap + c];
+    const uint16_t* src = tmp + ((int64_t)h * kLutCellCap + c) * kLutMaxList;
+    if (m == 0) cells[c] = 0xffffu;
+    else if (m == 1) cells[c] = (uint16_t)(0x8000u | src[0]);
+    else {
+      const uint32_t pm = (m + 3u) & ~3u;
+      cells[c] = (uint16_t)(run >> 2);
+      for (uint32_t i = 0; i < pm; ++i) {
+        uint16_t v = src[i < m ? i : m - 1];
+        if (i == pm - 4) v |= 0x8000u;
+        cands[run + i] = v;
+      }
+      run += pm;
+    }
   }
 }
 
-__global__ void lut_fill_kernel(const uint16_t* __restrict__ tmp, const uint32_t* __restrict__ cnt, uint32_t* __restrict__ lut,
-                                int H) {
-  const int h = blockIdx.y;
-  const int cell = blockIdx.x * blockDim.x + threadIdx.x;
-  if (cell >= kLutCells) return;
-  const uint32_t* hdr = lut + (int64_t)h * kLutHdr;
-  if (hdr[kLutCells + 1] != 1u) return;
-  uint16_t* cand = reinterpret_cast<uint16_t*>(lut + (int64_t)H * kLutHdr) + (int64_t)h * kLutCandCap;
-  const uint32_t n = cnt[(int64_t)h * kLutCells + cell], o = hdr[cell];
-  const uint16_t* src = tmp + ((int64_t)h * kLutCells + cell) * kLutMaxList;
-  for (uint32_t i = 0; i < n; ++i) cand[o + i] = src[i];
-}
-
-Mul8x24 make_mul() {
-  // (axis unit g) * (primary p) in the reference's index order, from exact arithmetic on doubles
+// (unit g) * (primary p) for all 24 units, as the native primary code (a << 3) | u of the product
+Mul24 make_mul24_native() {
   auto prim = [](int p, double v[4]) {
     for (int i = 0; i < 4; ++i) v[i] = 0;
     if (p < 8) v[p >> 1] = (p & 1) ? -1.0 : 1.0;
     else for (int i = 0; i < 4; ++i) v[i] = (((p - 8) >> (3 - i)) & 1) ? -0.5 : 0.5;
   };
-  Mul8x24 m;
-  for (int g = 0; g < 8; ++g)
+  Mul24 m;
+  for (int g = 0; g < 24; ++g)
     for (int p = 0; p < 24; ++p) {
       double a[4], b[4], c[4];
       prim(g, a); prim(p, b);
@@ -1430,20 +1500,27 @@ Mul8x24 make_mul() {
       c[1] = a[0] * b[1] + a[1] * b[0] + a[2] * b[3] - a[3] * b[2];
       c[2] = a[0] * b[2] - a[1] * b[3] + a[2] * b[0] + a[3] * b[1];
       c[3] = a[0] * b[3] + a[1] * b[2] - a[2] * b[1] + a[3] * b[0];
-      m.v[g][p] = 0;
+      int ref = 0;
       for (int q = 0; q < 24; ++q) {
         double e[4];
         prim(q, e);
         double dd = 0;
         for (int i = 0; i < 4; ++i) dd += (e[i] - c[i]) * (e[i] - c[i]);
-        if (dd < 1e-12) m.v[g][p] = (uint8_t)q;
+        if (dd < 1e-12) ref = q;
       }
+      m.v[g][p] = index_maps().ref_to_native[ref];
     }
   return m;
 }
+const Mul24& mul24_native() {
+  static const Mul24 m = make_mul24_native();
+  return m;
+}
 
-inline size_t lut_bytes(int H) { return (size_t)H * kLutHdr * 4 + (size_t)H * kLutCandCap * 2; }
-inline size_t lut_ws_bytes(int H) { return (size_t)H * kLutCells * 4 + (size_t)H * kLutCells * kLutMaxList * 2; }
+inline size_t lut_bytes(int H) { return kLutOffHeads + (size_t)H * kLutHeadBytes + 576; }   // (+ the index table for small calls)
+inline size_t lut_ws_bytes(int H) { return (size_t)H * kLutCellCap * 4 + (size_t)H * kLutCellCap * kLutMaxList * 2; }
+// shared memory a main-pass kernel can give to a table next to its other arrays (fp32 joint table, histograms, rows)
+inline size_t lut_smem_budget(int S) { return (size_t)226 * 1024 - (size_t)24 * S * 16 - (size_t)S * 16 - 3 * kHistBins * 4 - 4096; }
 
 struct WsPlan { size_t status, hist, sel, band, und, hist_s, sel_s, hist_fb, total; int blk0, nblk; };
 WsPlan plan_ws(const hqmq_encode_args& a) {
@@ -1495,6 +1572,23 @@ extern "C" size_t hqmq_encode_lut_workspace_bytes(int H, int S) {
   if (H < 1 || S < 1 || 24 * S > 65536) return 0;
   return lut_ws_bytes(H);
 }
+// Largest per-head candidate total of a built table, its grid, and whether every head is valid (synchronises).
+static int lut_read(const void* lut, int H, cudaStream_t st, int& n, int& n_cells, int& max_total, bool& valid) {
+  uint32_t gh[4];
+  HQMQ_CHECK_CUDA(cudaMemcpyAsync(gh, lut, 16, cudaMemcpyDeviceToHost, st));
+  HQMQ_CHECK_CUDA(cudaStreamSynchronize(st));
+  n = (int)gh[0]; n_cells = (int)gh[1];
+  max_total = 0; valid = n >= 2 && n <= kLutNMax && n_cells <= kLutCellCap;
+  for (int h = 0; h < H && valid; ++h) {
+    uint32_t v[2];
+    HQMQ_CHECK_CUDA(cudaMemcpyAsync(v, reinterpret_cast<const unsigned char*>(lut) + kLutOffHeads + (size_t)h * kLutHeadBytes, 8,
+                                    cudaMemcpyDeviceToHost, st));
+    HQMQ_CHECK_CUDA(cudaStreamSynchronize(st));
+    if (v[1] != 1u) valid = false;
+    if ((int)v[0] > max_total) max_total = (int)v[0];
+  }
+  return HQMQ_OK;
+}
 extern "C" int hqmq_encode_lut_build(const float* joint, int H, int S, void* lut, size_t lut_nbytes, void* workspace,
                                      size_t ws_nbytes, void* stream) {
   if (!joint || !lut || !workspace) return HQMQ_ERR_ARG;
@@ -1502,26 +1596,33 @@ extern "C" int hqmq_encode_lut_build(const float* joint, int H, int S, void* lut
   if (lut_nbytes < lut_bytes(H) || ws_nbytes < lut_ws_bytes(H)) return HQMQ_ERR_WORKSPACE;
   if (((uintptr_t)joint & 15) || ((uintptr_t)lut & 15) || ((uintptr_t)workspace & 15)) return HQMQ_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
+  unsigned char* L = reinterpret_cast<unsigned char*>(lut);
   uint32_t* cnt = reinterpret_cast<uint32_t*>(workspace);
-  uint16_t* tmp = reinterpret_cast<uint16_t*>(cnt + (size_t)H * kLutCells);
-  lut_cells_kernel<<<dim3(kLutCells, H), 128, 0, st>>>(joint, S, tmp, cnt);
-  lut_scan_kernel<<<H, 1024, 0, st>>>(cnt, reinterpret_cast<uint32_t*>(lut));
-  lut_fill_kernel<<<dim3(kLutCells / 256, H), 256, 0, st>>>(tmp, cnt, reinterpret_cast<uint32_t*>(lut), H);
-  HQMQ_LAUNCH_CHECK();
+  uint16_t* tmp = reinterpret_cast<uint16_t*>(cnt + (size_t)H * kLutCellCap);
+  // the index table of the fold units, for the kernels that read the table in place
+  HQMQ_CHECK_CUDA(cudaMemcpyAsync(L + kLutOffHeads + (size_t)H * kLutHeadBytes, &mul24_native(), 576, cudaMemcpyHostToDevice, st));
+  // the finest grid whose tables fit the encoder's shared memory next to this codebook
+  for (int n = kLutNMax; n >= 16; n -= 4) {
+    lut_rows_kernel<<<1, 1024, 0, st>>>(n, reinterpret_cast<uint32_t*>(L), reinterpret_cast<uint32_t*>(L + kLutOffRows));
+    lut_cells_kernel<<<dim3(n * n, H), 128, 0, st>>>(joint, S, n, reinterpret_cast<const uint32_t*>(L + kLutOffRows), tmp, cnt);
+    lut_pack_kernel<<<H, 1024, 0, st>>>(tmp, cnt, L, S);
+    HQMQ_LAUNCH_CHECK();
+    int nn, n_cells, max_total; bool valid;
+    const int rc = lut_read(lut, H, st, nn, n_cells, max_total, valid);
+    if (rc) return rc;
+    if (valid && lut_smem_bytes(nn, n_cells, max_total) <= lut_smem_budget(S)) return HQMQ_OK;
+    if (24 * S >= 32768) break;          // codeword ids need 15 bits: no table for this codebook
+  }
+  // no grid fits: mark every head invalid (the encoder then searches exhaustively)
+  for (int h = 0; h < H; ++h) HQMQ_CHECK_CUDA(cudaMemsetAsync(L + kLutOffHeads + (size_t)h * kLutHeadBytes, 0, 16, st));
   return HQMQ_OK;
 }
-extern "C" int hqmq_encode_lut_max_candidates(const void* lut, int H, int* max_cand, void* stream) {
-  if (!lut || !max_cand || H < 1) return HQMQ_ERR_ARG;
-  int best = 0;
-  for (int h = 0; h < H; ++h) {
-    uint32_t v[2];
-    HQMQ_CHECK_CUDA(cudaMemcpyAsync(v, reinterpret_cast<const uint32_t*>(lut) + (size_t)h * kLutHdr + kLutCells, 8,
-                                    cudaMemcpyDeviceToHost, (cudaStream_t)stream));
-    HQMQ_CHECK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    if (v[1] != 1u) { *max_cand = -1; return HQMQ_OK; }
-    if ((int)v[0] > best) best = (int)v[0];
-  }
-  *max_cand = best;
+extern "C" int hqmq_encode_lut_footprint(const void* lut, int H, int* footprint, void* stream) {
+  if (!lut || !footprint || H < 1) return HQMQ_ERR_ARG;
+  int n, n_cells, max_total; bool valid;
+  const int rc = lut_read(lut, H, (cudaStream_t)stream, n, n_cells, max_total, valid);
+  if (rc) return rc;
+  *footprint = valid ? (int)lut_smem_bytes(n, n_cells, max_total) : -1;
   return HQMQ_OK;
 }
 
@@ -1620,12 +1721,13 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   // Small calls (decode-time appends): one kernel per head does main pass, median and flags at once.
   const bool ext_med = med && a->med_in != nullptr;   // the median comes from the caller (batch of a head split over GPUs)
   if (!ext_med && (int64_t)d.B * a->T_new * g.n <= kSmallMax && (int64_t)d.B * a->T_new <= kSmallTok) {
-    static const Mul8x24 mul_s = make_mul();
-    const bool lut_ok = a->search == 0 && a->lut != nullptr && a->lut_max_cand >= 0;
+    const bool lut_ok = a->search == 0 && a->lut != nullptr && a->lut_footprint >= 0;
     if (lut_ok && ((uintptr_t)a->lut & 15)) return HQMQ_ERR_ALIGN;
+    const unsigned char* lut_b = reinterpret_cast<const unsigned char*>(a->lut);
     HQMQ_CHECK_CUDA(cudaMemsetAsync(ws, 0, 16, st));      // the status word
     encode_small_kernel<<<d.H, kSmallThreads, 0, st>>>(g, a->x, a->qs, d, a->t_start, maps, a->joint,
-                                                        lut_ok ? reinterpret_cast<const uint32_t*>(a->lut) : nullptr, mul_s,
+                                                        lut_ok ? lut_b : nullptr,
+                                                        lut_ok ? lut_b + kLutOffHeads + (size_t)d.H * kLutHeadBytes : nullptr,
                                                         a->median_mult, a->med_out);
     if (med || d.ofrag)
       scan_kernel<<<d.B * d.H, kScanWarps * 32, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, med ? 1 : 0, ws + wp.status);
@@ -1640,16 +1742,18 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   const size_t smem_base = (size_t)g.S * 16 + (size_t)kEncWarps * g.tpw * kMaxRowWords * 4 + kHistBins * 4;
   if (smem_base > 200 * 1024) return HQMQ_ERR_UNSUPPORTED;
   // look-up-table search when a table is given and it fits shared memory next to the joint codebook
-  int cand_smem = a->lut_max_cand > 0 ? a->lut_max_cand : kLutCandCap;
-  cand_smem = (cand_smem + 7) & ~7;
-  const size_t smem_lut = smem_base + (size_t)24 * g.S * 16 + (size_t)(kLutCells + 4) * 4 + (size_t)cand_smem * 2;
-  const bool use_lut = a->search == 0 && a->lut != nullptr && a->lut_max_cand >= 0 && smem_lut <= 220 * 1024;
+  // (lut_footprint: shared-memory bytes of the largest head's table, from hqmq_encode_lut_footprint; 0 = unknown:
+  //  assume the largest a table can be)
+  const size_t lut_foot = a->lut_footprint > 0 ? ((size_t)a->lut_footprint + 15) & ~(size_t)15
+                                                : lut_smem_bytes(kLutNMax, kLutCellCap, kLutCandCap);
+  const size_t smem_lut = smem_base + (size_t)24 * g.S * 16 + lut_foot;
+  const bool use_lut = a->search == 0 && a->lut != nullptr && a->lut_footprint >= 0 && smem_lut <= 226 * 1024;
   // fast passes: d_head 128, 16-bit input, token rows on 16-byte boundaries (the fused last pass lists
   // undecided chunks by a 32-bit index over the (batch, token, chunk) grid of a head)
   const bool fast32 = g.n == 32 && is_half_dtype(a->x_dtype) && ((uintptr_t)a->x & 15) == 0 && g.xs_b % 8 == 0 &&
                       g.xs_h % 8 == 0 && g.xs_t % 8 == 0 && (int64_t)d.B * a->T_new * 32 < ((int64_t)1 << 32);
   Fast32 f32{reinterpret_cast<const uint16_t*>(a->x), g.xs_b, g.xs_h, g.xs_t, d.H, a->T_new};
-  static const Mul8x24 mul = make_mul();
+  const Mul24& nmul = mul24_native();
   if (use_lut && (uintptr_t)a->lut & 15) return HQMQ_ERR_ALIGN;
   // specialised kernel: d_head 128, 16-bit input, one of the compiled field layouts
   const void* fastk = nullptr;
@@ -1663,15 +1767,8 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
 #undef HQMQ_PICK
   }
   if (fastk) {
-    static const NativeMul nmul = [] {
-      NativeMul m;
-      const Mul8x24 mm = make_mul();
-      for (int gi = 0; gi < 8; ++gi)
-        for (int pi = 0; pi < 24; ++pi) m.v[gi][pi] = index_maps().ref_to_native[mm.v[gi][pi]];
-      return m;
-    }();
-    const size_t smem_fast = (size_t)g.S * 16 + (size_t)kEnc32Warps * kMaxRowWords * 4 + kHistBins * 4 + (size_t)24 * g.S * 16 +
-                             (size_t)(kLutCells + 4) * 4 + 256 + (size_t)cand_smem * 2 + 16 + (size_t)2 * kHistBins * 4;
+    const size_t smem_fast = (size_t)g.S * 16 + (size_t)kEnc32Warps * kMaxRowWords * 4 + 3 * kHistBins * 4 + (size_t)24 * g.S * 16 +
+                             lut_foot + 16;
     // tokens per CTA: long enough to amortise loading the tables, short enough to fill the machine twice
     int iters = (int)(((int64_t)a->T_new * d.B * d.H + (int64_t)2 * 148 * kEnc32Warps - 1) / ((int64_t)2 * 148 * kEnc32Warps));
     if (iters < 1) iters = 1;
@@ -1695,22 +1792,21 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     const uint32_t* sel_s_arg = predicted ? ws + wp.sel_s : nullptr;
     const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a->x);
     uint32_t* hist_arg = med && !ext_med ? ws + wp.hist : nullptr;
-    const uint32_t* lut_arg = reinterpret_cast<const uint32_t*>(a->lut);
+    const unsigned char* lut_arg = reinterpret_cast<const unsigned char*>(a->lut);
     int t_start_arg = a->t_start;
     void* kargs[] = {(void*)&g, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&hist_arg, (void*)&maps,
-                     (void*)&a->joint, (void*)&lut_arg, (void*)&cand_smem, (void*)&nmul, (void*)&iters, (void*)&sel_s_arg};
+                     (void*)&a->joint, (void*)&lut_arg, (void*)&nmul, (void*)&iters, (void*)&sel_s_arg};
     HQMQ_CHECK_CUDA(cudaLaunchKernel(fastk, fgrid, dim3(kEnc32Threads), kargs, smem_fast, st));
   } else if (use_lut) {
     if (smem_lut > 48 * 1024)
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(encode_main_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_lut));
     encode_main_kernel<true><<<grid, kEncThreads, smem_lut, st>>>(g, a->x, a->qs, d, a->t_start, med && !ext_med ? ws + wp.hist : nullptr,
-                                                                  maps, a->joint, reinterpret_cast<const uint32_t*>(a->lut),
-                                                                  cand_smem, mul);
+                                                                  maps, a->joint, reinterpret_cast<const unsigned char*>(a->lut), nmul);
   } else {
     if (smem_base > 48 * 1024)
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(encode_main_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_base));
     encode_main_kernel<false><<<grid, kEncThreads, smem_base, st>>>(g, a->x, a->qs, d, a->t_start, med && !ext_med ? ws + wp.hist : nullptr,
-                                                                    maps, a->joint, nullptr, 0, mul);
+                                                                    maps, a->joint, nullptr, nmul);
   }
   HQMQ_LAUNCH_CHECK();
   if (!med) {

@@ -169,9 +169,9 @@ class HQMQQuantizer(KVQuantizer):
                 with torch.cuda.device(device):
                     _lib.check(L.hqmq_encode_lut_build(t["joint"].data_ptr(), H, S, lut.data_ptr(), lut.numel(),
                                                        ws.data_ptr(), ws.numel(), _lib.stream_ptr()), "hqmq_encode_lut_build")
-                    _lib.check(L.hqmq_encode_lut_max_candidates(lut.data_ptr(), H, C.byref(mc), _lib.stream_ptr()),
-                               "hqmq_encode_lut_max_candidates")
-                t["lut"], t["lut_max_cand"] = lut, mc.value
+                    _lib.check(L.hqmq_encode_lut_footprint(lut.data_ptr(), H, C.byref(mc), _lib.stream_ptr()),
+                               "hqmq_encode_lut_footprint")
+                t["lut"], t["lut_footprint"] = lut, mc.value
             self._tables[key] = t
         return t
 
@@ -217,7 +217,7 @@ class HQMQQuantizer(KVQuantizer):
             if med_in.dtype != torch.float32 or med_in.numel() != H or med_in.device != x.device or not med_in.is_contiguous():
                 raise ValueError("med_in must be a contiguous (H,) fp32 tensor on the device of x")
             a.med_in = med_in.data_ptr()
-        a.lut, a.lut_max_cand = tb["lut"].data_ptr(), tb["lut_max_cand"]
+        a.lut, a.lut_footprint = tb["lut"].data_ptr(), tb["lut_footprint"]
         a._keep = (x, tb, out, med_out, med_in)     # the struct holds raw addresses: keep their owners alive with it
         return a
 

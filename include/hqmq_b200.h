@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define HQMQ_ABI_VERSION 3
+#define HQMQ_ABI_VERSION 4
 
 /* error codes */
 #define HQMQ_OK 0
@@ -162,18 +162,21 @@ int hqmq_codebook_tables(const float* joint, int H, int S, uint16_t* table16, vo
 
 /* ---- encode --------------------------------------------------------------------------- */
 /*
- * Nearest-codeword look-up table of one joint codebook (H heads): a 16^3 grid over directions folded
- * by the 8 axis units, each cell listing every codeword that can win somewhere in the cell.  It turns
- * the reference's exhaustive argmax over 24*S similarities (src/quantizers/hqmq.py:158,164) into a
- * handful of dot products per chunk with the same result.  Build once per (layer, K|V) codebook.
- * hqmq_encode_lut_max_candidates synchronises the stream and returns the longest per-head candidate
- * array (-1 if some head's lists exceed the table capacity: the encoder then searches exhaustively).
+ * Nearest-codeword look-up table of one joint codebook (H heads).  A direction is folded by its nearest Hurwitz
+ * unit (the codebook is invariant under the 24 units), which leaves an octahedron of folded directions; a grid over
+ * it names, per cell, every codeword that can win somewhere in the cell -- a single one for almost half of the
+ * cells, two on average.  It turns the reference's exhaustive argmax over 24*S similarities
+ * (src/quantizers/hqmq.py:158,164) into zero to four dot products per chunk with the same result.  Build once per
+ * (layer, K|V) codebook.  hqmq_encode_lut_build picks the finest grid whose tables fit the encoder's shared memory
+ * next to the codebook and synchronises the stream to do so.  hqmq_encode_lut_footprint synchronises the stream and
+ * returns the shared-memory bytes of the largest head's table (-1 if the codebook got no table: the encoder then
+ * searches exhaustively); pass it on in hqmq_encode_args.lut_footprint.
  */
 size_t hqmq_encode_lut_bytes(int H, int S);
 size_t hqmq_encode_lut_workspace_bytes(int H, int S);
 int hqmq_encode_lut_build(const float* joint, int H, int S, void* lut, size_t lut_bytes, void* workspace,
                           size_t workspace_bytes, void* stream);
-int hqmq_encode_lut_max_candidates(const void* lut, int H, int* max_cand, void* stream);
+int hqmq_encode_lut_footprint(const void* lut, int H, int* footprint, void* stream);
 
 typedef struct hqmq_encode_args {
   uint32_t struct_size;
@@ -189,7 +192,7 @@ typedef struct hqmq_encode_args {
   hqmq_packed dst;          /* destination planes */
   float* med_out;           /* optional (H,) fp32: the per-head median of this call */
   const void* lut;          /* optional nearest-codeword table of this codebook (hqmq_encode_lut_build) */
-  int32_t lut_max_cand;     /* hqmq_encode_lut_max_candidates() of `lut` (0 = unknown, assume the capacity) */
+  int32_t lut_footprint;    /* hqmq_encode_lut_footprint() of `lut` (0 = unknown, assume the capacity) */
   int32_t reserved;
   const float* med_in;      /* optional (H,) fp32, device: per-head medians to use instead of this call's own; for a
                                head whose batch entries are spread over several GPUs (hqmq_med3x_hist / _select) */
@@ -232,7 +235,8 @@ int hqmq_med3x_select(int H, int level, uint64_t n_total, float median_mult, voi
  *                                   flags and counts are complete, payload entries beyond the
  *                                   capacity were dropped
  *   workspace of hqmq_attn_decode:  non-zero = some call on this workspace gave up on a bounded wait
- *                                   for a staged copy; that call's output rows are NaN
+ *                                   for a staged copy; the output rows of that call are not valid (NaN where
+ *                                   a merge still ran, untouched elsewhere)
  * No counterpart in the reference (its kernels have no device-side status).
  */
 int hqmq_read_status(const void* workspace, uint32_t* status, void* stream);

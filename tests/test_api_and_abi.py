@@ -105,7 +105,7 @@ def test_library_exports_every_declared_symbol(built_lib):
 
 def test_abi_host_helpers(built_lib):
     L = _lib.lib()
-    assert L.hqmq_abi_version() == _lib.ABI_VERSION == 3
+    assert L.hqmq_abi_version() == _lib.ABI_VERSION == 4
     assert L.hqmq_strerror(0) == b"ok" and b"workspace" in L.hqmq_strerror(-5)
     for n, S, b in [(32, 24, 3), (32, 96, 4), (32, 192, 6), (16, 96, 4), (12, 24, 3), (4, 24, 3)]:
         assert L.hqmq_row_bytes(n, S, b) == packed.row_bytes(n, S, b)

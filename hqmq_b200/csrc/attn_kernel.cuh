@@ -221,7 +221,7 @@ struct FastLoader {
       // two fields per word: both radii come out of one subtraction
       const uint32_t word = w[a];
       idx = FOLD ? (word >> (s + 1)) & ((1u << (IB - 1)) - 1u) : (word >> s) & ((1u << IB) - 1u);
-      uint32_t bits = ((word >> IB) & 0x000f000fu) | 0x64006400u;
+      uint32_t bits = ((word >> IB) & (((1u << RB) - 1u) * 0x10001u)) | 0x64006400u;
       const __half2 pair = __hsub2(*reinterpret_cast<__half2*>(&bits), __float2half2_rn(1024.f));
       uint32_t pu = *reinterpret_cast<const uint32_t*>(&pair);
       // sign bits of both fields (bits 0 and 16 of the word) into the sign bits of the two halves

@@ -145,6 +145,10 @@ def lib():
     L.hqmq_attn_workspace_bytes.argtypes = [C.POINTER(AttnArgs)]
     L.hqmq_attn_decode.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     L.hqmq_attn_decode_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+    L.hqmq_encode_pair_workspace_bytes.argtypes = [C.POINTER(EncodeArgs), C.POINTER(EncodeArgs)]
+    L.hqmq_encode_pair_workspace_bytes.restype = C.c_size_t
+    L.hqmq_encode_pair.argtypes = [C.POINTER(EncodeArgs), C.POINTER(EncodeArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    L.hqmq_encode_pair.restype = C.c_int
     L.hqmq_attn_static_status.argtypes = [C.POINTER(C.c_uint32), C.c_void_p]
     L.hqmq_exchange_recv_bytes.restype = C.c_size_t
     L.hqmq_exchange_recv_bytes.argtypes = [C.c_int, C.c_int64]
@@ -222,6 +226,15 @@ def read_status(workspace: torch.Tensor) -> int:
     with torch.cuda.device(workspace.device):
         check(lib().hqmq_read_status(workspace.data_ptr(), C.byref(st), stream_ptr()), "hqmq_read_status")
     return int(st.value)
+
+
+def static_status(device) -> int:
+    """Give-up word of the last ``hqmq_attn_decode_static`` call on ``device`` (0: every output row is valid), read
+    after synchronising the current stream (see hqmq_attn_static_status)."""
+    st = C.c_uint32(0)
+    with device_guard(torch.device(device)):
+        check(lib().hqmq_attn_static_status(C.byref(st), stream_ptr()), "hqmq_attn_static_status")
+    return st.value
 
 
 def ref_packed(idx: torch.Tensor, rq: torch.Tensor, rs: torch.Tensor) -> RefPacked:

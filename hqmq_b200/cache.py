@@ -63,8 +63,7 @@ class PackedKVCache:
         pair = self._layers.get(layer_idx)
         if pair is None:
             pair = self._layers[layer_idx] = self._new_pair(key_states)
-        self.quantizer.encode(key_states, layer_idx, 0, out=pair[0])
-        self.quantizer.encode(value_states, layer_idx, 1, out=pair[1])
+        self.quantizer.encode_pair(key_states, value_states, layer_idx, pair[0], pair[1])
         return pair
 
     def check(self) -> None:

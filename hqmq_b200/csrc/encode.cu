@@ -361,10 +361,11 @@ constexpr int kSmallMax = 2048;          // chunks per head and call
 constexpr int kSmallThreads = 1024;
 constexpr int kSmallTok = 512;           // tokens per head and call (kSmallMax / 4 chunks)
 
-__global__ void __launch_bounds__(kSmallThreads)
-encode_small_kernel(EncGeom g, const void* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
-                    int t_start, Maps24 maps, const float* __restrict__ joint_all, const unsigned char* __restrict__ lut,
-                    const uint8_t* __restrict__ nmul_dev, float C, float* __restrict__ med_out) {
+// (the body is shared by the kernel of one tensor and by the kernel that appends K and V of a layer in one launch)
+__device__ __forceinline__ void
+encode_small_body(const EncGeom& g, const void* __restrict__ x, const float* __restrict__ qs_all, const hqmq_packed& dst,
+                  int t_start, const Maps24& maps, const float* __restrict__ joint_all, const unsigned char* __restrict__ lut,
+                  const uint8_t* __restrict__ nmul_dev, float C, float* __restrict__ med_out) {
   __shared__ uint32_t keys[kSmallMax];                    // norm bits of every chunk of the head
   __shared__ uint32_t tokmax[kSmallTok];                  // bits of the largest radius of a token
   __shared__ uint32_t tokflags[kSmallTok];
@@ -535,6 +536,34 @@ encode_small_kernel(EncGeom g, const void* __restrict__ x, const float* __restri
     store_scale(dst, row, fmaxf(__uint_as_float(tokmax[tok]), 1e-8f));
     if (dst.flags) dst.flags[row] = tokflags[tok];
   }
+}
+
+// Everything one tensor of a small call needs; two of them make the K + V append of a layer.
+struct SmallArgs {
+  EncGeom g;
+  const void* x;
+  const float* qs;
+  hqmq_packed dst;
+  int t_start;
+  const float* joint;
+  const unsigned char* lut;
+  const uint8_t* nmul;
+  float C;
+  float* med_out;
+  uint32_t* status;     // first word of the tensor's workspace: cleared here, set by scan_kernel on an overflow
+  int blk0, nblk, scan, payload, side;
+};
+struct SmallPair { SmallArgs t[2]; Maps24 maps; };
+
+__global__ void __launch_bounds__(kSmallThreads) encode_small_kernel(SmallArgs a, Maps24 maps) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) *a.status = 0u;
+  encode_small_body(a.g, a.x, a.qs, a.dst, a.t_start, maps, a.joint, a.lut, a.nmul, a.C, a.med_out);
+}
+// grid (H, 2): blockIdx.y = 0 the K tensor, 1 the V tensor (same batch, heads, tokens and head dim)
+__global__ void __launch_bounds__(kSmallThreads) encode_small_pair_kernel(SmallPair p) {
+  const SmallArgs& a = p.t[blockIdx.y];
+  if (blockIdx.x == 0 && threadIdx.x == 0) *a.status = 0u;
+  encode_small_body(a.g, a.x, a.qs, a.dst, a.t_start, p.maps, a.joint, a.lut, a.nmul, a.C, a.med_out);
 }
 
 // ---- main pass for the common geometry ------------------------------------------------------------------
@@ -1099,8 +1128,8 @@ __device__ __forceinline__ int ofrag_records_for(uint32_t any_c) {
 // whose inclusive total exceeds the capacity).  `payload` = 0 on a call without Med3x (nothing flagged).
 constexpr int kScanWarps = 8;
 constexpr int kScanIters = 16;     // blocks per lane: up to 8 * 32 * 16 = 4096 blocks (64 k tokens) in one sweep
-__global__ void __launch_bounds__(kScanWarps * 32)
-scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk, int payload, uint32_t* __restrict__ status) {
+__device__ __forceinline__ void
+scan_body(const hqmq_packed& dst, int t_start, int T_new, int blk0, int nblk, int payload, uint32_t* __restrict__ status) {
   __shared__ uint32_t w_tot[kScanWarps], w_ftot[kScanWarps], s_last_ok[kScanWarps];
   const int bh = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1198,11 +1227,22 @@ scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk, int pay
   }
 }
 
+__global__ void __launch_bounds__(kScanWarps * 32)
+scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk, int payload, uint32_t* __restrict__ status) {
+  scan_body(dst, t_start, T_new, blk0, nblk, payload, status);
+}
+// grid (B * H, 2): blockIdx.y selects the tensor of a K + V append; a tensor that needs no scan returns at once
+__global__ void __launch_bounds__(kScanWarps * 32) scan_pair_kernel(SmallPair p) {
+  const SmallArgs& a = p.t[blockIdx.y];
+  if (!a.scan) return;
+  scan_body(a.dst, a.t_start, a.g.T_new, a.blk0, a.nblk, a.payload, a.status);
+}
+
 // Side planes of one 16-token block, one warp per block: the payload (original values of every flagged chunk,
 // in (token, chunk) order) and, for a block that owns fragment records, the records (layout in
 // include/hqmq_b200.h).  Lane l < 16 holds the flag word of token l of the block.
-__global__ void __launch_bounds__(256)
-side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, int blk0, int nblk) {
+__device__ __forceinline__ void
+side_body(const EncGeom& g, const void* __restrict__ x, const hqmq_packed& dst, int t_start, int blk0, int nblk) {
   const int bh = blockIdx.y;
   const int h = bh % g.H, b = bh / g.H;
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -1309,6 +1349,17 @@ side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start,
     if (lane == 0) *reinterpret_cast<uint4*>(recp) = make_uint4(hdr, 0u, 0u, 0u);
     *reinterpret_cast<uint4*>(recp + 16 + lane * 16) = make_uint4(a[0], a[1], a[2], a[3]);
   }
+}
+
+__global__ void __launch_bounds__(256)
+side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, int blk0, int nblk) {
+  side_body(g, x, dst, t_start, blk0, nblk);
+}
+// grid (blocks / 8, B * H, 2): blockIdx.z selects the tensor of a K + V append
+__global__ void __launch_bounds__(256) side_pair_kernel(SmallPair p) {
+  const SmallArgs& a = p.t[blockIdx.z];
+  if (!a.side) return;
+  side_body(a.g, a.x, a.dst, a.t_start, a.blk0, a.nblk);
 }
 
 // ---- look-up table construction ---------------------------------------------------------------------
@@ -1695,6 +1746,81 @@ extern "C" size_t hqmq_encode_workspace_bytes(const hqmq_encode_args* a) {
   return plan_ws(*a).total;
 }
 
+static EncGeom geom_of(const hqmq_encode_args* a) {
+  const hqmq_packed& d = a->dst;
+  EncGeom g;
+  g.B = d.B; g.H = d.H; g.T_new = a->T_new; g.n = d.n_chunks;
+  g.npl = 1; while (g.npl < g.n) g.npl <<= 1;
+  g.tpw = 32 / g.npl;
+  g.S = d.S; g.ib = idx_bits_for(d.S); g.rbits = d.radius_bits; g.qmax = (1 << d.radius_bits) - 1;
+  g.x_dtype = a->x_dtype;
+  g.xs_b = a->x_stride[0]; g.xs_h = a->x_stride[1]; g.xs_t = a->x_stride[2];
+  return g;
+}
+
+// Small calls (decode-time appends): one kernel per head does main pass, median and flags at once.
+static bool small_call(const hqmq_encode_args* a) {
+  const bool ext_med = a->median_mult > 0.f && a->med_in != nullptr;   // the median comes from the caller
+  const int64_t tok = (int64_t)a->dst.B * a->T_new;
+  return !ext_med && tok * a->dst.n_chunks <= kSmallMax && tok <= kSmallTok;
+}
+
+static int fill_small(const hqmq_encode_args* a, const WsPlan& wp, uint32_t* ws, SmallArgs& sa) {
+  const hqmq_packed& d = a->dst;
+  const bool med = a->median_mult > 0.f;
+  const bool lut_ok = a->search == 0 && a->lut != nullptr && a->lut_footprint >= 0;
+  if (lut_ok && ((uintptr_t)a->lut & 15)) return HQMQ_ERR_ALIGN;
+  const unsigned char* lut_b = reinterpret_cast<const unsigned char*>(a->lut);
+  sa.g = geom_of(a);
+  sa.x = a->x; sa.qs = a->qs; sa.dst = d; sa.t_start = a->t_start; sa.joint = a->joint;
+  sa.lut = lut_ok ? lut_b : nullptr;
+  sa.nmul = lut_ok ? lut_b + kLutOffHeads + (size_t)d.H * kLutHeadBytes : nullptr;
+  sa.C = a->median_mult; sa.med_out = a->med_out;
+  sa.status = ws + wp.status;
+  sa.blk0 = wp.blk0; sa.nblk = wp.nblk;
+  sa.scan = (med || d.ofrag) ? 1 : 0; sa.payload = med ? 1 : 0; sa.side = med ? 1 : 0;
+  return HQMQ_OK;
+}
+
+extern "C" size_t hqmq_encode_pair_workspace_bytes(const hqmq_encode_args* k, const hqmq_encode_args* v) {
+  const size_t wk = hqmq_encode_workspace_bytes(k), wv = hqmq_encode_workspace_bytes(v);
+  if (!wk || !wv) return 0;
+  return ((wk + 255) & ~(size_t)255) + wv;
+}
+
+extern "C" int hqmq_encode_pair(const hqmq_encode_args* k, const hqmq_encode_args* v, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  int rc = validate_encode(k);
+  if (rc) return rc;
+  rc = validate_encode(v);
+  if (rc) return rc;
+  const size_t wk = (plan_ws(*k).total + 255) & ~(size_t)255, wv = plan_ws(*v).total;
+  if (!workspace || workspace_bytes < wk + wv) return HQMQ_ERR_WORKSPACE;
+  if ((uintptr_t)workspace & 15) return HQMQ_ERR_ALIGN;
+  unsigned char* wsb = reinterpret_cast<unsigned char*>(workspace);
+  const hqmq_packed &dk = k->dst, &dv = v->dst;
+  const bool same = dk.B == dv.B && dk.H == dv.H && dk.n_chunks == dv.n_chunks && k->T_new == v->T_new;
+  if (!same || k->T_new == 0 || !small_call(k) || !small_call(v)) {
+    // no common launch shape: one tensor after the other, each with its part of the workspace
+    rc = hqmq_encode(k, wsb, wk, stream);
+    if (rc) return rc;
+    return hqmq_encode(v, wsb + wk, wv, stream);
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  SmallPair pr;
+  rc = fill_small(k, plan_ws(*k), reinterpret_cast<uint32_t*>(wsb), pr.t[0]);
+  if (rc) return rc;
+  rc = fill_small(v, plan_ws(*v), reinterpret_cast<uint32_t*>(wsb + wk), pr.t[1]);
+  if (rc) return rc;
+  memcpy(pr.maps.ref_to_native, index_maps().ref_to_native, 24);
+  encode_small_pair_kernel<<<dim3(dk.H, 2), kSmallThreads, 0, st>>>(pr);
+  const int nblk = pr.t[0].nblk > pr.t[1].nblk ? pr.t[0].nblk : pr.t[1].nblk;
+  if (pr.t[0].scan || pr.t[1].scan) scan_pair_kernel<<<dim3(dk.B * dk.H, 2), kScanWarps * 32, 0, st>>>(pr);
+  if (pr.t[0].side || pr.t[1].side) side_pair_kernel<<<dim3((nblk + 7) / 8, dk.B * dk.H, 2), 256, 0, st>>>(pr);
+  HQMQ_LAUNCH_CHECK();
+  return HQMQ_OK;
+}
+
 extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t workspace_bytes, void* stream) {
   int rc = validate_encode(a);
   if (rc) return rc;
@@ -1705,33 +1831,20 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   cudaStream_t st = (cudaStream_t)stream;
   const hqmq_packed& d = a->dst;
   const bool med = a->median_mult > 0.f;
-
-  EncGeom g;
-  g.B = d.B; g.H = d.H; g.T_new = a->T_new; g.n = d.n_chunks;
-  g.npl = 1; while (g.npl < g.n) g.npl <<= 1;
-  g.tpw = 32 / g.npl;
-  g.S = d.S; g.ib = idx_bits_for(d.S); g.rbits = d.radius_bits; g.qmax = (1 << d.radius_bits) - 1;
-  g.x_dtype = a->x_dtype;
-  g.xs_b = a->x_stride[0]; g.xs_h = a->x_stride[1]; g.xs_t = a->x_stride[2];
+  const EncGeom g = geom_of(a);
 
   uint32_t* ws = reinterpret_cast<uint32_t*>(workspace);
   Maps24 maps;
   memcpy(maps.ref_to_native, index_maps().ref_to_native, 24);
 
-  // Small calls (decode-time appends): one kernel per head does main pass, median and flags at once.
   const bool ext_med = med && a->med_in != nullptr;   // the median comes from the caller (batch of a head split over GPUs)
-  if (!ext_med && (int64_t)d.B * a->T_new * g.n <= kSmallMax && (int64_t)d.B * a->T_new <= kSmallTok) {
-    const bool lut_ok = a->search == 0 && a->lut != nullptr && a->lut_footprint >= 0;
-    if (lut_ok && ((uintptr_t)a->lut & 15)) return HQMQ_ERR_ALIGN;
-    const unsigned char* lut_b = reinterpret_cast<const unsigned char*>(a->lut);
-    HQMQ_CHECK_CUDA(cudaMemsetAsync(ws, 0, 16, st));      // the status word
-    encode_small_kernel<<<d.H, kSmallThreads, 0, st>>>(g, a->x, a->qs, d, a->t_start, maps, a->joint,
-                                                        lut_ok ? lut_b : nullptr,
-                                                        lut_ok ? lut_b + kLutOffHeads + (size_t)d.H * kLutHeadBytes : nullptr,
-                                                        a->median_mult, a->med_out);
-    if (med || d.ofrag)
-      scan_kernel<<<d.B * d.H, kScanWarps * 32, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, med ? 1 : 0, ws + wp.status);
-    if (med) side_kernel<<<dim3((wp.nblk + 7) / 8, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, wp.blk0, wp.nblk);
+  if (small_call(a)) {
+    SmallArgs sa;
+    rc = fill_small(a, wp, ws, sa);
+    if (rc) return rc;
+    encode_small_kernel<<<d.H, kSmallThreads, 0, st>>>(sa, maps);      // (clears the status word itself)
+    if (sa.scan) scan_kernel<<<d.B * d.H, kScanWarps * 32, 0, st>>>(d, a->t_start, a->T_new, wp.blk0, wp.nblk, sa.payload, ws + wp.status);
+    if (sa.side) side_kernel<<<dim3((wp.nblk + 7) / 8, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, wp.blk0, wp.nblk);
     HQMQ_LAUNCH_CHECK();
     return HQMQ_OK;
   }

@@ -14,7 +14,7 @@ import ctypes as C
 import math
 from abc import ABC, abstractmethod
 from itertools import product
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -291,6 +291,49 @@ class HQMQQuantizer(KVQuantizer):
         out.T += T
         return out
 
+    def encode_pair(self, k: torch.Tensor, v: torch.Tensor, layer_idx: int, out_k: PackedKV, out_v: PackedKV,
+                    median_mult: Optional[float] = None) -> Tuple[PackedKV, PackedKV]:
+        """Append the keys and the values of one layer (the reference cache quantises both on every update,
+        src/model_utils.py:29-32).  Same result as ``encode(k, layer_idx, 0, out=out_k)`` followed by
+        ``encode(v, layer_idx, 1, out=out_v)``; a decode-time append (a few tokens per sequence) runs both tensors
+        in the same launches (hqmq_encode_pair), which halves the launches per layer."""
+        small = (k.dim() == 4 and k.shape == v.shape and k.dtype == v.dtype and k.shape[2] <= 64 and k.is_cuda and v.is_cuda
+                 and k.stride(-1) == 1 and v.stride(-1) == 1 and not any(s % 4 for s in k.stride()[:3] + v.stride()[:3]))
+        if not small or k.shape[2] == 0:
+            return (self.encode(k, layer_idx, 0, out=out_k, median_mult=median_mult),
+                    self.encode(v, layer_idx, 1, out=out_v, median_mult=median_mult))
+        T = k.shape[2]
+        key = ("pair", id(self), id(out_v), layer_idx, tuple(k.shape), k.dtype, k.stride(), v.stride(), median_mult)
+        hit = out_k._enc_cache.get(key)
+        if hit is None:
+            why = self._unsupported()
+            if why:
+                raise NotImplementedError(f"hqmq_b200 accelerates the unit-magnitude linear-radius path only ({why})")
+            _lib.check_device(k.device)
+            if k.shape[1] != self.n_heads:
+                raise ValueError(f"x has {k.shape[1]} heads, quantizer has {self.n_heads}")
+            for x, out in ((k, out_k), (v, out_v)):
+                self._check_dst(x, out)
+                if median_mult is not None and not out.with_outliers:
+                    raise ValueError("destination cache was created without outlier planes")
+            ak = self._enc_args(k, layer_idx, 0, out_k, median_mult)
+            av = self._enc_args(v, layer_idx, 1, out_v, median_mult)
+            with _lib.device_guard(k.device):
+                nbytes = _lib.lib().hqmq_encode_pair_workspace_bytes(C.byref(ak), C.byref(av))
+            ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=k.device)
+            ak._keep, av._keep = (ak._keep[1], out_k), (av._keep[1], out_v)     # tables and planes, not this call's inputs
+            hit = out_k._enc_cache[key] = (ak, av, ws, nbytes)
+        ak, av, ws, nbytes = hit
+        if out_k.T + T > out_k.T_cap or out_v.T + T > out_v.T_cap:
+            raise _lib.HqmqError(f"hqmq_b200: cache capacity {out_k.T_cap} exceeded ({out_k.T} + {T})")
+        ak.x, ak.t_start, av.x, av.t_start = k.data_ptr(), out_k.T, v.data_ptr(), out_v.T
+        with _lib.device_guard(k.device):
+            _lib.check(_lib.lib().hqmq_encode_pair(C.byref(ak), C.byref(av), ws.data_ptr(), nbytes, _lib.stream_ptr()),
+                       "hqmq_encode_pair")
+        out_k.T += T
+        out_v.T += T
+        return out_k, out_v
+
     def decode(self, packed: PackedKV, layer_idx: int, kv: int, dtype: torch.dtype = torch.float32,
                t0: int = 0, T: Optional[int] = None, scale_first: bool = False,
                merge_outliers: bool = True) -> torch.Tensor:
@@ -460,6 +503,19 @@ class OutlierAwareHQMQQuantizer(KVQuantizer):
         if total:
             self._stats.end(pk, total)
         return pk
+
+    def encode_pair(self, k, v, layer_idx, out_k: PackedKV, out_v: PackedKV):
+        """Keys and values of one layer in one call (see ``HQMQQuantizer.encode_pair``), each with its own median."""
+        self._check_mode()
+        total = k.shape[0] * k.shape[1] * k.shape[2] * (k.shape[3] // 4)
+        if total:
+            self._stats.begin(out_k, total)
+            self._stats.begin(out_v, total)
+        pair = self.inner.encode_pair(k, v, layer_idx, out_k, out_v, median_mult=self.median_mult)
+        if total:
+            self._stats.end(out_k, total)
+            self._stats.end(out_v, total)
+        return pair
 
     def decode(self, packed, layer_idx, kv, **kw):
         return self.inner.decode(packed, layer_idx, kv, **kw)

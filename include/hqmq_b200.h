@@ -209,6 +209,19 @@ size_t hqmq_encode_workspace_bytes(const hqmq_encode_args* args);
 int hqmq_encode(const hqmq_encode_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The K and the V tensor of one layer in one call: the reference cache quantises both on every update
+ * (src/model_utils.py:29-32, QuantizedCache.update).  Same results as hqmq_encode(k) followed by
+ * hqmq_encode(v); each tensor keeps its own median, tables and planes.  For the decode-time append (a small
+ * call, the same batch / heads / new tokens / head dim for both tensors) the two share every launch, which
+ * halves the launches per layer; other shapes run one tensor after the other.  The workspace holds K's part
+ * first and V's part at the next multiple of 256 bytes; the first word of each part is that tensor's status
+ * word (hqmq_read_status on workspace, and on workspace + round_up(hqmq_encode_workspace_bytes(k), 256)).
+ */
+size_t hqmq_encode_pair_workspace_bytes(const hqmq_encode_args* k, const hqmq_encode_args* v);
+int hqmq_encode_pair(const hqmq_encode_args* k, const hqmq_encode_args* v, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+/*
  * Med3x median of heads whose batch entries live on SEVERAL GPUs.  The reference takes the median over every
  * batch entry of a head in one call (src/quantizers/outlier_aware.py:63-72); when the batch of a head is
  * partitioned across GPUs, the same number comes from a three-level radix select whose histograms are summed

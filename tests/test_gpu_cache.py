@@ -116,3 +116,51 @@ def test_padded_head_dim_matches_the_oracle():
     want = orc.fake_quant(xp, joint, br, None, enc=enc)[..., :d]
     near_tie = (enc["gap"] < 1e-6).unsqueeze(-1).expand(B, Hkv, T, 12, 4).reshape(B, Hkv, T, 48)[..., :d]
     assert torch.equal(got[~near_tie], want[~near_tie])
+
+
+def test_update_with_another_geometry_than_the_cache_is_refused():
+    """The library takes batch, heads and chunks per token from the destination planes, so a call whose x has
+    another batch (sequences that finished), head count or head dim must fail before anything is launched."""
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, 2, 24, 3, device="cuda"), 3.0)
+    dst = q.inner.new_cache(4, 64, 32, "cuda", with_outliers=True)
+    x = torch.randn(4, 2, 8, 32, device="cuda")
+    q.encode(x, 0, 0, out=dst)
+    assert dst.T == 8
+    for bad in (torch.randn(3, 2, 8, 32, device="cuda"),       # smaller batch
+                torch.randn(4, 2, 8, 64, device="cuda"),       # other head dim
+                torch.randn(4, 1, 8, 32, device="cuda")):      # other head count
+        with pytest.raises((ValueError, hqmq.HqmqError)):
+            q.encode(bad, 0, 0, out=dst)
+    assert dst.T == 8
+    other = hqmq.HQMQ(1, 2, 96, 4, device="cuda")
+    with pytest.raises(ValueError):
+        other.encode(x, 0, 0, out=dst)                          # another codebook than the planes were made for
+
+
+@pytest.mark.parametrize("outliers", [True, False])
+def test_pair_append_equals_two_single_appends(outliers):
+    """K and V of a layer appended in shared launches (hqmq_encode_pair) leave every plane byte-identical to one
+    tensor appended after the other, for a prompt (large call: run one after the other inside the library), then
+    one and three tokens at a time, across a block boundary."""
+    B, H, d, S, br = 3, 2, 64, 96, 4
+    inner = hqmq.HQMQ(1, H, S, br, device="cuda")
+    q = hqmq.with_outlier_extraction(inner, 3.0) if outliers else inner
+    mk = lambda kv: inner.new_cache(B, 128, d, "cuda", scale_dtype=torch.bfloat16, with_outliers=outliers,
+                                    out_dtype=torch.bfloat16, ofrag=outliers and kv == 0)
+    pair, single = (mk(0), mk(1)), (mk(0), mk(1))
+    g = torch.Generator().manual_seed(11)
+    for step, T in enumerate([40, 1, 1, 3, 1, 5, 1]):
+        k = torch.randn(B, H, T, d, generator=g)
+        k[:, :, :, 7] *= 9.0
+        v = torch.randn(B, H, T, d, generator=g)
+        k, v = k.bfloat16().cuda(), v.bfloat16().cuda()
+        q.encode_pair(k, v, 0, pair[0], pair[1])
+        q.encode(k, 0, 0, out=single[0])
+        q.encode(v, 0, 1, out=single[1])
+    torch.cuda.synchronize()
+    for a, b in zip(pair, single):
+        assert a.T == b.T == 52
+        names = ["codes", "rs"] + (["flags", "out_vals", "out_off", "out_count"] if outliers else [])
+        names += ["ofrag", "ofrag_off"] if a.with_ofrag else []
+        for name in names:
+            assert torch.equal(getattr(a, name), getattr(b, name)), name

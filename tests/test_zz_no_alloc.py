@@ -40,6 +40,8 @@ def test_static_scratch_matches_workspace_entry_point(outliers):
         err = (out - ref).abs().max().item()
         rel = ((out - ref).norm() / ref.norm()).item()
         assert err < MAX_ABS and rel < REL_L2, f"call {call}: max-abs {err:.2e}, rel-L2 {rel:.2e}"
+        # the give-up word of the built-in buffer is readable without its address, and says "all rows valid"
+        assert _lib.static_status(Q.device) == 0
     # a different shape afterwards reuses the same buffer with other contents in it
     Q2, K2, V2, tk2, tv2 = _case(1, 8, 2, 333, 64, 24, 3, seed=4, outliers=outliers)
     ref2 = torch.empty(Q2.shape, dtype=torch.float32, device="cuda")

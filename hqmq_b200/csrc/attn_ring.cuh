@@ -26,7 +26,6 @@ namespace attn {
 constexpr int kRingWarps = 15;                 // consumer warps (with the producer: 512 threads, 128 registers each)
 constexpr int kRingTiles = kRingWarps;         // tiles per stage: one per consumer warp
 constexpr int kRingTok = kRingTiles * kTile;   // tokens per stage
-constexpr int kRingPay = 126;                  // payload entries staged per stage and tensor (+2 alignment slack)
 constexpr int kRingRec = 16;                   // fragment records staged per stage
 constexpr int kRingThreads = (kRingWarps + 1) * 32;
 constexpr int kRingConsumerThreads = kRingWarps * 32;
@@ -44,9 +43,12 @@ struct RingLayout {
   static constexpr int kStageHdr = kFlV + kRingTok * 4;          // 32 bytes: what the producer staged
   static constexpr int kTileHdr = kStageHdr + 32;                // kRingTiles x 32 bytes: the tiles' side ranges
   static constexpr int kPayV = kTileHdr + kRingTiles * 32;
-  static constexpr int kSideK = kPayV + (kRingPay + 2) * 8;      // K payload slice, or the stage's fragment records
-  static constexpr int kSideKBytes = kRingRec * HQMQ_OFRAG_BYTES > (kRingPay + 2) * 8 ? kRingRec * HQMQ_OFRAG_BYTES
-                                                                                    : (kRingPay + 2) * 8;
+  // payload entries staged per stage and tensor (+2 alignment slack): d_head 64 has room for a stage whose every token
+  // owns a flagged chunk (one outlier channel per head: 240 entries)
+  static constexpr int kPay = N == 16 ? 254 : 126;
+  static constexpr int kSideK = kPayV + (kPay + 2) * 8;      // K payload slice, or the stage's fragment records
+  static constexpr int kSideKBytes = kRingRec * HQMQ_OFRAG_BYTES > (kPay + 2) * 8 ? kRingRec * HQMQ_OFRAG_BYTES
+                                                                                    : (kPay + 2) * 8;
   static constexpr int BYTES = OUTL ? kSideK + kSideKBytes : kPlainEnd;
   static_assert((kRingTok * ROW) % 16 == 0 && (kRingTok * 2) % 16 == 0 && BYTES % 16 == 0, "stage pieces must be multiples of 16 bytes");
 };
@@ -248,14 +250,14 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
           // (entries at or beyond out_cap were dropped by the encoder: nothing of them is copied, they read as 0)
           if (flk && stageK) {
             ak = k0s & ~1u;
-            nK = k1s - ak; if (nK > (uint32_t)kRingPay + 1u) nK = kRingPay + 1;
+            nK = k1s - ak; if (nK > (uint32_t)RL::kPay + 1u) nK = RL::kPay + 1;
             const uint32_t room = ak < (uint32_t)p.K.out_cap ? (uint32_t)p.K.out_cap - ak : 0u;
             if (nK > room) nK = room;
             nK = (nK + 1u) & ~1u;
           }
           if (flv && stageV) {
             av = v0s & ~1u;
-            nV = v1s - av; if (nV > (uint32_t)kRingPay + 1u) nV = kRingPay + 1;
+            nV = v1s - av; if (nV > (uint32_t)RL::kPay + 1u) nV = RL::kPay + 1;
             const uint32_t room = av < (uint32_t)p.V.out_cap ? (uint32_t)p.V.out_cap - av : 0u;
             if (nV > room) nV = room;
             nV = (nV + 1u) & ~1u;

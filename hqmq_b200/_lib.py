@@ -64,7 +64,7 @@ class EncodeArgs(C.Structure):
         ("struct_size", C.c_uint32), ("x_dtype", C.c_int32), ("x", C.c_void_p), ("x_stride", C.c_int64 * 3),
         ("T_new", C.c_int32), ("t_start", C.c_int32), ("qs", C.c_void_p), ("joint", C.c_void_p),
         ("median_mult", C.c_float), ("search", C.c_int32), ("dst", Packed), ("med_out", C.c_void_p),
-        ("lut", C.c_void_p), ("lut_footprint", C.c_int32), ("reserved", C.c_int32), ("med_in", C.c_void_p),
+        ("lut", C.c_void_p), ("lut_footprint", C.c_int32), ("quantile", C.c_float), ("med_in", C.c_void_p),
     ]
 
 

@@ -143,6 +143,27 @@ __device__ __forceinline__ float rcp_approx(float x) {
   return y;
 }
 
+// The order statistics torch.quantile(flat, q) interpolates between and its weight, with torch's own arithmetic
+// (ATen quantile_compute: rank = fl32(fl32(q) * fl32(N - 1)), below = trunc, above = ceil, weight = rank - below;
+// lerp with one fused multiply-add, a + w * (b - a) for w < 0.5, else b - (b - a) * (1 - w)).  q <= 0 names the
+// median of Med3x with exact integer ranks: (N - 1) / 2 and N / 2, weight 0.5 for an even count.
+struct QRank { uint64_t lo, hi; float w; };
+__host__ __device__ inline QRank quantile_rank(uint64_t N, float q) {
+  QRank r;
+  if (!(q > 0.f)) { r.lo = (N - 1) / 2; r.hi = N / 2; r.w = (N & 1) ? 0.f : 0.5f; return r; }
+  volatile float last = (float)(N - 1);
+  volatile float rf = q * last;
+  const float rfl = rf;
+  r.lo = (uint64_t)rfl;
+  r.hi = (uint64_t)ceilf(rfl);
+  r.w = rfl - (float)r.lo;
+  return r;
+}
+__device__ __forceinline__ float quantile_lerp(float a, float b, float w) {
+  const float diff = __fsub_rn(b, a);
+  return w < 0.5f ? __fmaf_rn(w, diff, a) : __fmaf_rn(-diff, __fsub_rn(1.f, w), b);
+}
+
 // Nearest codeword of the direction u through the table: writes nm[g][p'] and the secondary index, returns
 // false when the chunk has to take the exhaustive search (zero direction, a cell without a list).
 __device__ __forceinline__ bool search_fold24(const float4* __restrict__ joint, const LutView& L, int S, float inv_S,
@@ -365,7 +386,7 @@ constexpr int kSmallTok = 512;           // tokens per head and call (kSmallMax 
 __device__ __forceinline__ void
 encode_small_body(const EncGeom& g, const void* __restrict__ x, const float* __restrict__ qs_all, const hqmq_packed& dst,
                   int t_start, const Maps24& maps, const float* __restrict__ joint_all, const unsigned char* __restrict__ lut,
-                  const uint8_t* __restrict__ nmul_dev, float C, float* __restrict__ med_out) {
+                  const uint8_t* __restrict__ nmul_dev, float C, float* __restrict__ med_out, float quantile) {
   __shared__ uint32_t keys[kSmallMax];                    // norm bits of every chunk of the head
   __shared__ uint32_t tokmax[kSmallTok];                  // bits of the largest radius of a token
   __shared__ uint32_t tokflags[kSmallTok];
@@ -417,7 +438,8 @@ encode_small_body(const EncGeom& g, const void* __restrict__ x, const float* __r
   if (med) {
     __shared__ uint32_t shist[256];
     __shared__ uint32_t s_state[4];       // prefix, rank, keys <= a, smallest key > a
-    const uint32_t lo = (uint32_t)((N - 1) / 2), hi = (uint32_t)(N / 2);
+    const QRank qr = quantile_rank((uint64_t)N, quantile);
+    const uint32_t lo = (uint32_t)qr.lo, hi = (uint32_t)qr.hi;
     uint32_t prefix = 0u, rank = lo;
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
@@ -476,7 +498,7 @@ encode_small_body(const EncGeom& g, const void* __restrict__ x, const float* __r
     __syncthreads();
     const uint32_t b_bits = s_state[2] > hi ? a_bits : s_state[3];
     const float a = __uint_as_float(a_bits), b2 = __uint_as_float(b_bits);
-    const float m = (N & 1) ? a : __fsub_rn(b2, __fmul_rn(__fsub_rn(b2, a), 0.5f));
+    const float m = hi == lo ? a : quantile_lerp(a, b2, qr.w);
     thr = __fmul_rn(m, C);
     if (threadIdx.x == 0 && med_out) med_out[h] = m;
   }
@@ -550,6 +572,7 @@ struct SmallArgs {
   const uint8_t* nmul;
   float C;
   float* med_out;
+  float quantile;
   uint32_t* status;     // first word of the tensor's workspace: cleared here, set by scan_kernel on an overflow
   int blk0, nblk, scan, payload, side;
 };
@@ -557,13 +580,13 @@ struct SmallPair { SmallArgs t[2]; Maps24 maps; };
 
 __global__ void __launch_bounds__(kSmallThreads) encode_small_kernel(SmallArgs a, Maps24 maps) {
   if (blockIdx.x == 0 && threadIdx.x == 0) *a.status = 0u;
-  encode_small_body(a.g, a.x, a.qs, a.dst, a.t_start, maps, a.joint, a.lut, a.nmul, a.C, a.med_out);
+  encode_small_body(a.g, a.x, a.qs, a.dst, a.t_start, maps, a.joint, a.lut, a.nmul, a.C, a.med_out, a.quantile);
 }
 // grid (H, 2): blockIdx.y = 0 the K tensor, 1 the V tensor (same batch, heads, tokens and head dim)
 __global__ void __launch_bounds__(kSmallThreads) encode_small_pair_kernel(SmallPair p) {
   const SmallArgs& a = p.t[blockIdx.y];
   if (blockIdx.x == 0 && threadIdx.x == 0) *a.status = 0u;
-  encode_small_body(a.g, a.x, a.qs, a.dst, a.t_start, p.maps, a.joint, a.lut, a.nmul, a.C, a.med_out);
+  encode_small_body(a.g, a.x, a.qs, a.dst, a.t_start, p.maps, a.joint, a.lut, a.nmul, a.C, a.med_out, a.quantile);
 }
 
 // ---- main pass for the common geometry ------------------------------------------------------------------
@@ -693,7 +716,7 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
 __global__ void __launch_bounds__(256)
 select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level, uint64_t N, float C,
               float* __restrict__ med_out, uint32_t* __restrict__ band, const uint32_t* __restrict__ sel_s,
-              const uint32_t* __restrict__ hist_fb) {
+              const uint32_t* __restrict__ hist_fb, float quantile) {
   __shared__ uint64_t wtot[8];
   const int h = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;   // launched with 256 threads
@@ -701,7 +724,8 @@ select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level
   // level 1 with a sampled prediction: the main pass filled the level-1 histograms if the sample named the
   // right bins, else hist32_kernel filled the fallback ones
   const bool use_fb = level == 1 && sel_s && !(sel_s[h * 8 + 0] == st[0] && sel_s[h * 8 + 2] == st[2]);
-  const uint64_t lo = (N - 1) / 2, hi = N / 2;
+  const QRank qr = quantile_rank(N, quantile);
+  const uint64_t lo = qr.lo, hi = qr.hi;
   uint32_t* hl = hist + ((int64_t)h * 3 + level) * 2 * kHistBins;
   const int shift = level == 0 ? 21 : level == 1 ? 10 : 0;
   const int bins = level == 2 ? 1024 : kHistBins;
@@ -759,7 +783,7 @@ select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level
   }
   if (level == 2) {
     const float a = __uint_as_float(st[0]), b = __uint_as_float(st[2]);
-    float med = (N & 1) ? a : __fsub_rn(b, __fmul_rn(__fsub_rn(b, a), 0.5f));
+    float med = hi == lo ? a : quantile_lerp(a, b, qr.w);
     const float thr = __fmul_rn(med, C);
     st[4] = st[0]; st[5] = st[2];
     st[6] = __float_as_uint(thr);
@@ -1606,6 +1630,7 @@ static int validate_encode(const hqmq_encode_args* a) {
   int rc = check_packed(a->dst, med);
   if (rc) return rc;
   if (a->T_new < 0 || a->t_start < 0) return HQMQ_ERR_SHAPE;
+  if (!(a->quantile >= 0.f && a->quantile < 1.f)) return HQMQ_ERR_ARG;
   if ((int64_t)a->t_start + a->T_new > a->dst.T_cap) return HQMQ_ERR_CAPACITY;
   const int align = a->x_dtype == HQMQ_F32 ? 16 : 8;
   if ((uintptr_t)a->x & (align - 1)) return HQMQ_ERR_ALIGN;
@@ -1736,7 +1761,7 @@ extern "C" int hqmq_med3x_select(int H, int level, uint64_t n_total, float media
   uint32_t* hist = reinterpret_cast<uint32_t*>(state);
   uint32_t* sel = hist + (size_t)H * 3 * 2 * kHistBins;
   select_kernel<<<H, 256, 0, (cudaStream_t)stream>>>(hist, sel, level, n_total, median_mult, level == 2 ? med_out : nullptr,
-                                                     nullptr, nullptr, nullptr);
+                                                     nullptr, nullptr, nullptr, 0.f);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }
@@ -1775,7 +1800,7 @@ static int fill_small(const hqmq_encode_args* a, const WsPlan& wp, uint32_t* ws,
   sa.x = a->x; sa.qs = a->qs; sa.dst = d; sa.t_start = a->t_start; sa.joint = a->joint;
   sa.lut = lut_ok ? lut_b : nullptr;
   sa.nmul = lut_ok ? lut_b + kLutOffHeads + (size_t)d.H * kLutHeadBytes : nullptr;
-  sa.C = a->median_mult; sa.med_out = a->med_out;
+  sa.C = a->median_mult; sa.med_out = a->med_out; sa.quantile = a->quantile;
   sa.status = ws + wp.status;
   sa.blk0 = wp.blk0; sa.nblk = wp.nblk;
   sa.scan = (med || d.ofrag) ? 1 : 0; sa.payload = med ? 1 : 0; sa.side = med ? 1 : 0;
@@ -1900,7 +1925,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
       if (a->x_dtype == HQMQ_F16) sample32_kernel<HQMQ_F16><<<dim3(gs, d.B * d.H), 256, 0, st>>>(f32, ws + wp.hist_s);
       else sample32_kernel<HQMQ_BF16><<<dim3(gs, d.B * d.H), 256, 0, st>>>(f32, ws + wp.hist_s);
       select_kernel<<<d.H, 256, 0, st>>>(ws + wp.hist_s, ws + wp.sel_s, 0, (uint64_t)d.B * n_s * 32, a->median_mult, nullptr,
-                                         nullptr, nullptr, nullptr);
+                                         nullptr, nullptr, nullptr, a->quantile);
     }
     const uint32_t* sel_s_arg = predicted ? ws + wp.sel_s : nullptr;
     const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a->x);
@@ -1961,16 +1986,16 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     if (fb < 1) fb = 1;
     flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel);
   } else {
-  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr, nullptr, nullptr, nullptr);
+  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr, nullptr, nullptr, nullptr, a->quantile);
   if (fast32) {
     // (with a prediction this launch returns at once unless the sample named the wrong bins)
     if (h16) hist32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1, sel_s, hist_fb);
     else hist32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1, sel_s, hist_fb);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, band, sel_s, hist_fb);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, band, sel_s, hist_fb, a->quantile);
     // last histogram level and provisional flags in one pass, exact threshold, then the (normally empty) fix-up
     if (h16) histflags32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und);
     else histflags32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr, a->quantile);
     if (h16) {
       fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und);
       fixup_scan_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band);
@@ -1980,9 +2005,9 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     }
   } else {
     hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 1);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, nullptr, nullptr, nullptr);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, nullptr, nullptr, nullptr, a->quantile);
     hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 2);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr, a->quantile);
     const int tok_per_fblock = 8 * g.tpw;
     int fb = (a->T_new + 4 * tok_per_fblock - 1) / (4 * tok_per_fblock);
     const int fb_cap = (148 * 32 + bh_count - 1) / bh_count;

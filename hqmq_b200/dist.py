@@ -107,6 +107,8 @@ def split_batch_median(quant, x: torch.Tensor, layer_idx: int, kv: int, out, gro
     ``n_total`` = chunk norms per head over all ranks (computed with one more all_reduce when not given)."""
     import ctypes as C
     from . import _lib
+    if getattr(quant, "threshold_mode", "median_mult") != "median_mult":
+        raise NotImplementedError("split_batch_median: the batch of a head can be split over GPUs for threshold_mode='median_mult' only")
     inner, mult = quant.inner, float(quant.median_mult)
     B, H, T, d = x.shape
     inner._check_dst(x, out)

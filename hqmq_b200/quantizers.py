@@ -197,7 +197,7 @@ class HQMQQuantizer(KVQuantizer):
         if out.device != x.device:
             raise ValueError(f"x is on {x.device}, the destination cache on {out.device}")
 
-    def _enc_args(self, x, layer_idx, kv, out, median_mult=None, search=0, med_out=None, med_in=None):
+    def _enc_args(self, x, layer_idx, kv, out, median_mult=None, search=0, med_out=None, med_in=None, quantile=None):
         """The hqmq_encode_args of one call (x already validated and laid out, ``out`` the destination cache)."""
         tb = self.tables(layer_idx, kv, x.device)
         B, H, T, d = x.shape
@@ -208,6 +208,7 @@ class HQMQQuantizer(KVQuantizer):
         a.T_new, a.t_start = T, out.T
         a.qs, a.joint = tb["qs"].data_ptr(), tb["joint"].data_ptr()
         a.median_mult = float(median_mult) if median_mult is not None else 0.0
+        a.quantile = float(quantile) if quantile is not None else 0.0      # 0: the median
         a.search = search
         a.dst = out.c_struct()
         a.med_out = med_out.data_ptr() if med_out is not None else None
@@ -224,13 +225,16 @@ class HQMQQuantizer(KVQuantizer):
     def encode(self, x: torch.Tensor, layer_idx: int, kv: int, out: Optional[PackedKV] = None,
                median_mult: Optional[float] = None, scale_dtype: Optional[torch.dtype] = None,
                search: int = 0, med_out: Optional[torch.Tensor] = None, ofrag: Optional[bool] = None,
-               check_status: bool = False, med_in: Optional[torch.Tensor] = None) -> PackedKV:
+               check_status: bool = False, med_in: Optional[torch.Tensor] = None,
+               quantile: Optional[float] = None) -> PackedKV:
         """Encode x (B, H, T_new, d) and append it to ``out`` (a fresh cache when None).
 
         ``ofrag``: also keep the flagged chunks of every complete 16-token block as tensor-core operand
         records for the decode-attention kernel (K tensors only use them).  Default: on for a fresh K
         cache with Med3x, off otherwise.  ``check_status``: synchronise and raise if the outlier side buffer
-        overflowed (otherwise the caller may compare ``out_count`` with ``out_cap`` itself).  ``med_in``: (H,) fp32
+        overflowed (otherwise the caller may compare ``out_count`` with ``out_cap`` itself).  ``quantile``: flag
+        against ``median_mult`` times ``torch.quantile(norms, quantile)`` per head instead of the median (the
+        reference wrapper's "fraction" mode: quantile = 1 - fraction, median_mult = 1).  ``med_in``: (H,) fp32
         medians to flag against instead of this call's own (``hqmq_b200.dist.split_batch_median`` computes them
         when the batch entries of a head are spread over several GPUs)."""
         # Decode-time appends repeat one small call shape on one cache: the argument struct and the workspace of
@@ -238,7 +242,7 @@ class HQMQQuantizer(KVQuantizer):
         # (calls on one cache are ordered on a stream anyway, since they append to the same planes).
         fast_key = None
         if out is not None and med_out is None and med_in is None and not check_status and x.dim() == 4 and x.shape[2] <= 64:
-            fast_key = (id(self), layer_idx, kv, tuple(x.shape), x.dtype, x.stride(), median_mult, search)
+            fast_key = (id(self), layer_idx, kv, tuple(x.shape), x.dtype, x.stride(), median_mult, search, quantile)
             hit = out._enc_cache.get(fast_key)
             if hit is not None:
                 a, ws, nbytes = hit
@@ -277,7 +281,7 @@ class HQMQQuantizer(KVQuantizer):
             raise _lib.HqmqError(f"hqmq_b200: cache capacity {out.T_cap} exceeded ({out.T} + {T})")
         if T == 0:              # appending nothing leaves the cache as it is (an empty tensor has no address to pass)
             return out
-        a = self._enc_args(x, layer_idx, kv, out, median_mult, search, med_out, med_in)
+        a = self._enc_args(x, layer_idx, kv, out, median_mult, search, med_out, med_in, quantile)
         L = _lib.lib()
         with _lib.device_guard(x.device):
             nbytes = L.hqmq_encode_workspace_bytes(C.byref(a))
@@ -292,7 +296,7 @@ class HQMQQuantizer(KVQuantizer):
         return out
 
     def encode_pair(self, k: torch.Tensor, v: torch.Tensor, layer_idx: int, out_k: PackedKV, out_v: PackedKV,
-                    median_mult: Optional[float] = None) -> Tuple[PackedKV, PackedKV]:
+                    median_mult: Optional[float] = None, quantile: Optional[float] = None) -> Tuple[PackedKV, PackedKV]:
         """Append the keys and the values of one layer (the reference cache quantises both on every update,
         src/model_utils.py:29-32).  Same result as ``encode(k, layer_idx, 0, out=out_k)`` followed by
         ``encode(v, layer_idx, 1, out=out_v)``; a decode-time append (a few tokens per sequence) runs both tensors
@@ -300,10 +304,10 @@ class HQMQQuantizer(KVQuantizer):
         small = (k.dim() == 4 and k.shape == v.shape and k.dtype == v.dtype and k.shape[2] <= 64 and k.is_cuda and v.is_cuda
                  and k.stride(-1) == 1 and v.stride(-1) == 1 and not any(s % 4 for s in k.stride()[:3] + v.stride()[:3]))
         if not small or k.shape[2] == 0:
-            return (self.encode(k, layer_idx, 0, out=out_k, median_mult=median_mult),
-                    self.encode(v, layer_idx, 1, out=out_v, median_mult=median_mult))
+            return (self.encode(k, layer_idx, 0, out=out_k, median_mult=median_mult, quantile=quantile),
+                    self.encode(v, layer_idx, 1, out=out_v, median_mult=median_mult, quantile=quantile))
         T = k.shape[2]
-        key = ("pair", id(self), id(out_v), layer_idx, tuple(k.shape), k.dtype, k.stride(), v.stride(), median_mult)
+        key = ("pair", id(self), id(out_v), layer_idx, tuple(k.shape), k.dtype, k.stride(), v.stride(), median_mult, quantile)
         hit = out_k._enc_cache.get(key)
         if hit is None:
             why = self._unsupported()
@@ -316,8 +320,8 @@ class HQMQQuantizer(KVQuantizer):
                 self._check_dst(x, out)
                 if median_mult is not None and not out.with_outliers:
                     raise ValueError("destination cache was created without outlier planes")
-            ak = self._enc_args(k, layer_idx, 0, out_k, median_mult)
-            av = self._enc_args(v, layer_idx, 1, out_v, median_mult)
+            ak = self._enc_args(k, layer_idx, 0, out_k, median_mult, quantile=quantile)
+            av = self._enc_args(v, layer_idx, 1, out_v, median_mult, quantile=quantile)
             with _lib.device_guard(k.device):
                 nbytes = _lib.lib().hqmq_encode_pair_workspace_bytes(C.byref(ak), C.byref(av))
             ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=k.device)
@@ -356,7 +360,8 @@ class HQMQQuantizer(KVQuantizer):
             _lib.check(_lib.lib().hqmq_dequant(C.byref(a), _lib.stream_ptr()), "hqmq_dequant")
         return out
 
-    def _qdq(self, x: torch.Tensor, layer_idx: int, kv: int, median_mult: Optional[float] = None) -> torch.Tensor:
+    def _qdq(self, x: torch.Tensor, layer_idx: int, kv: int, median_mult: Optional[float] = None,
+             quantile: Optional[float] = None) -> torch.Tensor:
         """Fake-quantise: decode(encode(x)).  The scale plane is kept in fp32 and the radius is
         rebuilt as rq * (r_max / qmax), the reference's own order (src/quantizers/hqmq.py:210-216)."""
         B, H, T, d = x.shape
@@ -366,7 +371,7 @@ class HQMQQuantizer(KVQuantizer):
             return x.clone()
         pk = self.new_cache(B, T, d, x.device, scale_dtype=torch.float32, with_outliers=median_mult is not None,
                             out_dtype=x.dtype if x.dtype != torch.float64 else torch.float32)
-        self.encode(x, layer_idx, kv, out=pk, median_mult=median_mult)
+        self.encode(x, layer_idx, kv, out=pk, median_mult=median_mult, quantile=quantile)
         self._last_packed = pk
         return self.decode(pk, layer_idx, kv, dtype=x.dtype, scale_first=True)
 
@@ -489,17 +494,22 @@ class OutlierAwareHQMQQuantizer(KVQuantizer):
         self.inner._refresh_rotations()
 
     def _check_mode(self):
-        if self.threshold_mode == "fraction":
-            raise NotImplementedError("hqmq_b200 accelerates threshold_mode='median_mult' only")
-        if self.threshold_mode != "median_mult":
+        if self.threshold_mode not in ("median_mult", "fraction"):
             raise ValueError(self.threshold_mode)
+
+    def _thr(self) -> dict:
+        """The threshold of a call as the encoder takes it (src/quantizers/outlier_aware.py:63-72): ``median_mult``
+        times the per-head median, or ("fraction") the per-head quantile 1 - outlier_fraction itself."""
+        if self.threshold_mode == "fraction":
+            return dict(median_mult=1.0, quantile=1.0 - self.outlier_fraction)
+        return dict(median_mult=self.median_mult)
 
     def encode(self, x, layer_idx, kv, out: Optional[PackedKV] = None, **kw) -> PackedKV:
         self._check_mode()
         total = x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4)
         if total:
             self._stats.begin(out, total)
-        pk = self.inner.encode(x, layer_idx, kv, out=out, median_mult=self.median_mult, **kw)
+        pk = self.inner.encode(x, layer_idx, kv, out=out, **self._thr(), **kw)
         if total:
             self._stats.end(pk, total)
         return pk
@@ -511,7 +521,7 @@ class OutlierAwareHQMQQuantizer(KVQuantizer):
         if total:
             self._stats.begin(out_k, total)
             self._stats.begin(out_v, total)
-        pair = self.inner.encode_pair(k, v, layer_idx, out_k, out_v, median_mult=self.median_mult)
+        pair = self.inner.encode_pair(k, v, layer_idx, out_k, out_v, **self._thr())
         if total:
             self._stats.end(out_k, total)
             self._stats.end(out_v, total)
@@ -522,7 +532,7 @@ class OutlierAwareHQMQQuantizer(KVQuantizer):
 
     def _qdq(self, x, layer_idx, kv):
         self._check_mode()
-        out = self.inner._qdq(x, layer_idx, kv, median_mult=self.median_mult)
+        out = self.inner._qdq(x, layer_idx, kv, **self._thr())
         if x.shape[0] and x.shape[2]:
             self._stats.push_count(self.inner._last_packed.out_count.sum(), x.shape[0] * x.shape[1] * x.shape[2] * (x.shape[3] // 4))
         return out

@@ -187,13 +187,15 @@ typedef struct hqmq_encode_args {
   int32_t t_start;          /* row of the packed planes that receives token 0 of x */
   const float* qs;          /* (H,S,4) unit secondary quaternions, fp32 */
   const float* joint;       /* (H,24*S,4) fp32 joint table, reference order */
-  float median_mult;        /* Med3x multiplier C; <= 0 disables outlier flagging */
+  float median_mult;        /* multiplier C of the threshold statistic (Med3x: 3); <= 0 disables outlier flagging */
   int32_t search;           /* 0 = default (look-up table when `lut` is given), 1 = exhaustive scan over the S secondaries */
   hqmq_packed dst;          /* destination planes */
   float* med_out;           /* optional (H,) fp32: the per-head median of this call */
   const void* lut;          /* optional nearest-codeword table of this codebook (hqmq_encode_lut_build) */
   int32_t lut_footprint;    /* hqmq_encode_lut_footprint() of `lut` (0 = unknown, assume the capacity) */
-  int32_t reserved;
+  float quantile;           /* 0: the threshold is median_mult x the per-head median (Med3x).  q in (0, 1): median_mult x
+                               torch.quantile(norms, q) per head, with torch's rank arithmetic and interpolation (the
+                               reference wrapper's threshold_mode="fraction": q = 1 - fraction, median_mult = 1) */
   const float* med_in;      /* optional (H,) fp32, device: per-head medians to use instead of this call's own; for a
                                head whose batch entries are spread over several GPUs (hqmq_med3x_hist / _select) */
 } hqmq_encode_args;

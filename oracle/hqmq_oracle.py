@@ -122,20 +122,41 @@ def median_quantile(flat: torch.Tensor) -> torch.Tensor:
     return b - (b - a) * (torch.tensor(1.0) - w)
 
 
-def med3x_flags(norms: torch.Tensor, C: float):
-    """Per-KV-head median threshold and strict outlier flag
-    (src/quantizers/outlier_aware.py:63-72, threshold_mode="median_mult").
-    norms (B,H,T,n) fp32 -> (med (H,), thr (H,), flags (B,H,T,n) bool)."""
+def quantile_torch(flat: torch.Tensor, q: float) -> torch.Tensor:
+    """``torch.quantile(flat, q, dim=-1)`` for fp32 ``flat`` of shape (H, N) and any q in [0, 1]
+    (src/quantizers/outlier_aware.py:64-66), restated with the arithmetic ATen uses: the rank is the fp32 product
+    fl32(q) * fl32(N - 1), the neighbours are its truncation and its ceiling, the weight their fp32 difference, and
+    the interpolation is one fused multiply-add: a + w*(b-a) for w < 0.5, else b - (b-a)*(1-w)."""
+    H, N = flat.shape
+    srt = np.sort(flat.numpy().astype(np.float32), axis=-1)
+    rank = np.float32(np.float32(q) * np.float32(N - 1))
+    lo, hi = int(rank), int(math.ceil(rank))
+    w = np.float32(rank - np.float32(lo))
+    a, b = srt[:, lo], srt[:, hi]
+    diff = (b - a).astype(np.float32)
+    # (the fp32 product w * diff is exact in float64, so one rounding of the float64 sum is the fused result
+    #  up to double rounding, which the pin against torch.quantile has not met)
+    if abs(float(w)) < 0.5:
+        out = a.astype(np.float64) + np.float64(w) * diff.astype(np.float64)
+    else:
+        out = b.astype(np.float64) - diff.astype(np.float64) * np.float64(np.float32(1.0) - w)
+    return torch.from_numpy(out.astype(np.float32))
+
+
+def med3x_flags(norms: torch.Tensor, C: float, quantile: Optional[float] = None):
+    """Per-KV-head threshold and strict outlier flag (src/quantizers/outlier_aware.py:63-72): C times the median
+    (threshold_mode="median_mult"), or with ``quantile`` C times that quantile (threshold_mode="fraction" is
+    quantile = 1 - outlier_fraction, C = 1).  norms (B,H,T,n) fp32 -> (statistic (H,), thr (H,), flags bool)."""
     B, H, T, n = norms.shape
     flat = norms.permute(1, 0, 2, 3).reshape(H, -1).float()
-    med = median_quantile(flat)
+    med = median_quantile(flat) if quantile is None else quantile_torch(flat, quantile)
     thr = med * C
     flags = norms > thr.view(1, H, 1, 1)
     return med, thr, flags
 
 
 def encode(x: torch.Tensor, joint: torch.Tensor, radius_bits: int,
-           median_mult: Optional[float] = None, t_slice: int = 0) -> dict:
+           median_mult: Optional[float] = None, t_slice: int = 0, quantile: Optional[float] = None) -> dict:
     """Encoder with the intermediates exposed.
 
     Follows src/quantizers/hqmq.py:150-152 (norm, clamp), :157-158,164 (direction, einsum
@@ -174,13 +195,14 @@ def encode(x: torch.Tensor, joint: torch.Tensor, radius_bits: int,
     rq = (radius / scale.unsqueeze(-1)).round().clamp(0, qmax).to(torch.int32)
     out = dict(idx=idx, rq=rq, r_max=r_max, norms=nrm, gap=gap)
     if median_mult is not None:
-        med, thr, flags = med3x_flags(nrm, float(median_mult))
+        med, thr, flags = med3x_flags(nrm, float(median_mult), quantile)
         out.update(med=med, thr=thr, flags=flags)
     return out
 
 
 def fake_quant(x: torch.Tensor, joint: torch.Tensor, radius_bits: int,
-               median_mult: Optional[float] = None, enc: Optional[dict] = None) -> torch.Tensor:
+               median_mult: Optional[float] = None, enc: Optional[dict] = None,
+               quantile: Optional[float] = None) -> torch.Tensor:
     """What ``quantize_K`` / ``quantize_V`` return for fp32 input: codeword * (rq * scale)
     (src/quantizers/hqmq.py:166-169,210-211,216), and with Med3x the original chunk where
     flagged (src/quantizers/outlier_aware.py:86)."""
@@ -188,7 +210,7 @@ def fake_quant(x: torch.Tensor, joint: torch.Tensor, radius_bits: int,
     B, H, T, d = x.shape
     n = d // CHUNK
     if enc is None:
-        enc = encode(x, joint, radius_bits, median_mult)
+        enc = encode(x, joint, radius_bits, median_mult, quantile=quantile)
     qmax = (1 << radius_bits) - 1
     cw = gather_codewords(enc["idx"], joint.float())
     scale = enc["r_max"] / qmax

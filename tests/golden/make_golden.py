@@ -31,6 +31,13 @@ ENC_CASES = [
     ("s96_r4_d64", 96, 4, 3.0, (3, 2, 7, 64), "hot"),
 ]
 
+FRACTION_CASES = [
+    # name, S, b_r, outlier_fraction, (B,H,T,d), kind   (sizes with fractional and with whole ranks)
+    ("frac1_s96_r4", 96, 4, 0.01, (2, 2, 24, 128), "hot"),
+    ("frac5_s24_r3", 24, 3, 0.05, (1, 2, 33, 64), "spiky"),
+    ("frac10_s96_r4", 96, 4, 0.10, (3, 2, 7, 64), "randn"),
+]
+
 
 def make_input(kind, shape, seed):
     g = torch.Generator().manual_seed(seed)
@@ -98,6 +105,34 @@ def main(ref_root):
                 out[key + ".med"] = enc["med"].numpy()
         out[name + ".meta"] = np.array([S, br, -1.0 if C is None else C, B, H, T, d], dtype=np.float64)
     np.savez_compressed(os.path.join(HERE, "golden_encode.npz"), **out)
+
+    # ---- the wrapper's other threshold: the per-head quantile 1 - outlier_fraction ("fraction" mode) -------------
+    from src.quantizers.outlier_aware import OutlierAwareHQMQQuantizer
+    fr = {}
+    for i, (name, S, br, frac, shape, kind) in enumerate(FRACTION_CASES):
+        B, H, T, d = shape
+        q = hqmq.HQMQ(n_layers=1, n_heads=H, secondary_size=S, radius_bits=br, device="cpu", seed=42)
+        raw = orc.secondary_raw(1, H, S, 42)
+        x = make_input(kind, shape, 3000 + i)
+        qq = OutlierAwareHQMQQuantizer(q, outlier_fraction=frac, threshold_mode="fraction")
+        joint = orc.joint_codebook(raw[0, :, 0])
+        with torch.no_grad():
+            ref = qq.quantize_K(x, 0)
+        quant = 1.0 - frac
+        enc = orc.encode(x, joint, br, 1.0, quantile=quant)
+        assert torch.equal(ref, orc.fake_quant(x, joint, br, 1.0, enc=enc)), f"{name}: oracle != reference"
+        flat = enc["norms"].permute(1, 0, 2, 3).reshape(H, -1)
+        assert torch.equal(torch.quantile(flat, quant, dim=-1), enc["med"]), name
+        fr[name + ".x"] = x.numpy()
+        fr[name + ".raw"] = raw[0, :, 0].numpy()
+        fr[name + ".ref_fake_quant"] = ref.numpy()
+        fr[name + ".thr"] = enc["thr"].numpy()
+        fr[name + ".flags"] = np.packbits(enc["flags"].numpy().reshape(-1))
+        fr[name + ".idx"] = enc["idx"].numpy().astype(np.uint16)
+        fr[name + ".rq"] = enc["rq"].numpy().astype(np.uint8)
+        fr[name + ".gap"] = enc["gap"].numpy()
+        fr[name + ".meta"] = np.array([S, br, frac, B, H, T, d], dtype=np.float64)
+    np.savez_compressed(os.path.join(HERE, "golden_fraction.npz"), **fr)
 
     # ---- packed decode + attention --------------------------------------------------
     att = {}

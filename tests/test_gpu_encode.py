@@ -14,14 +14,14 @@ pytestmark = pytest.mark.gpu
 NEAR_TIE = 1e-6
 
 
-def _encode_and_compare(x, S, br, C, layer=0, kv=0, n_layers=2, search=0, scale_dtype=torch.float32):
+def _encode_and_compare(x, S, br, C, layer=0, kv=0, n_layers=2, search=0, scale_dtype=torch.float32, quantile=None):
     B, H, T, d = x.shape
     q = hqmq.HQMQ(n_layers=n_layers, n_heads=H, secondary_size=S, radius_bits=br, device="cuda", seed=42)
     joint = orc.joint_codebook(orc.secondary_raw(n_layers, H, S, 42)[layer, :, kv])
-    enc = orc.encode(x, joint, br, C)
+    enc = orc.encode(x, joint, br, C, quantile=quantile)
     med = torch.zeros(H, device="cuda")
     pk = q.encode(x.cuda(), layer, kv, median_mult=C, scale_dtype=scale_dtype, search=search,
-                  med_out=med if C is not None else None)
+                  med_out=med if C is not None else None, quantile=quantile)
     idx, rq, rs, flags = pk.to_reference()
     torch.cuda.synchronize()
     # the packed row stores 0 as the radius code of a flagged chunk (its values are in the side buffer)
@@ -351,3 +351,38 @@ def test_split_batch_median_and_encode_match_the_whole_batch(shape, dtype, S, br
                 k = int(cw[b, h])
                 assert torch.equal(ov_c[b, h, :k], ov_w[b, h, :k])
         b0 += nb
+
+
+@pytest.mark.parametrize("name", ["frac1_s96_r4", "frac5_s24_r3", "frac10_s96_r4"])
+def test_fraction_threshold_matches_reference_fixtures(name):
+    """threshold_mode="fraction" of the reference wrapper (src/quantizers/outlier_aware.py:64-66): the per-head
+    quantile 1 - outlier_fraction of the chunk norms is the threshold.  Flags, radius codes and the fake-quant
+    output against what the reference itself produced (small calls: the one-kernel path)."""
+    z = load_npz("golden_fraction.npz")
+    S, br, frac, B, H, T, d = z[name + ".meta"]
+    S, br, B, H, T = int(S), int(br), int(B), int(H), int(T)
+    x = torch.from_numpy(z[name + ".x"])
+    inner = hqmq.HQMQ(n_layers=1, n_heads=H, secondary_size=S, radius_bits=br, device="cuda", seed=42)
+    qq = hqmq.OutlierAwareHQMQQuantizer(inner, outlier_fraction=float(frac), threshold_mode="fraction")
+    pk = qq.encode(x.cuda(), 0, 0)
+    idx, rq, rs, flags = pk.to_reference()
+    gold_flags = np.unpackbits(z[name + ".flags"])[: rq.numel()].reshape(rq.shape).astype(bool)
+    assert np.array_equal(flags.cpu().numpy(), gold_flags)
+    gold_rq = z[name + ".rq"].copy()
+    gold_rq[gold_flags] = 0
+    assert np.array_equal(rq.cpu().numpy().astype(np.uint8), gold_rq)
+    mism = idx.cpu().numpy().astype(np.uint16) != z[name + ".idx"]
+    assert not (mism & (z[name + ".gap"] >= NEAR_TIE)).any()
+    fq = qq.quantize_K(x.cuda(), 0).cpu()
+    if not mism.any():
+        assert torch.equal(fq, torch.from_numpy(z[name + ".ref_fake_quant"]))
+    assert abs(qq._observed_outlier_rate - gold_flags.mean()) < 1e-6
+
+
+@pytest.mark.parametrize("S,br,kind,q", [(96, 4, "hot", 0.97), (24, 3, "spiky", 0.995), (192, 6, "student", 0.9)])
+def test_fraction_threshold_large_calls(S, br, kind, q):
+    """The same statistic through the multi-pass path of large calls (sampled prediction, three-level select,
+    threshold bounds and fix-up), against the oracle's torch.quantile restatement."""
+    x = make_kv(kind, (2, 2, 3000, 128), seed=21, dtype=torch.bfloat16).float()
+    _encode_and_compare(x, S, br, 1.0, quantile=q)
+    _encode_and_compare(x[:, :, :1500, :64].contiguous(), S, br, 1.0, quantile=q)       # generic geometry

@@ -94,3 +94,31 @@ def test_combine_partials_equals_unsplit_softmax():
         ms.append(m); ls.append(p.sum(-1)); os_.append(p @ v[lo:hi])
     out = orc.combine_partials(torch.stack(ms), torch.stack(ls), torch.stack(os_))
     assert torch.allclose(out, full, atol=1e-5)
+
+
+def test_fraction_threshold_matches_reference_fixtures():
+    """The wrapper's threshold_mode="fraction" (src/quantizers/outlier_aware.py:64-66) against the reference's output."""
+    z = load_npz("golden_fraction.npz")
+    for name in ("frac1_s96_r4", "frac5_s24_r3", "frac10_s96_r4"):
+        S, br, frac, B, H, T, d = z[name + ".meta"]
+        x = torch.from_numpy(z[name + ".x"])
+        joint = orc.joint_codebook(torch.from_numpy(z[name + ".raw"]))
+        enc = orc.encode(x, joint, int(br), 1.0, quantile=1.0 - float(frac))
+        assert np.array_equal(enc["thr"].numpy(), z[name + ".thr"]), name
+        assert np.array_equal(np.packbits(enc["flags"].numpy().reshape(-1)), z[name + ".flags"]), name
+        mism = enc["idx"].numpy().astype(np.uint16) != z[name + ".idx"]
+        if not mism.any():
+            assert torch.equal(orc.fake_quant(x, joint, int(br), 1.0, enc=enc), torch.from_numpy(z[name + ".ref_fake_quant"]))
+
+
+def test_quantile_restatement_equals_torch_quantile():
+    """Ranks in fp32, fused interpolation: bit-equal to torch.quantile for whole and fractional ranks, from two
+    elements up to the most torch.quantile accepts (2^24 elements, where the fp32 rank has no fraction bits left)."""
+    g = torch.Generator().manual_seed(5)
+    for N in (2, 7, 100, 4099, 65537, 1000003):
+        flat = torch.randn(3, N, generator=g).abs()
+        for q in (0.5, 0.9, 0.95, 0.99, 0.999, 0.37):
+            assert torch.equal(orc.quantile_torch(flat, q), torch.quantile(flat, q, dim=-1)), (N, q)
+    flat = torch.rand(1, (1 << 24) - 3, generator=g)
+    for q in (0.99, 0.9, 0.731):
+        assert torch.equal(orc.quantile_torch(flat, q), torch.quantile(flat, q, dim=-1)), q

@@ -451,10 +451,19 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
             uint32_t n = fr.y - fr.x; if (n > HQMQ_OFRAG_MAX_PER_TILE) n = HQMQ_OFRAG_MAX_PER_TILE;
             for (uint32_t g = 0; g < n; ++g) {
               const uint32_t ri = fr.x + g - sh1.x;        // index among the staged records
-              const unsigned char* rec = ri < sh1.y ? sb + RL::kSideK + ri * HQMQ_OFRAG_BYTES
-                                                    : p.K.ofrag + (bh * p.K.ofrag_cap + fr.x + g) * HQMQ_OFRAG_BYTES;
-              const uint32_t hdr = *reinterpret_cast<const uint32_t*>(rec);
-              const uint4 a = *reinterpret_cast<const uint4*>(rec + 16 + lane * 16);
+              uint32_t hdr;
+              uint4 a;
+              // (two loads per address space instead of one through a selected pointer: a generic load is served
+              //  like a global one, and the staged record is the common case)
+              if (ri < sh1.y) {
+                const unsigned char* rec = sb + RL::kSideK + ri * HQMQ_OFRAG_BYTES;
+                hdr = *reinterpret_cast<const uint32_t*>(rec);
+                a = *reinterpret_cast<const uint4*>(rec + 16 + lane * 16);
+              } else {
+                const unsigned char* rec = p.K.ofrag + (bh * p.K.ofrag_cap + fr.x + g) * HQMQ_OFRAG_BYTES;
+                hdr = __ldg(reinterpret_cast<const uint32_t*>(rec));
+                a = __ldg(reinterpret_cast<const uint4*>(rec + 16 + lane * 16));
+              }
               const uint32_t cj = (hdr >> (8 * j)) & 0xffu;
               uint2 qv = make_uint2(0u, 0u);
               if (cj != 0xffu) qv = *reinterpret_cast<const uint2*>(qh16 + r * qstride + 4 * cj);

@@ -14,6 +14,9 @@ bool ring_kernel(int n_chunks, int ib, int rb, bool outl, int scale_dtype, RingK
 size_t ring_smem_total(int table_rows, int repk_log2, int repv_log2, int d, bool outl, int stages, int merge_slots,
                        size_t stage_bytes);
 constexpr int kRingMinKeys = 1024;       // shorter key ranges keep the per-warp staging rings
+// ... and so do small problems: below about four stages per SM the ring kernel's set-up (it replicates the tables
+// up to sixteen times) outweighs its faster tile loop (B1, 8 KV heads, 4096 keys: 42 against 26 us per step)
+constexpr int64_t kRingMinTiles = 148 * 4 * 15;
 constexpr size_t kSmemLimit = 226 * 1024;
 constexpr int kFastStages = 2;   // must equal kStages of the staged kernels
 constexpr int kFastQPad = 8;     // must equal kQPad of the staged kernels
@@ -198,7 +201,8 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   // third stage bought nothing where it cost a table replica).
   RingKernelInfo rk;
   bool ring = false;
-  if (fast && keys >= kRingMinKeys && ring_kernel(n, pl.ib, a->K.radius_bits, outl, a->K.scale_dtype, rk)) {
+  const int64_t tiles_all = (int64_t)a->B * a->T_q * a->H_kv * ((keys + kTile - 1) / kTile);
+  if (fast && keys >= kRingMinKeys && tiles_all >= kRingMinTiles && ring_kernel(n, pl.ib, a->K.radius_bits, outl, a->K.scale_dtype, rk)) {
     auto fits = [&](int rsum, int ns, int ms) {
       return ring_smem_total(pl.table_rows, (rsum + 1) / 2, rsum / 2, a->d, outl, ns, ms, rk.stage_bytes) <= kSmemLimit;
     };

@@ -134,6 +134,24 @@ __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
+// The producer's wait for a released buffer.  It has a whole stage of slack (the consumers work on the other buffers
+// meanwhile), so it tests the barrier without blocking and sleeps between tests: a waiting producer then costs
+// the consumers neither issue slots nor shared-memory cycles.  Bounded like ring_wait (about a second).
+constexpr uint32_t kProducerSleepNs = 160u;
+constexpr uint32_t kProducerTries = 6u * 1000u * 1000u;
+__device__ __forceinline__ bool ring_wait_producer(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word) {
+  uint32_t tries = 0;
+  for (;;) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if (++tries > kProducerTries || *abort_word) return false;
+    __nanosleep(kProducerSleepNs);
+  }
+}
+
 template <int N, int IB, int RB, bool OUTL, int SDT>
 __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
   using G_ = Geo<N>;
@@ -308,6 +326,13 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
 
   // =============================== consumer warps =============================================================
   const int j = lane & 3, r = lane >> 2;
+  // The V rows of a tile are read by four groups of lanes (j), each its tokens 2j and 2j + 1: with rows of 64 bytes
+  // the four groups' loads would meet in the same banks (rows 0, 2, 4, 6 lie 128 bytes apart), so the odd groups
+  // take their pair in the other order, and P is swapped to match (measured 280 -> 272 us per step on 64-byte rows;
+  // on 32-byte rows the same trick measured no gain, other row sizes spread by themselves).
+  constexpr int kVSwz = ROW % 128 == 64 ? 1 : 0;
+  const int vswz = kVSwz == 1 ? (j & 1) : kVSwz == 2 ? ((j >> 1) & 1) : 0;
+  const uint32_t pair_sel = vswz ? 0x1032u : 0x3210u;
   const uint32_t strideK = 8u << p.rep_log2, strideV = 8u << p.repv_log2;
   const uint32_t laneoffK = (uint32_t)(lane & ((1 << p.rep_log2) - 1)) * 8u;
   const uint32_t laneoffV = (uint32_t)(lane & ((1 << p.repv_log2) - 1)) * 8u;
@@ -402,7 +427,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int tr = 2 * j + (i & 1) + (i >> 1) * 8;
+          const int tr = 2 * j + ((i & 1) ^ vswz) + (i >> 1) * 8;
           ld.template load_span<FL::VW, FL::LV>(cur.vw[i], vc + tr * ROW, r, !EDGE || t0 + tr < t_end);
         }
         float ksc[2], vsc[2];
@@ -556,13 +581,21 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
           }
           const __half2 h0 = __floats2half2_rn(praw[0] * vsc[0], praw[1] * vsc[0]);
           const __half2 h1 = __floats2half2_rn(praw[2] * vsc[1], praw[3] * vsc[1]);
-          const float iv0 = vsc[0] > 0.f ? rcp_fast(vsc[0]) : 0.f, iv1 = vsc[1] > 0.f ? rcp_fast(vsc[1]) : 0.f;
           const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-          pe[0] = f0.x * iv0; pe[1] = f0.y * iv0; pe[2] = f1.x * iv1; pe[3] = f1.y * iv1;
+          // (a token whose scale is zero -- an all-zero V row under fp16 scales -- adds nothing to the numerator but
+          //  keeps its weight in the denominator; a masked token has weight 0 already)
+          if (vsc[0] > 0.f) { const float iv0 = rcp_fast(vsc[0]); pe[0] = f0.x * iv0; pe[1] = f0.y * iv0; }
+          else { pe[0] = praw[0]; pe[1] = praw[1]; }
+          if (vsc[1] > 0.f) { const float iv1 = rcp_fast(vsc[1]); pe[2] = f1.x * iv1; pe[3] = f1.y * iv1; }
+          else { pe[2] = praw[2]; pe[3] = praw[3]; }
           l_run[0] += pe[0] + pe[2];
           l_run[1] += pe[1] + pe[3];
           pb[0] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h0));
           pb[1] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h1));
+          if constexpr (kVSwz != 0) {   // tokens 2j and 2j + 1 trade places where the V rows were loaded in the other order
+            pb[0] = __byte_perm(pb[0], 0u, pair_sel);
+            pb[1] = __byte_perm(pb[1], 0u, pair_sel);
+          }
         }
 
         // ---- O^T += V^T P^T -----------------------------------------------------------------------------------
@@ -600,7 +633,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
               hi[i] = hmul2_u32(cw.y, rr);
               if constexpr (PATCH) {
                 const int c = r * NVG + g;
-                const uint4 ti = vinfo[warp * kTile + 2 * j + (i & 1) + (i >> 1) * 8];
+                const uint4 ti = vinfo[warp * kTile + 2 * j + ((i & 1) ^ vswz) + (i >> 1) * 8];
                 if ((ti.x >> c) & 1u) {
                   const uint32_t e = th0.z + ti.y + __popc(ti.x & ((1u << c) - 1u));
                   const float vi = __uint_as_float(ti.z);

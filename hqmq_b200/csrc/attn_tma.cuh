@@ -423,6 +423,9 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
           for (int i = 0; i < NOT; ++i) { o[i][e] *= alpha; o[i][2 + e] *= alpha; }
         }
       }
+      // P goes to the tensor cores as fp16(p * rs_V / qmax); the weights summed into l are those rounded products
+      // divided by the same scale again, so numerator and denominator of the output use one set of weights and the
+      // rounding of P cancels instead of adding 2^-11 of relative error to an output that a single key dominates.
       uint32_t pb[2];
       {
         float pe[4];
@@ -431,10 +434,19 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
           const float m_use = m_run[e] == -INFINITY ? 0.f : m_run[e];
           pe[e] = fast_exp2(s[e] - m_use);
           pe[2 + e] = fast_exp2(s[2 + e] - m_use);
-          l_run[e] += pe[e] + pe[2 + e];
         }
-        pb[0] = movmatrix_trans(pack_half2(pe[0] * vsc[0], pe[1] * vsc[0]));
-        pb[1] = movmatrix_trans(pack_half2(pe[2] * vsc[1], pe[3] * vsc[1]));
+        const __half2 h0 = __floats2half2_rn(pe[0] * vsc[0], pe[1] * vsc[0]);
+        const __half2 h1 = __floats2half2_rn(pe[2] * vsc[1], pe[3] * vsc[1]);
+        float iv0 = 0.f, iv1 = 0.f;
+        if (vsc[0] > 0.f) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(iv0) : "f"(vsc[0]));
+        if (vsc[1] > 0.f) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(iv1) : "f"(vsc[1]));
+        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+        // (a token whose scale is zero -- an all-zero V row under fp16 scales -- adds nothing to the numerator but
+        //  keeps its weight in the denominator; a masked token has weight 0 already)
+        l_run[0] += (vsc[0] > 0.f ? f0.x * iv0 : pe[0]) + (vsc[1] > 0.f ? f1.x * iv1 : pe[2]);
+        l_run[1] += (vsc[0] > 0.f ? f0.y * iv0 : pe[1]) + (vsc[1] > 0.f ? f1.y * iv1 : pe[3]);
+        pb[0] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h0));
+        pb[1] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&h1));
       }
 
       // ---- O^T += V^T P^T -------------------------------------------------------------------------------------

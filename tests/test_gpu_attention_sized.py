@@ -146,3 +146,18 @@ def test_side_buffer_overflow_is_memory_safe():
     dense = inner.decode(Kp, 0, 0, dtype=torch.float32).cpu()
     want = orc.merge_outliers(orc.decode_packed(ki, kr, ks, tk["joint"].cpu(), 15), kf, drop(K, kf, cap))
     assert torch.equal(dense, want)
+
+
+@pytest.mark.parametrize("T,B", [(640, 1), (20000, 4)])
+def test_all_zero_value_rows_keep_their_softmax_weight(T, B):
+    """A token whose V row is all zero gets scale 0 under fp16 scales (1e-8 is below fp16's range): it adds nothing
+    to the output's numerator but its weight stays in the denominator.  Short range: the per-warp-ring kernel; long
+    range with a large batch: the CTA-wide ring kernel."""
+    S, br, d, Hq, Hkv = 24, 3, 128, 8, 2
+    K = make_kv("randn", (B, Hkv, T, d), seed=1101, dtype=torch.float16)
+    V = make_kv("randn", (B, Hkv, T, d), seed=2101, dtype=torch.float16)
+    V[:, :, ::3] = 0.0                       # every third token
+    V[:, 1, 5:200] = 0.0                     # and a long run in one head
+    for q in (hqmq.HQMQ(1, Hkv, S, br, device="cuda"), hqmq.with_outlier_extraction(hqmq.HQMQ(1, Hkv, S, br, device="cuda"), 3.0)):
+        Kp, Vp = _attend_and_check(q, _queries(B, Hq, d, 3101, dtype=torch.float16), K, V, S, br, "zero V rows", splits=(None, 3))
+        assert (Vp.to_reference()[2][:, :, ::3] == 0).all()

@@ -107,7 +107,7 @@ def fused_attention_packed(
     _fill_q(a, Q, O)
     a.B, a.H_q, a.H_kv, a.T_q, a.d = B, H_q, K.H, T_q, d_h
     a.T_kv = K.T if T_kv is None else T_kv
-    a.r_qmax, a.causal = K.qmax, int(bool(causal))
+    a.r_qmax, a.causal = K.qmax, _causal_mode(causal)
     a.window = int(window) if window else 0
     a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 0.0
     a.kv_splits = int(kv_splits) if kv_splits else 0
@@ -137,7 +137,7 @@ def fused_attention_packed_noalloc(Q: torch.Tensor, K: PackedKV, V: PackedKV, ta
     a.layout = 0
     _fill_q(a, Q, out)
     a.B, a.H_q, a.H_kv, a.T_q, a.d, a.T_kv = B, H_q, K.H, T_q, d_h, K.T
-    a.r_qmax, a.causal = K.qmax, int(bool(causal))
+    a.r_qmax, a.causal = K.qmax, _causal_mode(causal)
     a.window = int(window) if window else 0
     a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 0.0
     a.K, a.V = K.c_struct(), V.c_struct()
@@ -145,6 +145,16 @@ def fused_attention_packed_noalloc(Q: torch.Tensor, K: PackedKV, V: PackedKV, ta
     with _lib.device_guard(Q.device):
         _lib.check(_lib.lib().hqmq_attn_decode_static(C.byref(a), _lib.stream_ptr()), "hqmq_attn_decode_static")
     return out
+
+
+def _causal_mode(causal) -> int:
+    """False / True (the reference's top-left aligned mask) / "bottom_right" (the queries are the last T_q positions
+    of the keys: a prompt chunk attending over a cache that already holds it)."""
+    if causal == "bottom_right":
+        return 2
+    if isinstance(causal, str):
+        raise ValueError(f"causal={causal!r}: expected False, True or 'bottom_right'")
+    return int(bool(causal))
 
 
 def combine_partials(parts: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:

@@ -85,12 +85,15 @@ class PackedKVCache:
 
     def attend(self, query_states: torch.Tensor, layer_idx: int, softmax_scale: Optional[float] = None,
                out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Attention of (B, H_q, 1, d) queries over everything cached for the layer (its last ``window`` tokens
-        for a sliding-window layer), read in place from the compressed planes."""
+        """Attention of (B, H_q, T_q, d) queries over everything cached for the layer (its last ``window`` tokens
+        for a sliding-window layer), read in place from the compressed planes.  The queries are the last ``T_q``
+        positions of the cache (call ``update`` first): one decode token sees everything, a prompt chunk is masked
+        causally, bottom-right aligned."""
         Kp, Vp = self._layers[layer_idx]
         dev = query_states.device
         tk, tv = self._inner.tables(layer_idx, 0, dev), self._inner.tables(layer_idx, 1, dev)
-        return fused_attention_packed(query_states, Kp, Vp, tk["table16"], tv["table16"], causal=False,
+        return fused_attention_packed(query_states, Kp, Vp, tk["table16"], tv["table16"],
+                                      causal="bottom_right" if query_states.shape[2] > 1 else False,
                                       softmax_scale=softmax_scale, window=self.sliding_window.get(layer_idx), out=out)
 
     def dense(self, layer_idx: int, dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -121,7 +121,7 @@ static int validate_attn(const hqmq_attn_args* a) {
   if (!(n == 4 || n == 8 || n == 12 || n == 16 || n == 32)) return HQMQ_ERR_UNSUPPORTED;
   if (a->r_qmax < 1 || a->r_qmax > 1023) return HQMQ_ERR_SHAPE;
   if (a->partials_only && !a->partials) return HQMQ_ERR_ARG;
-  if (a->kv_splits < 0 || a->window < 0) return HQMQ_ERR_ARG;
+  if (a->kv_splits < 0 || a->window < 0 || a->causal < 0 || a->causal > 2) return HQMQ_ERR_ARG;
   if (a->layout == 0) {
     int rc = check_packed(a->K, false);
     if (rc) return rc;

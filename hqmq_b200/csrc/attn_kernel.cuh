@@ -75,9 +75,12 @@ struct AttnParams {
 struct RingKernelInfo { const void* fn; size_t stage_bytes; };
 constexpr int kRingWarpsHost = 15;   // consumer warps of the ring kernels (one more warp produces)
 
-// Key range [beg, end) of query position tq and the tiles that cover it.
-__host__ __device__ inline void key_range(int Tkv, int causal, int window, int tq, int& beg, int& end) {
-  end = causal ? (tq + 1 < Tkv ? tq + 1 : Tkv) : Tkv;
+// Key range [beg, end) of query position tq.  causal 1: the reference's top-left aligned mask (query i sees keys
+// 0..i); causal 2: bottom-right aligned (the Tq queries are the LAST Tq positions of the Tkv keys: query i sees keys
+// 0..Tkv - Tq + i, a prompt chunk attending over a cache that already holds it).
+__host__ __device__ inline void key_range(int Tkv, int Tq, int causal, int window, int tq, int& beg, int& end) {
+  end = causal == 1 ? (tq + 1 < Tkv ? tq + 1 : Tkv) : causal == 2 ? (Tkv - Tq + tq + 1 > 0 ? Tkv - Tq + tq + 1 : 0) : Tkv;
+  if (end > Tkv) end = Tkv;
   beg = window > 0 ? (end - window > 0 ? end - window : 0) : 0;
 }
 
@@ -498,7 +501,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnParams& p) {
 
     // ---- this CTA's tiles of the unit ----------------------------------------------------------------
     int t_beg, t_end;
-    key_range(p.Tkv, p.causal, p.window, tq, t_beg, t_end);
+    key_range(p.Tkv, p.Tq, p.causal, p.window, tq, t_beg, t_end);
     const int tile_lo = t_beg / kTile, tile_hi = (t_end + kTile - 1) / kTile;
     const int64_t ubase = (int64_t)u * p.tpu_v;
     const int rel_lo = (int)(flat_lo > ubase ? flat_lo - ubase : 0);

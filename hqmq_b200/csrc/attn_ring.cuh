@@ -103,7 +103,7 @@ __device__ __forceinline__ UnitPiece unit_piece(const AttnParams& p, int u, int6
   q.h = u / upb;
   const int bt = u - q.h * upb;
   q.b = bt / p.Tq; q.tq = bt - q.b * p.Tq;
-  key_range(p.Tkv, p.causal, p.window, q.tq, q.t_beg, q.t_end);
+  key_range(p.Tkv, p.Tq, p.causal, p.window, q.tq, q.t_beg, q.t_end);
   const int tile_lo = q.t_beg / kTile, tile_hi = (q.t_end + kTile - 1) / kTile;
   const int64_t ubase = (int64_t)u * p.tpu_v;
   const int rel_lo = (int)(flat_lo > ubase ? flat_lo - ubase : 0);

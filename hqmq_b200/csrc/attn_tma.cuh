@@ -125,7 +125,7 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
     __syncthreads();
 
     int t_beg, t_end;
-    key_range(p.Tkv, p.causal, p.window, tq, t_beg, t_end);
+    key_range(p.Tkv, p.Tq, p.causal, p.window, tq, t_beg, t_end);
     const int tile_lo = t_beg / kTile, tile_hi = (t_end + kTile - 1) / kTile;
     const int64_t ubase = (int64_t)u * p.tpu_v;
     const int rel_lo = (int)(flat_lo > ubase ? flat_lo - ubase : 0);

@@ -303,7 +303,9 @@ typedef struct hqmq_attn_args {
   int64_t o_stride[3];
   int32_t B, H_q, H_kv, T_q, T_kv, d;
   int32_t r_qmax;
-  int32_t causal;            /* top-left aligned: query i sees keys 0..i (hqmq_attention.py:100,229) */
+  int32_t causal;            /* 0: none.  1: top-left aligned, query i sees keys 0..i (hqmq_attention.py:100,229).
+                                2: bottom-right aligned, query i sees keys 0..T_kv - T_q + i (the queries are the
+                                last T_q positions of a cache that already holds them: a prompt chunk) */
   int32_t window;            /* > 0: only the last `window` keys (sliding window); 0 = all */
   float softmax_scale;       /* <= 0: 1/sqrt(d) */
   int32_t kv_splits;         /* 0 = choose; n > 0 = split the key range into n pieces */

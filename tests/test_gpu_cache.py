@@ -164,3 +164,34 @@ def test_pair_append_equals_two_single_appends(outliers):
         names += ["ofrag", "ofrag_off"] if a.with_ofrag else []
         for name in names:
             assert torch.equal(getattr(a, name), getattr(b, name)), name
+
+
+@pytest.mark.parametrize("T_prompt,T_chunk,window", [(300, 5, None), (1500, 37, None), (200, 9, 64), (3, 3, None)])
+def test_prompt_chunk_attends_causally_over_the_cache(T_prompt, T_chunk, window):
+    """A chunk of T_q prompt tokens is appended and then attends over the cache that now holds it: query i sees
+    the keys up to its own position (bottom-right aligned mask), within the layer's window if it has one.  Against
+    the oracle called once per query position over the keys that position may see."""
+    B, Hkv, Hq, d, S, br = 2, 2, 8, 64, 96, 4
+    inner = hqmq.HQMQ(1, Hkv, S, br, device="cuda")
+    q = hqmq.with_outlier_extraction(inner, 3.0)
+    cache = PackedKVCache(q, max_tokens=2048, sliding_window={0: window} if window else None)
+    K = make_kv("hot", (B, Hkv, T_prompt, d), seed=61, dtype=torch.bfloat16)
+    V = make_kv("randn", (B, Hkv, T_prompt, d), seed=62, dtype=torch.bfloat16)
+    first = T_prompt - T_chunk
+    if first:
+        cache.update(K[:, :, :first].cuda(), V[:, :, :first].cuda(), 0)
+    Kp, Vp = cache.update(K[:, :, first:].cuda(), V[:, :, first:].cuda(), 0)
+    Q = (torch.randn(B, Hq, T_chunk, d, generator=torch.Generator().manual_seed(63)) / math.sqrt(d)).bfloat16()
+    O = torch.empty(Q.shape, dtype=torch.float32, device="cuda")
+    cache.attend(Q.cuda(), 0, out=O)
+    ki, kr, ks, kf = (t.cpu() for t in Kp.to_reference())
+    vi, vr, vs, vf = (t.cpu() for t in Vp.to_reference())
+    tk, tv = inner.tables(0, 0, "cuda"), inner.tables(0, 1, "cuda")
+    for i in range(T_chunk):
+        n = first + i + 1                      # keys query i may see
+        ref = orc.fused_attention(Q[:, :, i:i + 1], ki[:, :, :n], kr[:, :, :n], ks[:, :, :n], tk["joint"].cpu(),
+                                  vi[:, :, :n], vr[:, :, :n], vs[:, :, :n], tv["joint"].cpu(), (1 << br) - 1, causal=False,
+                                  K_flags=kf[:, :, :n], K_orig=K[:, :, :n], V_flags=vf[:, :, :n], V_orig=V[:, :, :n],
+                                  window=window)
+        err = (O[:, :, i:i + 1].cpu() - ref).abs().max().item()
+        assert err < 2e-3, f"query {i}: max-abs {err:.2e}"

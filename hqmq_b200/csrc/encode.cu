@@ -594,12 +594,35 @@ __global__ void __launch_bounds__(kSmallThreads) encode_small_pair_kernel(SmallP
 // one lane per chunk, no run-time geometry in the loop.  Results are the ones encode_main_kernel gives.
 constexpr int kEnc32Threads = 1024;   // one CTA per SM (the tables fill half of shared memory): 32 warps hide the search latency
 constexpr int kEnc32Warps = kEnc32Threads / 32;
-template <int DT, int IB, int RB>
+// Bracket mode (BR): a two-level select over a sample of the tokens has predicted the threshold statistic to a
+// relative 2^-13; the main pass then does everything that needs x in its one read.  Per head, `bp` holds a range
+// [R_lo, R_hi] of norm bits around the predicted statistic (+-1 %) and the bounds thr_lo / thr_hi of the threshold
+// that follow from it.  A chunk above thr_hi is flagged here (radius code 0, bit in the token's flag word), a chunk
+// at or below thr_lo is not, the few in between are listed for the fix-up; the norms inside the range are appended
+// to a list (one region per CTA) and the norms below it are counted, from which list_select_kernel takes the exact
+// order statistics -- and finds out whether the prediction held: if not, it raises the gate word and the
+// multi-pass kernels, which otherwise return at once, redo the call.
+struct BracketArgs {
+  const uint32_t* bp;       // [H][8]: R_lo, R_hi, thr_lo, thr_hi (float bits), norms below R_lo, ...
+  uint32_t* bp_count;       // same array, for the atomics
+  uint32_t* band;           // [H][kBandWords]: word 2 counts the undecided chunks
+  uint32_t* und;            // [H][kUndCap] undecided chunks
+  uint32_t* rcnt;           // [regions] norms appended per region (may exceed rcap: the list then overflowed)
+  uint32_t* rlist;          // [regions][rcap]
+  uint32_t* histA;          // [H][kHistBins] top digit of (norm bits - R_lo) of the norms inside the range
+  int rcap, und_cap;
+  const uint32_t* run_if;   // multi-pass (non-bracket) launch: return unless this word is non-zero (nullptr: run)
+};
+constexpr int kBpWords = 16;
+
+template <int DT, int IB, int RB, bool BR>
 __global__ void __launch_bounds__(kEnc32Threads, 1)
 encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __restrict__ qs_all, hqmq_packed dst,
                      int t_start, uint32_t* __restrict__ hist, Maps24 maps, const float* __restrict__ joint_all,
                      const unsigned char* __restrict__ lut, Mul24 nmul, int iters,
-                     const uint32_t* __restrict__ sel_s) {
+                     const uint32_t* __restrict__ sel_s, BracketArgs br) {
+  if (!BR && br.run_if && *br.run_if == 0u) return;
+  __shared__ uint32_t s_below, s_rcount;
   constexpr int CB = IB + RB;
   constexpr int RW = 32 * CB / 32;                       // words per row
   constexpr float qmaxf = (float)((1 << RB) - 1);
@@ -615,13 +638,22 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = g.S;
   for (int i = threadIdx.x; i < S; i += blockDim.x) qs[i] = reinterpret_cast<const float4*>(qs_all)[(int64_t)h * S + i];
-  if (hist) for (int i = threadIdx.x; i < 3 * kHistBins; i += blockDim.x) shist[i] = 0;   // shist and sh1
+  if (hist || BR) for (int i = threadIdx.x; i < 3 * kHistBins; i += blockDim.x) shist[i] = 0;   // shist and sh1
   for (int i = threadIdx.x; i < 24 * S; i += blockDim.x) sjoint[i] = reinterpret_cast<const float4*>(joint_all)[(int64_t)h * 24 * S + i];
   const LutView L = lut_to_smem(lut, h, reinterpret_cast<unsigned char*>(sjoint + 24 * S), nmul);
   const float inv_S = 1.0f / (float)S;
   // Bins (norm bits 31:21) that a sample of the call says hold the two middle order statistics: their next
   // 11-bit digit is histogrammed here too, which spares a pass over x when the sample was right.
   const uint32_t pb0 = sel_s ? sel_s[h * 8 + 0] >> 21 : 0xffffffffu, pb1 = sel_s ? sel_s[h * 8 + 2] >> 21 : 0xffffffffu;
+  uint32_t r_lo = 0u, r_hi = 0u, n_below = 0u, s1 = 0u;
+  float thr_lo = 0.f, thr_hi = 0.f;
+  const int region = blockIdx.y * gridDim.x + blockIdx.x;
+  if constexpr (BR) {
+    r_lo = br.bp[h * kBpWords + 0]; r_hi = br.bp[h * kBpWords + 1];
+    thr_lo = __uint_as_float(br.bp[h * kBpWords + 2]); thr_hi = __uint_as_float(br.bp[h * kBpWords + 3]);
+    s1 = br.bp[h * kBpWords + 5];
+    if (threadIdx.x == 0) { s_below = 0u; s_rcount = 0u; }
+  }
   __syncthreads();
 
   uint32_t* myrow = rows + warp * kMaxRowWords;
@@ -649,6 +681,30 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
     float rqf = rintf(quo);
     if (fabsf(quo - rqf) > 0.499f) rqf = rintf(__fdiv_rn(radius, scale));
     rqf = fminf(fmaxf(rqf, 0.f), qmaxf);
+    uint32_t flag_word = 0u;
+    if constexpr (BR) {
+      const uint32_t key = __float_as_uint(nrm);
+      const bool certain = nrm > thr_hi;
+      if (certain) rqf = 0.f;                       // a flagged chunk's values live in the side buffer
+      flag_word = __ballot_sync(0xffffffffu, certain);
+      if (!certain && nrm > thr_lo) {               // rare: settled against the exact threshold afterwards
+        const uint32_t pos = atomicAdd(&br.band[h * kBandWords + 2], 1u);
+        if (pos < (uint32_t)br.und_cap) br.und[(int64_t)h * br.und_cap + pos] = (uint32_t)(((int64_t)b * g.T_new + t) * 32 + lane);
+      }
+      n_below += __popc(__ballot_sync(0xffffffffu, key < r_lo));       // (every lane keeps the warp's count)
+      const bool in_range = key >= r_lo && key <= r_hi;
+      const uint32_t m = __ballot_sync(0xffffffffu, in_range);
+      if (m) {
+        uint32_t base = 0u;
+        if (lane == 0) base = atomicAdd(&s_rcount, (uint32_t)__popc(m));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (in_range) {
+          const uint32_t pos = base + __popc(m & ((1u << lane) - 1u));
+          if (pos < (uint32_t)br.rcap) br.rlist[(int64_t)region * br.rcap + pos] = key;
+          atomicAdd(&shist[((key - r_lo) >> s1) & (kHistBins - 1)], 1u);
+        }
+      }
+    }
 
     // ---- nearest codeword ---------------------------------------------------------------------------
     // (the nearest codeword does not depend on the chunk's length: a cheaply normalised copy keeps the
@@ -683,16 +739,28 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
     }
     if (lane == 0) {
       store_scale(dst, row, rmax);
-      if (dst.flags) dst.flags[row] = 0u;
+      if (dst.flags) dst.flags[row] = flag_word;
     }
-    if (hist) {
+    if (!BR && hist) {
       const uint32_t key = __float_as_uint(nrm), top = key >> 21;
       atomicAdd(&shist[top], 1u);
       if (top == pb0) atomicAdd(&sh1[(key >> 10) & 0x7ffu], 1u);
       else if (top == pb1) atomicAdd(&sh1[kHistBins + ((key >> 10) & 0x7ffu)], 1u);
     }
   }
-  if (hist) {
+  if constexpr (BR) {
+    if (lane == 0 && n_below) atomicAdd(&s_below, n_below);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (s_below) atomicAdd(&br.bp_count[h * kBpWords + 4], s_below);
+      br.rcnt[region] = s_rcount;
+      if (s_rcount > (uint32_t)br.rcap) atomicOr(&br.bp_count[h * kBpWords + 10], 1u);
+    }
+    uint32_t* gA = br.histA + (int64_t)h * kHistBins;
+    for (int i = threadIdx.x; i < kHistBins; i += blockDim.x)
+      if (shist[i]) atomicAdd(&gA[i], shist[i]);
+  }
+  if (!BR && hist) {
     __syncthreads();
     uint32_t* gh = hist + (int64_t)h * 3 * 2 * kHistBins;  // level 0, query 0
     for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) {
@@ -716,8 +784,10 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
 __global__ void __launch_bounds__(256)
 select_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ sel, int level, uint64_t N, float C,
               float* __restrict__ med_out, uint32_t* __restrict__ band, const uint32_t* __restrict__ sel_s,
-              const uint32_t* __restrict__ hist_fb, float quantile) {
+              const uint32_t* __restrict__ hist_fb, float quantile, const uint32_t* __restrict__ gate, int gate_want) {
   __shared__ uint64_t wtot[8];
+  if (gate && (*gate != 0u) != (gate_want != 0)) return;   // (this launch belongs to the other of the two paths)
+
   const int h = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;   // launched with 256 threads
   uint32_t* st = sel + h * 8;
@@ -865,8 +935,10 @@ __device__ __forceinline__ void norms_of_two(const uint4& r, float& n0, float& n
 template <int DT>
 __global__ void __launch_bounds__(256)
 hist32_kernel(Fast32 f, uint32_t* __restrict__ hist, const uint32_t* __restrict__ sel, int level,
-              const uint32_t* __restrict__ sel_s, uint32_t* __restrict__ hist_fb) {
+              const uint32_t* __restrict__ sel_s, uint32_t* __restrict__ hist_fb, const uint32_t* __restrict__ gate, int gate_want) {
   __shared__ uint32_t sh[2][kHistBins];
+  if (gate && (*gate != 0u) != (gate_want != 0)) return;   // (this launch belongs to the other of the two paths)
+
   const int bh = blockIdx.y;
   const int h = bh % f.H, b = bh / f.H;
   // with a sampled prediction this pass is only the fallback: nothing to do when the sample named the right bins
@@ -915,17 +987,19 @@ hist32_kernel(Fast32 f, uint32_t* __restrict__ hist, const uint32_t* __restrict_
   }
 }
 
-// Level-0 histogram (norm bits 31:21) of every kSampleStride-th token: predicts the bins of the two middle
-// order statistics before the main pass runs.
+// Histogram of every kSampleStride-th token: level 0 (norm bits 31:21) predicts the bins of the two order
+// statistics before the main pass runs; level 1 (bits 20:10 of the sampled norms inside those bins, `sel_s` holding
+// the level-0 result) refines the prediction to 22 bits for the bracket mode of the main pass.
 constexpr int kSampleStride = 32;
 template <int DT>
 __global__ void __launch_bounds__(256)
-sample32_kernel(Fast32 f, uint32_t* __restrict__ hist_s) {
-  __shared__ uint32_t sh[kHistBins];
+sample32_kernel(Fast32 f, uint32_t* __restrict__ hist_s, int level, const uint32_t* __restrict__ sel_s) {
+  __shared__ uint32_t sh[2][kHistBins];
   const int bh = blockIdx.y;
   const int h = bh % f.H, b = bh / f.H;
-  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) sh[i] = 0;
+  for (int i = threadIdx.x; i < 2 * kHistBins; i += blockDim.x) (&sh[0][0])[i] = 0;
   __syncthreads();
+  const uint32_t q0 = level ? sel_s[h * 8 + 0] >> 21 : 0u, q1 = level ? sel_s[h * 8 + 2] >> 21 : 0u;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, l16 = lane & 15;
   const int n_s = (f.T_new + kSampleStride - 1) / kSampleStride;       // sampled tokens of this (b, h)
   const uint16_t* base = f.x + b * f.xs_b + h * f.xs_h + 8 * l16;
@@ -933,13 +1007,176 @@ sample32_kernel(Fast32 f, uint32_t* __restrict__ hist_s) {
     const uint4 r = *reinterpret_cast<const uint4*>(base + (int64_t)k * kSampleStride * f.xs_t);
     float n[2];
     norms_of_two<DT>(r, n[0], n[1]);
-    atomicAdd(&sh[__float_as_uint(n[0]) >> 21], 1u);
-    atomicAdd(&sh[__float_as_uint(n[1]) >> 21], 1u);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const uint32_t key = __float_as_uint(n[e]);
+      if (level == 0) atomicAdd(&sh[0][key >> 21], 1u);
+      else if ((key >> 21) == q0) atomicAdd(&sh[0][(key >> 10) & 0x7ffu], 1u);
+      else if ((key >> 21) == q1) atomicAdd(&sh[1][(key >> 10) & 0x7ffu], 1u);
+    }
   }
   __syncthreads();
-  uint32_t* gh = hist_s + (int64_t)h * 3 * 2 * kHistBins;   // laid out like the level-0 slot of the full histograms
-  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x)
-    if (sh[i]) atomicAdd(&gh[i], sh[i]);
+  // laid out like the full histograms: level 0 has one slot, level 1 one per order statistic
+  uint32_t* gh = hist_s + ((int64_t)h * 3 + level) * 2 * kHistBins;
+  const bool same = q0 == q1;
+  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) {
+    const uint32_t c0 = sh[0][i];
+    if (c0) atomicAdd(&gh[i], c0);
+    if (level) {
+      const uint32_t c1 = same ? c0 : sh[1][i];
+      if (c1) atomicAdd(&gh[kHistBins + i], c1);
+    }
+  }
+}
+
+// Bracket of the main pass from the sample's two-level select: the order statistics a <= b of the whole call are
+// expected inside [R_lo, R_hi] = [a_s (1 - delta), b_s (1 + delta)], where a_s / b_s are the sample's statistics known to
+// 22 bits (low bits 0 / all ones).  The threshold is fl(lerp(a, b, w) * C) with lerp(a, b, w) in [a, b] and fl
+// monotone, so it then lies in [fl(R_lo * C), fl(R_hi * C)].  Whether the expectation held is checked exactly by
+// list_select_kernel.
+__global__ void bracket_kernel(const uint32_t* __restrict__ sel_s, float C, float delta, int H, uint32_t* __restrict__ bp,
+                               uint32_t* __restrict__ band) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  const float a_s = __uint_as_float(sel_s[h * 8 + 0]), b_s = __uint_as_float(sel_s[h * 8 + 2] | 0x3ffu);
+  const float r_lo = __fmul_rn(a_s, 1.f - delta), r_hi = __fmul_rn(b_s, 1.f + delta);
+  bp[h * kBpWords + 0] = __float_as_uint(r_lo);
+  bp[h * kBpWords + 1] = __float_as_uint(r_hi);
+  bp[h * kBpWords + 2] = __float_as_uint(__fmul_rn(r_lo, C));
+  bp[h * kBpWords + 3] = __float_as_uint(__fmul_rn(r_hi, C));
+  // top digit of (norm bits - R_lo): 2048 bins of 2^s1 keys cover the range (a range wider than 2^22 keys -- a
+  // statistic next to zero -- is left to the multi-pass path)
+  const uint32_t width = __float_as_uint(r_hi) - __float_as_uint(r_lo);
+  const int bits = 32 - __clz(width | 1u);
+  bp[h * kBpWords + 5] = (uint32_t)(bits > 11 ? bits - 11 : 0);
+  band[h * kBandWords + 0] = bp[h * kBpWords + 2];
+  band[h * kBandWords + 1] = bp[h * kBpWords + 3];
+}
+
+// ---- exact order statistics of a head from what the bracket pass left ------------------------------------------
+// The pass counted the norms below the range, histogrammed the top digit of (norm bits - R_lo) for the norms inside
+// it (`histA`, 2048 bins of 2^s1 keys each) and listed those norms per CTA region.  list_pickA_kernel checks that both
+// order statistics fall inside the range (else the prediction failed and the gate word is raised) and names the bin
+// of the lower one and the next non-empty bin; list_histB_kernel histograms the low s1 bits of the listed norms
+// of those two bins; list_pickB_kernel then has both statistics exactly and writes the select words of the head
+// (a, b, threshold, statistic) like the last level of select_kernel.
+// bp words: 0 R_lo, 1 R_hi, 2 thr_lo, 3 thr_hi, 4 norms below R_lo, 5 s1, 6 bin of a, 7 next non-empty bin (or ~0),
+// 8 rank of a inside its bin, 9 listed norms before the bin of a, 10 a region overflowed
+template <int NT>
+__device__ __forceinline__ void block_find_rank(const uint32_t* __restrict__ hist, int nbins, uint32_t rank, uint32_t* s_part,
+                                                int& bin, uint32_t& before, int& next_bin) {
+  // hist in shared or global memory; every thread sums its stretch, thread 0 walks the stretch sums
+  const int tid = threadIdx.x, per = (nbins + NT - 1) / NT;
+  uint32_t mine = 0;
+  for (int i = tid * per; i < min(nbins, (tid + 1) * per); ++i) mine += hist[i];
+  s_part[tid] = mine;
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t acc = 0; int t = 0;
+    while (t < NT - 1 && acc + s_part[t] <= rank) acc += s_part[t++];
+    int i = t * per;
+    const int end = min(nbins, (t + 1) * per);
+    while (i < end - 1 && acc + hist[i] <= rank) acc += hist[i++];
+    int nx = i + 1;
+    while (nx < nbins && hist[nx] == 0u) ++nx;
+    s_part[NT] = (uint32_t)i; s_part[NT + 1] = acc; s_part[NT + 2] = nx < nbins ? (uint32_t)nx : 0xffffffffu;
+  }
+  __syncthreads();
+  bin = (int)s_part[NT]; before = s_part[NT + 1]; next_bin = (int)s_part[NT + 2];
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(256)
+list_pickA_kernel(uint32_t* __restrict__ bp, const uint32_t* __restrict__ histA, uint64_t N, float quantile,
+                  uint32_t* __restrict__ gate) {
+  __shared__ uint32_t s_part[256 + 4];
+  __shared__ uint32_t s_tot;
+  const int h = blockIdx.x, tid = threadIdx.x;
+  const uint32_t* hA = histA + (int64_t)h * kHistBins;
+  if (tid == 0) s_tot = 0u;
+  __syncthreads();
+  uint32_t mine = 0;
+  for (int i = tid; i < kHistBins; i += 256) mine += hA[i];
+  if (mine) atomicAdd(&s_tot, mine);
+  __syncthreads();
+  const QRank qr = quantile_rank(N, quantile);
+  const uint64_t below = bp[h * kBpWords + 4];
+  const bool ok = !bp[h * kBpWords + 10] && bp[h * kBpWords + 5] <= 11u && qr.lo >= below && qr.hi < below + s_tot;
+  if (!ok) {
+    if (tid == 0) atomicExch(gate, 1u);
+    return;
+  }
+  int bin, next_bin; uint32_t before;
+  block_find_rank<256>(hA, kHistBins, (uint32_t)(qr.lo - below), s_part, bin, before, next_bin);
+  if (tid == 0) {
+    bp[h * kBpWords + 6] = (uint32_t)bin;
+    bp[h * kBpWords + 7] = (uint32_t)next_bin;
+    bp[h * kBpWords + 8] = (uint32_t)(qr.lo - below) - before;
+    bp[h * kBpWords + 9] = before;
+  }
+}
+
+// grid = the main pass's grid (one CTA per list region)
+__global__ void __launch_bounds__(256)
+list_histB_kernel(const uint32_t* __restrict__ bp, const uint32_t* __restrict__ rcnt, const uint32_t* __restrict__ rlist, int rcap,
+                  int H, uint32_t* __restrict__ histB, const uint32_t* __restrict__ gate) {
+  if (*gate) return;
+  const int bh = blockIdx.y, h = bh % H;
+  const int region = blockIdx.y * gridDim.x + blockIdx.x;
+  const uint32_t r_lo = bp[h * kBpWords + 0], s1 = bp[h * kBpWords + 5];
+  const uint32_t bin0 = bp[h * kBpWords + 6], bin1 = bp[h * kBpWords + 7];
+  const uint32_t lowmask = (1u << s1) - 1u;
+  uint32_t c = rcnt[region];
+  if (c > (uint32_t)rcap) c = rcap;
+  const uint32_t* keys = rlist + (int64_t)region * rcap;
+  uint32_t* hB = histB + (int64_t)h * 2 * kHistBins;
+  // (the bins hold few keys: straight to the global histograms)
+  for (uint32_t i0 = threadIdx.x; i0 < c; i0 += 4 * 256) {
+    uint32_t k[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) k[u] = i0 + u * 256 < c ? keys[i0 + u * 256] : 0xffffffffu;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (i0 + u * 256 < c) {
+        const uint32_t off = k[u] - r_lo, top = off >> s1;
+        if (top == bin0) atomicAdd(&hB[off & lowmask], 1u);
+        else if (top == bin1) atomicAdd(&hB[kHistBins + (off & lowmask)], 1u);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+list_pickB_kernel(const uint32_t* __restrict__ bp, const uint32_t* __restrict__ histB, uint64_t N, float C, float quantile,
+                  uint32_t* __restrict__ sel, float* __restrict__ med_out, const uint32_t* __restrict__ gate) {
+  __shared__ uint32_t s_part[256 + 4];
+  if (*gate) return;
+  const int h = blockIdx.x, tid = threadIdx.x;
+  const uint32_t r_lo = bp[h * kBpWords + 0], s1 = bp[h * kBpWords + 5];
+  const uint32_t bin0 = bp[h * kBpWords + 6], bin1 = bp[h * kBpWords + 7], rank = bp[h * kBpWords + 8];
+  const uint32_t* hB = histB + (int64_t)h * 2 * kHistBins;
+  const int nb = 1 << s1;
+  int bin, next_bin; uint32_t before;
+  block_find_rank<256>(hB, nb, rank, s_part, bin, before, next_bin);
+  // smallest key of the next non-empty top bin (the upper statistic when a is the last key of its bin)
+  int first1 = 0, dummy_n; uint32_t dummy_b;
+  if (bin1 != 0xffffffffu) block_find_rank<256>(hB + kHistBins, nb, 0u, s_part, first1, dummy_b, dummy_n);
+  if (tid == 0) {
+    const QRank qr = quantile_rank(N, quantile);
+    const uint32_t a_bits = r_lo + (bin0 << s1) + (uint32_t)bin;
+    uint32_t b_bits = a_bits;
+    if (qr.hi != qr.lo && before + hB[bin] <= rank + 1u) {      // the key after a's run of equal keys
+      if (next_bin != -1) b_bits = r_lo + (bin0 << s1) + (uint32_t)next_bin;
+      else b_bits = r_lo + (bin1 << s1) + (uint32_t)first1;      // (pickA made sure the statistic exists in the list)
+    }
+    const float a = __uint_as_float(a_bits), b = __uint_as_float(b_bits);
+    const float med = qr.hi == qr.lo ? a : quantile_lerp(a, b, qr.w);
+    uint32_t* st = sel + h * 8;
+    st[4] = a_bits; st[5] = b_bits;
+    st[6] = __float_as_uint(__fmul_rn(med, C));
+    st[7] = __float_as_uint(med);
+    if (med_out) med_out[h] = med;
+  }
 }
 
 // Clear the radius code of chunk c in a packed row (atomics: other threads may own neighbouring chunks).
@@ -968,8 +1205,11 @@ __device__ __forceinline__ void flag_late(const hqmq_packed& dst, int64_t row, i
 template <int DT>
 __global__ void __launch_bounds__(256)
 histflags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, uint32_t* __restrict__ hist,
-                   const uint32_t* __restrict__ sel, uint32_t* __restrict__ band, uint32_t* __restrict__ und) {
+                   const uint32_t* __restrict__ sel, uint32_t* __restrict__ band, uint32_t* __restrict__ und,
+                   const uint32_t* __restrict__ gate, int gate_want) {
   __shared__ uint32_t sh[2][1024];
+  if (gate && (*gate != 0u) != (gate_want != 0)) return;   // (this launch belongs to the other of the two paths)
+
   const int bh = blockIdx.y;
   const int h = bh % f.H, b = bh / f.H;
   for (int i = threadIdx.x; i < 2 * 1024; i += blockDim.x) (&sh[0][0])[i] = 0;
@@ -1046,13 +1286,15 @@ histflags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, ui
 template <int DT>
 __global__ void __launch_bounds__(256)
 fixup_list_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, const uint32_t* __restrict__ sel,
-                  const uint32_t* __restrict__ band, const uint32_t* __restrict__ und) {
+                  const uint32_t* __restrict__ band, const uint32_t* __restrict__ und, const uint32_t* __restrict__ gate,
+                  int gate_want, int und_cap) {
+  if (gate && (*gate != 0u) != (gate_want != 0)) return;   // (this launch belongs to the other of the two paths)
   const int h = blockIdx.x;
   const uint32_t n = band[h * kBandWords + 2];
-  if (n == 0 || n > (uint32_t)kUndCap) return;
+  if (n == 0 || n > (uint32_t)und_cap) return;
   const float thr = __uint_as_float(sel[h * 8 + 6]);
   for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-    const uint32_t e = und[(int64_t)h * kUndCap + i];
+    const uint32_t e = und[(int64_t)h * und_cap + i];
     const int c = e & 31;
     const int64_t bt = e >> 5;
     const int b = (int)(bt / f.T_new), t = (int)(bt - (int64_t)b * f.T_new);
@@ -1068,10 +1310,11 @@ fixup_list_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, con
 template <int DT>
 __global__ void __launch_bounds__(256)
 fixup_scan_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, const uint32_t* __restrict__ sel,
-                  const uint32_t* __restrict__ band) {
+                  const uint32_t* __restrict__ band, const uint32_t* __restrict__ gate, int gate_want, int und_cap) {
+  if (gate && (*gate != 0u) != (gate_want != 0)) return;   // (this launch belongs to the other of the two paths)
   const int bh = blockIdx.y;
   const int h = bh % f.H, b = bh / f.H;
-  if (band[h * kBandWords + 2] <= (uint32_t)kUndCap) return;
+  if (band[h * kBandWords + 2] <= (uint32_t)und_cap) return;
   const float thr = __uint_as_float(sel[h * 8 + 6]);
   const float thr_lo = __uint_as_float(band[h * kBandWords + 0]), thr_hi = __uint_as_float(band[h * kBandWords + 1]);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, l16 = lane & 15;
@@ -1597,7 +1840,31 @@ inline size_t lut_ws_bytes(int H) { return (size_t)H * kLutCellCap * 4 + (size_t
 // shared memory a main-pass kernel can give to a table next to its other arrays (fp32 joint table, histograms, rows)
 inline size_t lut_smem_budget(int S) { return (size_t)226 * 1024 - (size_t)24 * S * 16 - (size_t)S * 16 - 3 * kHistBins * 4 - 4096; }
 
-struct WsPlan { size_t status, hist, sel, band, und, hist_s, sel_s, hist_fb, total; int blk0, nblk; };
+// Geometry of the main pass for the common case (d_head 128, 16-bit input): tokens per CTA and CTAs per (b, h).
+struct MainGrid { int iters, gx; };
+static MainGrid main_grid(int T_new, int B, int H) {
+  MainGrid m;
+  // tokens per CTA: long enough to amortise loading the tables, short enough to fill the machine twice
+  int64_t it = ((int64_t)T_new * B * H + (int64_t)2 * 148 * kEnc32Warps - 1) / ((int64_t)2 * 148 * kEnc32Warps);
+  m.iters = it < 1 ? 1 : it > 128 ? 128 : (int)it;
+  m.gx = (T_new + kEnc32Warps * m.iters - 1) / (kEnc32Warps * m.iters);
+  return m;
+}
+// The bracket pass pays when the sample predicts well: the statistic's sampling error falls with the square root of
+// the sampled norms per head (a 1/32 sample of B * T_new tokens, 32 norms each), so the bracket's half-width is
+// 3 / sqrt(norms) (about six standard errors of a median), at least 0.2 % and at most 1.2 %; calls too small for that,
+// and quantiles out in the tails (few norms nearby: a much larger error), take the multi-pass path as before.
+constexpr int64_t kBracketMinTokens = 65536;     // B * T_new per head
+static bool bracket_wanted(const hqmq_encode_args& a) {
+  return a.median_mult > 0.f && !a.med_in && a.dst.n_chunks == 32 && is_half_dtype(a.x_dtype) &&
+         (int64_t)a.dst.B * a.T_new >= kBracketMinTokens && a.T_new >= 1024 &&
+         (a.quantile == 0.f || (a.quantile >= 0.25f && a.quantile <= 0.75f));
+}
+
+struct WsPlan {
+  size_t status, hist, sel, band, und, hist_s, sel_s, hist_fb, gate, bp, histA, histB, band_b, und_b, sel_b, rcnt, rlist, zero_bytes, total;
+  int blk0, nblk, rcap, regions, und_cap;
+};
 WsPlan plan_ws(const hqmq_encode_args& a) {
   WsPlan w;
   const int H = a.dst.H;
@@ -1612,6 +1879,29 @@ WsPlan plan_ws(const hqmq_encode_args& a) {
   w.hist_s = o; o += (size_t)H * 3 * 2 * kHistBins;   // sampled histograms (level-0 slot used)
   w.sel_s = o; o += (size_t)H * 8;
   w.hist_fb = o; o += (size_t)H * 2 * kHistBins;      // level 1 when the sample mispredicted
+  // bracket mode of the main pass (reserved whenever the call could take it)
+  w.gate = w.bp = w.histA = w.histB = w.band_b = w.und_b = w.sel_b = w.rcnt = w.rlist = 0;
+  w.rcap = w.regions = w.und_cap = 0;
+  w.zero_bytes = o * sizeof(uint32_t);
+  if (bracket_wanted(a)) {
+    const MainGrid mg = main_grid(a.T_new, a.dst.B, H);
+    w.regions = mg.gx * a.dst.B * H;
+    w.rcap = kEnc32Warps * mg.iters * 32 / 16;        // a sixteenth of a CTA's chunks (the range holds about 2 %)
+    w.gate = o; o += 4;
+    w.bp = o; o += (size_t)H * kBpWords;
+    w.histA = o; o += (size_t)H * kHistBins;
+    w.histB = o; o += (size_t)H * 2 * kHistBins;
+    w.band_b = o; o += (size_t)H * kBandWords;
+    w.sel_b = o; o += (size_t)H * 8;
+    w.rcnt = o; o += (size_t)w.regions;
+    w.zero_bytes = o * sizeof(uint32_t);              // everything up to here starts at zero; the lists need not
+    // the undecided list: the bracket is wider than the multi-pass path's band (a few per mille of the chunks of a
+    // head with many outliers fall inside it)
+    const int64_t per_head = (int64_t)a.dst.B * a.T_new * 32;
+    w.und_cap = (int)(per_head / 256 > kUndCap ? (per_head / 256 < (1 << 20) ? per_head / 256 : (1 << 20)) : kUndCap);
+    w.und_b = o; o += (size_t)H * w.und_cap;
+    w.rlist = o; o += (size_t)w.regions * w.rcap;
+  }
   w.total = o * sizeof(uint32_t);
   return w;
 }
@@ -1761,7 +2051,7 @@ extern "C" int hqmq_med3x_select(int H, int level, uint64_t n_total, float media
   uint32_t* hist = reinterpret_cast<uint32_t*>(state);
   uint32_t* sel = hist + (size_t)H * 3 * 2 * kHistBins;
   select_kernel<<<H, 256, 0, (cudaStream_t)stream>>>(hist, sel, level, n_total, median_mult, level == 2 ? med_out : nullptr,
-                                                     nullptr, nullptr, nullptr, 0.f);
+                                                     nullptr, nullptr, nullptr, 0.f, nullptr, 0);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }
@@ -1873,7 +2163,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     HQMQ_LAUNCH_CHECK();
     return HQMQ_OK;
   }
-  HQMQ_CHECK_CUDA(cudaMemsetAsync(ws, 0, wp.total, st));
+  HQMQ_CHECK_CUDA(cudaMemsetAsync(ws, 0, wp.zero_bytes, st));
 
   const int tok_per_block = kEncWarps * g.tpw * kEncIters;
   dim3 grid((a->T_new + tok_per_block - 1) / tok_per_block, d.B * d.H);
@@ -1895,45 +2185,95 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   if (use_lut && (uintptr_t)a->lut & 15) return HQMQ_ERR_ALIGN;
   // specialised kernel: d_head 128, 16-bit input, one of the compiled field layouts
   const void* fastk = nullptr;
+  const void* fastk_br = nullptr;
   bool predicted = false;
+  const uint32_t* gate = nullptr;      // bracket mode: the word that sends the call through the multi-pass kernels after all
   if (use_lut && g.n == 32 && is_half_dtype(a->x_dtype)) {
     const bool h16 = a->x_dtype == HQMQ_F16;
 #define HQMQ_PICK(IB_, RB_)                                                                              \
-    if (g.ib == IB_ && g.rbits == RB_)                                                                     \
-      fastk = h16 ? (const void*)&encode_main32_kernel<HQMQ_F16, IB_, RB_> : (const void*)&encode_main32_kernel<HQMQ_BF16, IB_, RB_>;
+    if (g.ib == IB_ && g.rbits == RB_) {                                                                   \
+      fastk = h16 ? (const void*)&encode_main32_kernel<HQMQ_F16, IB_, RB_, false>                          \
+                  : (const void*)&encode_main32_kernel<HQMQ_BF16, IB_, RB_, false>;                        \
+      fastk_br = h16 ? (const void*)&encode_main32_kernel<HQMQ_F16, IB_, RB_, true>                        \
+                     : (const void*)&encode_main32_kernel<HQMQ_BF16, IB_, RB_, true>;                      \
+    }
     HQMQ_PICK(10, 3) HQMQ_PICK(12, 4) HQMQ_PICK(13, 6)
 #undef HQMQ_PICK
   }
   if (fastk) {
     const size_t smem_fast = (size_t)g.S * 16 + (size_t)kEnc32Warps * kMaxRowWords * 4 + 3 * kHistBins * 4 + (size_t)24 * g.S * 16 +
                              lut_foot + 16;
-    // tokens per CTA: long enough to amortise loading the tables, short enough to fill the machine twice
-    int iters = (int)(((int64_t)a->T_new * d.B * d.H + (int64_t)2 * 148 * kEnc32Warps - 1) / ((int64_t)2 * 148 * kEnc32Warps));
-    if (iters < 1) iters = 1;
-    if (iters > 128) iters = 128;
-    if (smem_fast > 48 * 1024)
+    const MainGrid mg = main_grid(a->T_new, d.B, d.H);
+    int iters = mg.iters;
+    if (smem_fast > 48 * 1024) {
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(fastk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fast));
-    dim3 fgrid((a->T_new + kEnc32Warps * iters - 1) / (kEnc32Warps * iters), d.B * d.H);
-    // Med3x: a sample of the tokens predicts which bins hold the two middle order statistics, so that this
-    // pass can histogram their next digit as well (level 1 of the radix select then needs no pass of its own)
+      HQMQ_CHECK_CUDA(cudaFuncSetAttribute(fastk_br, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fast));
+    }
+    dim3 fgrid(mg.gx, d.B * d.H);
+    // Med3x: a sample of the tokens predicts the threshold statistic.  Two select levels over the sample give it
+    // to 22 bits, the bracket pass then needs x only once; should the prediction fail, the multi-pass kernels
+    // below (gated on a word the bracket's check raises) redo the call, with the sample's first level telling the
+    // main pass which bins to refine.
     predicted = med && !ext_med && fast32 && a->T_new >= 1024;
+    const bool bracket = predicted && bracket_wanted(*a) && wp.regions == (int)(fgrid.x * fgrid.y);
+    const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a->x);
+    const unsigned char* lut_arg = reinterpret_cast<const unsigned char*>(a->lut);
+    int t_start_arg = a->t_start;
+    BracketArgs brargs{};
     if (predicted) {
       const int n_s = (a->T_new + kSampleStride - 1) / kSampleStride;
+      const uint64_t N_s = (uint64_t)d.B * n_s * 32;
       int gs = (148 * 8 + d.B * d.H - 1) / (d.B * d.H);
       if (gs > (n_s + 15) / 16) gs = (n_s + 15) / 16;
       if (gs < 1) gs = 1;
-      if (a->x_dtype == HQMQ_F16) sample32_kernel<HQMQ_F16><<<dim3(gs, d.B * d.H), 256, 0, st>>>(f32, ws + wp.hist_s);
-      else sample32_kernel<HQMQ_BF16><<<dim3(gs, d.B * d.H), 256, 0, st>>>(f32, ws + wp.hist_s);
-      select_kernel<<<d.H, 256, 0, st>>>(ws + wp.hist_s, ws + wp.sel_s, 0, (uint64_t)d.B * n_s * 32, a->median_mult, nullptr,
-                                         nullptr, nullptr, nullptr, a->quantile);
+      const bool h16s = a->x_dtype == HQMQ_F16;
+      uint32_t* hist_s = ws + wp.hist_s;
+      uint32_t* sel_s_w = ws + wp.sel_s;
+      for (int level = 0; level < (bracket ? 2 : 1); ++level) {
+        if (h16s) sample32_kernel<HQMQ_F16><<<dim3(gs, d.B * d.H), 256, 0, st>>>(f32, hist_s, level, sel_s_w);
+        else sample32_kernel<HQMQ_BF16><<<dim3(gs, d.B * d.H), 256, 0, st>>>(f32, hist_s, level, sel_s_w);
+        select_kernel<<<d.H, 256, 0, st>>>(hist_s, sel_s_w, level, N_s, a->median_mult, nullptr, nullptr, nullptr, nullptr,
+                                           a->quantile, nullptr, 0);
+      }
+    }
+    if (bracket) {
+      const bool h16s = a->x_dtype == HQMQ_F16;
+      uint32_t* sel_s_w = ws + wp.sel_s;
+      const int n_s = (a->T_new + kSampleStride - 1) / kSampleStride;
+      float delta = 3.0f / sqrtf((float)d.B * (float)n_s * 32.f);
+      delta = delta < 0.002f ? 0.002f : delta > 0.012f ? 0.012f : delta;
+      uint32_t* bp = ws + wp.bp;
+      bracket_kernel<<<(d.H + 63) / 64, 64, 0, st>>>(sel_s_w, a->median_mult, delta, d.H, bp, ws + wp.band_b);
+      gate = ws + wp.gate;
+      brargs.bp = bp; brargs.bp_count = bp; brargs.band = ws + wp.band_b; brargs.und = ws + wp.und_b;
+      brargs.rcnt = ws + wp.rcnt; brargs.rlist = ws + wp.rlist; brargs.histA = ws + wp.histA; brargs.rcap = wp.rcap; brargs.und_cap = wp.und_cap;
+      brargs.run_if = nullptr;
+      uint32_t* no_hist = nullptr;
+      const uint32_t* no_sel = nullptr;
+      void* kargs_b[] = {(void*)&g, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&no_hist, (void*)&maps,
+                         (void*)&a->joint, (void*)&lut_arg, (void*)&nmul, (void*)&iters, (void*)&no_sel, (void*)&brargs};
+      HQMQ_CHECK_CUDA(cudaLaunchKernel(fastk_br, fgrid, dim3(kEnc32Threads), kargs_b, smem_fast, st));
+      const uint64_t N_all = (uint64_t)d.B * a->T_new * d.n_chunks;
+      list_pickA_kernel<<<d.H, 256, 0, st>>>(bp, ws + wp.histA, N_all, a->quantile, ws + wp.gate);
+      list_histB_kernel<<<fgrid, 256, 0, st>>>(bp, ws + wp.rcnt, ws + wp.rlist, wp.rcap, d.H, ws + wp.histB, gate);
+      list_pickB_kernel<<<d.H, 256, 0, st>>>(bp, ws + wp.histB, N_all, a->median_mult, a->quantile, ws + wp.sel_b, a->med_out, gate);
+      int fg = (148 * 32 + d.B * d.H - 1) / (d.B * d.H);
+      const int fg_max = (a->T_new + kF32Tok - 1) / kF32Tok;
+      if (fg > fg_max) fg = fg_max;
+      if (fg < 1) fg = 1;
+      if (h16s) {
+        fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, ws + wp.und_b, gate, 0, wp.und_cap);
+        fixup_scan_kernel<HQMQ_F16><<<dim3(fg, d.B * d.H), 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, gate, 0, wp.und_cap);
+      } else {
+        fixup_list_kernel<HQMQ_BF16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, ws + wp.und_b, gate, 0, wp.und_cap);
+        fixup_scan_kernel<HQMQ_BF16><<<dim3(fg, d.B * d.H), 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, gate, 0, wp.und_cap);
+      }
+      brargs.run_if = gate;       // the multi-pass launch below runs only if the check raised the gate
     }
     const uint32_t* sel_s_arg = predicted ? ws + wp.sel_s : nullptr;
-    const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a->x);
     uint32_t* hist_arg = med && !ext_med ? ws + wp.hist : nullptr;
-    const unsigned char* lut_arg = reinterpret_cast<const unsigned char*>(a->lut);
-    int t_start_arg = a->t_start;
     void* kargs[] = {(void*)&g, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&hist_arg, (void*)&maps,
-                     (void*)&a->joint, (void*)&lut_arg, (void*)&nmul, (void*)&iters, (void*)&sel_s_arg};
+                     (void*)&a->joint, (void*)&lut_arg, (void*)&nmul, (void*)&iters, (void*)&sel_s_arg, (void*)&brargs};
     HQMQ_CHECK_CUDA(cudaLaunchKernel(fastk, fgrid, dim3(kEnc32Threads), kargs, smem_fast, st));
   } else if (use_lut) {
     if (smem_lut > 48 * 1024)
@@ -1986,28 +2326,28 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     if (fb < 1) fb = 1;
     flags_kernel<<<dim3(fb, d.B * d.H), 256, 0, st>>>(g, a->x, d, a->t_start, sel);
   } else {
-  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr, nullptr, nullptr, nullptr, a->quantile);
+  select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 0, N, a->median_mult, nullptr, nullptr, nullptr, nullptr, a->quantile, gate, 1);
   if (fast32) {
     // (with a prediction this launch returns at once unless the sample named the wrong bins)
-    if (h16) hist32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1, sel_s, hist_fb);
-    else hist32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1, sel_s, hist_fb);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, band, sel_s, hist_fb, a->quantile);
+    if (h16) hist32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1, sel_s, hist_fb, gate, 1);
+    else hist32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, hist, sel, 1, sel_s, hist_fb, gate, 1);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, band, sel_s, hist_fb, a->quantile, gate, 1);
     // last histogram level and provisional flags in one pass, exact threshold, then the (normally empty) fix-up
-    if (h16) histflags32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und);
-    else histflags32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr, a->quantile);
+    if (h16) histflags32_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und, gate, 1);
+    else histflags32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und, gate, 1);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr, a->quantile, gate, 1);
     if (h16) {
-      fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und);
-      fixup_scan_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band);
+      fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und, gate, 1, kUndCap);
+      fixup_scan_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, gate, 1, kUndCap);
     } else {
-      fixup_list_kernel<HQMQ_BF16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und);
-      fixup_scan_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band);
+      fixup_list_kernel<HQMQ_BF16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und, gate, 1, kUndCap);
+      fixup_scan_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, gate, 1, kUndCap);
     }
   } else {
     hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 1);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, nullptr, nullptr, nullptr, a->quantile);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 1, N, a->median_mult, nullptr, nullptr, nullptr, nullptr, a->quantile, nullptr, 0);
     hist_kernel<<<dim3(hb, d.B * d.H), 256, 0, st>>>(g, a->x, hist, sel, 2);
-    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr, a->quantile);
+    select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr, a->quantile, nullptr, 0);
     const int tok_per_fblock = 8 * g.tpw;
     int fb = (a->T_new + 4 * tok_per_fblock - 1) / (4 * tok_per_fblock);
     const int fb_cap = (148 * 32 + bh_count - 1) / bh_count;

@@ -386,3 +386,62 @@ def test_fraction_threshold_large_calls(S, br, kind, q):
     x = make_kv(kind, (2, 2, 3000, 128), seed=21, dtype=torch.bfloat16).float()
     _encode_and_compare(x, S, br, 1.0, quantile=q)
     _encode_and_compare(x[:, :, :1500, :64].contiguous(), S, br, 1.0, quantile=q)       # generic geometry
+
+
+def _threshold_compare(x, S, br, C, quantile=None):
+    """Scales, threshold statistic, flags and radius codes of a large call against the oracle (the codeword search
+    does not depend on the threshold path and has its own tests; leaving it out keeps the oracle fast here)."""
+    B, H, T, d = x.shape
+    q = hqmq.HQMQ(n_layers=1, n_heads=H, secondary_size=S, radius_bits=br, device="cuda", seed=42)
+    med = torch.zeros(H, device="cuda")
+    pk = q.encode(x.cuda(), 0, 0, median_mult=C, scale_dtype=torch.float32, med_out=med, quantile=quantile)
+    _, rq, rs, flags = pk.to_reference()
+    qmax = (1 << br) - 1
+    nrm = orc.chunk_norms(x.float())
+    want_med, _, want_flags = orc.med3x_flags(nrm, C, quantile)
+    radius = nrm.clamp(min=1e-8)
+    r_max = radius.amax(dim=-1).clamp(min=1e-8)
+    want_rq = (radius / (r_max / qmax).unsqueeze(-1)).round().clamp(0, qmax).to(torch.int32)
+    assert torch.equal(med.cpu(), want_med), "threshold statistic differs"
+    assert torch.equal(flags.cpu(), want_flags), f"{int((flags.cpu() != want_flags).sum())} flags differ"
+    assert torch.equal(rs.cpu(), r_max)
+    assert torch.equal(rq.cpu(), torch.where(want_flags, 0, want_rq)), "radius codes differ"
+    return pk
+
+
+@pytest.mark.parametrize("kind,S,br", [("hot", 96, 4), ("spiky", 24, 3), ("student", 192, 6), ("randn", 96, 4)])
+def test_single_read_pass_of_large_calls(kind, S, br):
+    """Calls with at least 65536 tokens per head decide the flags in the pass that reads x, around a threshold
+    predicted from a sample, and take the exact order statistics from the norms listed near the prediction."""
+    x = make_kv(kind, (16, 2, 4096, 128), seed=41, dtype=torch.bfloat16).float()
+    pk = _threshold_compare(x, S, br, 3.0)
+    _threshold_compare(x[:, :, :4095], S, br, 3.0)                  # odd count: one middle order statistic
+    _threshold_compare(x, S, br, 1.0, quantile=0.7)
+    if kind == "hot":
+        assert pk.n_outliers() > 0.03 * x.numel() / 4
+
+
+@pytest.mark.parametrize("kind", ["constant", "two_levels", "tiny", "drift"])
+def test_single_read_pass_gives_way_when_its_prediction_cannot_hold(kind):
+    """When the list cannot hold the norms around the prediction (every chunk has the same norm), when the statistic
+    sits where the sample does not place it (the sampled tokens differ from the rest, or the distribution drifts
+    along the sequence in step with the sampling), or when it is next to zero, the multi-pass kernels must take the
+    call over and give the oracle's result all the same."""
+    g = torch.Generator().manual_seed(31)
+    B, H, T, d = 16, 2, 4096, 128
+    sign = torch.where(torch.rand(B, H, T, d, generator=g) < 0.5, -1.0, 1.0)
+    if kind == "constant":
+        x = sign * 0.5                                    # every chunk norm is exactly 1
+        x[:, :, ::97, 8:12] *= 10.0                       # and a few outliers
+    elif kind == "two_levels":
+        x = sign * 0.5
+        x[:, :, 1::2] *= 1.5                              # half of the tokens at 1.5: the median falls between two spikes
+        x[0, 0, :33] *= 1.5
+    elif kind == "drift":
+        x = torch.randn(B, H, T, d, generator=g)
+        x[:, :, ::32] *= 1.2                              # exactly the sampled tokens are larger than the others
+    else:
+        x = sign * 1e-30                                  # norms far down among the small floats
+        x[:, :, ::50, :4] = 3e-29
+    _threshold_compare(x.bfloat16().float(), 96, 4, 3.0)
+    _threshold_compare(x.bfloat16().float(), 24, 3, 1.0, quantile=0.5)

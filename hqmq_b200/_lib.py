@@ -149,6 +149,9 @@ def lib():
     L.hqmq_encode_pair_workspace_bytes.restype = C.c_size_t
     L.hqmq_encode_pair.argtypes = [C.POINTER(EncodeArgs), C.POINTER(EncodeArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     L.hqmq_encode_pair.restype = C.c_int
+    L.hqmq_exchange_step.argtypes = [C.POINTER(Exchange), C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_int64,
+                                     C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    L.hqmq_exchange_step.restype = C.c_int
     L.hqmq_attn_static_status.argtypes = [C.POINTER(C.c_uint32), C.c_void_p]
     L.hqmq_exchange_recv_bytes.restype = C.c_size_t
     L.hqmq_exchange_recv_bytes.argtypes = [C.c_int, C.c_int64]

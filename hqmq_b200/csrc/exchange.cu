@@ -66,6 +66,77 @@ wait_kernel(hqmq_exchange x, uint32_t epoch, uint32_t max_polls, uint32_t* __res
   if (r == 0 && miss) atomicOr(status, miss);     // bit r = rank r's block of this step never arrived
 }
 
+// Push, bounded wait and merge of one step in ONE launch.  CTAs [0, world) store this rank's block into the ranks'
+// receive buffers and publish the epoch (as push_kernel does); CTA world + r waits, with the bound of wait_kernel, for
+// all ranks' epoch words in this GPU's own memory and then merges row r of their blocks.  The CTAs that wait depend
+// on other GPUs' stores only, never on a CTA of this launch or of another kernel of this GPU, and the grid
+// (world + rows CTAs) is far below what the GPU holds resident, so the pushing CTAs always get to run.  The received
+// blocks were written by other GPUs while this kernel may already be running: they are read past the L1 (ld.global.cg).
+__global__ void __launch_bounds__(128)
+step_kernel(hqmq_exchange x, const float* __restrict__ local, uint32_t epoch, uint32_t max_polls, uint32_t* __restrict__ status,
+            int rows, int d, int out_dtype, void* __restrict__ out) {
+  const int par = (int)(epoch & 1u);
+  if ((int)blockIdx.x < x.world) {
+    const int p = blockIdx.x;
+    float* dst = x.recv[p] + ((int64_t)par * x.world + x.rank) * x.block_floats;
+    const int64_t n4 = x.block_floats >> 2;
+    const float4* s4 = reinterpret_cast<const float4*>(local);
+    float4* d4 = reinterpret_cast<float4*>(dst);
+    for (int64_t i = threadIdx.x; i < n4; i += blockDim.x) d4[i] = s4[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(x.flags[p] + par * x.world + x.rank, epoch);
+    return;
+  }
+  const int row = (int)blockIdx.x - x.world;
+  if (row >= rows) return;
+  __shared__ float s_m[HQMQ_EXCHANGE_MAX_RANKS], s_l[HQMQ_EXCHANGE_MAX_RANKS];
+  __shared__ uint32_t s_miss;
+  if (threadIdx.x == 0) s_miss = 0u;
+  __syncthreads();
+  const float* blocks = x.recv[x.rank] + (int64_t)par * x.world * x.block_floats;
+  if ((int)threadIdx.x < x.world) {
+    const int r = threadIdx.x;
+    const uint32_t* f = x.flags[x.rank] + par * x.world + r;
+    uint32_t polls = 0;
+    bool missing = false;
+    while (ld_acquire_sys(f) != epoch) {
+      if (++polls >= max_polls) { missing = true; break; }
+      __nanosleep(100);
+    }
+    if (missing) atomicOr(&s_miss, 1u << r);
+    const float* pr = blocks + (int64_t)r * x.block_floats + (int64_t)row * (d + 2);
+    s_m[r] = __ldcg(pr + d);
+    s_l[r] = __ldcg(pr + d + 1);
+  }
+  __syncthreads();
+  if (s_miss) {                                   // some rank's block of this step never arrived: report, write nothing valid
+    if (threadIdx.x == 0 && row == 0) atomicOr(status, s_miss);
+  }
+  float m_star = -INFINITY;
+  for (int r = 0; r < x.world; ++r) m_star = fmaxf(m_star, s_m[r]);
+  const float m_use = m_star == -INFINITY ? 0.f : m_star;
+  // (the denominator is summed in the order hqmq_combine_partials uses -- one term per lane, a butterfly over the
+  //  warp -- so that this launch and the three-call form give the same bits)
+  __shared__ float s_lstar;
+  if (threadIdx.x < 32) {
+    float l_loc = (int)threadIdx.x < x.world ? s_l[threadIdx.x] * exp2f(s_m[threadIdx.x] - m_use) : 0.f;
+    for (int o = 16; o > 0; o >>= 1) l_loc += __shfl_xor_sync(0xffffffffu, l_loc, o);
+    if (threadIdx.x == 0) s_lstar = l_loc;
+  }
+  __syncthreads();
+  const float l_star = s_lstar;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < x.world; ++r) {
+      const float w = exp2f(s_m[r] - m_use);
+      if (w != 0.f) acc += __ldcg(blocks + (int64_t)r * x.block_floats + (int64_t)row * (d + 2) + c) * w;
+    }
+    if (s_miss) acc = NAN;
+    store_float(out, (int64_t)row * d + c, l_star > 0.f || s_miss ? acc / l_star : 0.f, out_dtype);
+  }
+}
+
 int validate(const hqmq_exchange* x) {
   if (!x || x->struct_size != sizeof(hqmq_exchange)) return HQMQ_ERR_ARG;
   if (x->world < 1 || x->world > HQMQ_EXCHANGE_MAX_RANKS || x->rank < 0 || x->rank >= x->world) return HQMQ_ERR_ARG;
@@ -179,6 +250,22 @@ extern "C" int hqmq_exchange_wait(const hqmq_exchange* x, uint32_t epoch, uint32
   if (rc) return rc;
   if (!status || epoch == 0) return HQMQ_ERR_ARG;
   wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(*x, epoch, max_polls ? max_polls : kDefaultPolls, status);
+  HQMQ_LAUNCH_CHECK();
+  return HQMQ_OK;
+}
+
+extern "C" int hqmq_exchange_step(const hqmq_exchange* x, const float* local, uint32_t epoch, uint32_t max_polls,
+                                  uint32_t* status, int64_t rows, int d, int out_dtype, void* out, void* stream) {
+  int rc = validate(x);
+  if (rc) return rc;
+  if (!local || !status || !out || epoch == 0) return HQMQ_ERR_ARG;
+  if ((uintptr_t)local & 15) return HQMQ_ERR_ALIGN;
+  if (rows < 1 || d < 1 || rows * (int64_t)(d + 2) != x->block_floats) return HQMQ_ERR_SHAPE;
+  if (!is_float_dtype(out_dtype)) return HQMQ_ERR_DTYPE;
+  if (rows + x->world > 148 * 8) return HQMQ_ERR_UNSUPPORTED;   // every CTA of the launch resident at once, so that the pushing
+                                                                // CTAs never queue behind waiting ones (larger problems: push, wait, merge)
+  step_kernel<<<(unsigned)(x->world + rows), 128, 0, (cudaStream_t)stream>>>(*x, local, epoch, max_polls ? max_polls : kDefaultPolls,
+                                                                            status, (int)rows, d, out_dtype, out);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }

@@ -206,9 +206,9 @@ class PushExchange:
         self.x, self.max_polls, self.epoch = x, max_polls, 0
         dist.barrier(group=group)              # every rank has mapped every buffer before anyone stores into one
 
-    def step(self, part: torch.Tensor, out: torch.Tensor) -> None:
+    def step(self, part: torch.Tensor, out: torch.Tensor, fused: bool = True) -> None:
         """Enqueue on the current stream: push ``part`` (rows, d + 2 fp32, contiguous) to all ranks, wait for all
-        ranks' blocks of this step, merge them into ``out`` (rows, d)."""
+        ranks' blocks of this step, merge them into ``out`` (rows, d) -- in one launch (``fused``) or as three."""
         import ctypes as C
         from . import _lib
         L = _lib.lib()
@@ -216,6 +216,12 @@ class PushExchange:
             raise ValueError("part must be contiguous fp32 with rows * (d + 2) elements")
         self.epoch += 1
         st = _lib.stream_ptr()
+        if fused and self.rows + self.world <= 148 * 8:
+            # one launch: the block goes out, the ranks' blocks are awaited (bounded) and merged
+            _lib.check(L.hqmq_exchange_step(C.byref(self.x), part.data_ptr(), self.epoch, self.max_polls, self.status.data_ptr(),
+                                            self.rows, self.d, _lib.dtype_enum(out.dtype), out.data_ptr(), st),
+                       "hqmq_exchange_step")
+            return
         _lib.check(L.hqmq_exchange_push(C.byref(self.x), part.data_ptr(), self.epoch, st), "hqmq_exchange_push")
         _lib.check(L.hqmq_exchange_wait(C.byref(self.x), self.epoch, self.max_polls, self.status.data_ptr(), st),
                    "hqmq_exchange_wait")

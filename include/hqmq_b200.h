@@ -424,6 +424,12 @@ size_t hqmq_exchange_recv_bytes(int world, int64_t block_floats);
 size_t hqmq_exchange_flag_bytes(int world);
 int hqmq_exchange_push(const hqmq_exchange* x, const float* local, uint32_t epoch, void* stream);
 int hqmq_exchange_wait(const hqmq_exchange* x, uint32_t epoch, uint32_t max_polls, uint32_t* status, void* stream);
+/* push + wait + hqmq_combine_partials(part_major) of one step in ONE launch: `local` (rows x (d + 2) fp32) goes to every
+ * rank, the blocks of all ranks are awaited (same bound, same status word as hqmq_exchange_wait) and merged into
+ * out (rows x d, out_dtype).  rows + world <= 1184 (HQMQ_ERR_UNSUPPORTED beyond: use the three calls).  Two such
+ * launches that wait for EACH OTHER must not share one GPU (ranks are GPUs). */
+int hqmq_exchange_step(const hqmq_exchange* x, const float* local, uint32_t epoch, uint32_t max_polls, uint32_t* status,
+                       int64_t rows, int d, int out_dtype, void* out, void* stream);
 #ifdef __cplusplus
 }
 #endif

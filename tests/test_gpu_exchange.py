@@ -93,3 +93,57 @@ def test_exchange_arguments_are_validated():
     host = (C.c_float * 64)()
     xs[0].recv[1] = C.addressof(host)                                                    # not device memory
     assert L.hqmq_exchange_verify(C.byref(xs[0])) in (-1, -4)
+
+
+def test_fused_step_equals_gathered_merge():
+    """Push, wait and merge in one launch (hqmq_exchange_step).  On one device the launches that stand for the
+    other ranks must not be waited for by an earlier launch, so the other ranks' blocks are pushed first (plain
+    push), and a rank's fused step then finds their epoch words set and waits only for its own pushing CTAs,
+    which never wait themselves."""
+    world, rows, d = 3, 32, 128
+    block = rows * (d + 2)
+    L = _lib.lib()
+    xs, recv, flags = _pair(world, block)
+    status = torch.zeros(world, dtype=torch.int32, device="cuda")
+    st = _lib.stream_ptr()
+    for epoch in (1, 2, 3, 4):
+        parts = _parts(world, rows, d, seed=20 + epoch)
+        want = combine_partials(parts.view(world, 1, rows, 1, d + 2), torch.float32).view(rows, d)
+        for r in range(1, world):
+            _lib.check(L.hqmq_exchange_push(C.byref(xs[r]), parts[r].data_ptr(), epoch, st), "push")
+        for r in range(world):          # rank 0 pushes inside its step; the later ranks push once more (same bytes)
+            out = torch.empty(rows, d, device="cuda")
+            _lib.check(L.hqmq_exchange_step(C.byref(xs[r]), parts[r].data_ptr(), epoch, 0, status[r:].data_ptr(), rows, d,
+                                            _lib.dtype_enum(torch.float32), out.data_ptr(), st), "step")
+            assert torch.equal(out, want), (epoch, r)
+    assert int(status.abs().sum()) == 0
+    # a 16-bit output rounds the same merge once
+    out16 = torch.empty(rows, d, dtype=torch.bfloat16, device="cuda")
+    for r in range(1, world):
+        _lib.check(L.hqmq_exchange_push(C.byref(xs[r]), parts[r].data_ptr(), 5, st), "push")
+    _lib.check(L.hqmq_exchange_step(C.byref(xs[0]), parts[0].data_ptr(), 5, 0, status.data_ptr(), rows, d,
+                                    _lib.dtype_enum(torch.bfloat16), out16.data_ptr(), st), "step")
+    assert torch.allclose(out16.float(), want.bfloat16().float(), rtol=1e-2, atol=1e-2)
+
+
+def test_fused_step_gives_up_and_names_the_missing_rank():
+    """Rank 1 never delivers: the waiting CTAs of rank 0's step run out of polls (a few milliseconds), set bit 1 of the
+    status word and write NaN rows; the device keeps working and a complete step afterwards succeeds."""
+    world, rows, d = 2, 4, 62
+    block = rows * (d + 2)
+    L = _lib.lib()
+    xs, recv, flags = _pair(world, block)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = _lib.stream_ptr()
+    parts = _parts(world, rows, d, seed=10)
+    out = torch.zeros(rows, d, device="cuda")
+    _lib.check(L.hqmq_exchange_step(C.byref(xs[0]), parts[0].data_ptr(), 1, 64, status.data_ptr(), rows, d,
+                                    _lib.dtype_enum(torch.float32), out.data_ptr(), st), "step")
+    assert int(status.item()) == 0b10 and torch.isnan(out).all()
+    status.zero_()
+    _lib.check(L.hqmq_exchange_push(C.byref(xs[1]), parts[1].data_ptr(), 2, st), "push")
+    _lib.check(L.hqmq_exchange_step(C.byref(xs[0]), parts[0].data_ptr(), 2, 64, status.data_ptr(), rows, d,
+                                    _lib.dtype_enum(torch.float32), out.data_ptr(), st), "step")
+    want = combine_partials(parts.view(world, 1, rows, 1, d + 2), torch.float32).view(rows, d)
+    assert int(status.item()) == 0 and torch.allclose(out, want, rtol=1e-6, atol=1e-6)
+    assert L.hqmq_exchange_step(C.byref(xs[0]), parts[0].data_ptr(), 3, 0, status.data_ptr(), rows + 1, d, 0, out.data_ptr(), st) == -2

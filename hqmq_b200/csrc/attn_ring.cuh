@@ -760,6 +760,11 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
 #pragma unroll
       for (int q = 0; q < PER; ++q) acc[q] = 0.f;
       const float wg0 = w_s[warp * 8 + 2 * j], wg1 = w_s[warp * 8 + 2 * j + 1];
+      // Where element x of head pair jj sits in a slot row.  The lanes of a store differ in r (bits 6:4 of x at d_head
+      // 128, 5:3 at 64) and in j, which as plain indices would all fall into two banks (16-way conflicts, 4 us per
+      // merge): the upper bits of r are folded into bits 3:2 and j into bits 1:0, which spreads a store over all 32
+      // banks.  The map is its own inverse (it changes bits 3:0 only, by bits it leaves alone).
+      auto slot_swz = [](int jj, int x) { return x ^ (((x >> 5) & (D / 32 - 1)) << 2) ^ (jj & 3); };
       for (int round = 0; round < kRingWarps / MS; ++round) {
         if (warp / MS == round) {
           float* mine = slots + (size_t)(warp % MS) * 8 * D;
@@ -768,10 +773,10 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
             const int chunk = r * NVG + (i >> 1);
             if (chunk < N) {
               const int x = 4 * chunk + 2 * (i & 1);
-              mine[(2 * j) * D + x] = o[i][0] * wg0;          // row r (element 0 / 2), head 2j
-              mine[(2 * j + 1) * D + x] = o[i][1] * wg1;      // head 2j+1
-              mine[(2 * j) * D + x + 1] = o[i][2] * wg0;      // row r+8 (element 1 / 3)
-              mine[(2 * j + 1) * D + x + 1] = o[i][3] * wg1;
+              mine[(2 * j) * D + slot_swz(j, x)] = o[i][0] * wg0;              // row r (element 0 / 2), head 2j
+              mine[(2 * j + 1) * D + slot_swz(j, x)] = o[i][1] * wg1;          // head 2j+1
+              mine[(2 * j) * D + slot_swz(j, x + 1)] = o[i][2] * wg0;          // row r+8 (element 1 / 3)
+              mine[(2 * j + 1) * D + slot_swz(j, x + 1)] = o[i][3] * wg1;
             }
           }
         }
@@ -803,7 +808,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
         for (int q = 0; q < PER; ++q) {
           const int i = threadIdx.x + q * kRingConsumerThreads;
           if (i < 8 * D) {
-            const int g = i / D, x = i - g * D;
+            const int g = i / D, x = slot_swz(g >> 1, i - g * D);
             if (g < p.G) emit(g, x, acc[q], ms_s[g], ms_s[8 + g]);
           }
         }
@@ -812,7 +817,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
         for (int q = 0; q < PER; ++q) {
           const int i = threadIdx.x + q * kRingConsumerThreads;
           if (i < 8 * D) {
-            const int g = i / D, x = i - g * D;
+            const int g = i / D, x = slot_swz(g >> 1, i - g * D);
             if (g < p.G) {
               const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
               float* dst = p.partials + (row * p.P + up.part) * (D + 2);

@@ -65,6 +65,11 @@ struct EncGeom {
   int S, ib, rbits, qmax;
   int x_dtype;
   int64_t xs_b, xs_h, xs_t;
+  // d_head 64 through the kernels written for 32 chunks per token: with the tokens contiguous in memory, an even
+  // token count and an even first row, two consecutive tokens form one "token" of 32 chunks (T_new, xs_t and the
+  // packed rows are then those of the pairs); what is per token -- the maximum radius, the scale, the flag word, the
+  // row number -- is taken per half-warp.
+  int pair16;
 };
 
 // Workspace layout (uint32 words)
@@ -673,7 +678,11 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
     const float radius = fmaxf(nrm, 1e-8f);
     float rmax = radius;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+    for (int o = 8; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+    {
+      const float other = __shfl_xor_sync(0xffffffffu, rmax, 16);
+      if (!g.pair16) rmax = fmaxf(rmax, other);       // (pairs: each half-warp is a token of its own)
+    }
     const float scale = __fdiv_rn(rmax, qmaxf);
     // radius code: the quotient is first taken with an approximate reciprocal; only a lane whose quotient
     // lies close to a rounding boundary repeats it with the IEEE division the contract names
@@ -689,7 +698,10 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
       flag_word = __ballot_sync(0xffffffffu, certain);
       if (!certain && nrm > thr_lo) {               // rare: settled against the exact threshold afterwards
         const uint32_t pos = atomicAdd(&br.band[h * kBandWords + 2], 1u);
-        if (pos < (uint32_t)br.und_cap) br.und[(int64_t)h * br.und_cap + pos] = (uint32_t)(((int64_t)b * g.T_new + t) * 32 + lane);
+        if (pos < (uint32_t)br.und_cap)
+          br.und[(int64_t)h * br.und_cap + pos] =
+              g.pair16 ? (uint32_t)(((int64_t)b * (2 * g.T_new) + 2 * t + (lane >> 4)) * 32 + (lane & 15))
+                       : (uint32_t)(((int64_t)b * g.T_new + t) * 32 + lane);
       }
       n_below += __popc(__ballot_sync(0xffffffffu, key < r_lo));       // (every lane keeps the warp's count)
       const bool in_range = key >= r_lo && key <= r_hi;
@@ -722,7 +734,7 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
     const uint32_t f = ni | ((uint32_t)rqf << IB);
 
     // ---- packed row, scale, flag word ---------------------------------------------------------------------
-    const int64_t row = (int64_t)bh * dst.T_cap + t_start + t;
+    const int64_t row = (int64_t)bh * dst.T_cap + t_start + (g.pair16 ? 2 * t : t);   // (pairs: two rows, contiguous)
     uint32_t* out = reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes);
     if constexpr (CB == 16) {
       const uint32_t other = __shfl_xor_sync(0xffffffffu, f, 1);
@@ -737,9 +749,10 @@ encode_main32_kernel(EncGeom g, const uint16_t* __restrict__ x, const float* __r
       if (lane < RW) out[lane] = myrow[lane];
       __syncwarp();
     }
-    if (lane == 0) {
-      store_scale(dst, row, rmax);
-      if (dst.flags) dst.flags[row] = flag_word;
+    if (lane == 0 || (g.pair16 && lane == 16)) {
+      const int half = lane >> 4;
+      store_scale(dst, row + half, rmax);
+      if (dst.flags) dst.flags[row + half] = g.pair16 ? (half ? flag_word >> 16 : flag_word & 0xffffu) : flag_word;
     }
     if (!BR && hist) {
       const uint32_t key = __float_as_uint(nrm), top = key >> 21;
@@ -919,6 +932,7 @@ struct Fast32 {
   const uint16_t* x;
   int64_t xs_b, xs_h, xs_t;
   int H, T_new;
+  int pair;      // 1: every "token" here is two consecutive tokens of 16 chunks (d_head 64), see EncGeom::pair16
 };
 constexpr int kF32Tok = 64;   // tokens per CTA iteration: 8 warps x 2 tokens x 4 loads
 
@@ -1247,7 +1261,11 @@ histflags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, ui
           if (n[e] > thr_hi) m |= 1u << e;
           else if (n[e] > thr_lo) {
             const uint32_t pos = atomicAdd(&band[h * kBandWords + 2], 1u);
-            if (pos < (uint32_t)kUndCap) und[(int64_t)h * kUndCap + pos] = (uint32_t)(((int64_t)b * f.T_new + tu) * 32 + 2 * l16 + e);
+            const int c32 = 2 * l16 + e;
+            if (pos < (uint32_t)kUndCap)
+              und[(int64_t)h * kUndCap + pos] =
+                  f.pair ? (uint32_t)(((int64_t)b * (2 * f.T_new) + 2 * tu + (c32 >> 4)) * 32 + (c32 & 15))
+                         : (uint32_t)(((int64_t)b * f.T_new + tu) * 32 + c32);
           }
         }
       }
@@ -1258,7 +1276,7 @@ histflags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, ui
       word |= __shfl_xor_sync(0xffffffffu, word, 4);
       word |= __shfl_xor_sync(0xffffffffu, word, 8);
       if (live) {
-        const int64_t row = (int64_t)bh * dst.T_cap + t_start + tu;
+        const int64_t row = (int64_t)bh * dst.T_cap + t_start + (f.pair ? 2 * tu : tu);   // (pairs: two contiguous rows)
         if (m) {
           uint32_t* rowp = reinterpret_cast<uint32_t*>(dst.codes + row * dst.row_bytes);
           if (cb16) {
@@ -1269,7 +1287,10 @@ histflags32_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, ui
             if (m & 2u) clear_radius(rowp, 2 * l16 + 1, ib, rbits);
           }
         }
-        if (l16 == 0) dst.flags[row] = word;
+        if (l16 == 0) {
+          if (f.pair) { dst.flags[row] = word & 0xffffu; dst.flags[row + 1] = word >> 16; }
+          else dst.flags[row] = word;
+        }
       }
     }
   }
@@ -1328,8 +1349,11 @@ fixup_scan_kernel(Fast32 f, hqmq_packed dst, int t_start, int ib, int rbits, con
     norms_of_two<DT>(r, n[0], n[1]);
 #pragma unroll
     for (int e = 0; e < 2; ++e)
-      if (n[e] > thr_lo && !(n[e] > thr_hi) && n[e] > thr)
-        flag_late(dst, (int64_t)bh * dst.T_cap + t_start + t, 2 * l16 + e, ib, rbits);
+      if (n[e] > thr_lo && !(n[e] > thr_hi) && n[e] > thr) {
+        const int c32 = 2 * l16 + e;
+        if (f.pair) flag_late(dst, (int64_t)bh * dst.T_cap + t_start + 2 * t + (c32 >> 4), c32 & 15, ib, rbits);
+        else flag_late(dst, (int64_t)bh * dst.T_cap + t_start + t, c32, ib, rbits);
+      }
   }
 }
 
@@ -1854,10 +1878,17 @@ static MainGrid main_grid(int T_new, int B, int H) {
 // the sampled norms per head (a 1/32 sample of B * T_new tokens, 32 norms each), so the bracket's half-width is
 // 3 / sqrt(norms) (about six standard errors of a median), at least 0.2 % and at most 1.2 %; calls too small for that,
 // and quantiles out in the tails (few norms nearby: a much larger error), take the multi-pass path as before.
-constexpr int64_t kBracketMinTokens = 65536;     // B * T_new per head
+// d_head 64 as pairs of tokens (see EncGeom::pair16): the call's geometry must allow it.
+static bool pair16_of(const hqmq_encode_args& a) {
+  return a.dst.n_chunks == 16 && is_half_dtype(a.x_dtype) && a.x_stride[2] == 64 && a.T_new >= 2 && a.T_new % 2 == 0 &&
+         a.t_start % 2 == 0;
+}
+constexpr int64_t kBracketMinTokens = 65536;     // B * T_new per head (of 32 chunks each)
 static bool bracket_wanted(const hqmq_encode_args& a) {
-  return a.median_mult > 0.f && !a.med_in && a.dst.n_chunks == 32 && is_half_dtype(a.x_dtype) &&
-         (int64_t)a.dst.B * a.T_new >= kBracketMinTokens && a.T_new >= 1024 &&
+  const bool pair = pair16_of(a);
+  const int T32 = pair ? a.T_new / 2 : a.T_new;
+  return a.median_mult > 0.f && !a.med_in && (a.dst.n_chunks == 32 || pair) && is_half_dtype(a.x_dtype) &&
+         (int64_t)a.dst.B * T32 >= kBracketMinTokens && T32 >= 1024 &&
          (a.quantile == 0.f || (a.quantile >= 0.25f && a.quantile <= 0.75f));
 }
 
@@ -1884,7 +1915,8 @@ WsPlan plan_ws(const hqmq_encode_args& a) {
   w.rcap = w.regions = w.und_cap = 0;
   w.zero_bytes = o * sizeof(uint32_t);
   if (bracket_wanted(a)) {
-    const MainGrid mg = main_grid(a.T_new, a.dst.B, H);
+    const int T32 = pair16_of(a) ? a.T_new / 2 : a.T_new;
+    const MainGrid mg = main_grid(T32, a.dst.B, H);
     w.regions = mg.gx * a.dst.B * H;
     w.rcap = kEnc32Warps * mg.iters * 32 / 16;        // a sixteenth of a CTA's chunks (the range holds about 2 %)
     w.gate = o; o += 4;
@@ -1897,7 +1929,7 @@ WsPlan plan_ws(const hqmq_encode_args& a) {
     w.zero_bytes = o * sizeof(uint32_t);              // everything up to here starts at zero; the lists need not
     // the undecided list: the bracket is wider than the multi-pass path's band (a few per mille of the chunks of a
     // head with many outliers fall inside it)
-    const int64_t per_head = (int64_t)a.dst.B * a.T_new * 32;
+    const int64_t per_head = (int64_t)a.dst.B * T32 * 32;
     w.und_cap = (int)(per_head / 256 > kUndCap ? (per_head / 256 < (1 << 20) ? per_head / 256 : (1 << 20)) : kUndCap);
     w.und_b = o; o += (size_t)H * w.und_cap;
     w.rlist = o; o += (size_t)w.regions * w.rcap;
@@ -2070,6 +2102,7 @@ static EncGeom geom_of(const hqmq_encode_args* a) {
   g.S = d.S; g.ib = idx_bits_for(d.S); g.rbits = d.radius_bits; g.qmax = (1 << d.radius_bits) - 1;
   g.x_dtype = a->x_dtype;
   g.xs_b = a->x_stride[0]; g.xs_h = a->x_stride[1]; g.xs_t = a->x_stride[2];
+  g.pair16 = 0;
   return g;
 }
 
@@ -2178,9 +2211,15 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   const bool use_lut = a->search == 0 && a->lut != nullptr && a->lut_footprint >= 0 && smem_lut <= 226 * 1024;
   // fast passes: d_head 128, 16-bit input, token rows on 16-byte boundaries (the fused last pass lists
   // undecided chunks by a 32-bit index over the (batch, token, chunk) grid of a head)
-  const bool fast32 = g.n == 32 && is_half_dtype(a->x_dtype) && ((uintptr_t)a->x & 15) == 0 && g.xs_b % 8 == 0 &&
+  // (d_head 64 with contiguous tokens runs the same kernels on pairs of tokens)
+  const bool pair16 = pair16_of(*a);
+  const int T32 = pair16 ? a->T_new / 2 : a->T_new;
+  EncGeom g32 = g;
+  if (pair16) { g32.n = 32; g32.npl = 32; g32.tpw = 1; g32.T_new = T32; g32.xs_t = 2 * g.xs_t; g32.pair16 = 1; }
+  const bool fast32 = (g.n == 32 || pair16) && is_half_dtype(a->x_dtype) && ((uintptr_t)a->x & 15) == 0 && g.xs_b % 8 == 0 &&
                       g.xs_h % 8 == 0 && g.xs_t % 8 == 0 && (int64_t)d.B * a->T_new * 32 < ((int64_t)1 << 32);
-  Fast32 f32{reinterpret_cast<const uint16_t*>(a->x), g.xs_b, g.xs_h, g.xs_t, d.H, a->T_new};
+  Fast32 f32{reinterpret_cast<const uint16_t*>(a->x), g.xs_b, g.xs_h, g32.xs_t, d.H, T32, pair16 ? 1 : 0};
+  Fast32 f32_tok{reinterpret_cast<const uint16_t*>(a->x), g.xs_b, g.xs_h, g.xs_t, d.H, a->T_new, 0};   // per real token (the fix-up list)
   const Mul24& nmul = mul24_native();
   if (use_lut && (uintptr_t)a->lut & 15) return HQMQ_ERR_ALIGN;
   // specialised kernel: d_head 128, 16-bit input, one of the compiled field layouts
@@ -2188,7 +2227,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   const void* fastk_br = nullptr;
   bool predicted = false;
   const uint32_t* gate = nullptr;      // bracket mode: the word that sends the call through the multi-pass kernels after all
-  if (use_lut && g.n == 32 && is_half_dtype(a->x_dtype)) {
+  if (use_lut && is_half_dtype(a->x_dtype) && (g.n == 32 || (pair16 && fast32))) {
     const bool h16 = a->x_dtype == HQMQ_F16;
 #define HQMQ_PICK(IB_, RB_)                                                                              \
     if (g.ib == IB_ && g.rbits == RB_) {                                                                   \
@@ -2203,7 +2242,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   if (fastk) {
     const size_t smem_fast = (size_t)g.S * 16 + (size_t)kEnc32Warps * kMaxRowWords * 4 + 3 * kHistBins * 4 + (size_t)24 * g.S * 16 +
                              lut_foot + 16;
-    const MainGrid mg = main_grid(a->T_new, d.B, d.H);
+    const MainGrid mg = main_grid(T32, d.B, d.H);
     int iters = mg.iters;
     if (smem_fast > 48 * 1024) {
       HQMQ_CHECK_CUDA(cudaFuncSetAttribute(fastk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fast));
@@ -2214,14 +2253,14 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     // to 22 bits, the bracket pass then needs x only once; should the prediction fail, the multi-pass kernels
     // below (gated on a word the bracket's check raises) redo the call, with the sample's first level telling the
     // main pass which bins to refine.
-    predicted = med && !ext_med && fast32 && a->T_new >= 1024;
+    predicted = med && !ext_med && fast32 && T32 >= 1024;
     const bool bracket = predicted && bracket_wanted(*a) && wp.regions == (int)(fgrid.x * fgrid.y);
     const uint16_t* x16 = reinterpret_cast<const uint16_t*>(a->x);
     const unsigned char* lut_arg = reinterpret_cast<const unsigned char*>(a->lut);
     int t_start_arg = a->t_start;
     BracketArgs brargs{};
     if (predicted) {
-      const int n_s = (a->T_new + kSampleStride - 1) / kSampleStride;
+      const int n_s = (T32 + kSampleStride - 1) / kSampleStride;
       const uint64_t N_s = (uint64_t)d.B * n_s * 32;
       int gs = (148 * 8 + d.B * d.H - 1) / (d.B * d.H);
       if (gs > (n_s + 15) / 16) gs = (n_s + 15) / 16;
@@ -2239,7 +2278,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     if (bracket) {
       const bool h16s = a->x_dtype == HQMQ_F16;
       uint32_t* sel_s_w = ws + wp.sel_s;
-      const int n_s = (a->T_new + kSampleStride - 1) / kSampleStride;
+      const int n_s = (T32 + kSampleStride - 1) / kSampleStride;
       float delta = 3.0f / sqrtf((float)d.B * (float)n_s * 32.f);
       delta = delta < 0.002f ? 0.002f : delta > 0.012f ? 0.012f : delta;
       uint32_t* bp = ws + wp.bp;
@@ -2250,7 +2289,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
       brargs.run_if = nullptr;
       uint32_t* no_hist = nullptr;
       const uint32_t* no_sel = nullptr;
-      void* kargs_b[] = {(void*)&g, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&no_hist, (void*)&maps,
+      void* kargs_b[] = {(void*)&g32, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&no_hist, (void*)&maps,
                          (void*)&a->joint, (void*)&lut_arg, (void*)&nmul, (void*)&iters, (void*)&no_sel, (void*)&brargs};
       HQMQ_CHECK_CUDA(cudaLaunchKernel(fastk_br, fgrid, dim3(kEnc32Threads), kargs_b, smem_fast, st));
       const uint64_t N_all = (uint64_t)d.B * a->T_new * d.n_chunks;
@@ -2258,21 +2297,21 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
       list_histB_kernel<<<fgrid, 256, 0, st>>>(bp, ws + wp.rcnt, ws + wp.rlist, wp.rcap, d.H, ws + wp.histB, gate);
       list_pickB_kernel<<<d.H, 256, 0, st>>>(bp, ws + wp.histB, N_all, a->median_mult, a->quantile, ws + wp.sel_b, a->med_out, gate);
       int fg = (148 * 32 + d.B * d.H - 1) / (d.B * d.H);
-      const int fg_max = (a->T_new + kF32Tok - 1) / kF32Tok;
+      const int fg_max = (T32 + kF32Tok - 1) / kF32Tok;
       if (fg > fg_max) fg = fg_max;
       if (fg < 1) fg = 1;
       if (h16s) {
-        fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, ws + wp.und_b, gate, 0, wp.und_cap);
+        fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32_tok, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, ws + wp.und_b, gate, 0, wp.und_cap);
         fixup_scan_kernel<HQMQ_F16><<<dim3(fg, d.B * d.H), 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, gate, 0, wp.und_cap);
       } else {
-        fixup_list_kernel<HQMQ_BF16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, ws + wp.und_b, gate, 0, wp.und_cap);
+        fixup_list_kernel<HQMQ_BF16><<<d.H, 256, 0, st>>>(f32_tok, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, ws + wp.und_b, gate, 0, wp.und_cap);
         fixup_scan_kernel<HQMQ_BF16><<<dim3(fg, d.B * d.H), 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, ws + wp.sel_b, ws + wp.band_b, gate, 0, wp.und_cap);
       }
       brargs.run_if = gate;       // the multi-pass launch below runs only if the check raised the gate
     }
     const uint32_t* sel_s_arg = predicted ? ws + wp.sel_s : nullptr;
     uint32_t* hist_arg = med && !ext_med ? ws + wp.hist : nullptr;
-    void* kargs[] = {(void*)&g, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&hist_arg, (void*)&maps,
+    void* kargs[] = {(void*)&g32, (void*)&x16, (void*)&a->qs, (void*)&d, (void*)&t_start_arg, (void*)&hist_arg, (void*)&maps,
                      (void*)&a->joint, (void*)&lut_arg, (void*)&nmul, (void*)&iters, (void*)&sel_s_arg, (void*)&brargs};
     HQMQ_CHECK_CUDA(cudaLaunchKernel(fastk, fgrid, dim3(kEnc32Threads), kargs, smem_fast, st));
   } else if (use_lut) {
@@ -2307,7 +2346,7 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
   uint32_t* hist = ws + wp.hist;
   uint32_t* sel = ws + wp.sel;
   int fgrid = (148 * 32 + bh_count - 1) / bh_count;
-  const int fgrid_max = (a->T_new + kF32Tok - 1) / kF32Tok;
+  const int fgrid_max = (T32 + kF32Tok - 1) / kF32Tok;
   if (fgrid > fgrid_max) fgrid = fgrid_max;
   if (fgrid < 1) fgrid = 1;
   const dim3 f32_grid(fgrid, d.B * d.H);
@@ -2337,10 +2376,10 @@ extern "C" int hqmq_encode(const hqmq_encode_args* a, void* workspace, size_t wo
     else histflags32_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, hist, sel, band, und, gate, 1);
     select_kernel<<<d.H, 256, 0, st>>>(hist, sel, 2, N, a->median_mult, a->med_out, nullptr, nullptr, nullptr, a->quantile, gate, 1);
     if (h16) {
-      fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und, gate, 1, kUndCap);
+      fixup_list_kernel<HQMQ_F16><<<d.H, 256, 0, st>>>(f32_tok, d, a->t_start, g.ib, g.rbits, sel, band, und, gate, 1, kUndCap);
       fixup_scan_kernel<HQMQ_F16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, gate, 1, kUndCap);
     } else {
-      fixup_list_kernel<HQMQ_BF16><<<d.H, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, und, gate, 1, kUndCap);
+      fixup_list_kernel<HQMQ_BF16><<<d.H, 256, 0, st>>>(f32_tok, d, a->t_start, g.ib, g.rbits, sel, band, und, gate, 1, kUndCap);
       fixup_scan_kernel<HQMQ_BF16><<<f32_grid, 256, 0, st>>>(f32, d, a->t_start, g.ib, g.rbits, sel, band, gate, 1, kUndCap);
     }
   } else {

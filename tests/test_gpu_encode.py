@@ -445,3 +445,40 @@ def test_single_read_pass_gives_way_when_its_prediction_cannot_hold(kind):
         x[:, :, ::50, :4] = 3e-29
     _threshold_compare(x.bfloat16().float(), 96, 4, 3.0)
     _threshold_compare(x.bfloat16().float(), 24, 3, 1.0, quantile=0.5)
+
+
+@pytest.mark.parametrize("S,br,kind", [(96, 4, "hot"), (24, 3, "spiky"), (192, 6, "student")])
+def test_head_dim_64_through_the_token_pair_kernels(S, br, kind):
+    """d_head 64 with contiguous tokens, an even token count and an even first row runs the kernels written for 32
+    chunks per token on pairs of tokens (scale, flag word and row per half-warp): every plane against the oracle,
+    for a call that starts a cache and for one appended behind an even number of tokens; an odd count or an odd
+    first row takes the generic kernels and must agree too."""
+    x = make_kv(kind, (2, 2, 2304, 64), seed=51, dtype=torch.bfloat16).float()
+    q, pk, enc, _ = _encode_and_compare(x, S, br, 3.0)
+    _encode_and_compare(x[:, :, :2303].contiguous(), S, br, 3.0)               # odd count: generic kernels
+    # appended behind 16 tokens (even first row) and behind 17 (odd): rows, scales and flags of the appended part
+    for first in (16, 17):
+        qq = hqmq.with_outlier_extraction(hqmq.HQMQ(n_layers=2, n_heads=2, secondary_size=S, radius_bits=br, device="cuda", seed=42), 3.0)
+        dst = qq.inner.new_cache(2, 4096, 64, "cuda", scale_dtype=torch.float32, with_outliers=True, out_dtype=torch.float32)
+        qq.encode(x[:, :, :first].contiguous().cuda(), 0, 0, out=dst)
+        qq.encode(x[:, :, first:first + 2048].contiguous().cuda(), 0, 0, out=dst)
+        joint = orc.joint_codebook(orc.secondary_raw(2, 2, S, 42)[0, :, 0])
+        want = orc.encode(x[:, :, first:first + 2048], joint, br, 3.0)
+        idx, rq, rs, flags = dst.to_reference(first, 2048)
+        assert torch.equal(flags.cpu(), want["flags"]) and torch.equal(rs.cpu(), want["r_max"])
+        assert torch.equal(rq.cpu(), torch.where(want["flags"], 0, want["rq"]))
+        n_mis, n_bad = classify_idx(idx, want, NEAR_TIE)
+        assert n_bad == 0
+
+
+@pytest.mark.parametrize("kind", ["hot", "spiky", "constant"])
+def test_head_dim_64_single_read_pass(kind):
+    """The same pairs through the single-read pass of large calls (and through its fallback for a constant-norm tensor)."""
+    if kind == "constant":
+        g = torch.Generator().manual_seed(33)
+        x = torch.where(torch.rand(16, 2, 8192, 64, generator=g) < 0.5, -0.5, 0.5)
+        x[:, :, ::97, 8:12] *= 10.0
+    else:
+        x = make_kv(kind, (16, 2, 8192, 64), seed=52, dtype=torch.bfloat16).float()
+    _threshold_compare(x.bfloat16().float(), 96, 4, 3.0)
+    _threshold_compare(x.bfloat16().float()[:, :, :8190], 24, 3, 1.0, quantile=0.5)

@@ -1,6 +1,6 @@
 """Put the UNMODIFIED reference packages next to the oracle so that they travel with a snapshot of this tree.
 
-    python oracle/make_ref.py [/path/to/the/reference/checkout]
+    python oracle/make_ref.py [/path/to/the/reference/checkout]      # default: $HQMQ_REFERENCE_CHECKOUT
 
 The reference (kswain98/hqmq) is pure Python: its ``hqmq`` and ``src`` packages are installed, file for file,
 under ``oracle/_ref/`` (git-ignored: nothing of it enters the history of this repository).  ``bench.py`` times
@@ -14,9 +14,15 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 PACKAGES = ("hqmq", "src")
+# where a checkout of the reference lives on the build host (overridable; absent on the machines that only run)
+CHECKOUT = os.environ.get("HQMQ_REFERENCE_CHECKOUT", os.path.join(os.sep, "root", "reference"))
 
 
-def install(ref_root: str = "/root/reference") -> str:
+def checkout_present(ref_root: str = CHECKOUT) -> bool:
+    return all(os.path.isdir(os.path.join(ref_root, p)) for p in PACKAGES)
+
+
+def install(ref_root: str = CHECKOUT) -> str:
     if not all(os.path.isdir(os.path.join(ref_root, p)) for p in PACKAGES):
         raise FileNotFoundError(f"no reference checkout at {ref_root}")
     os.makedirs(DEST, exist_ok=True)
@@ -46,4 +52,4 @@ def import_reference():
 
 
 if __name__ == "__main__":
-    print(install(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    print(install(sys.argv[1] if len(sys.argv) > 1 else CHECKOUT))

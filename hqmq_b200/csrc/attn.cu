@@ -268,6 +268,23 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   const int64_t total = (int64_t)pl.units * pl.tpu_v;
   pl.grid = (int)((total + pl.L - 1) / pl.L);
   pl.P = (pl.tpu_v - 1 + pl.L - 1) / pl.L + 1;
+  // Ring kernels with fewer units than CTAs: CTA boundaries snapped to unit boundaries when that is cheaper than the
+  // flat split, whose straddling CTAs pay a second unit's set-up and merge -- about 80 tiles' worth of time, 130 when
+  // the next unit is another KV head and the tables are reloaded (one sequence of 131072 tokens: the 7 straddling CTAs
+  // finished at 138 us, the other 141 at 105).  Every unit is cut into c = slots / units equal pieces of Lu tiles; in
+  // the kernel's terms that is a flat split of L = Lu over units of c * Lu virtual tiles (the tiles past a unit's real
+  // ones are empty), so the kernel needs no other code for it.
+  if (pl.ring_stages > 0 && a->kv_splits == 0 && pl.units < slots) {
+    const int c = slots / pl.units;
+    const int Lu = (tpu + c - 1) / c;
+    const int straddle = a->B * a->T_q == 1 ? 130 : 80;
+    if (pl.L < tpu && Lu >= pl.nw && Lu < pl.L + straddle) {
+      pl.L = Lu;
+      pl.tpu_v = c * Lu;
+      pl.grid = pl.units * c;
+      pl.P = c;
+    }
+  }
   const int64_t rows = (int64_t)a->B * a->H_q * a->T_q;
   pl.ticket_bytes = pl.ring_stages ? (((size_t)pl.units * 4 + 15) & ~(size_t)15) : 0;
   pl.ws_bytes = 16 + pl.ticket_bytes + (size_t)rows * pl.P * pl.ppc * (a->d + 2) * sizeof(float);

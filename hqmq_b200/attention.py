@@ -40,6 +40,7 @@ def _run(a: _lib.AttnArgs, device):
             _lib.check(L.hqmq_attn_decode(C.byref(a), None, 0, _lib.stream_ptr()), "hqmq_attn_decode")
         ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _lib.check(L.hqmq_attn_decode(C.byref(a), ws.data_ptr(), nbytes, _lib.stream_ptr()), "hqmq_attn_decode")
+    return ws, nbytes
 
 
 def fused_hqmq_attention(
@@ -94,6 +95,37 @@ def fused_attention_packed(
     quantizer).  With ``partials`` (B, H_q, T_q, d+2) fp32 given, the un-normalised result
     (o[d], m, l) is written there instead of O, for merging across sequence shards."""
     _lib.require_cuda(Q, "fused_attention_packed")
+    # A decode loop repeats one call shape on one pair of caches: the argument struct and the workspace of such a call
+    # are kept with the K cache (per stream: calls on one stream are ordered, calls on different streams get their
+    # own workspace), and a repeat only patches the addresses and the key count.
+    st = _lib.stream_ptr()
+    T_now = K.T if T_kv is None else T_kv
+    key = None
+    if Q.stride(-1) == 1 and (out is not None or partials is not None):
+        dst = partials if partials is not None else out
+        key = (id(V), st, Q.dtype, tuple(Q.shape), Q.stride(), dst.dtype, dst.stride(), partials is not None, causal, window,
+               softmax_scale, kv_splits, table_K.data_ptr(), table_V.data_ptr(), K.with_ofrag, V.with_ofrag)
+        hit = K._attn_cache.get(key)
+        if hit is not None:
+            a, ws, _, t_sized, _ = hit
+            a.Q, a.T_kv = Q.data_ptr(), T_now
+            if partials is not None:
+                a.partials = partials.data_ptr()
+            else:
+                a.O = out.data_ptr()
+            L = _lib.lib()
+            with _lib.device_guard(Q.device):
+                if T_now != t_sized:
+                    nbytes = L.hqmq_attn_workspace_bytes(C.byref(a))
+                    if nbytes == 0:
+                        _lib.check(L.hqmq_attn_decode(C.byref(a), None, 0, st), "hqmq_attn_decode")
+                    if nbytes > ws.numel():
+                        ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device)
+                    K._attn_cache[key] = (a, ws, nbytes, T_now, hit[4])
+                else:
+                    nbytes = hit[2]
+                _lib.check(L.hqmq_attn_decode(C.byref(a), ws.data_ptr(), nbytes, st), "hqmq_attn_decode")
+            return partials if partials is not None else out
     _lib.check_device(Q.device)
     B, H_q, T_q, d_h = Q.shape
     if Q.stride(-1) != 1:
@@ -115,7 +147,11 @@ def fused_attention_packed(
     a.table_K, a.table_V = table_K.data_ptr(), table_V.data_ptr()
     if partials is not None:
         a.partials_only, a.partials = 1, partials.data_ptr()
-    _run(a, Q.device)
+    ws, nbytes = _run(a, Q.device)
+    if key is not None:
+        if len(K._attn_cache) > 64:
+            K._attn_cache.clear()
+        K._attn_cache[key] = (a, ws, nbytes, T_now, (V, table_K, table_V))      # (the last item keeps what the struct points to alive)
     return partials if partials is not None else O
 
 

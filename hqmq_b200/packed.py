@@ -37,6 +37,7 @@ class PackedKV:
         self.T_cap = max(_lib.T_ALIGN, ((T_cap + _lib.T_ALIGN - 1) // _lib.T_ALIGN) * _lib.T_ALIGN)
         self.T = 0
         self._enc_cache = {}      # argument structs of repeated small encode calls (see HQMQQuantizer.encode)
+        self._attn_cache = {}        # argument structs and workspaces of repeated attention calls (hqmq_b200.attention)
         self.row_bytes = row_bytes(n_chunks, S, radius_bits)
         self.scale_dtype, self.out_dtype = scale_dtype, out_dtype
         dev = torch.device(device)
@@ -93,6 +94,7 @@ class PackedKV:
         """Forget the fragment records: attention then merges K outliers from flags / out_vals."""
         self.with_ofrag, self.ofrag_cap, self.ofrag, self.ofrag_off = False, 0, None, None
         self._enc_cache.clear()
+        self._attn_cache.clear()
 
     # ---- accounting -------------------------------------------------------------------------
     def n_outliers(self) -> int:

@@ -482,6 +482,16 @@ def build_cache(hqmq, quant, inner, w, x_of, B, T, dev, dtype, no_ofrag, time_it
         n_pass = 4 if (len(calls) == 1 and time_it) else 1
         x_one = x_of(kv, 0, T) if len(calls) == 1 else None
         reps = []
+        if len(calls) > 1 and time_it:
+            # one untimed call of the same size into a throw-away cache: allocator, attributes and tables are warm
+            # before the single timed pass
+            t0w, t1w = calls[0]
+            pkw = inner.new_cache(B, t1w - t0w, d, dev, scale_dtype=dtype, with_outliers=Cm is not None, out_dtype=dtype,
+                                  out_cap=None if Cm is None else max(1024, int(0.2 * (t1w - t0w) * (d // 4))),
+                                  ofrag=kv == 0 and Cm is not None and not no_ofrag)
+            quant.encode(x_of(kv, t0w, t1w), 0, kv, out=pkw)
+            torch.cuda.synchronize()
+            del pkw
         for rep in range(n_pass):
             pk = inner.new_cache(B, T, d, dev, scale_dtype=dtype, with_outliers=Cm is not None, out_dtype=dtype, out_cap=cap,
                                  ofrag=kv == 0 and Cm is not None and not no_ofrag)
@@ -865,7 +875,7 @@ def main():
         "encode": {"tokens_per_s": float(tot[1]), "GBps_per_gpu": enc_gbs, "frac_of_peak": enc_gbs / peak,
                    "tokens": B * T, "seconds_K_V": enc_times, "append_one_token_us_per_call": append_us,
                    "note": f"calls of at most {ENC_CALL_TOKENS} tokens per tensor over the whole (B, H_kv, T, d) input, Med3x median "
-                           "per call; median of 3 timed passes after 1 warm-up pass (one timed pass when a tensor takes several calls); "
+                           "per call; median of 3 timed passes after 1 warm-up pass (one timed pass after one warm-up call when a tensor takes several calls); "
                            "append_one_token_us_per_call: one token per sequence, host wall clock over 128 K + V pair calls "
                            "(encode_pair, what the cache's update() issues) divided by the 256 tensors"},
         "clocks": clocks,

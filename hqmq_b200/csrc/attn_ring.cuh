@@ -352,12 +352,25 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
       const int repsK = 1 << p.rep_log2, repsV = 1 << p.repv_log2;
       const uint2* srcK = reinterpret_cast<const uint2*>(p.tblK) + (int64_t)h * p.table_rows;
       const uint2* srcV = reinterpret_cast<const uint2*>(p.tblV) + (int64_t)h * p.table_rows;
-      for (int i = threadIdx.x; i < rows_f; i += kRingConsumerThreads) {
-        const uint2 ek = srcK[2 * i], ev = srcV[2 * i];
-        uint2* dk = reinterpret_cast<uint2*>(tblK + (size_t)i * strideK);
-        uint2* dv = reinterpret_cast<uint2*>(tblV + (size_t)i * strideV);
-        for (int q = 0; q < repsK; ++q) dk[q] = ek;
-        for (int q = 0; q < repsV; ++q) dv[q] = ev;
+      // A warp loads 32 consecutive entries (one per lane) and writes their replicas -- entry after entry, `reps` copies
+      // each, which is one contiguous stretch -- with lane-contiguous stores, the values passed by shuffles.  (One lane
+      // storing all replicas of its own entry put every store of a warp into two banks: 4 us per table load.)
+      for (int i0 = warp * 32; i0 < rows_f; i0 += kRingConsumerThreads) {
+        const int i = i0 + lane;
+        uint2 ek = make_uint2(0u, 0u), ev = make_uint2(0u, 0u);
+        if (i < rows_f) { ek = srcK[2 * i]; ev = srcV[2 * i]; }
+        uint2* dk = reinterpret_cast<uint2*>(tblK) + ((size_t)i0 << p.rep_log2);
+        uint2* dv = reinterpret_cast<uint2*>(tblV) + ((size_t)i0 << p.repv_log2);
+        for (int k = 0; k < repsK; ++k) {
+          const int s = k * 32 + lane, from = s >> p.rep_log2;
+          const uint2 v = make_uint2(__shfl_sync(0xffffffffu, ek.x, from), __shfl_sync(0xffffffffu, ek.y, from));
+          if (i0 + from < rows_f) dk[s] = v;
+        }
+        for (int k = 0; k < repsV; ++k) {
+          const int s = k * 32 + lane, from = s >> p.repv_log2;
+          const uint2 v = make_uint2(__shfl_sync(0xffffffffu, ev.x, from), __shfl_sync(0xffffffffu, ev.y, from));
+          if (i0 + from < rows_f) dv[s] = v;
+        }
       }
       cur_h = h;
     }

@@ -12,7 +12,7 @@ const void* fast_kernel(int n_chunks, int ib, int rb, bool outl);
 size_t fast_warp_bytes(int n_chunks, int ib, int rb, bool outl);
 bool ring_kernel(int n_chunks, int ib, int rb, bool outl, int scale_dtype, RingKernelInfo& k);
 size_t ring_smem_total(int table_rows, int repk_log2, int repv_log2, int d, bool outl, int stages, int merge_slots,
-                       size_t stage_bytes);
+                       size_t stage_bytes, int warps);
 constexpr int kRingMinKeys = 1024;       // shorter key ranges keep the per-warp staging rings
 // ... and so do small problems: below about four stages per SM the ring kernel's set-up (it replicates the tables
 // up to sixteen times) outweighs its faster tile loop (B1, 8 KV heads, 4096 keys: 42 against 26 us per step)
@@ -204,7 +204,7 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   const int64_t tiles_all = (int64_t)a->B * a->T_q * a->H_kv * ((keys + kTile - 1) / kTile);
   if (fast && keys >= kRingMinKeys && tiles_all >= kRingMinTiles && ring_kernel(n, pl.ib, a->K.radius_bits, outl, a->K.scale_dtype, rk)) {
     auto fits = [&](int rsum, int ns, int ms) {
-      return ring_smem_total(pl.table_rows, (rsum + 1) / 2, rsum / 2, a->d, outl, ns, ms, rk.stage_bytes) <= kSmemLimit;
+      return ring_smem_total(pl.table_rows, (rsum + 1) / 2, rsum / 2, a->d, outl, ns, ms, rk.stage_bytes, rk.warps) <= kSmemLimit;
     };
     if (fits(0, 2, 1)) {
       int rsum = 0;
@@ -218,9 +218,9 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   }
   if (ring) {
     pl.kernel = rk.fn;
-    pl.nw = kRingWarpsHost;
-    pl.threads = (kRingWarpsHost + 1) * 32;
-    pl.smem = ring_smem_total(pl.table_rows, pl.rep_log2, pl.repv_log2, a->d, outl, pl.ring_stages, pl.merge_slots, rk.stage_bytes);
+    pl.nw = rk.warps;
+    pl.threads = (rk.warps + 1) * 32;
+    pl.smem = ring_smem_total(pl.table_rows, pl.rep_log2, pl.repv_log2, a->d, outl, pl.ring_stages, pl.merge_slots, rk.stage_bytes, rk.warps);
   } else {
   const int nheads = G > 8 ? 16 : 8;
   size_t extra = outl ? (size_t)nheads * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * nheads * 4) : 0;

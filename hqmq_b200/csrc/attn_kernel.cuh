@@ -72,8 +72,7 @@ struct AttnParams {
 };
 
 // A ring kernel (attn_ring.cu) and the bytes of one of its stages.
-struct RingKernelInfo { const void* fn; size_t stage_bytes; };
-constexpr int kRingWarpsHost = 15;   // consumer warps of the ring kernels (one more warp produces)
+struct RingKernelInfo { const void* fn; size_t stage_bytes; int warps; };   // warps: consumers (one more warp produces)
 
 // Key range [beg, end) of query position tq.  causal 1: the reference's top-left aligned mask (query i sees keys
 // 0..i); causal 2: bottom-right aligned (the Tq queries are the LAST Tq positions of the Tkv keys: query i sees keys

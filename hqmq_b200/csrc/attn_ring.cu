@@ -7,7 +7,7 @@ namespace attn {
 
 // SDT: element type of the per-token scale planes (HQMQ_F16 or HQMQ_BF16), fixed at compile time like the field layout.
 template <int N, int IB, int RB, bool OUTL, int SDT>
-__global__ void __launch_bounds__(kRingThreads, 1) attn_ring_kernel(const AttnParams p) {
+__global__ void __launch_bounds__((ring_warps(N) + 1) * 32, 1) attn_ring_kernel(const AttnParams p) {
   attn_ring_body<N, IB, RB, OUTL, SDT>(p);
 }
 
@@ -16,6 +16,7 @@ static void fill(int sdt, RingKernelInfo& k) {
   k.fn = sdt == HQMQ_F16 ? reinterpret_cast<const void*>(&attn_ring_kernel<N, IB, RB, OUTL, HQMQ_F16>)
                          : reinterpret_cast<const void*>(&attn_ring_kernel<N, IB, RB, OUTL, HQMQ_BF16>);
   k.stage_bytes = RingLayout<N, IB, RB, OUTL>::BYTES;
+  k.warps = ring_warps(N);
 }
 
 template <int N, bool OUTL>
@@ -36,8 +37,8 @@ bool ring_kernel(int n_chunks, int ib, int rb, bool outl, int scale_dtype, RingK
 }
 
 size_t ring_smem_total(int table_rows, int repk_log2, int repv_log2, int d, bool outl, int stages, int merge_slots,
-                       size_t stage_bytes) {
-  return ring_smem(table_rows, repk_log2, repv_log2, d, outl, stages, merge_slots, stage_bytes).total;
+                       size_t stage_bytes, int warps) {
+  return ring_smem(table_rows, repk_log2, repv_log2, d, outl, stages, merge_slots, stage_bytes, warps).total;
 }
 
 }  // namespace attn

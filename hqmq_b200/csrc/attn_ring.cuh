@@ -1,12 +1,12 @@
 // Decode attention over the native compressed cache, long key ranges: one CTA per SM with ONE staging ring
 // shared by all of its warps.
 //
-//   producer   one extra warp.  A stage of the ring holds kRingTiles consecutive 16-token tiles of a unit
-//              (240 tokens): the code rows of K and V, the two scale vectors and, with Med3x, the flag words,
+//   producer   one extra warp.  A stage of the ring holds one 16-token tile per consumer warp, consecutive tiles of
+//              a unit (240 or 304 tokens): the code rows of K and V, the two scale vectors and, with Med3x, the flag words,
 //              the tiles' slices of the outlier side buffers and the K fragment records.  A stage is a handful
 //              of bulk asynchronous copies (cp.async.bulk, 8-20 KB each) that complete on the stage's "full"
-//              mbarrier, so the cost of issuing copies is shared by fifteen tiles.
-//   consumers  kRingWarps warps; warp w decodes tile w of every stage, then arrives on the stage's "empty"
+//              mbarrier, so the cost of issuing copies is shared by all tiles of the stage.
+//   consumers  ring_warps(chunks per token) warps; warp w decodes tile w of every stage, then arrives on the stage's "empty"
 //              mbarrier, which lets the producer refill the buffer.
 // The codeword tables are SIGN-FOLDED (only the even native indices are kept, the sign of the axis unit goes
 // into the radius) and replicated 2^r times, interleaved entry by entry: random 8-byte gathers cost 5.0 / 4.6 /
@@ -15,7 +15,8 @@
 // Outliers: a tile of K that owns fragment records adds them with one shared-memory load and one MMA per
 // record; every other flagged chunk (K tiles without records, all of V) is corrected in fp32 on the CUDA cores,
 // one warp-wide step per flagged chunk, from the staged payload slice: its decoded value is 0 (radius code 0),
-// so the correction is purely additive.
+// so the correction is purely additive.  V tiles of d_head 64 whose flagged chunks fill a few chunk columns (an
+// outlier channel) add them column by column with two MMAs each instead.
 // The arithmetic of the tile (fragment layouts, online softmax) is the one described in attn_kernel.cuh.
 #pragma once
 #include "attn_tma.cuh"
@@ -23,52 +24,53 @@
 namespace hqmq {
 namespace attn {
 
-constexpr int kRingWarps = 15;                 // consumer warps (with the producer: 512 threads, 128 registers each)
-constexpr int kRingTiles = kRingWarps;         // tiles per stage: one per consumer warp
-constexpr int kRingTok = kRingTiles * kTile;   // tokens per stage
-constexpr int kRingRec = 16;                   // fragment records staged per stage
-constexpr int kRingThreads = (kRingWarps + 1) * 32;
-constexpr int kRingConsumerThreads = kRingWarps * 32;
+// Consumer warps of a CTA (one more warp produces).  d_head 128: 15, with the producer 512 threads of 128 registers.
+// d_head 64: a tile keeps half the accumulators and fields and fits 96 registers, so 19 consumers (640 threads, five
+// warps per scheduler instead of four) hide more of the latencies of a tile whose fixed work -- softmax, headers,
+// outlier columns -- is spread over half the bytes (measured on a B64 x 16384-token layer: 500 -> 458 us).
+__host__ __device__ constexpr int ring_warps(int n_chunks) { return n_chunks == 16 ? 19 : 15; }
 
 template <int N, int IB, int RB, bool OUTL>
 struct RingLayout {
+  static constexpr int W = ring_warps(N);        // tiles per stage: one per consumer warp
+  static constexpr int kTok = W * kTile;         // tokens per stage
+  static constexpr int kRec = W + 1;             // fragment records staged per stage
   static constexpr int ROW = N * (IB + RB) / 8;
   static constexpr int kK = 0;
-  static constexpr int kV = kK + kRingTok * ROW;
-  static constexpr int kRsK = kV + kRingTok * ROW;
-  static constexpr int kRsV = kRsK + kRingTok * 2;
-  static constexpr int kPlainEnd = kRsV + kRingTok * 2;
+  static constexpr int kV = kK + kTok * ROW;
+  static constexpr int kRsK = kV + kTok * ROW;
+  static constexpr int kRsV = kRsK + kTok * 2;
+  static constexpr int kPlainEnd = kRsV + kTok * 2;
   static constexpr int kFlK = kPlainEnd;
-  static constexpr int kFlV = kFlK + kRingTok * 4;
-  static constexpr int kStageHdr = kFlV + kRingTok * 4;          // 32 bytes: what the producer staged
-  static constexpr int kTileHdr = kStageHdr + 32;                // kRingTiles x 32 bytes: the tiles' side ranges
-  static constexpr int kPayV = kTileHdr + kRingTiles * 32;
+  static constexpr int kFlV = kFlK + kTok * 4;
+  static constexpr int kStageHdr = kFlV + kTok * 4;          // 32 bytes: what the producer staged
+  static constexpr int kTileHdr = kStageHdr + 32;                // W x 32 bytes: the tiles' side ranges
+  static constexpr int kPayV = kTileHdr + W * 32;
   // payload entries staged per stage and tensor (+2 alignment slack): d_head 64 has room for a stage whose every token
-  // owns a flagged chunk (one outlier channel per head: 240 entries)
-  static constexpr int kPay = N == 16 ? 254 : 126;
+  // owns a flagged chunk (one outlier channel per head: an entry per token)
+  static constexpr int kPay = N == 16 ? (W * kTile + 14) : 126;
   static constexpr int kSideK = kPayV + (kPay + 2) * 8;      // K payload slice, or the stage's fragment records
-  static constexpr int kSideKBytes = kRingRec * HQMQ_OFRAG_BYTES > (kPay + 2) * 8 ? kRingRec * HQMQ_OFRAG_BYTES
+  static constexpr int kSideKBytes = kRec * HQMQ_OFRAG_BYTES > (kPay + 2) * 8 ? kRec * HQMQ_OFRAG_BYTES
                                                                                     : (kPay + 2) * 8;
   static constexpr int BYTES = OUTL ? kSideK + kSideKBytes : kPlainEnd;
-  static_assert((kRingTok * ROW) % 16 == 0 && (kRingTok * 2) % 16 == 0 && BYTES % 16 == 0, "stage pieces must be multiples of 16 bytes");
+  static_assert((kTok * ROW) % 16 == 0 && (kTok * 2) % 16 == 0 && BYTES % 16 == 0, "stage pieces must be multiples of 16 bytes");
 };
 
 // What the host must know about the kernel's shared memory (the device derives the same offsets).
 struct RingSmem {
-  size_t tblK, tblV, q, vinfo, bars, merge, ring, total;
+  size_t tblK, tblV, q, bars, merge, ring, total;
 };
 __host__ __device__ inline RingSmem ring_smem(int table_rows, int repk_log2, int repv_log2, int d, bool outl, int stages,
-                                               int merge_slots, size_t stage_bytes) {
+                                               int merge_slots, size_t stage_bytes, int warps) {
   RingSmem s;
   size_t o = 0;
   s.tblK = o; o += (size_t)(table_rows >> 1) * (8u << repk_log2);
   s.tblV = o; o += (size_t)(table_rows >> 1) * (8u << repv_log2);
   s.q = o; o += outl ? (size_t)8 * (d + kQPad) * 2 : 0;
   o = (o + 15) & ~(size_t)15;
-  s.vinfo = o; o += outl ? (size_t)kRingWarps * kTile * 16 : 0;   // per warp and token: V flag word, entries before it, qmax / rs
   s.bars = o; o += 64;                                   // full[4], empty[4]
   // merge area: m[warps][8], l[warps][8], weight[warps][8], m*[8], l*[8], abort word, then `merge_slots` slots of [8][d] floats
-  s.merge = o; o += (size_t)(3 * kRingWarps * 8 + 16 + 4) * 4 + (size_t)merge_slots * 8 * d * 4;
+  s.merge = o; o += (size_t)(3 * warps * 8 + 16 + 4) * 4 + (size_t)merge_slots * 8 * d * 4;
   o = (o + 127) & ~(size_t)127;
   s.ring = o; o += (size_t)stages * stage_bytes;
   s.total = o;
@@ -83,15 +85,17 @@ __device__ __forceinline__ float rcp_fast(float x) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void consumer_bar() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kRingConsumerThreads) : "memory");
+template <int THREADS>
+__device__ __forceinline__ void consumer_bar_n() {
+  asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
 }
 // Barrier among the consumer threads that also ORs a predicate over them.
-__device__ __forceinline__ bool consumer_bar_or(bool pred) {
+template <int THREADS>
+__device__ __forceinline__ bool consumer_bar_or_n(bool pred) {
   uint32_t r;
   asm volatile(
       "{\n .reg .pred p, q;\n setp.ne.u32 p, %1, 0;\n barrier.cta.red.or.pred q, 1, %2, p;\n selp.u32 %0, 1, 0, q;\n}\n"
-      : "=r"(r) : "r"((uint32_t)pred), "n"(kRingConsumerThreads) : "memory");
+      : "=r"(r) : "r"((uint32_t)pred), "n"(THREADS) : "memory");
   return r != 0;
 }
 
@@ -160,13 +164,15 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
   constexpr int NKS = G_::NKS, NVG = G_::NVG, NOT = 2 * G_::NVG;
   constexpr int ROW = RL::ROW;
   constexpr int D = 4 * N;
+  constexpr int kRingWarps = RL::W, kRingTiles = RL::W, kRingRec = RL::kRec, kRingConsumerThreads = RL::W * 32;
+  auto consumer_bar = [] { consumer_bar_n<kRingConsumerThreads>(); };
+  auto consumer_bar_or = [](bool pred) { return consumer_bar_or_n<kRingConsumerThreads>(pred); };
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int NS = p.ring_stages;
-  const RingSmem sl = ring_smem(p.table_rows, p.rep_log2, p.repv_log2, p.d, OUTL, NS, p.merge_slots, RL::BYTES);
+  const RingSmem sl = ring_smem(p.table_rows, p.rep_log2, p.repv_log2, p.d, OUTL, NS, p.merge_slots, RL::BYTES, kRingWarps);
   unsigned char* tblK = smem_raw + sl.tblK;
   unsigned char* tblV = smem_raw + sl.tblV;
   __half* qh16 = reinterpret_cast<__half*>(smem_raw + sl.q);
-  uint4* vinfo = reinterpret_cast<uint4*>(smem_raw + sl.vinfo);     // [warp][16 tokens] (OUTL)
   constexpr int qstride = D + kQPad;
   const uint32_t bar_full = smem_u32(smem_raw + sl.bars), bar_empty = bar_full + 32;
   float* m_s = reinterpret_cast<float*>(smem_raw + sl.merge);      // [16][8]
@@ -612,82 +618,102 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
         }
 
         // ---- O^T += V^T P^T -----------------------------------------------------------------------------------
-        // A tile with many flagged V chunks (a hot channel: one per token) patches them into the decoded fragments on
-        // the way (x * qmax / rs in place of the zero the codeword path gives); a tile with a few takes the additive
-        // fp32 correction below, which costs nothing when there is none.
-        // (compiled for d_head 64 only: in the d_head 128 kernels the second copy of the loop costs registers that the
-        //  common path needs -- measured 3 to 15 % of a step -- so there a dense tile takes the additive correction too)
-        constexpr bool kPatchV = OUTL && N == 16;
-        const bool dense_v = kPatchV && th0.w - th0.z > 5u;
-        auto v_side = [&](auto patch_) {
-          constexpr bool PATCH = decltype(patch_)::value;
-          if constexpr (PATCH) {
-            // per token of the tile: flag word, flagged chunks of the tile's earlier tokens, qmax / rs -- parked in
-            // shared memory and fetched per gather, so that the patch keeps no registers alive across the loop
-            uint32_t fw = 0;
-            float inv = 0.f;
-            if (lane < kTile) {
-              if (t0 + lane < t_end) fw = reinterpret_cast<const uint32_t*>(sb + RL::kFlV)[warp * kTile + lane];
-              inv = __fdividef(p.qmaxf, bits16_to_float(reinterpret_cast<const uint16_t*>(sb + RL::kRsV)[warp * kTile + lane], SDT));
-            }
-            const uint32_t ex = excl_scan16(__popc(fw), lane);
-            if (lane < kTile) vinfo[warp * kTile + lane] = make_uint4(fw, ex, __float_as_uint(inv), 0u);
-            __syncwarp();
-          }
-          static_for<0, NVG>([&](auto g_) {
-            constexpr int g = decltype(g_)::value;
-            uint32_t lo[4], hi[4];
-            static_for<0, 4>([&](auto i_) {
-              constexpr int i = decltype(i_)::value;
-              uint32_t idx; __half2 rr;
-              FL::template cut<g>(cur.vw[i], idx, rr);
-              const uint2 cw = *reinterpret_cast<const uint2*>(tblV + (idx * strideV + laneoffV));
-              lo[i] = hmul2_u32(cw.x, rr);
-              hi[i] = hmul2_u32(cw.y, rr);
-              if constexpr (PATCH) {
-                const int c = r * NVG + g;
-                const uint4 ti = vinfo[warp * kTile + 2 * j + ((i & 1) ^ vswz) + (i >> 1) * 8];
-                if ((ti.x >> c) & 1u) {
-                  const uint32_t e = th0.z + ti.y + __popc(ti.x & ((1u << c) - 1u));
-                  const float vi = __uint_as_float(ti.z);
-                  float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
-                  if (e < (uint32_t)p.V.out_cap) {
-                    if (p.V.out_dtype == HQMQ_F32) {
-                      const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.V.out_vals) + (bh * p.V.out_cap + e) * 4);
-                      x0 = v.x; x1 = v.y; x2 = v.z; x3 = v.w;
-                    } else {
-                      const uint32_t rel = e - sh0.z;
-                      const uint2 v = rel < sh0.w ? reinterpret_cast<const uint2*>(sb + RL::kPayV)[rel]
-                                                  : reinterpret_cast<const uint2*>(p.V.out_vals)[bh * p.V.out_cap + e];
-                      const float2 a = pair16_to_float2(v.x, p.V.out_dtype), bb = pair16_to_float2(v.y, p.V.out_dtype);
-                      x0 = a.x; x1 = a.y; x2 = bb.x; x3 = bb.y;
-                    }
-                  }
-                  lo[i] = pack_half2(x0 * vi, x1 * vi);
-                  hi[i] = pack_half2(x2 * vi, x3 * vi);
-                }
-              }
-            });
-            const uint32_t a0 = __byte_perm(lo[0], lo[1], 0x5410), a1 = __byte_perm(lo[0], lo[1], 0x7632);
-            const uint32_t a2 = __byte_perm(lo[2], lo[3], 0x5410), a3 = __byte_perm(lo[2], lo[3], 0x7632);
-            const uint32_t c0 = __byte_perm(hi[0], hi[1], 0x5410), c1 = __byte_perm(hi[0], hi[1], 0x7632);
-            const uint32_t c2 = __byte_perm(hi[2], hi[3], 0x5410), c3 = __byte_perm(hi[2], hi[3], 0x7632);
-            mma16816(o[2 * g], a0, a1, a2, a3, pb[0], pb[1]);
-            mma16816(o[2 * g + 1], c0, c1, c2, c3, pb[0], pb[1]);
+        static_for<0, NVG>([&](auto g_) {
+          constexpr int g = decltype(g_)::value;
+          uint32_t lo[4], hi[4];
+          static_for<0, 4>([&](auto i_) {
+            constexpr int i = decltype(i_)::value;
+            uint32_t idx; __half2 rr;
+            FL::template cut<g>(cur.vw[i], idx, rr);
+            const uint2 cw = *reinterpret_cast<const uint2*>(tblV + (idx * strideV + laneoffV));
+            lo[i] = hmul2_u32(cw.x, rr);
+            hi[i] = hmul2_u32(cw.y, rr);
           });
-        };
-        if constexpr (kPatchV) {
-          if (dense_v) v_side(std::true_type{});
-          else v_side(std::false_type{});
-        } else {
-          v_side(std::false_type{});
-        }
+          const uint32_t a0 = __byte_perm(lo[0], lo[1], 0x5410), a1 = __byte_perm(lo[0], lo[1], 0x7632);
+          const uint32_t a2 = __byte_perm(lo[2], lo[3], 0x5410), a3 = __byte_perm(lo[2], lo[3], 0x7632);
+          const uint32_t c0 = __byte_perm(hi[0], hi[1], 0x5410), c1 = __byte_perm(hi[0], hi[1], 0x7632);
+          const uint32_t c2 = __byte_perm(hi[2], hi[3], 0x5410), c3 = __byte_perm(hi[2], hi[3], 0x7632);
+          mma16816(o[2 * g], a0, a1, a2, a3, pb[0], pb[1]);
+          mma16816(o[2 * g + 1], c0, c1, c2, c3, pb[0], pb[1]);
+        });
 
         // ---- V outliers: o[g][4c + e] += P[t][g] * x[e] for every flagged chunk (t, c), in fp32 ------------------
         if constexpr (OUTL) {
-          if (th0.w > th0.z && !dense_v) {
+          if (th0.w > th0.z) {
             uint32_t fw = 0;
             if (lane < kTile && t0 + lane < t_end) fw = reinterpret_cast<const uint32_t*>(sb + RL::kFlV)[warp * kTile + lane];
+            // A tile whose flagged chunks sit in a few chunk columns (an outlier channel: one chunk of every token) takes
+            // them column by column through the tensor cores: lane t < 16 turns token t's entry of the column into
+            // fp16(x * qmax / rs) -- what the codeword path would have decoded had the chunk not been flagged -- the four
+            // lanes that own the column's rows of V^T collect their tokens' values by shuffles, and two MMAs with the
+            // tile's P add the column to the output.  About 45 warp instructions per column, whatever it holds; the
+            // per-chunk fp32 step below costs about 25 per flagged chunk and stays the path of scattered outliers.
+            // (compiled for d_head 64 only, like its predecessor, a patch of the decoded fragments inside the V loop:
+            //  in the d_head 128 kernels any addition to the tile costs registers that the common path needs)
+            bool by_column = false;
+            if constexpr (N == 16) {
+              const uint32_t cnt = th0.w - th0.z;
+              if (cnt > 5u) {
+                const uint32_t cols = __reduce_or_sync(0xffffffffu, fw);
+                float rsv = 1.f;
+                if (lane < kTile) rsv = bits16_to_float(reinterpret_cast<const uint16_t*>(sb + RL::kRsV)[warp * kTile + lane], SDT);
+                // (P reaches the tensor cores multiplied by the token's scale, so a flagged chunk in a token whose
+                //  stored scale is zero -- a scale below the range of its 16-bit type -- cannot be carried that way)
+                const bool zero_scale = __any_sync(0xffffffffu, fw != 0u && !(rsv > 0.f));
+                by_column = !zero_scale && (uint32_t)__popc(cols) * 8u < cnt * 5u;
+                if (by_column) {
+                  const float inv = __fdividef(p.qmaxf, rsv);
+                  const uint32_t ex = excl_scan16(__popc(fw), lane);
+                  uint32_t left = cols;
+                  while (left) {
+                    const int c = __ffs(left) - 1;
+                    left &= left - 1;
+                    uint32_t xlo = 0u, xhi = 0u;
+                    if ((fw >> c) & 1u) {
+                      const uint32_t e = th0.z + ex + __popc(fw & ((1u << c) - 1u));
+                      if (e < (uint32_t)p.V.out_cap) {
+                        float x0, x1, x2, x3;
+                        if (p.V.out_dtype == HQMQ_F32) {
+                          const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.V.out_vals) + (bh * p.V.out_cap + e) * 4);
+                          x0 = v.x; x1 = v.y; x2 = v.z; x3 = v.w;
+                        } else {
+                          const uint32_t rel = e - sh0.z;
+                          uint2 v;
+                          if (rel < sh0.w) v = reinterpret_cast<const uint2*>(sb + RL::kPayV)[rel];
+                          else v = __ldg(reinterpret_cast<const uint2*>(p.V.out_vals) + bh * p.V.out_cap + e);
+                          const float2 a = pair16_to_float2(v.x, p.V.out_dtype), bb = pair16_to_float2(v.y, p.V.out_dtype);
+                          x0 = a.x; x1 = a.y; x2 = bb.x; x3 = bb.y;
+                        }
+                        xlo = pack_half2(x0 * inv, x1 * inv);
+                        xhi = pack_half2(x2 * inv, x3 * inv);
+                      }
+                    }
+                    // rows r and r + 8 of the MMA's A operand are elements 0 and 1 (then 2 and 3) of chunk r * NVG + g;
+                    // the lanes of other rows fetch from lane 31, which holds zeros
+                    const bool mine = r == c / NVG;
+                    uint32_t lo[4], hi[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      const int src = mine ? 2 * j + ((i & 1) ^ vswz) + (i >> 1) * 8 : 31;
+                      lo[i] = __shfl_sync(0xffffffffu, xlo, src);
+                      hi[i] = __shfl_sync(0xffffffffu, xhi, src);
+                    }
+                    const uint32_t a0 = __byte_perm(lo[0], lo[1], 0x5410), a1 = __byte_perm(lo[0], lo[1], 0x7632);
+                    const uint32_t a2 = __byte_perm(lo[2], lo[3], 0x5410), a3 = __byte_perm(lo[2], lo[3], 0x7632);
+                    const uint32_t c0 = __byte_perm(hi[0], hi[1], 0x5410), c1 = __byte_perm(hi[0], hi[1], 0x7632);
+                    const uint32_t c2 = __byte_perm(hi[2], hi[3], 0x5410), c3 = __byte_perm(hi[2], hi[3], 0x7632);
+                    static_for<0, NVG>([&](auto gg_) {
+                      constexpr int gg = decltype(gg_)::value;
+                      if (c % NVG == gg) {
+                        mma16816(o[2 * gg], a0, a1, a2, a3, pb[0], pb[1]);
+                        mma16816(o[2 * gg + 1], c0, c1, c2, c3, pb[0], pb[1]);
+                      }
+                    });
+                  }
+                }
+              }
+            }
+            if (!by_column) {
             uint32_t tm = __ballot_sync(0xffffffffu, fw != 0u);
             uint32_t e = th0.z;
             while (tm) {
@@ -728,6 +754,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
                 ++e;
               }
             }
+            }   // !by_column
           }
         }
         };   // tile_body
@@ -778,7 +805,11 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
       // merge): the upper bits of r are folded into bits 3:2 and j into bits 1:0, which spreads a store over all 32
       // banks.  The map is its own inverse (it changes bits 3:0 only, by bits it leaves alone).
       auto slot_swz = [](int jj, int x) { return x ^ (((x >> 5) & (D / 32 - 1)) << 2) ^ (jj & 3); };
-      for (int round = 0; round < kRingWarps / MS; ++round) {
+      // (15 warps: the host picks a divisor of 15 as slot count; otherwise the last round fills only some of the slots)
+      constexpr bool kWhole = kRingWarps % 15 == 0;
+      const int rounds = kWhole ? kRingWarps / MS : (kRingWarps + MS - 1) / MS;
+      for (int round = 0; round < rounds; ++round) {
+        const int live = kWhole ? MS : min(MS, kRingWarps - round * MS);
         if (warp / MS == round) {
           float* mine = slots + (size_t)(warp % MS) * 8 * D;
 #pragma unroll
@@ -798,7 +829,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
         for (int q = 0; q < PER; ++q) {
           const int i = threadIdx.x + q * kRingConsumerThreads;
           if (i < 8 * D)
-            for (int sidx = 0; sidx < MS; ++sidx) acc[q] += slots[(size_t)sidx * 8 * D + i];
+            for (int sidx = 0; sidx < live; ++sidx) acc[q] += slots[(size_t)sidx * 8 * D + i];
         }
         consumer_bar();
       }

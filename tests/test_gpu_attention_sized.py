@@ -147,6 +147,33 @@ def test_side_buffer_overflow_is_memory_safe():
     want = orc.merge_outliers(orc.decode_packed(ki, kr, ks, tk["joint"].cpu(), 15), kf, drop(K, kf, cap))
     assert torch.equal(dense, want)
 
+def test_head_dim_64_value_outlier_columns():
+    """d_head 64, V tiles whose flagged chunks fill chunk columns (added column by column through the tensor cores)
+    next to the cases that must not take that path: one outlier channel; two channels in different chunks; a channel
+    plus scattered spikes (tiles with many columns fall back to the per-chunk correction); a channel in rows that are
+    zero otherwise (every seventh token: the row's scale is the outlier's own norm, its codes decode to nothing)."""
+    S, br, d, Hq, Hkv, T, B = 96, 4, 64, 16, 4, 16384, 4
+    g = torch.Generator().manual_seed(6006)
+    K = make_kv("randn", (B, Hkv, T, d), seed=1006)
+    V = make_kv("randn", (B, Hkv, T, d), seed=2006)
+    V[:, 0, :, 13] *= 25.0
+    V[:, 1, :, 6] *= 25.0
+    V[:, 1, :, 41] *= 40.0
+    V[:, 2, :, 30] *= 25.0
+    spikes = torch.rand(B, T, d // 4, generator=g) < 0.02
+    V[:, 2] *= 1.0 + 19.0 * spikes.repeat_interleave(4, dim=-1).float()
+    V[:, 3, :, 57] *= 30.0
+    hot = V[:, 3, ::7, 57].clone()
+    V[:, 3, ::7] = 0.0
+    V[:, 3, ::7, 57] = hot
+    K, V = K.bfloat16(), V.bfloat16()
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, Hkv, S, br, device="cuda"), 3.0)
+    Kp, Vp = _attend_and_check(q, _queries(B, Hq, d, 3006), K, V, S, br, "d_head 64 outlier columns", splits=(None, 1, 3))
+    vi, vr, vs, vf = Vp.to_reference()
+    assert vf[:, 0, :, 13 // 4].float().mean() > 0.7 and vf[:, 1, :, 41 // 4].float().mean() > 0.7, \
+        "the outlier channels were not flagged"
+    assert vf[:, 3, ::7, 57 // 4].float().mean() > 0.5, "the lone outliers were not flagged"
+
 
 @pytest.mark.parametrize("T,B", [(640, 1), (20000, 4)])
 def test_all_zero_value_rows_keep_their_softmax_weight(T, B):

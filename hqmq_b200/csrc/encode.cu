@@ -1441,6 +1441,9 @@ scan_body(const hqmq_packed& dst, int t_start, int T_new, int blk0, int nblk, in
     for (int it = 0; it < kScanIters; ++it) {
       const int i = s0 + (warp * kScanIters + it) * 32 + lane, ba = blk0 + i;
       uint32_t cc = 0, any_c = 0;
+      // (an iteration whose 32 blocks all lie past the call -- every one but the first in a one-token append --
+      //  is skipped here and in the scan below: it would add zeros)
+      if (i - lane >= nblk) { c[it] = fc[it] = 0u; continue; }
       if (i < nblk) {
         const int tb = ba * HQMQ_OUT_BLOCK;
 #pragma unroll
@@ -1474,6 +1477,7 @@ scan_body(const hqmq_packed& dst, int t_start, int T_new, int blk0, int nblk, in
 #pragma unroll
     for (int it = 0; it < kScanIters; ++it) {
       const int i = s0 + (warp * kScanIters + it) * 32 + lane, ba = blk0 + i;
+      if (i - lane >= nblk) continue;
       uint32_t incl = c[it], fincl = fc[it];
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {

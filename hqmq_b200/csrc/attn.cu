@@ -212,6 +212,13 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
       ring = true;
       pl.rep_log2 = (rsum + 1) / 2; pl.repv_log2 = rsum / 2; pl.ring_stages = 2; pl.merge_slots = 1;
       while (pl.ring_stages < 4 && fits(rsum, pl.ring_stages + 1, 1)) ++pl.ring_stages;
+      // The d_head-64 kernels (19 consumer warps, bigger stages, a tile that is done sooner) run out of staged tiles
+      // with two stages: there the last replica of V goes to a third stage instead (measured on a B64 x 16384-token
+      // layer: 463 -> 437 us; at d_head 128 a third stage bought nothing where it cost a replica).
+      if (rk.warps > 15 && pl.ring_stages < 3 && rsum > 0 && fits(rsum - 1, 3, 1)) {
+        --rsum;
+        pl.rep_log2 = (rsum + 1) / 2; pl.repv_log2 = rsum / 2; pl.ring_stages = 3;
+      }
       for (int ms : {5, 3})
         if (fits(rsum, pl.ring_stages, ms)) { pl.merge_slots = ms; break; }
     }

@@ -587,12 +587,6 @@ __global__ void __launch_bounds__(kSmallThreads) encode_small_kernel(SmallArgs a
   if (blockIdx.x == 0 && threadIdx.x == 0) *a.status = 0u;
   encode_small_body(a.g, a.x, a.qs, a.dst, a.t_start, maps, a.joint, a.lut, a.nmul, a.C, a.med_out, a.quantile);
 }
-// grid (H, 2): blockIdx.y = 0 the K tensor, 1 the V tensor (same batch, heads, tokens and head dim)
-__global__ void __launch_bounds__(kSmallThreads) encode_small_pair_kernel(SmallPair p) {
-  const SmallArgs& a = p.t[blockIdx.y];
-  if (blockIdx.x == 0 && threadIdx.x == 0) *a.status = 0u;
-  encode_small_body(a.g, a.x, a.qs, a.dst, a.t_start, p.maps, a.joint, a.lut, a.nmul, a.C, a.med_out, a.quantile);
-}
 
 // ---- main pass for the common geometry ------------------------------------------------------------------
 // 32 chunks per token, 16-bit input, look-up-table search, compile-time field layout: one warp per token,
@@ -1526,22 +1520,14 @@ __global__ void __launch_bounds__(kScanWarps * 32)
 scan_kernel(hqmq_packed dst, int t_start, int T_new, int blk0, int nblk, int payload, uint32_t* __restrict__ status) {
   scan_body(dst, t_start, T_new, blk0, nblk, payload, status);
 }
-// grid (B * H, 2): blockIdx.y selects the tensor of a K + V append; a tensor that needs no scan returns at once
-__global__ void __launch_bounds__(kScanWarps * 32) scan_pair_kernel(SmallPair p) {
-  const SmallArgs& a = p.t[blockIdx.y];
-  if (!a.scan) return;
-  scan_body(a.dst, a.t_start, a.g.T_new, a.blk0, a.nblk, a.payload, a.status);
-}
 
 // Side planes of one 16-token block, one warp per block: the payload (original values of every flagged chunk,
 // in (token, chunk) order) and, for a block that owns fragment records, the records (layout in
 // include/hqmq_b200.h).  Lane l < 16 holds the flag word of token l of the block.
 __device__ __forceinline__ void
-side_body(const EncGeom& g, const void* __restrict__ x, const hqmq_packed& dst, int t_start, int blk0, int nblk) {
-  const int bh = blockIdx.y;
+side_block(const EncGeom& g, const void* __restrict__ x, const hqmq_packed& dst, int t_start, int blk0, int nblk, int bh, int i,
+           int lane) {
   const int h = bh % g.H, b = bh / g.H;
-  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
   if (i >= nblk) return;
   const int ba = blk0 + i;
   const int nb_cap = dst.T_cap / HQMQ_OUT_BLOCK + 1;
@@ -1646,15 +1632,93 @@ side_body(const EncGeom& g, const void* __restrict__ x, const hqmq_packed& dst, 
   }
 }
 
+// (grid (blocks / warps per CTA, B * H): one warp per block)
+__device__ __forceinline__ void
+side_body(const EncGeom& g, const void* __restrict__ x, const hqmq_packed& dst, int t_start, int blk0, int nblk) {
+  side_block(g, x, dst, t_start, blk0, nblk, blockIdx.y, blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), threadIdx.x & 31);
+}
 __global__ void __launch_bounds__(256)
 side_kernel(EncGeom g, const void* __restrict__ x, hqmq_packed dst, int t_start, int blk0, int nblk) {
   side_body(g, x, dst, t_start, blk0, nblk);
 }
-// grid (blocks / 8, B * H, 2): blockIdx.z selects the tensor of a K + V append
-__global__ void __launch_bounds__(256) side_pair_kernel(SmallPair p) {
-  const SmallArgs& a = p.t[blockIdx.z];
+
+// The offset scan of scan_body for a call that touches at most 32 blocks of a (b, h): one warp, one lane per block, a
+// single sweep.  Same results word for word (payload offsets of the blocks this call starts, record offsets of the
+// blocks it completes with the capacity rule, the running totals).
+constexpr int kScanSmallBlocks = 32;
+__device__ __forceinline__ void
+scan_small_warp(const hqmq_packed& dst, int bh, int t_start, int T_new, int blk0, int nblk, int payload,
+                uint32_t* __restrict__ status, int lane) {
+  const int nb_cap = dst.T_cap / HQMQ_OUT_BLOCK + 1;
+  uint32_t* off = dst.out_off + (int64_t)bh * nb_cap;
+  uint32_t* foff = dst.ofrag ? dst.ofrag_off + (int64_t)bh * nb_cap : nullptr;
+  const uint32_t* fl = dst.flags + (int64_t)bh * dst.T_cap;
+  // (the totals are read by one lane and handed round, so that the reads are done before lane 0 rewrites them)
+  uint32_t run = 0u, frun = 0u;
+  if (lane == 0) { run = payload ? dst.out_count[bh] : 0u; frun = foff ? foff[blk0] : 0u; }
+  run = __shfl_sync(0xffffffffu, run, 0);
+  frun = __shfl_sync(0xffffffffu, frun, 0);
+  const int t_end = t_start + T_new;
+  const int i = lane, ba = blk0 + i;
+  uint32_t cc = 0, any_c = 0;
+  if (i < nblk) {
+    const int tb = ba * HQMQ_OUT_BLOCK;
+#pragma unroll
+    for (int q = 0; q < HQMQ_OUT_BLOCK / 4; ++q) {
+      const uint4 w = *reinterpret_cast<const uint4*>(fl + tb + 4 * q);
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int t = tb + 4 * q + k;
+        if (t >= t_start && t < t_end) cc += __popc(ww[k]);
+        if (t < t_end) any_c |= ww[k];
+      }
+    }
+  }
+  const bool complete = i < nblk && (ba + 1) * HQMQ_OUT_BLOCK <= t_end;
+  const uint32_t fcnt = foff && complete ? (uint32_t)ofrag_records_for(any_c) : 0u;
+  uint32_t incl = cc, fincl = fcnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+    const uint32_t fv = __shfl_up_sync(0xffffffffu, fincl, o);
+    if (lane >= o) { incl += v; fincl += fv; }
+  }
+  if (payload && i < nblk && !(i == 0 && (t_start % HQMQ_OUT_BLOCK) != 0)) off[ba] = run + incl - cc;
+  if (foff) {
+    fincl += frun;
+    const bool ok = fincl <= (uint32_t)dst.ofrag_cap;
+    const uint32_t last_ok = __reduce_max_sync(0xffffffffu, ok && i < nblk ? fincl : frun);
+    if (i < nblk) foff[ba + 1] = ok ? fincl : last_ok;
+  }
+  const uint32_t total = run + __shfl_sync(0xffffffffu, incl, 31);
+  if (payload && lane == 0) {
+    off[blk0 + nblk] = total;
+    if (total > (uint32_t)dst.out_cap) atomicOr(&status[0], 1u);
+    dst.out_count[bh] = total;
+  }
+}
+
+// The K + V append of a layer in ONE launch, grid (H, 2): blockIdx.y = 0 the K tensor, 1 the V tensor (same batch,
+// heads, tokens and head dim).  After the head's codes, scales and flags, the same CTA scans the offsets of its batch
+// entries (a warp per entry) and writes their side planes (a warp per block) -- what scan_kernel and side_kernel do in
+// two more launches of a single-tensor call.  For calls that touch at most kScanSmallBlocks blocks per (b, h).
+// The status words are cleared by the host (a memset ahead of the launch): a CTA may report an overflow before
+// another CTA has started.
+__global__ void __launch_bounds__(kSmallThreads) append_pair_kernel(SmallPair p) {
+  const SmallArgs& a = p.t[blockIdx.y];
+  encode_small_body(a.g, a.x, a.qs, a.dst, a.t_start, p.maps, a.joint, a.lut, a.nmul, a.C, a.med_out, a.quantile);
+  if (!a.scan) return;
+  __syncthreads();          // the head's flag words and scales are in global memory for the other warps of the CTA
+  const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int b = warp; b < a.g.B; b += kSmallThreads / 32)
+    scan_small_warp(a.dst, b * a.g.H + h, a.t_start, a.g.T_new, a.blk0, a.nblk, a.payload, a.status, lane);
   if (!a.side) return;
-  side_body(a.g, a.x, a.dst, a.t_start, a.blk0, a.nblk);
+  __syncthreads();          // ... and so are the offsets
+  for (int w = warp; w < a.g.B * a.nblk; w += kSmallThreads / 32) {
+    const int b = w / a.nblk, i = w - b * a.nblk;
+    side_block(a.g, a.x, a.dst, a.t_start, a.blk0, a.nblk, b * a.g.H + h, i, lane);
+  }
 }
 
 // ---- look-up table construction ---------------------------------------------------------------------
@@ -2152,7 +2216,8 @@ extern "C" int hqmq_encode_pair(const hqmq_encode_args* k, const hqmq_encode_arg
   unsigned char* wsb = reinterpret_cast<unsigned char*>(workspace);
   const hqmq_packed &dk = k->dst, &dv = v->dst;
   const bool same = dk.B == dv.B && dk.H == dv.H && dk.n_chunks == dv.n_chunks && k->T_new == v->T_new;
-  if (!same || k->T_new == 0 || !small_call(k) || !small_call(v)) {
+  if (!same || k->T_new == 0 || !small_call(k) || !small_call(v) || plan_ws(*k).nblk > kScanSmallBlocks ||
+      plan_ws(*v).nblk > kScanSmallBlocks) {
     // no common launch shape: one tensor after the other, each with its part of the workspace
     rc = hqmq_encode(k, wsb, wk, stream);
     if (rc) return rc;
@@ -2165,10 +2230,9 @@ extern "C" int hqmq_encode_pair(const hqmq_encode_args* k, const hqmq_encode_arg
   rc = fill_small(v, plan_ws(*v), reinterpret_cast<uint32_t*>(wsb + wk), pr.t[1]);
   if (rc) return rc;
   memcpy(pr.maps.ref_to_native, index_maps().ref_to_native, 24);
-  encode_small_pair_kernel<<<dim3(dk.H, 2), kSmallThreads, 0, st>>>(pr);
-  const int nblk = pr.t[0].nblk > pr.t[1].nblk ? pr.t[0].nblk : pr.t[1].nblk;
-  if (pr.t[0].scan || pr.t[1].scan) scan_pair_kernel<<<dim3(dk.B * dk.H, 2), kScanWarps * 32, 0, st>>>(pr);
-  if (pr.t[0].side || pr.t[1].side) side_pair_kernel<<<dim3((nblk + 7) / 8, dk.B * dk.H, 2), 256, 0, st>>>(pr);
+  // one launch for the whole append; the two status words (first word of each tensor's part) are cleared ahead of it
+  HQMQ_CHECK_CUDA(cudaMemset2DAsync(wsb, wk, 0, sizeof(uint32_t), 2, st));
+  append_pair_kernel<<<dim3(dk.H, 2), kSmallThreads, 0, st>>>(pr);
   HQMQ_LAUNCH_CHECK();
   return HQMQ_OK;
 }

@@ -139,17 +139,18 @@ def test_update_with_another_geometry_than_the_cache_is_refused():
 
 @pytest.mark.parametrize("outliers", [True, False])
 def test_pair_append_equals_two_single_appends(outliers):
-    """K and V of a layer appended in shared launches (hqmq_encode_pair) leave every plane byte-identical to one
-    tensor appended after the other, for a prompt (large call: run one after the other inside the library), then
-    one and three tokens at a time, across a block boundary."""
+    """K and V of a layer appended in one launch (hqmq_encode_pair: codes, offset scan and side planes of both tensors)
+    leave every plane byte-identical to one tensor appended after the other by single-tensor calls: a prompt and longer
+    chunks (large calls: run one after the other inside the library), one to five tokens at a time across block
+    boundaries, a chunk of three blocks."""
     B, H, d, S, br = 3, 2, 64, 96, 4
     inner = hqmq.HQMQ(1, H, S, br, device="cuda")
     q = hqmq.with_outlier_extraction(inner, 3.0) if outliers else inner
-    mk = lambda kv: inner.new_cache(B, 128, d, "cuda", scale_dtype=torch.bfloat16, with_outliers=outliers,
+    mk = lambda kv: inner.new_cache(B, 1024, d, "cuda", scale_dtype=torch.bfloat16, with_outliers=outliers,
                                     out_dtype=torch.bfloat16, ofrag=outliers and kv == 0)
     pair, single = (mk(0), mk(1)), (mk(0), mk(1))
     g = torch.Generator().manual_seed(11)
-    for step, T in enumerate([40, 1, 1, 3, 1, 5, 1]):
+    for step, T in enumerate([40, 1, 1, 3, 1, 5, 1, 33, 1, 170, 2, 600, 1]):
         k = torch.randn(B, H, T, d, generator=g)
         k[:, :, :, 7] *= 9.0
         v = torch.randn(B, H, T, d, generator=g)
@@ -159,7 +160,7 @@ def test_pair_append_equals_two_single_appends(outliers):
         q.encode(v, 0, 1, out=single[1])
     torch.cuda.synchronize()
     for a, b in zip(pair, single):
-        assert a.T == b.T == 52
+        assert a.T == b.T == 859
         names = ["codes", "rs"] + (["flags", "out_vals", "out_off", "out_count"] if outliers else [])
         names += ["ofrag", "ofrag_off"] if a.with_ofrag else []
         for name in names:

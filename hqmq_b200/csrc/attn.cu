@@ -1,5 +1,6 @@
 // Decode attention: host side (validation, work decomposition, launch), the generic kernels (any
 // field width, reference layout, G up to 16) and the partial-merge kernel.
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 
@@ -105,6 +106,7 @@ struct Plan {
   int repv_log2, ring_stages, merge_slots; // ring kernels only
   size_t ticket_bytes;                     // ring kernels: one ticket word per unit between the status word and the partials
   int ppc;   // partials a CTA writes per unit and head: 1 for the staged kernels (merged in shared memory), nw otherwise
+  int warp_units;   // staged kernels: warp mode (the warps walk through the units independently; ppc = nw)
   int units, tpu_v, L, P, grid;
   size_t ws_bytes;
 };
@@ -161,7 +163,14 @@ static int resident_ctas(const void* kernel, size_t smem, int threads) {
     if (cache[i].k == kernel && cache[i].smem == smem && cache[i].dev == dev) return cache[i].val;
   int sms = 0, occ = 0;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  // The limit is set to the device's opt-in maximum, not to this size: one kernel runs with several shared-memory
+  // sizes (replication and warp mode depend on the problem), and a limit set to a later, smaller size would fail the
+  // launch of an earlier size whose cached answer skips this step.
+  if (smem > 48 * 1024) {
+    int optin = 0;
+    cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin > (int)smem ? optin : (int)smem);
+  }
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem) != cudaSuccess || occ < 1) occ = 1;
   cudaGetLastError();
   const int val = (sms > 0 ? sms : 148) * occ;
@@ -169,7 +178,10 @@ static int resident_ctas(const void* kernel, size_t smem, int threads) {
   return val;
 }
 
-static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
+// Units of at most this many tiles run the staged kernels in warp mode (every warp has at most two tiles of a unit)
+constexpr int kWarpModeMaxTiles = 32;
+
+static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device, bool allow_warp_mode = true) {
   const int n = a->d / 4;
   const int G = a->H_q / a->H_kv;
   const bool outl = a->layout == 0 && (a->K.flags != nullptr || a->V.flags != nullptr);
@@ -223,6 +235,18 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
         if (fits(rsum, pl.ring_stages, ms)) { pl.merge_slots = ms; break; }
     }
   }
+  // tiles a unit can have (a window may straddle one extra tile)
+  int tpu = (keys + kTile - 1) / kTile + (a->window > 0 ? 1 : 0);
+  if (tpu < 1) tpu = 1;
+  pl.units = a->B * a->T_q * a->H_kv;
+  // Staged kernels, many short units: warp mode.  Every warp then writes its own partial per unit and CTA (16 times
+  // the scratch of the in-CTA merge), so a caller whose scratch is fixed can rule it out.
+  {
+    // (a CTA's piece of the flat tile sequence: at least a tile per warp; warp mode pays when it spans several units)
+    const int64_t piece = std::max<int64_t>(((int64_t)pl.units * tpu + 147) / 148, pl.nw);
+    pl.warp_units = fast && !ring && allow_warp_mode && a->kv_splits == 0 && tpu <= kWarpModeMaxTiles && tpu < piece;
+  }
+  if (pl.warp_units) pl.ppc = pl.nw;
   if (ring) {
     pl.kernel = rk.fn;
     pl.nw = rk.warps;
@@ -232,7 +256,7 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
   const int nheads = G > 8 ? 16 : 8;
   size_t extra = outl ? (size_t)nheads * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * nheads * 4) : 0;
   if (fast)
-    extra = (outl ? (size_t)8 * (a->d + kFastQPad) * 2 : 0) + (((size_t)pl.nw * kFastStages * 8 + 15) & ~(size_t)15) +
+    extra = (outl ? (size_t)(pl.warp_units ? pl.nw : 1) * 8 * (a->d + kFastQPad) * 2 : 0) + (((size_t)pl.nw * kFastStages * 8 + 15) & ~(size_t)15) +
             (size_t)pl.nw * fast_warp_bytes(n, pl.ib, a->K.radius_bits, outl);
   // The big-CTA kernels own a whole SM: replicate the tables (interleaved) as far as shared memory
   // allows, which spreads the random codeword gathers over more banks.
@@ -245,17 +269,13 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device) {
     if (!fast) return HQMQ_ERR_UNSUPPORTED;
     // the staged kernel does not fit next to this codebook: use the generic one
     pl.kernel = slow_kernel(n, outl, false);
-    pl.nw = kSlowWarps; pl.rep_log2 = 0; pl.ppc = kSlowWarps;
+    pl.nw = kSlowWarps; pl.rep_log2 = 0; pl.ppc = kSlowWarps; pl.warp_units = 0;
     pl.threads = pl.nw * 32;
     pl.smem = (size_t)pl.table_rows * 16 + (outl ? (size_t)8 * a->d * 4 + (size_t)pl.nw * (2 * kStage * 8 + 16 * 8 * 4) : 0);
     if (pl.smem > kSmemLimit) return HQMQ_ERR_UNSUPPORTED;
   }
   }
 
-  // tiles a unit can have (a window may straddle one extra tile)
-  int tpu = (keys + kTile - 1) / kTile + (a->window > 0 ? 1 : 0);
-  if (tpu < 1) tpu = 1;
-  pl.units = a->B * a->T_q * a->H_kv;
   // (asked on every path: the first query of a kernel also raises its dynamic shared-memory limit)
   int slots = query_device ? resident_ctas(pl.kernel, pl.smem, pl.threads) : 148;
   if (slots < 1) slots = 1;
@@ -332,6 +352,11 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   Plan pl;
   rc = make_plan(a, pl, true);
   if (rc) return rc;
+  if (workspace && workspace_bytes < pl.ws_bytes && pl.warp_units) {
+    // a scratch sized for the in-CTA merge (the built-in one of hqmq_attn_decode_static): plan without warp mode
+    rc = make_plan(a, pl, true, false);
+    if (rc) return rc;
+  }
   if (!workspace || workspace_bytes < pl.ws_bytes) return HQMQ_ERR_WORKSPACE;
   if ((uintptr_t)workspace & 15) return HQMQ_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
@@ -343,7 +368,7 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   const float scale = a->softmax_scale > 0.f ? a->softmax_scale : 1.0f / sqrtf((float)a->d);
   p.sscale = scale * 1.4426950408889634f / (float)a->r_qmax;
   p.qscale = scale * 1.4426950408889634f;
-  p.nw = pl.nw; p.rep_log2 = pl.rep_log2;
+  p.nw = pl.nw; p.rep_log2 = pl.rep_log2; p.warp_units = pl.warp_units;
   p.repv_log2 = pl.repv_log2; p.ring_stages = pl.ring_stages; p.merge_slots = pl.merge_slots;
   p.vscale = 1.0f / (float)a->r_qmax;
   p.qmaxf = (float)a->r_qmax;
@@ -398,6 +423,10 @@ extern "C" int hqmq_attn_decode_static(const hqmq_attn_args* a, void* stream) {
   Plan pl;
   rc = make_plan(a, pl, true);
   if (rc) return rc;
+  if (pl.ws_bytes > (size_t)HQMQ_ATTN_STATIC_SCRATCH_BYTES && pl.warp_units) {
+    rc = make_plan(a, pl, true, false);   // (hqmq_attn_decode below makes the same choice from the size it is given)
+    if (rc) return rc;
+  }
   if (pl.ws_bytes > (size_t)HQMQ_ATTN_STATIC_SCRATCH_BYTES) return HQMQ_ERR_STATIC_SCRATCH;
   int dev = -1;
   HQMQ_CHECK_CUDA(cudaGetDevice(&dev));

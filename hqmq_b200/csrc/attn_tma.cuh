@@ -72,9 +72,12 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
   const size_t tbl_bytes = (size_t)rows_f * rstride;
   unsigned char* tblK = smem_raw;
   unsigned char* tblV = smem_raw + tbl_bytes;
-  __half* qh16 = reinterpret_cast<__half*>(smem_raw + 2 * tbl_bytes);                         // [8][d] (OUTL)
+  // Warp mode (p.warp_units): the warps of a CTA work on different units at the same time -- see the unit loop.
+  const bool wm = p.warp_units != 0;
   const int qstride = p.d + kQPad;
-  unsigned char* after_q = smem_raw + 2 * tbl_bytes + (OUTL ? (size_t)NHEADS * qstride * 2 : 0);
+  // [8][d] queries of the unit in fp16 (OUTL); in warp mode every warp has its own copy
+  __half* qh16 = reinterpret_cast<__half*>(smem_raw + 2 * tbl_bytes) + (wm ? (size_t)(threadIdx.x >> 5) * NHEADS * qstride : 0);
+  unsigned char* after_q = smem_raw + 2 * tbl_bytes + (OUTL ? (size_t)(wm ? NW : 1) * NHEADS * qstride * 2 : 0);
   uint64_t* bars = reinterpret_cast<uint64_t*>(after_q);                                      // [NW][kStages]
   unsigned char* warp_area = after_q + ((NW * kStages * 8 + 15) & ~15);
   // per-warp share of the staging area; it also holds one warp's partial [8 heads][d + 2] during the merge
@@ -92,7 +95,7 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
   }
   __syncwarp();
   uint32_t it = 0;        // tiles this warp has consumed so far (stage = it % kStages, parity from it / kStages)
-  bool failed = false;
+  bool failed = false, drained = false;
 
   const int64_t flat_lo = (int64_t)blockIdx.x * p.L;
   const int64_t flat_total = (int64_t)p.units * p.tpu_v;
@@ -103,7 +106,14 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
   for (int u = (int)(flat_lo / p.tpu_v); (int64_t)u * p.tpu_v < flat_hi; ++u) {
     const int h = u / upb, bt = u - h * upb;
     const int b = bt / p.Tq, tq = bt - b * p.Tq;
-    if (h != cur_h || OUTL) __syncthreads();
+    // CTA mode: all warps share the unit -- barriers around the tables and the staged queries of every unit, the warps'
+    // results merged in shared memory at its end.  Warp mode (units of a few tiles each, many of them per CTA): the
+    // CTA's tiles go round-robin to its warps over the whole flat range, every warp runs through the units on its
+    // own -- its queries staged in its own copy, its partial written to its own slot, empty where it had no tile --
+    // and the CTA meets only where the KV head, and with it the tables, changes.  (In CTA mode a unit of ten tiles kept
+    // six of sixteen warps idle and every unit paid barriers, a merge and the latency of its first copies in turn:
+    // 42 us for 512 units of ten tiles at d_head 64.)
+    if (wm ? h != cur_h : (h != cur_h || OUTL)) __syncthreads();
     if (h != cur_h) {
       const int reps = 1 << p.rep_log2;
       for (int i = threadIdx.x; i < rows_f; i += NW * 32) {
@@ -114,15 +124,18 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         for (int q = 0; q < reps; ++q) { dk[q] = ek; dv[q] = ev; }
       }
       cur_h = h;
+      if (wm) __syncthreads();
     }
-    if constexpr (OUTL) {
-      for (int i = threadIdx.x; i < NHEADS * p.d; i += NW * 32) {
-        const int g = i / p.d, x = i - g * p.d;
-        qh16[g * qstride + x] = __float2half_rn(g < p.G ? load_float(p.Q, (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t +
-                                                                           (int64_t)(h * p.G + g) * p.qs_h + x, p.q_dtype) : 0.f);
+    if (!wm) {
+      if constexpr (OUTL) {
+        for (int i = threadIdx.x; i < NHEADS * p.d; i += NW * 32) {
+          const int g = i / p.d, x = i - g * p.d;
+          qh16[g * qstride + x] = __float2half_rn(g < p.G ? load_float(p.Q, (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t +
+                                                                             (int64_t)(h * p.G + g) * p.qs_h + x, p.q_dtype) : 0.f);
+        }
       }
+      __syncthreads();
     }
-    __syncthreads();
 
     int t_beg, t_end;
     key_range(p.Tkv, p.Tq, p.causal, p.window, tq, t_beg, t_end);
@@ -133,6 +146,13 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
     const int my_lo = tile_lo + rel_lo;
     const int my_hi = min(tile_hi, tile_lo + rel_hi);
     const int part = (int)blockIdx.x - (int)(ubase / p.L);   // this CTA's slot among the CTAs that share the unit
+    // this warp's first tile of the piece is my_lo + w0: the warp's own index, or in warp mode its turn in the
+    // round-robin over the CTA's flat range
+    int w0 = warp;
+    if (wm) {
+      const int lo_i = (int)(ubase + (my_lo - tile_lo) - flat_lo);
+      w0 = (warp - lo_i % NW + NW) % NW;
+    }
 
     // ---- Q as B fragments -------------------------------------------------------------------------------
     uint32_t qb[NKS][2];
@@ -149,6 +169,14 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
         }
         qb[ks][0] = pack_half2(q0, q1);
         qb[ks][1] = pack_half2(q2, q3);
+      }
+    }
+    if constexpr (OUTL) {
+      if (wm) {   // the lanes of a warp hold all 8 x d query values between them: park them for the outlier paths
+#pragma unroll
+        for (int ks = 0; ks < NKS; ++ks)
+          *reinterpret_cast<uint2*>(qh16 + r * qstride + 4 * (j * NKS + ks)) = make_uint2(qb[ks][0], qb[ks][1]);
+        __syncwarp();
       }
     }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -234,21 +262,22 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
       }
     };
 
-    const int n_my = my_hi > my_lo + warp ? (my_hi - my_lo - warp + NW - 1) / NW : 0;
+    // (a warp that gave up on a wait takes no more tiles; in warp mode it still walks the units, for the barriers)
+    const int n_my = !failed && my_hi > my_lo + w0 ? (my_hi - my_lo - w0 + NW - 1) / NW : 0;
     // prologue: kStages-1 tiles in flight
     if (lane == 0 && !failed) {
-      if constexpr (OUTL) load_offsets(my_lo + warp);
+      if constexpr (OUTL) load_offsets(my_lo + w0);
 #pragma unroll
       for (int k = 0; k < kStages - 1; ++k) {
         if (k < n_my) {
-          issue(my_lo + warp + k * NW, it + k);
-          if constexpr (OUTL) load_offsets(my_lo + warp + (k + 1) * NW);
+          issue(my_lo + w0 + k * NW, it + k);
+          if constexpr (OUTL) load_offsets(my_lo + w0 + (k + 1) * NW);
         }
       }
     }
 
     for (int k = 0; k < n_my && !failed; ++k, ++it) {
-      const int tile = my_lo + warp + k * NW;
+      const int tile = my_lo + w0 + k * NW;
       if (lane == 0 && k + kStages - 1 < n_my) {
         issue(tile + (kStages - 1) * NW, it + kStages - 1);
         if constexpr (OUTL) load_offsets(tile + kStages * NW);
@@ -499,13 +528,43 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
       else v_side(std::false_type{});
       __syncwarp();   // every lane is done with the stage before lane 0 refills it
     }
-    if (failed) {
+    if (failed && !drained) {
+      drained = true;
       // drain: the copies still in flight for this warp land in its own buffers; wait for them (bounded)
       // so that no copy is outstanding when the CTA exits
       for (int k = 0; k < kStages; ++k) {
         uint32_t spins = 0;
         while (!mbar_try_wait(bar0 + 8 * ((it + k) % kStages), ((it + k) / kStages) & 1u) && ++spins < kWaitLimit) {}
       }
+    }
+
+    // ---- warp mode: this warp's partial of the unit goes to its own slot (part, warp); the merge kernel skips the
+    // empty ones by their header -----------------------------------------------------------------------------------
+    if (wm) {
+      const int n_parts = p.P * NW;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float l = l_run[e];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        const int g = 2 * j + e;
+        if (g >= p.G) continue;
+        const int64_t row = ((int64_t)b * p.Hq + h * p.G + g) * p.Tq + tq;
+        float* dst = p.partials + (row * n_parts + part * NW + warp) * (4 * N + 2);
+        if (n_my > 0) {
+#pragma unroll
+          for (int i = 0; i < NOT; ++i) {
+            const int chunk = r * NVG + (i >> 1);
+            if (chunk < N) {
+              dst[4 * chunk + 2 * (i & 1)] = o[i][e];
+              dst[4 * chunk + 2 * (i & 1) + 1] = o[i][2 + e];
+            }
+          }
+        }
+        if (r == 0) { dst[4 * N] = m_run[e]; dst[4 * N + 1] = l; }
+      }
+      continue;
     }
 
     // ---- one partial per (CTA, unit, head): the warps' results are merged in shared memory ---------------------

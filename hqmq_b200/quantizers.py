@@ -300,7 +300,7 @@ class HQMQQuantizer(KVQuantizer):
         """Append the keys and the values of one layer (the reference cache quantises both on every update,
         src/model_utils.py:29-32).  Same result as ``encode(k, layer_idx, 0, out=out_k)`` followed by
         ``encode(v, layer_idx, 1, out=out_v)``; a decode-time append (a few tokens per sequence) runs both tensors
-        in the same launches (hqmq_encode_pair), which halves the launches per layer."""
+        in one kernel launch (hqmq_encode_pair) instead of three per tensor."""
         small = (k.dim() == 4 and k.shape == v.shape and k.dtype == v.dtype and k.shape[2] <= 64 and k.is_cuda and v.is_cuda
                  and k.stride(-1) == 1 and v.stride(-1) == 1 and not any(s % 4 for s in k.stride()[:3] + v.stride()[:3]))
         if not small or k.shape[2] == 0:

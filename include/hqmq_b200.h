@@ -214,8 +214,9 @@ int hqmq_encode(const hqmq_encode_args* args, void* workspace, size_t workspace_
  * The K and the V tensor of one layer in one call: the reference cache quantises both on every update
  * (src/model_utils.py:29-32, QuantizedCache.update).  Same results as hqmq_encode(k) followed by
  * hqmq_encode(v); each tensor keeps its own median, tables and planes.  For the decode-time append (a small
- * call, the same batch / heads / new tokens / head dim for both tensors) the two share every launch, which
- * halves the launches per layer; other shapes run one tensor after the other.  The workspace holds K's part
+ * call, the same batch / heads / new tokens / head dim for both tensors) the whole append -- codes, scales, flags,
+ * offset scan and side planes of both tensors -- is ONE kernel launch after a memset of the two status words (a
+ * single-tensor small call takes three launches); other shapes run one tensor after the other.  The workspace holds K's part
  * first and V's part at the next multiple of 256 bytes; the first word of each part is that tensor's status
  * word (hqmq_read_status on workspace, and on workspace + round_up(hqmq_encode_workspace_bytes(k), 256)).
  */

@@ -154,31 +154,6 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
       w0 = (warp - lo_i % NW + NW) % NW;
     }
 
-    // ---- Q as B fragments -------------------------------------------------------------------------------
-    uint32_t qb[NKS][2];
-    {
-      const int64_t q0off = (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t;
-#pragma unroll
-      for (int ks = 0; ks < NKS; ++ks) {
-        const int dim = 4 * (j * NKS + ks);
-        float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
-        if (r < p.G) {
-          const int64_t o = q0off + (int64_t)(h * p.G + r) * p.qs_h + dim;
-          q0 = load_float(p.Q, o, p.q_dtype); q1 = load_float(p.Q, o + 1, p.q_dtype);
-          q2 = load_float(p.Q, o + 2, p.q_dtype); q3 = load_float(p.Q, o + 3, p.q_dtype);
-        }
-        qb[ks][0] = pack_half2(q0, q1);
-        qb[ks][1] = pack_half2(q2, q3);
-      }
-    }
-    if constexpr (OUTL) {
-      if (wm) {   // the lanes of a warp hold all 8 x d query values between them: park them for the outlier paths
-#pragma unroll
-        for (int ks = 0; ks < NKS; ++ks)
-          *reinterpret_cast<uint2*>(qh16 + r * qstride + 4 * (j * NKS + ks)) = make_uint2(qb[ks][0], qb[ks][1]);
-        __syncwarp();
-      }
-    }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[NOT][4];
 #pragma unroll
@@ -276,6 +251,31 @@ __device__ __forceinline__ void attn_decode_tma_body(const AttnParams& p, uint32
       }
     }
 
+    // ---- Q as B fragments (loaded while the first copies are in flight) ------------------------------------------
+    uint32_t qb[NKS][2];
+    {
+      const int64_t q0off = (int64_t)b * p.qs_b + (int64_t)tq * p.qs_t;
+#pragma unroll
+      for (int ks = 0; ks < NKS; ++ks) {
+        const int dim = 4 * (j * NKS + ks);
+        float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+        if (r < p.G) {
+          const int64_t o = q0off + (int64_t)(h * p.G + r) * p.qs_h + dim;
+          q0 = load_float(p.Q, o, p.q_dtype); q1 = load_float(p.Q, o + 1, p.q_dtype);
+          q2 = load_float(p.Q, o + 2, p.q_dtype); q3 = load_float(p.Q, o + 3, p.q_dtype);
+        }
+        qb[ks][0] = pack_half2(q0, q1);
+        qb[ks][1] = pack_half2(q2, q3);
+      }
+    }
+    if constexpr (OUTL) {
+      if (wm) {   // the lanes of a warp hold all 8 x d query values between them: park them for the outlier paths
+#pragma unroll
+        for (int ks = 0; ks < NKS; ++ks)
+          *reinterpret_cast<uint2*>(qh16 + r * qstride + 4 * (j * NKS + ks)) = make_uint2(qb[ks][0], qb[ks][1]);
+        __syncwarp();
+      }
+    }
     for (int k = 0; k < n_my && !failed; ++k, ++it) {
       const int tile = my_lo + w0 + k * NW;
       if (lane == 0 && k + kStages - 1 < n_my) {

@@ -181,7 +181,7 @@ static int resident_ctas(const void* kernel, size_t smem, int threads) {
 // Units of at most this many tiles run the staged kernels in warp mode (every warp has at most two tiles of a unit)
 constexpr int kWarpModeMaxTiles = 32;
 
-static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device, bool allow_warp_mode = true) {
+static int make_plan_impl(const hqmq_attn_args* a, Plan& pl, bool query_device, bool allow_warp_mode) {
   const int n = a->d / 4;
   const int G = a->H_q / a->H_kv;
   const bool outl = a->layout == 0 && (a->K.flags != nullptr || a->V.flags != nullptr);
@@ -316,6 +316,14 @@ static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device, bool 
   pl.ticket_bytes = pl.ring_stages ? (((size_t)pl.units * 4 + 15) & ~(size_t)15) : 0;
   pl.ws_bytes = 16 + pl.ticket_bytes + (size_t)rows * pl.P * pl.ppc * (a->d + 2) * sizeof(float);
   return HQMQ_OK;
+}
+
+// Warp mode is dropped where its scratch (a partial per warp instead of one per CTA) would pass kWarpModeMaxScratch.
+constexpr size_t kWarpModeMaxScratch = (size_t)256 << 20;
+static int make_plan(const hqmq_attn_args* a, Plan& pl, bool query_device, bool allow_warp_mode = true) {
+  int rc = make_plan_impl(a, pl, query_device, allow_warp_mode);
+  if (rc == HQMQ_OK && pl.warp_units && pl.ws_bytes > kWarpModeMaxScratch) rc = make_plan_impl(a, pl, query_device, false);
+  return rc;
 }
 
 // The workspace must not depend on the device's occupancy answer changing between the size query

@@ -60,8 +60,13 @@ ENC_CALL_TOKENS = 131072     # tokens per encode call (a chunked prefill; keeps 
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read + dram__bytes_write of the attention kernel divided by the algorithmic bytes of the same launch,
 # from one ncu capture per workload at a batch that still exceeds L2 (traffic grows in proportion to the tokens):
-# c2 at batch 4 (163 MB algorithmic): 174.8 MB read + 4.1 MB written.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"c2": 1.097}
+# c2 at batch 4 (163 MB algorithmic): 174.8 MB read + 4.1 MB written; c4_128k at its own size (124.3 MB): 154.7 + 4.7 MB;
+# c5_layer at batch 16 (172.3 MB): 230.3 + 4.8 MB (fragment records and 16-byte-rounded payload slices are the excess).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {
+    "c2": (1.097, "batch 4 of the same workload (163 MB, larger than L2), scaled by the tokens of this launch"),
+    "c4_128k": (1.282, "the same workload at its full size (124 MB, L2 flushed before the launch)"),
+    "c5_layer": (1.364, "batch 16 of the same workload (172 MB, larger than L2), scaled by the tokens of this launch"),
+}
 L2_BYTES = 126e6     # B200 L2; a cache within twice this size is timed with a flush before every step
 
 
@@ -839,8 +844,10 @@ def main():
     peak, peak_kind = hbm_peak()
     per_gpu_gbs = algo_bytes / step_s / 1e9
     ring = Tl >= 1024
-    kernel = ("attn_ring_kernel" if ring else "attn_fast_kernel") + " (+ combine_kernel inside the same timed region)"
-    traffic_ratio = NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get(args.workload) if (Cm is not None and not args.no_ofrag) else None
+    kernel = ("attn_ring_kernel (merges its partials itself: one launch per step)" if ring
+              else "attn_fast_kernel (+ combine_kernel inside the same timed region)")
+    traffic_ratio, traffic_from = (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get(args.workload, (None, None))
+                                   if (Cm is not None and not args.no_ofrag) else (None, None))
     sharding = (f"sequence x{world} (context {T} total, partials pushed into the peers' memory + local merge)" if px is not None
                 else f"sequence x{world} (context {T} total, partials all_gather + merge)" if seq_mode
                 else f"fixed job split by (KV head, batch): {Hl} KV heads x {Bl} sequences per GPU, outputs all_gathered" if strong
@@ -869,8 +876,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8TBs_nominal": per_gpu_gbs / 8000.0, "kernel": kernel,
                      "traffic": traffic_ratio * algo_bytes if traffic_ratio else None,
-                     "traffic_note": "dram read + write bytes of one ncu capture of this kernel at batch 4 of the same workload "
-                                     "(163 MB, larger than L2), scaled by the tokens of this launch" if traffic_ratio else
+                     "traffic_note": f"dram read + write bytes of one ncu capture of this kernel at {traffic_from}" if traffic_ratio else
                                      "no ncu capture of this workload"},
         "encode": {"tokens_per_s": float(tot[1]), "GBps_per_gpu": enc_gbs, "frac_of_peak": enc_gbs / peak,
                    "tokens": B * T, "seconds_K_V": enc_times, "append_one_token_us_per_call": append_us,

@@ -843,7 +843,7 @@ def main():
     gbs = total_bytes / step_s / 1e9
     peak, peak_kind = hbm_peak()
     per_gpu_gbs = algo_bytes / step_s / 1e9
-    ring = Tl >= 1024
+    ring = Tl >= 1024 and Bl * Hl * ((Tl + 15) // 16) >= 148 * 4 * 15     # the library's choice of kernel (csrc/attn.cu)
     kernel = ("attn_ring_kernel (merges its partials itself: one launch per step)" if ring
               else "attn_fast_kernel (+ combine_kernel inside the same timed region)")
     traffic_ratio, traffic_from = (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get(args.workload, (None, None))

@@ -153,14 +153,16 @@ def test_side_buffer_overflow_is_memory_safe():
 
 def test_head_dim_64_value_outlier_columns():
     """d_head 64, V tiles whose flagged chunks fill chunk columns (added column by column through the tensor cores)
-    next to the cases that must not take that path: one outlier channel; two channels in different chunks; a channel
+    next to the cases that must not take that path: one outlier channel that moves to another chunk half way through
+    the context; two channels in different chunks; a channel
     plus scattered spikes (tiles with many columns fall back to the per-chunk correction); a channel in rows that are
     zero otherwise (every seventh token: the row's scale is the outlier's own norm, its codes decode to nothing)."""
-    S, br, d, Hq, Hkv, T, B = 96, 4, 64, 16, 4, 16384, 4
+    S, br, d, Hq, Hkv, T, B = 96, 4, 64, 16, 4, 16379, 4       # (the last tile is a partial one)
     g = torch.Generator().manual_seed(6006)
     K = make_kv("randn", (B, Hkv, T, d), seed=1006)
     V = make_kv("randn", (B, Hkv, T, d), seed=2006)
-    V[:, 0, :, 13] *= 25.0
+    V[:, 0, :8000, 13] *= 25.0                                   # the channel moves to another chunk half way
+    V[:, 0, 8000:, 50] *= 25.0
     V[:, 1, :, 6] *= 25.0
     V[:, 1, :, 41] *= 40.0
     V[:, 2, :, 30] *= 25.0
@@ -174,7 +176,8 @@ def test_head_dim_64_value_outlier_columns():
     q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, Hkv, S, br, device="cuda"), 3.0)
     Kp, Vp = _attend_and_check(q, _queries(B, Hq, d, 3006), K, V, S, br, "d_head 64 outlier columns", splits=(None, 1, 3))
     vi, vr, vs, vf = Vp.to_reference()
-    assert vf[:, 0, :, 13 // 4].float().mean() > 0.7 and vf[:, 1, :, 41 // 4].float().mean() > 0.7, \
+    assert vf[:, 0, :8000, 13 // 4].float().mean() > 0.7 and vf[:, 0, 8000:, 50 // 4].float().mean() > 0.7 and \
+        vf[:, 1, :, 41 // 4].float().mean() > 0.7, \
         "the outlier channels were not flagged"
     assert vf[:, 3, ::7, 57 // 4].float().mean() > 0.5, "the lone outliers were not flagged"
 

@@ -377,6 +377,8 @@ extern "C" int hqmq_attn_decode(const hqmq_attn_args* a, void* workspace, size_t
   p.sscale = scale * 1.4426950408889634f / (float)a->r_qmax;
   p.qscale = scale * 1.4426950408889634f;
   p.nw = pl.nw; p.rep_log2 = pl.rep_log2; p.warp_units = pl.warp_units;
+  // (ring kernels of d_head 64 with two or more units per CTA: the units of a CTA are taken from different KV heads)
+  p.unit_hfast = pl.ring_stages > 0 && a->d == 64 && a->H_kv > 1 && pl.units >= 2 * pl.grid;
   p.repv_log2 = pl.repv_log2; p.ring_stages = pl.ring_stages; p.merge_slots = pl.merge_slots;
   p.vscale = 1.0f / (float)a->r_qmax;
   p.qmaxf = (float)a->r_qmax;

@@ -52,6 +52,7 @@ struct AttnParams {
   int repv_log2;      // ring kernels: replication of the V table (rep_log2 is then the K table's)
   int ring_stages;    // ring kernels: stages of the CTA-wide staging ring
   int merge_slots;    // ring kernels: warps whose partials are merged per round at the end of a unit
+  int unit_hfast;     // ring kernels: units are numbered with the KV head running fastest (u = (b, tq) * H_kv + h)
   int warp_units;     // staged kernels: the warps of a CTA walk through the units independently (one partial per warp)
   // flat tile space: units * tpu_v virtual tiles, L per CTA; a unit is touched by at most P CTAs
   int units, tpu_v, L, P;

@@ -101,11 +101,19 @@ __device__ __forceinline__ bool consumer_bar_or_n(bool pred) {
 
 // The piece of unit u that belongs to this CTA: tiles [my_lo, my_hi) and the CTA's slot among the unit's CTAs.
 struct UnitPiece { int h, b, tq, t_beg, t_end, my_lo, my_hi, part; };
+// HFAST: the kernel honours p.unit_hfast -- units numbered with the KV head running fastest, u = (b, tq) * H_kv + h, so
+// that the units of one CTA belong to different heads.  Heads differ in outlier density (an outlier channel flags a
+// chunk in every token of one head and hardly any of another), and with equal tile counts the CTAs of the dense heads
+// set the kernel's time: B64 x 8 heads x 16384 tokens at d_head 64, 3.5 units per CTA, 444 -> 419 us for a table
+// reload at every unit boundary.  (The d_head 128 kernels keep the head-major order: their CTAs hold at most two units
+// in the configurations measured, and the order made no difference there.)
+template <bool HFAST>
 __device__ __forceinline__ UnitPiece unit_piece(const AttnParams& p, int u, int64_t flat_lo, int64_t flat_hi) {
   UnitPiece q;
   const int upb = p.B * p.Tq;
-  q.h = u / upb;
-  const int bt = u - q.h * upb;
+  int bt;
+  if (HFAST && p.unit_hfast) { bt = u / p.Hkv; q.h = u - bt * p.Hkv; }
+  else { q.h = u / upb; bt = u - q.h * upb; }
   q.b = bt / p.Tq; q.tq = bt - q.b * p.Tq;
   key_range(p.Tkv, p.Tq, p.causal, p.window, q.tq, q.t_beg, q.t_end);
   const int tile_lo = q.t_beg / kTile, tile_hi = (q.t_end + kTile - 1) / kTile;
@@ -209,7 +217,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
     auto seek = [&](StageIt& it) {          // first unit from it.u on that has tiles here
       it.valid = false;
       for (; (int64_t)it.u * p.tpu_v < flat_hi; ++it.u) {
-        it.up = unit_piece(p, it.u, flat_lo, flat_hi);
+        it.up = unit_piece<N == 16>(p, it.u, flat_lo, flat_hi);
         if (it.up.my_lo < it.up.my_hi) { it.tile0 = it.up.my_lo; it.valid = true; break; }
       }
     };
@@ -350,7 +358,7 @@ __device__ __forceinline__ void attn_ring_body(const AttnParams& p) {
   ld.row_bytes = ROW; ld.row_words = ROW / 4; ld.j = j; ld.r = r; ld.sdt = SDT;
 
   for (int u = u_first; (int64_t)u * p.tpu_v < flat_hi; ++u) {
-    const UnitPiece up = unit_piece(p, u, flat_lo, flat_hi);
+    const UnitPiece up = unit_piece<N == 16>(p, u, flat_lo, flat_hi);
     const int h = up.h, b = up.b, tq = up.tq, t_beg = up.t_beg, t_end = up.t_end;
     // ---- tables of the KV head (sign-folded, replicated) and the unit's queries --------------------------------
     // (every consumer is past the previous unit's merge barrier here, so nobody still reads the old contents)

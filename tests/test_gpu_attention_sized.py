@@ -180,6 +180,21 @@ def test_head_dim_64_value_outlier_columns():
         vf[:, 1, :, 41 // 4].float().mean() > 0.7, \
         "the outlier channels were not flagged"
     assert vf[:, 3, ::7, 57 // 4].float().mean() > 0.5, "the lone outliers were not flagged"
+def test_head_dim_64_many_units_per_cta():
+    """d_head 64 with more than two units per CTA of the ring kernel (320 units of 65 tiles): the units of a CTA are
+    taken from different KV heads there, so heads of very different outlier density -- a strong channel, a weak one,
+    none -- are mixed in every CTA; the last tile of every unit is a partial one."""
+    S, br, d, Hq, Hkv, T, B = 96, 4, 64, 16, 8, 1035, 40
+    K = make_kv("randn", (B, Hkv, T, d), seed=1008)
+    V = make_kv("randn", (B, Hkv, T, d), seed=2008)
+    for h, scale in enumerate([40.0, 1.0, 6.0, 1.0, 25.0, 3.0, 1.0, 90.0]):
+        K[:, h, :, (5 * h + 2) % d] *= scale
+        V[:, h, :, (11 * h + 7) % d] *= scale
+    K, V = K.bfloat16(), V.bfloat16()
+    q = hqmq.with_outlier_extraction(hqmq.HQMQ(1, Hkv, S, br, device="cuda"), 3.0)
+    _attend_and_check(q, _queries(B, Hq, d, 3008), K, V, S, br, "d_head 64, many units per CTA", splits=(None, 2),
+                      min_k_flag=0.01, relative_to_output=True)
+
 
 @pytest.mark.parametrize("d,S,br,window", [(64, 96, 4, 128), (64, 96, 4, None), (128, 24, 3, 128), (128, 96, 4, None)])
 def test_many_units_short_ranges(d, S, br, window):
